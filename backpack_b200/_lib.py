@@ -1,0 +1,71 @@
+"""ctypes binding of libbpq4k.so (the C ABI declared in include/bpq4k.h).
+
+There is no fallback: if the shared library is missing, or a symbol the header
+declares is absent, importing fails with an error that says how to build it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "lib", "libbpq4k.so")
+
+u32 = C.c_uint32
+u64 = C.c_uint64
+vp = C.c_void_p
+
+# name -> (restype, argtypes); mirrors include/bpq4k.h one to one
+SIGNATURES = {
+    "bpq4k_version": (C.c_int, []),
+    "bpq4k_status_string": (C.c_char_p, [C.c_int]),
+    "bpq4k_create": (C.c_int, [C.c_int, C.POINTER(vp)]),
+    "bpq4k_destroy": (C.c_int, [vp]),
+    "bpq4k_last_error_string": (C.c_char_p, [vp]),
+    "bpq4k_set_option": (C.c_int, [vp, C.c_int, C.c_int]),
+    "bpq4k_get_option": (C.c_int, [vp, C.c_int, C.POINTER(C.c_int)]),
+    "bpq4k_launch_count": (u64, [vp, C.c_int]),
+    "bpq4k_n_blocks": (u32, [u32]),
+    "bpq4k_row_stride_words": (u32, [u32]),
+    "bpq4k_pack_q4k_host": (C.c_int, [vp, u32, u32, vp]),
+    "bpq4k_upload_weights": (C.c_int, [vp, vp, u64, C.POINTER(vp)]),
+    "bpq4k_free_device": (C.c_int, [vp, vp]),
+    "bpq4k_dequant_f32": (C.c_int, [vp, vp, u32, u32, u32, vp, vp]),
+    "bpq4k_matmul_f32": (C.c_int, [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
+    "bpq4k_matmul_moe_f32": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, vp]),
+    "bpq4k_matmul_host_f32": (C.c_int, [vp, vp, vp, vp, vp, u32, u32, u32, u32, vp]),
+}
+
+_lib = None
+
+
+class LibraryMissing(ImportError):
+    pass
+
+
+def build() -> None:
+    """Compile the CUDA sources in csrc/ for sm_100a into lib/libbpq4k.so."""
+    import subprocess
+
+    subprocess.run(["make", "-s", "-C", os.path.join(PKG_DIR, "csrc")], check=True)
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.isfile(LIB_PATH):
+        raise LibraryMissing(
+            f"{LIB_PATH} not found. Build it with `make -C {os.path.join(PKG_DIR, 'csrc')}` "
+            "(needs nvcc with sm_100a support). There is no CPU or PyTorch fallback."
+        )
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as e:  # stale build
+            raise LibraryMissing(f"{LIB_PATH} does not export {name}; rebuild it") from e
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

@@ -1,0 +1,338 @@
+// C ABI of libbpq4k.so (declared in include/bpq4k.h): handle, argument
+// validation, kernel selection.  No kernel code lives here.
+#include "../../include/bpq4k.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "kernels.h"
+
+using namespace bpq4k;
+
+struct bpq4k_context {
+    int device = 0;
+    int sm_count = 0;
+    int cc_major = 0;
+    char err[512] = "no error";
+    int gemv_variant = BPQ4K_GEMV_AUTO;
+    int prefill_mode = BPQ4K_PREFILL_F16X3;
+    int prefill_min_m = 64;
+    uint64_t launches = 0;
+    // staging for the *_host entry point
+    float* stage_x = nullptr;
+    size_t stage_x_bytes = 0;
+    float* stage_y = nullptr;
+    size_t stage_y_bytes = 0;
+    // scratch for kernels that need it (split activations, partial sums)
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+};
+
+namespace {
+
+int fail(bpq4k_context* h, int status, const char* fmt, ...) {
+    if (h) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(h->err, sizeof(h->err), fmt, ap);
+        va_end(ap);
+    }
+    return status;
+}
+
+int cuda_fail(bpq4k_context* h, cudaError_t e, const char* what) {
+    return fail(h, BPQ4K_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+        else prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Shape and layout checks shared by every matmul-like entry point.
+int check_weights(bpq4k_context* h, const void* W, uint32_t N, uint32_t K, uint32_t rowStrideWords) {
+    (void)N;
+    if (K == 0 || K % BPQ4K_QK_K != 0)
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "K=%u is not a positive multiple of 256", K);
+    if (!W) return fail(h, BPQ4K_ERR_INVALID_ARG, "W is null");
+    const uint32_t need = (K / BPQ4K_QK_K) * BPQ4K_BLOCK_WORDS;
+    if (rowStrideWords < need)
+        return fail(h, BPQ4K_ERR_INVALID_ARG, "rowStrideWords=%u is smaller than (K/256)*36=%u", rowStrideWords, need);
+    if (rowStrideWords % 4u != 0)
+        return fail(h, BPQ4K_ERR_MISALIGNED, "rowStrideWords=%u is not a multiple of 4 words (16 bytes)", rowStrideWords);
+    if (!aligned16(W)) return fail(h, BPQ4K_ERR_MISALIGNED, "W is not 16-byte aligned");
+    return BPQ4K_OK;
+}
+
+int ensure_bytes(bpq4k_context* h, void** p, size_t* have, size_t need) {
+    if (*have >= need) return BPQ4K_OK;
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+    *have = 0;
+    size_t want = need < (1u << 20) ? (1u << 20) : need;
+    cudaError_t e = cudaMalloc(p, want);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(h, BPQ4K_ERR_ALLOC, "cudaMalloc(%zu) failed: %s", want, cudaGetErrorString(e));
+    }
+    *have = want;
+    return BPQ4K_OK;
+}
+
+int run_matmul(bpq4k_context* h, const MatmulArgs& a, cudaStream_t st) {
+    int launches = 0;
+    cudaError_t e = cudaSuccess;
+    int variant = h->gemv_variant;
+    (void)variant;
+    e = launch_gemv_fp32(a, st, &launches);
+    h->launches += (uint64_t)launches;
+    if (e != cudaSuccess) return cuda_fail(h, e, "matmul launch");
+    return BPQ4K_OK;
+}
+
+}  // namespace
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+int bpq4k_version(void) { return BPQ4K_VERSION; }
+
+const char* bpq4k_status_string(int s) {
+    switch (s) {
+        case BPQ4K_OK: return "ok";
+        case BPQ4K_ERR_INVALID_ARG: return "invalid argument";
+        case BPQ4K_ERR_UNSUPPORTED: return "unsupported shape";
+        case BPQ4K_ERR_MISALIGNED: return "misaligned pointer or stride";
+        case BPQ4K_ERR_CUDA: return "CUDA error";
+        case BPQ4K_ERR_NCCL: return "NCCL error";
+        case BPQ4K_ERR_TIMEOUT: return "device-side wait timed out";
+        case BPQ4K_ERR_NO_DEVICE: return "no usable device";
+        case BPQ4K_ERR_ALLOC: return "allocation failed";
+        default: return "unknown status";
+    }
+}
+
+int bpq4k_create(int device, bpq4k_handle_t* out) {
+    if (!out) return BPQ4K_ERR_INVALID_ARG;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return BPQ4K_ERR_NO_DEVICE;
+    }
+    if (device < 0 || device >= count) return BPQ4K_ERR_INVALID_ARG;
+    bpq4k_context* h = new (std::nothrow) bpq4k_context();
+    if (!h) return BPQ4K_ERR_ALLOC;
+    h->device = device;
+    cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, device);
+    cudaDeviceGetAttribute(&h->cc_major, cudaDevAttrComputeCapabilityMajor, device);
+    if (h->cc_major != 10) {
+        // The kernels are built for sm_100a only; there is no other code path.
+        delete h;
+        return BPQ4K_ERR_NO_DEVICE;
+    }
+    *out = h;
+    return BPQ4K_OK;
+}
+
+int bpq4k_destroy(bpq4k_handle_t h) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    {
+        DeviceGuard g(h->device);
+        if (h->stage_x) cudaFree(h->stage_x);
+        if (h->stage_y) cudaFree(h->stage_y);
+        if (h->scratch) cudaFree(h->scratch);
+    }
+    delete h;
+    return BPQ4K_OK;
+}
+
+const char* bpq4k_last_error_string(bpq4k_handle_t h) { return h ? h->err : "null handle"; }
+
+int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    switch (option) {
+        case BPQ4K_OPT_GEMV_VARIANT:
+            if (value < BPQ4K_GEMV_AUTO || value > BPQ4K_GEMV_STREAM)
+                return fail(h, BPQ4K_ERR_INVALID_ARG, "gemv variant %d out of range", value);
+            h->gemv_variant = value;
+            return BPQ4K_OK;
+        case BPQ4K_OPT_PREFILL_MODE:
+            if (value < BPQ4K_PREFILL_F16X3 || value > BPQ4K_PREFILL_BF16)
+                return fail(h, BPQ4K_ERR_INVALID_ARG, "prefill mode %d out of range", value);
+            h->prefill_mode = value;
+            return BPQ4K_OK;
+        case BPQ4K_OPT_PREFILL_MIN_M:
+            if (value < 1) return fail(h, BPQ4K_ERR_INVALID_ARG, "prefill_min_m must be >= 1");
+            h->prefill_min_m = value;
+            return BPQ4K_OK;
+        default: return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown option %d", option);
+    }
+}
+
+int bpq4k_get_option(bpq4k_handle_t h, int option, int* value) {
+    if (!h || !value) return BPQ4K_ERR_INVALID_ARG;
+    switch (option) {
+        case BPQ4K_OPT_GEMV_VARIANT: *value = h->gemv_variant; return BPQ4K_OK;
+        case BPQ4K_OPT_PREFILL_MODE: *value = h->prefill_mode; return BPQ4K_OK;
+        case BPQ4K_OPT_PREFILL_MIN_M: *value = h->prefill_min_m; return BPQ4K_OK;
+        default: return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown option %d", option);
+    }
+}
+
+uint64_t bpq4k_launch_count(bpq4k_handle_t h, int reset) {
+    if (!h) return 0;
+    const uint64_t v = h->launches;
+    if (reset) h->launches = 0;
+    return v;
+}
+
+uint32_t bpq4k_n_blocks(uint32_t K) { return (K + BPQ4K_QK_K - 1u) / BPQ4K_QK_K; }
+uint32_t bpq4k_row_stride_words(uint32_t K) { return bpq4k_n_blocks(K) * BPQ4K_BLOCK_WORDS; }
+
+int bpq4k_pack_q4k_host(const void* raw_host, uint32_t N, uint32_t K, uint32_t* words_host) {
+    if ((!raw_host || !words_host) && N != 0 && K != 0) return BPQ4K_ERR_INVALID_ARG;
+    const uint64_t row_bytes = (uint64_t)bpq4k_n_blocks(K) * BPQ4K_BLOCK_BYTES;
+    const uint64_t stride = bpq4k_row_stride_words(K);
+    const uint8_t* src = static_cast<const uint8_t*>(raw_host);
+    for (uint32_t r = 0; r < N; r++) std::memcpy(words_host + r * stride, src + r * row_bytes, row_bytes);
+    return BPQ4K_OK;
+}
+
+int bpq4k_upload_weights(bpq4k_handle_t h, const uint32_t* words_host, uint64_t n_words, void** w_dev) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (!w_dev || (!words_host && n_words)) return fail(h, BPQ4K_ERR_INVALID_ARG, "null pointer");
+    DeviceGuard g(h->device);
+    *w_dev = nullptr;
+    const size_t bytes = n_words ? (size_t)n_words * 4u : 16u;
+    cudaError_t e = cudaMalloc(w_dev, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(h, BPQ4K_ERR_ALLOC, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+    }
+    if (n_words) {
+        e = cudaMemcpy(*w_dev, words_host, (size_t)n_words * 4u, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) {
+            cudaFree(*w_dev);
+            *w_dev = nullptr;
+            return cuda_fail(h, e, "weight upload");
+        }
+    }
+    return BPQ4K_OK;
+}
+
+int bpq4k_free_device(bpq4k_handle_t h, void* p) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (!p) return BPQ4K_OK;
+    DeviceGuard g(h->device);
+    cudaError_t e = cudaFree(p);
+    if (e != cudaSuccess) return cuda_fail(h, e, "cudaFree");
+    return BPQ4K_OK;
+}
+
+int bpq4k_dequant_f32(bpq4k_handle_t h, const void* W, uint32_t N, uint32_t K, uint32_t rowStrideWords, float* out,
+                      void* stream) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (N == 0) return BPQ4K_OK;
+    if (int s = check_weights(h, W, N, K, rowStrideWords)) return s;
+    if (!out) return fail(h, BPQ4K_ERR_INVALID_ARG, "out is null");
+    if (!aligned16(out)) return fail(h, BPQ4K_ERR_MISALIGNED, "out is not 16-byte aligned");
+    DeviceGuard g(h->device);
+    cudaError_t e = launch_dequant_f32(static_cast<const uint8_t*>(W), N, K, (uint64_t)rowStrideWords * 4u, out,
+                                       static_cast<cudaStream_t>(stream));
+    h->launches += 1;
+    if (e != cudaSuccess) return cuda_fail(h, e, "dequant launch");
+    return BPQ4K_OK;
+}
+
+int bpq4k_matmul_f32(bpq4k_handle_t h, const float* X, const void* W, const float* bias, float* Y, uint32_t M,
+                     uint32_t N, uint32_t K, uint32_t rowStrideWords, uint32_t yOffset, void* stream) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return BPQ4K_OK;
+    if (int s = check_weights(h, W, N, K, rowStrideWords)) return s;
+    if (!X || !Y) return fail(h, BPQ4K_ERR_INVALID_ARG, "X or Y is null");
+    if (!aligned16(X)) return fail(h, BPQ4K_ERR_MISALIGNED, "X is not 16-byte aligned");
+    if (!aligned16(Y)) return fail(h, BPQ4K_ERR_MISALIGNED, "Y is not 16-byte aligned");
+    DeviceGuard g(h->device);
+    MatmulArgs a{};
+    a.X = X;
+    a.W = static_cast<const uint8_t*>(W);
+    a.bias = bias;
+    a.Y = Y + yOffset;
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
+    return run_matmul(h, a, static_cast<cudaStream_t>(stream));
+}
+
+int bpq4k_matmul_moe_f32(bpq4k_handle_t h, const float* X, const void* W, const float* bias, float* Y,
+                         const uint32_t* offsets, const uint32_t* x_rows, uint32_t nSlots, uint32_t N, uint32_t K,
+                         uint32_t rowStrideWords, void* stream) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (nSlots == 0 || N == 0) return BPQ4K_OK;
+    if (int s = check_weights(h, W, N, K, rowStrideWords)) return s;
+    if (!X || !Y || !offsets) return fail(h, BPQ4K_ERR_INVALID_ARG, "X, Y or offsets is null");
+    if (!aligned16(X)) return fail(h, BPQ4K_ERR_MISALIGNED, "X is not 16-byte aligned");
+    if (!aligned16(Y)) return fail(h, BPQ4K_ERR_MISALIGNED, "Y is not 16-byte aligned");
+    DeviceGuard g(h->device);
+    MatmulArgs a{};
+    a.X = X;
+    a.W = static_cast<const uint8_t*>(W);
+    a.bias = bias;
+    a.Y = Y;
+    a.M = 1;
+    a.N = N;
+    a.K = K;
+    a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
+    a.offsets = offsets;
+    a.x_rows = x_rows;
+    a.n_slots = nSlots;
+    return run_matmul(h, a, static_cast<cudaStream_t>(stream));
+}
+
+int bpq4k_matmul_host_f32(bpq4k_handle_t h, const float* X_host, const void* W_dev, const float* bias_dev,
+                          float* Y_host, uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords,
+                          void* stream) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return BPQ4K_OK;
+    if (!X_host || !Y_host) return fail(h, BPQ4K_ERR_INVALID_ARG, "X_host or Y_host is null");
+    if (int s = check_weights(h, W_dev, N, K, rowStrideWords)) return s;
+    DeviceGuard g(h->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t xb = (size_t)M * K * 4u, yb = (size_t)M * N * 4u;
+    if (int s = ensure_bytes(h, reinterpret_cast<void**>(&h->stage_x), &h->stage_x_bytes, xb)) return s;
+    if (int s = ensure_bytes(h, reinterpret_cast<void**>(&h->stage_y), &h->stage_y_bytes, yb)) return s;
+    cudaError_t e = cudaMemcpyAsync(h->stage_x, X_host, xb, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return cuda_fail(h, e, "activation upload");
+    MatmulArgs a{};
+    a.X = h->stage_x;
+    a.W = static_cast<const uint8_t*>(W_dev);
+    a.bias = bias_dev;
+    a.Y = h->stage_y;
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
+    if (int s = run_matmul(h, a, st)) return s;
+    e = cudaMemcpyAsync(Y_host, h->stage_y, yb, cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) return cuda_fail(h, e, "result read-back");
+    e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(h, e, "stream synchronize");
+    return BPQ4K_OK;
+}
+
+}  // extern "C"
+#pragma GCC visibility pop

@@ -1,0 +1,186 @@
+"""Host-side mirror of the reference's Q4_K operator interface, on top of the C ABI.
+
+Names follow the reference: ``KQuantPacked`` / ``pack_q4k``
+(runtime/gguf_loader.h:108-117, gguf_loader.cpp:359-379), ``upload`` for
+``uploadKQWeight`` (runtime/model_runner.cpp:958-963), ``matmul`` for the
+``q4k_matmul*`` dispatches with their five bindings X, W, Bias, Y, params
+(runtime/kernels/quant_kq/q4k_matmul.wgsl:1-5), ``matmul_moe`` for the indirect
+expert form (runtime/kernels/quant_kq/iq4xs_matmul_moe.wgsl:5-10) and
+``dequant`` for ``dequant_kquant`` (gguf_loader.cpp:455-496).
+
+PyTorch is used only to own device memory and streams; all arithmetic happens
+in libbpq4k.so.  Nothing here computes on the CPU and nothing falls back.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib
+
+QK_K = 256
+BLOCK_BYTES = 144
+BLOCK_WORDS = 36
+
+OPT_GEMV_VARIANT = 1
+OPT_PREFILL_MODE = 2
+OPT_PREFILL_MIN_M = 3
+GEMV_AUTO, GEMV_FP32, GEMV_STREAM = 0, 1, 2
+PREFILL_F16X3, PREFILL_F16, PREFILL_BF16 = 0, 1, 2
+
+
+class Q4KError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"bpq4k status {status} ({_lib.load().bpq4k_status_string(status).decode()}): {message}")
+        self.status = status
+
+
+@dataclass
+class KQuantPacked:
+    """pack_q4k's result: raw block words plus the derived strides."""
+    data: np.ndarray          # uint32 [N * rowStrideWords]
+    N: int
+    K: int
+    rowStrideWords: int
+    nBlocks: int
+
+
+def pack_q4k(raw, N: int, K: int) -> KQuantPacked:
+    """Row-wise copy of raw 144-byte blocks into u32 words (identity re-layout)."""
+    lib = _lib.load()
+    raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+    nb = lib.bpq4k_n_blocks(K)
+    rs = lib.bpq4k_row_stride_words(K)
+    if raw.size < N * nb * BLOCK_BYTES:
+        raise ValueError(f"raw has {raw.size} bytes, need {N * nb * BLOCK_BYTES}")
+    words = np.zeros(N * rs, np.uint32)
+    st = lib.bpq4k_pack_q4k_host(raw.ctypes.data, N, K, words.ctypes.data)
+    if st:
+        raise Q4KError(st, "pack_q4k")
+    return KQuantPacked(words, N, K, rs, nb)
+
+
+@dataclass
+class Q4KWeight:
+    """A packed weight resident on the device (a torch uint8 tensor owns the bytes)."""
+    buf: "torch.Tensor"       # uint8 [N * rowStrideWords * 4]
+    N: int
+    K: int
+    rowStrideWords: int
+
+    @property
+    def nbytes(self) -> int:
+        return self.N * self.rowStrideWords * 4
+
+    def rows(self, n0: int, n1: int) -> "Q4KWeight":
+        """A contiguous row range [n0, n1) as a view: rows are contiguous byte ranges."""
+        rb = self.rowStrideWords * 4
+        return Q4KWeight(self.buf[n0 * rb:n1 * rb], n1 - n0, self.K, self.rowStrideWords)
+
+
+class Q4KContext:
+    """One handle on one device; not thread-safe (like the reference's GPUContext)."""
+
+    def __init__(self, device: int = 0):
+        import torch
+
+        self._torch = torch
+        self.lib = _lib.load()
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: this library has no CPU path")
+        self.device = int(device)
+        h = C.c_void_p()
+        st = self.lib.bpq4k_create(self.device, C.byref(h))
+        if st:
+            raise Q4KError(st, "bpq4k_create")
+        self.h = h
+
+    def close(self) -> None:
+        if getattr(self, "h", None):
+            self.lib.bpq4k_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- helpers ---------------------------------------------------------
+    def _check(self, st: int) -> None:
+        if st:
+            raise Q4KError(st, self.lib.bpq4k_last_error_string(self.h).decode())
+
+    def _stream(self) -> int:
+        return self._torch.cuda.current_stream(self.device).cuda_stream
+
+    def set_option(self, option: int, value: int) -> None:
+        self._check(self.lib.bpq4k_set_option(self.h, option, value))
+
+    def get_option(self, option: int) -> int:
+        v = C.c_int()
+        self._check(self.lib.bpq4k_get_option(self.h, option, C.byref(v)))
+        return v.value
+
+    def launch_count(self, reset: bool = False) -> int:
+        return int(self.lib.bpq4k_launch_count(self.h, 1 if reset else 0))
+
+    # -- weights ---------------------------------------------------------
+    def upload(self, packed: KQuantPacked) -> Q4KWeight:
+        """uploadKQWeight: device buffer + copy of the packed words."""
+        torch = self._torch
+        host = torch.from_numpy(packed.data.view(np.uint8))
+        buf = torch.empty(max(host.numel(), 16), dtype=torch.uint8, device=f"cuda:{self.device}")
+        buf[: host.numel()].copy_(host)
+        return Q4KWeight(buf, packed.N, packed.K, packed.rowStrideWords)
+
+    # -- operators -------------------------------------------------------
+    def dequant(self, w: Q4KWeight, out=None):
+        torch = self._torch
+        if out is None:
+            out = torch.empty((w.N, w.K), dtype=torch.float32, device=w.buf.device)
+        self._check(self.lib.bpq4k_dequant_f32(self.h, w.buf.data_ptr(), w.N, w.K, w.rowStrideWords,
+                                               out.data_ptr(), self._stream()))
+        return out
+
+    def matmul(self, x, w: Q4KWeight, bias=None, out=None, y_offset: int = 0):
+        """Y[yOffset + m*N + n] = sum_k X[m,k] * deq(W)[n,k] + bias[n]; X float32 [..., K]."""
+        torch = self._torch
+        assert x.dtype == torch.float32 and x.is_cuda and x.is_contiguous()
+        K = x.shape[-1]
+        if K != w.K:
+            raise ValueError(f"X has K={K}, weight has K={w.K}")
+        M = x.numel() // K if K else 0
+        if out is None:
+            out = torch.empty(tuple(x.shape[:-1]) + (w.N,), dtype=torch.float32, device=x.device)
+        self._check(self.lib.bpq4k_matmul_f32(
+            self.h, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
+            out.data_ptr(), M, w.N, K, w.rowStrideWords, y_offset, self._stream()))
+        return out
+
+    def matmul_moe(self, x, w: Q4KWeight, n_rows_per_expert: int, offsets, x_rows=None, bias=None, out=None):
+        """Indirect form: slot s uses weight rows offsets[s] .. offsets[s]+N of the expert stack."""
+        torch = self._torch
+        assert x.dtype == torch.float32 and x.is_contiguous()
+        assert offsets.dtype == torch.int32 or offsets.dtype == torch.uint32
+        S = offsets.numel()
+        N = n_rows_per_expert
+        if out is None:
+            out = torch.empty((S, N), dtype=torch.float32, device=x.device)
+        self._check(self.lib.bpq4k_matmul_moe_f32(
+            self.h, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
+            out.data_ptr(), offsets.data_ptr(), x_rows.data_ptr() if x_rows is not None else None,
+            S, N, w.K, w.rowStrideWords, self._stream()))
+        return out
+
+    def matmul_host(self, x_host: np.ndarray, w: Q4KWeight, y_host: np.ndarray, bias=None) -> np.ndarray:
+        """Host activations in, host outputs out; copies and the wait are inside the call."""
+        assert x_host.dtype == np.float32 and y_host.dtype == np.float32
+        assert x_host.flags.c_contiguous and y_host.flags.c_contiguous
+        M = x_host.size // w.K
+        self._check(self.lib.bpq4k_matmul_host_f32(
+            self.h, x_host.ctypes.data, w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
+            y_host.ctypes.data, M, w.N, w.K, w.rowStrideWords, self._stream()))
+        return y_host

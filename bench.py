@@ -1,0 +1,390 @@
+"""Benchmark of the Q4_K matmul path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (``config.workload``): the decode projections of a Llama-3-8B-shaped
+model, M = 1, GGUF Q4_K weights -- q 4096x4096, k/v 1024x4096, o 4096x4096,
+gate/up 14336x4096, down 4096x14336, lm_head 128256x4096 -- random weights and
+N(0,1) activations from seeded generators (no model files are involved).  One
+step = one pass over all eight projections, each with its own activation and
+output buffer.  The weights of one pass (418 MB) exceed the 126 MB L2, so every
+launch streams its weights from HBM.
+
+``value``     whole-job algorithmic GB/s (weights + activations + outputs moved
+              once) with everything resident in HBM, the step replayed from a
+              CUDA graph, timed with CUDA events; max over ranks.
+``e2e``       the same metric through the host-buffer C-ABI call: every step
+              copies the activations from pinned host memory, runs the kernels
+              on the resident weights and reads the outputs back.
+``roofline``  the dominant kernel (the streaming matmul kernel) against the
+              measured HBM copy bandwidth.
+``cpu_baseline`` the reference's own CPU code for the path (dequant_kquant +
+              float dot) timed on this machine's host cores on a bounded sample.
+
+With N > 1 ranks every rank holds its own row shard of each projection (the
+shard has the single-GPU shape, i.e. the global matrix has N times the rows:
+weak scaling) and the output slices are all-gathered over NCCL.
+
+``--impl reference`` times the reference's CPU implementation only (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from backpack_b200 import synth  # noqa: E402
+
+METRIC = "q4k_matmul_m1_algorithmic_bandwidth"
+UNIT = "GB/s"
+WORKLOAD = "llama3-8b decode projections, M=1, Q4_K (config 1)"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_PEAKS["hbm_gbs"], "fallback"
+
+
+def step_bytes(M=1):
+    return sum(synth.algorithmic_bytes(M, N, K) for _, N, K in synth.LLAMA3_8B)
+
+
+def weight_bytes_total():
+    return sum(synth.weight_bytes(N, K) for _, N, K in synth.LLAMA3_8B)
+
+
+# --------------------------------------------------------------------------
+# clocks (read-only NVML sampling during the timed regions)
+# --------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+        0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting",
+    }
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.dev = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.dev, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.dev, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.dev))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def start(self):
+        if self.nv:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        med = int(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------
+# CPU baseline / reference arm
+# --------------------------------------------------------------------------
+def cpu_pass(kind_ref: bool, threads: int, shapes, weights, xs):
+    from oracle import q4k_oracle as orc
+
+    t0 = time.perf_counter()
+    for (name, N, K) in shapes:
+        orc.matmul(xs[name], weights[name], None, N, K, threads=threads, use_ref=kind_ref)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(budget_s: float, shapes, weights, xs):
+    """Time the reference's CPU path on a bounded sample: whole passes over `shapes`."""
+    from oracle import q4k_oracle as orc
+
+    kind_ref = orc.ref_available()
+    cores = os.cpu_count() or 1
+    best, reps, spent = None, 0, 0.0
+    while reps < 2 or (spent < budget_s and reps < 50):
+        dt = cpu_pass(kind_ref, cores, shapes, weights, xs)
+        best = dt if best is None else min(best, dt)
+        spent += dt
+        reps += 1
+    nbytes = sum(synth.algorithmic_bytes(1, N, K) for _, N, K in shapes)
+    return {"value": nbytes / best / 1e9, "unit": UNIT, "cores": cores,
+            "kind": "reference" if kind_ref else "port",
+            "sample": f"{reps} passes over {len(shapes)} projections ({nbytes / 1e6:.0f} MB each), best pass"}, best
+
+
+def make_host_inputs(shapes, config_tag, rank=0):
+    weights, xs = {}, {}
+    for name, N, K in shapes:
+        weights[name] = synth.make_q4k_weights(N, K, synth.shape_seed(config_tag, name) + rank)
+        xs[name] = synth.make_activations(1, K, synth.shape_seed(config_tag, name + ".x") + rank)
+    return weights, xs
+
+
+def run_reference_arm(args, rank):
+    """The reference's CPU implementation of the path on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    shapes = list(synth.LLAMA3_8B)
+    weights, xs = make_host_inputs(shapes, "config1")
+    from oracle import q4k_oracle as orc
+
+    kind_ref = orc.ref_available()
+    cores = os.cpu_count() or 1
+    steps, warm = max(args.steps, 1), max(args.warmup, 0)
+    # Bound the run: if (steps + warmup) full passes would take more than the
+    # budget, each step processes the same leading fraction of every projection's rows.
+    t_full = cpu_pass(kind_ref, cores, shapes, weights, xs)
+    frac = min(1.0, args.ref_budget / ((steps + warm) * t_full))
+    if frac < 1.0:
+        shapes = [(n, max(min(N, 8 * cores), int(N * frac)), K) for n, N, K in shapes]
+        weights = {n: weights[n][:N] for n, N, K in shapes}
+    nbytes = sum(synth.algorithmic_bytes(1, N, K) for _, N, K in shapes)
+    for _ in range(warm):
+        cpu_pass(kind_ref, cores, shapes, weights, xs)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_pass(kind_ref, cores, shapes, weights, xs)
+    dt = (time.perf_counter() - t0) / steps
+    val = nbytes / dt / 1e9
+    sample = (f"each step = the leading {100 * nbytes / step_bytes():.1f}% of the rows of all 8 projections "
+              f"({nbytes / 1e6:.1f} MB), all host threads")
+    line = {
+        "metric": METRIC, "value": val, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "M": 1, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "reference" if kind_ref else "port",
+                         "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------
+def run_gpu_arm(args, rank, world, local_rank):
+    import torch
+
+    import backpack_b200 as bp
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    ctx = bp.Q4KContext(local_rank)
+    shapes = synth.LLAMA3_8B
+    weights_h, xs_h = make_host_inputs(shapes, "config1", rank)
+    dev = f"cuda:{local_rank}"
+    W, X, Y, Yall = {}, {}, {}, {}
+    for name, N, K in shapes:
+        W[name] = ctx.upload(bp.pack_q4k(weights_h[name], N, K))
+        X[name] = torch.from_numpy(xs_h[name]).to(dev)
+        if world > 1:
+            Yall[name] = torch.zeros(world * N, dtype=torch.float32, device=dev)
+            Y[name] = Yall[name][rank * N:(rank + 1) * N]      # the rank's slice, written in place
+        else:
+            Y[name] = torch.zeros(1, N, dtype=torch.float32, device=dev)
+
+    def one_pass():
+        for name, N, K in shapes:
+            ctx.matmul(X[name], W[name], out=Y[name])
+            if world > 1:
+                dist.all_gather_into_tensor(Yall[name], Y[name])
+
+    # correctness spot-check before timing (one projection against the CPU checker)
+    from oracle import q4k_oracle as orc
+
+    one_pass()
+    torch.cuda.synchronize()
+    want = orc.matmul(xs_h["k"], weights_h["k"], None, 1024, 4096)
+    got = Y["k"].reshape(1, -1).cpu().numpy()
+    rel = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+    assert rel < 1e-3, f"parity check failed before timing: rel_l2={rel}"
+
+    # ---- resident (graph-replayed) timing --------------------------------
+    stream = torch.cuda.Stream()
+    graph = None
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            one_pass()
+        stream.synchronize()
+        if world == 1:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                one_pass()
+        run_step = graph.replay if graph is not None else one_pass
+        for _ in range(max(args.warmup, 3)):
+            run_step()
+        stream.synchronize()
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        ctx.launch_count(reset=True)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            run_step()
+        e1.record(stream)
+        stream.synchronize()
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        launches_eager = ctx.launch_count()
+
+        # ---- kernel-only duration of the dominant kernel (no collectives) ----
+        def kernels_only():
+            for name, N, K in shapes:
+                ctx.matmul(X[name], W[name], out=Y[name])
+
+        kgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(kgraph, stream=stream):
+            kernels_only()
+        ctx.launch_count(reset=True)
+        kernels_only()
+        launches_per_step = ctx.launch_count()
+        for _ in range(3):
+            kgraph.replay()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record(stream)
+        for _ in range(args.steps):
+            kgraph.replay()
+        k1.record(stream)
+        stream.synchronize()
+        kernel_ms = k0.elapsed_time(k1)
+
+        # ---- end to end through the host-buffer entry point ---------------
+        xs_pin = {n: torch.from_numpy(xs_h[n]).pin_memory() for n, _, _ in shapes}
+        ys_pin = {n: torch.zeros(1, N, dtype=torch.float32).pin_memory() for n, N, _ in shapes}
+        xs_np = {n: xs_pin[n].numpy() for n in xs_pin}
+        ys_np = {n: ys_pin[n].numpy() for n in ys_pin}
+
+        def e2e_pass():
+            for name, N, K in shapes:
+                ctx.matmul_host(xs_np[name], W[name], ys_np[name])
+                if world > 1:
+                    dist.all_gather_into_tensor(Yall[name], Y[name])
+
+        for _ in range(3):
+            e2e_pass()
+        e2e_steps = max(1, min(args.steps, 200))
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_pass()
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        sampler.stop()
+
+    times = torch.tensor([ms, kernel_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    if dist:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, kernel_ms, e2e_ms = (float(v) for v in times.cpu())
+
+    if rank == 0:
+        peak, peak_src = load_peaks()
+        sb = step_bytes()
+        value = world * sb * args.steps / (ms * 1e-3) / 1e9
+        e2e_val = world * sb * e2e_steps / (e2e_ms * 1e-3) / 1e9
+        per_launch_bytes = sb / launches_per_step
+        per_launch_s = kernel_ms * 1e-3 / (args.steps * launches_per_step)
+        achieved = per_launch_bytes / per_launch_s / 1e9
+        cpu, _ = cpu_baseline(args.cpu_budget, shapes, weights_h, xs_h)
+        h2d = sum(K * 4 for _, _, K in shapes)
+        d2h = sum(N * 4 for _, N, _ in shapes)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "M": 1, "projections": [list(s) for s in shapes],
+                       "bytes_per_step_per_gpu": sb, "weight_bytes_per_step_per_gpu": weight_bytes_total(),
+                       "l2": "inputs larger than L2 (418 MB of weights per pass vs 126 MB L2)",
+                       "replay": "cuda graph" if graph is not None else "eager + nccl all-gather",
+                       "sharding": "rows (N) per rank, output slices all-gathered" if world > 1 else "none"},
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": int(launches_per_step * args.steps),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "q4k matmul (M=1)", "launches_per_step": launches_per_step,
+                         "avg_launch_us": per_launch_s * 1e6, "alg_bytes_per_launch": per_launch_bytes},
+            "cpu_baseline": cpu,
+            "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+    _ = launches_eager
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
+    ap.add_argument("--ref-budget", type=float, default=120.0, help="seconds the --impl reference run may take")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    run_gpu_arm(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,168 @@
+/*
+ * bpq4k.h -- C ABI of libbpq4k.so: the GGUF Q4_K dequantize-fused matrix
+ * multiply for NVIDIA B200 (sm_100a).
+ *
+ * The library replaces, for this one operator, what the Backpack runtime does
+ * through Dawn/WGSL: its six `q4k_*` compute shaders, the host-side packer and
+ * the CPU decode.  Every entry point below names the reference interface it
+ * stands in for (file:line relative to the reference tree).
+ *
+ * Conventions
+ *  - Plain C: pointers, sizes, an opaque handle.  No C++ or framework types.
+ *  - Unless a name ends in `_host`, every data pointer is a DEVICE pointer on
+ *    the handle's device, owned by the caller.  The library owns only the
+ *    scratch memory inside the handle.
+ *  - `stream` is a cudaStream_t / CUstream passed as void*; NULL is the
+ *    default stream.  Calls are asynchronous with respect to the host and
+ *    ordered on that stream, like dispatches on the reference's single WebGPU
+ *    queue (runtime/model_runner.h:27-30).
+ *  - A handle is bound to one device and is not thread-safe, like the
+ *    reference's GPUContext/ExecutionContext.
+ *  - Every call returns a bpq4k_status; nothing aborts, traps or throws.  The
+ *    reference's ops return void and leave the output invalid on bad input
+ *    (runtime/ops/matmul.cpp:212,333); callers here map a non-zero status to
+ *    that behaviour.
+ *  - Weights are the raw GGUF Q4_K bytes, exactly what the reference uploads
+ *    (runtime/gguf_loader.cpp:359-379, runtime/model_runner.cpp:958-963):
+ *    row-major [N][K/256] super-blocks of 144 bytes; `rowStrideWords` is the
+ *    distance between rows in 32-bit words (KQuantPacked::rowStrideWords,
+ *    runtime/gguf_loader.h:108-117) and must be a multiple of 4 (16 bytes) and
+ *    at least (K/256)*36.  K must be a multiple of 256.
+ */
+#ifndef BPQ4K_H
+#define BPQ4K_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BPQ4K_VERSION 100
+#define BPQ4K_QK_K 256u
+#define BPQ4K_BLOCK_BYTES 144u
+#define BPQ4K_BLOCK_WORDS 36u
+
+typedef struct bpq4k_context* bpq4k_handle_t;
+
+typedef enum bpq4k_status {
+    BPQ4K_OK = 0,
+    BPQ4K_ERR_INVALID_ARG = 1,   /* null pointer, zero handle, bad enum */
+    BPQ4K_ERR_UNSUPPORTED = 2,   /* K not a multiple of 256, size beyond a stated limit */
+    BPQ4K_ERR_MISALIGNED = 3,    /* pointer or stride not aligned as documented */
+    BPQ4K_ERR_CUDA = 4,          /* a CUDA runtime call failed; see last_error_string */
+    BPQ4K_ERR_NCCL = 5,          /* reserved for callers that layer a collective on top */
+    BPQ4K_ERR_TIMEOUT = 6,       /* a bounded device-side wait ran out */
+    BPQ4K_ERR_NO_DEVICE = 7,     /* no usable sm_100 device */
+    BPQ4K_ERR_ALLOC = 8          /* device or host allocation failed */
+} bpq4k_status;
+
+/* Options (bpq4k_set_option).  The reference selects kernels with environment
+ * switches such as BP_Q4K_DECODE_256 (runtime/model_runner.cpp:2045-2053);
+ * here the choice is an explicit per-handle option. */
+typedef enum bpq4k_option {
+    BPQ4K_OPT_GEMV_VARIANT = 1,  /* bpq4k_gemv_variant; default AUTO */
+    BPQ4K_OPT_PREFILL_MODE = 2,  /* bpq4k_prefill_mode; default F16X3 */
+    BPQ4K_OPT_PREFILL_MIN_M = 3  /* smallest M routed to the tensor-core prefill kernel; default 64 */
+} bpq4k_option;
+
+typedef enum bpq4k_gemv_variant {
+    BPQ4K_GEMV_AUTO = 0,
+    BPQ4K_GEMV_FP32 = 1,   /* one warp per output row, float FMAs (the reference shader's arithmetic) */
+    BPQ4K_GEMV_STREAM = 2  /* bulk-copy ring + tensor-core dot products, split-precision activations */
+} bpq4k_gemv_variant;
+
+typedef enum bpq4k_prefill_mode {
+    BPQ4K_PREFILL_F16X3 = 0,  /* three-term half split of W and X: meets the float tolerance */
+    BPQ4K_PREFILL_F16 = 1,    /* single half-precision pass */
+    BPQ4K_PREFILL_BF16 = 2    /* single bfloat16 pass */
+} bpq4k_prefill_mode;
+
+/* ---- library and handle ------------------------------------------------ */
+
+int bpq4k_version(void);
+const char* bpq4k_status_string(int status);
+
+/* Create a handle on CUDA device `device`.  Stands in for GPUContext::init +
+ * pipeline creation (runtime/gpu_context.h:151-220): after this call no entry
+ * point below compiles, loads or allocates anything except where it says so. */
+int bpq4k_create(int device, bpq4k_handle_t* out);
+int bpq4k_destroy(bpq4k_handle_t h);
+
+/* Text of the last failure on this handle (never NULL).  Stands in for the
+ * stderr reporting of Dawn's error callbacks (runtime/gpu_context.cpp:212-237). */
+const char* bpq4k_last_error_string(bpq4k_handle_t h);
+
+int bpq4k_set_option(bpq4k_handle_t h, int option, int value);
+int bpq4k_get_option(bpq4k_handle_t h, int option, int* value);
+
+/* Number of kernels this handle has launched since creation (or since the
+ * counter was last reset with reset != 0).  The reference counts dispatches in
+ * GPUContext::timing (runtime/gpu_context.h:223-231). */
+uint64_t bpq4k_launch_count(bpq4k_handle_t h, int reset);
+
+/* ---- host-side packing -------------------------------------------------- */
+
+/* nBlocks and rowStrideWords of KQuantPacked for a given K
+ * (runtime/gguf_loader.cpp:366-367). */
+uint32_t bpq4k_n_blocks(uint32_t K);
+uint32_t bpq4k_row_stride_words(uint32_t K);
+
+/* pack_q4k (runtime/gguf_loader.cpp:359-379): copy N rows of raw blocks into
+ * `words_host` (N * bpq4k_row_stride_words(K) words).  Host memory only. */
+int bpq4k_pack_q4k_host(const void* raw_host, uint32_t N, uint32_t K, uint32_t* words_host);
+
+/* uploadKQWeight (runtime/model_runner.cpp:958-963): allocate a device buffer
+ * and copy packed words into it.  The copy is synchronous.  Free with
+ * bpq4k_free_device. */
+int bpq4k_upload_weights(bpq4k_handle_t h, const uint32_t* words_host, uint64_t n_words, void** w_dev);
+int bpq4k_free_device(bpq4k_handle_t h, void* dev_ptr);
+
+/* ---- device operators ---------------------------------------------------- */
+
+/* dequant_kquant(raw, out, N, K, GGUF_TYPE_Q4_K) (runtime/gguf_loader.cpp:455-496)
+ * on the device: out[n*K + k] = (d*sc)*q - dmin*mn, bit-identical to the
+ * reference's float arithmetic.  `out` is float[N*K]. */
+int bpq4k_dequant_f32(bpq4k_handle_t h, const void* W, uint32_t N, uint32_t K,
+                      uint32_t rowStrideWords, float* out, void* stream);
+
+/* The Q4_K matmul dispatch: Y[yOffset + m*N + n] = sum_k X[m*K+k]*deq(W)[n][k] + bias[n].
+ * One call covers every shader variant the reference picks by M
+ * (runtime/model_runner.cpp:2032-2054, 5841-5845): q4k_matmul.wgsl:20-95,
+ * q4k_matmul_128.wgsl:8-17 (yOffset), q4k_matmul_batched4/8.wgsl:9-23; bindings
+ * X, W, Bias, Y and params {K, N, nBlocks, rowStrideWords, yOffset}
+ * (runtime/model_runner.cpp:2404-2413).  Grid and tile choices are internal.
+ * `bias` may be NULL (the reference always binds a zero buffer).  X, W and Y
+ * must be 16-byte aligned.  M >= the PREFILL_MIN_M option goes to the
+ * tensor-core kernel in the PREFILL_MODE option's precision. */
+int bpq4k_matmul_f32(bpq4k_handle_t h, const float* X, const void* W, const float* bias, float* Y,
+                     uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords,
+                     uint32_t yOffset, void* stream);
+
+/* Indirect (expert-stacked) form, the ABI of the reference's `*_matmul_moe`
+ * shaders (runtime/kernels/quant_kq/iq4xs_matmul_moe.wgsl:5-10,55-66,96-99) with
+ * every routed slot served by ONE launch instead of one dispatch per slot
+ * (runtime/model_runner.cpp:3584-3651).  W stacks all experts row-wise
+ * ([nExperts*N][K], runtime/model_runner.cpp:1520-1562); offsets[s] is the first
+ * weight row of slot s's expert (compute_offsets.wgsl:26-36: expert*N).  Slot s
+ * reads activation row x_rows[s] of X (x_rows NULL: row s) and writes
+ * Y[s*N + n] = sum_k X[x_rows[s]*K + k]*deq(W)[offsets[s]+n][k] + bias[n]. */
+int bpq4k_matmul_moe_f32(bpq4k_handle_t h, const float* X, const void* W, const float* bias, float* Y,
+                         const uint32_t* offsets, const uint32_t* x_rows, uint32_t nSlots,
+                         uint32_t N, uint32_t K, uint32_t rowStrideWords, void* stream);
+
+/* Same operator with HOST activations and HOST outputs: copies X_host to the
+ * handle's staging buffer, runs the matmul on the resident device weights and
+ * copies Y back, then waits.  This is the per-token host<->device traffic of
+ * the reference's decode loop (one input write, one result read-back:
+ * runtime/model_runner.cpp:5725-5764).  Allocates staging on first use and
+ * when sizes grow. */
+int bpq4k_matmul_host_f32(bpq4k_handle_t h, const float* X_host, const void* W_dev,
+                          const float* bias_dev, float* Y_host, uint32_t M, uint32_t N, uint32_t K,
+                          uint32_t rowStrideWords, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BPQ4K_H */

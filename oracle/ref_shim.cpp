@@ -1,0 +1,73 @@
+// ref_shim.cpp -- C-callable doorway into the reference's own CPU code for the
+// Q4_K path, so the restatement in q4k_oracle.c can be checked against it and
+// so the benchmark can time the reference itself on the host cores.
+//
+// TEST INFRASTRUCTURE ONLY.  This file contains no reference code: it includes
+// the reference's header and is linked with the reference's gguf_loader.cpp,
+// both compiled where they lie in the mounted reference tree (see the Makefile
+// target `ref`).  The result goes to oracle/_ref/, which is not committed.
+#include "gguf_loader.h"   // -I <reference>/runtime
+
+#include <cstdint>
+#include <cstring>
+#include <thread>
+#include <vector>
+
+extern "C" {
+
+// dequant_kquant(..., GGUF_TYPE_Q4_K) -- runtime/gguf_loader.cpp:455-496
+void ref_q4k_dequant(const void* raw, float* out, uint32_t N, uint32_t K) {
+    dequant_kquant(raw, out, N, K, GGUF_TYPE_Q4_K);
+}
+
+// pack_q4k -- runtime/gguf_loader.cpp:359-379.  Copies the packed words out and
+// reports the two derived fields of KQuantPacked.
+void ref_pack_q4k(const void* raw, uint32_t N, uint32_t K, uint32_t* words,
+                  uint32_t* rowStrideWords, uint32_t* nBlocks) {
+    KQuantPacked p = pack_q4k(raw, N, K);
+    if (rowStrideWords) *rowStrideWords = p.rowStrideWords;
+    if (nBlocks) *nBlocks = p.nBlocks;
+    if (words) std::memcpy(words, p.data.data(), p.data.size() * sizeof(uint32_t));
+}
+
+// The expected-value computation of runtime/tests/kernel_test.cpp:1682,1688,
+// 1728,1746: dequant_kquant, then for each (m, n) a float accumulator that
+// starts at bias[n] and adds x*w for k ascending.  The tests decode the whole
+// matrix first; here rows are decoded in slabs of 64 with the same reference
+// routine so the scratch stays cache-sized (the arithmetic per output is the
+// same sequence of float operations).
+static void rows(const float* X, const uint8_t* raw, const float* bias, float* Y,
+                 uint32_t M, uint32_t N, uint32_t K, uint32_t n0, uint32_t n1) {
+    const uint32_t nb = K / 256, SLAB = 64;
+    std::vector<float> deq((size_t)SLAB * K);
+    for (uint32_t s0 = n0; s0 < n1; s0 += SLAB) {
+        const uint32_t cnt = (n1 - s0 < SLAB) ? n1 - s0 : SLAB;
+        dequant_kquant(raw + (size_t)s0 * nb * 144, deq.data(), cnt, K, GGUF_TYPE_Q4_K);
+        for (uint32_t m = 0; m < M; m++)
+            for (uint32_t r = 0; r < cnt; r++) {
+                const uint32_t n = s0 + r;
+                float a = bias ? bias[n] : 0.0f;
+                for (uint32_t k = 0; k < K; k++) a += X[(size_t)m * K + k] * deq[(size_t)r * K + k];
+                Y[(size_t)m * N + n] = a;
+            }
+    }
+}
+
+void ref_q4k_matmul(const float* X, const void* raw, const float* bias, float* Y,
+                    uint32_t M, uint32_t N, uint32_t K, uint32_t threads) {
+    const uint8_t* src = (const uint8_t*)raw;
+    if (threads <= 1 || N < threads) {
+        rows(X, src, bias, Y, M, N, K, 0, N);
+        return;
+    }
+    // Row-parallel: each thread decodes and multiplies its own contiguous rows.
+    std::vector<std::thread> pool;
+    for (uint32_t t = 0; t < threads; t++) {
+        uint32_t n0 = (uint32_t)((uint64_t)N * t / threads);
+        uint32_t n1 = (uint32_t)((uint64_t)N * (t + 1) / threads);
+        pool.emplace_back([=]() { rows(X, src, bias, Y, M, N, K, n0, n1); });
+    }
+    for (auto& th : pool) th.join();
+}
+
+}  // extern "C"

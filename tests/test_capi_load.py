@@ -1,0 +1,60 @@
+"""CPU-only checks of the boundary: the shared library loads, exports every symbol the
+header declares, and the entry points that need no device behave."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+
+from backpack_b200 import _lib, pack_q4k, synth
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "bpq4k.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(bpq4k_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = header_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/bpq4k.h but not exported"
+    assert set(names) == set(_lib.SIGNATURES), "ctypes signature table out of sync with the header"
+
+
+def test_version_and_status_strings():
+    lib = _lib.load()
+    assert lib.bpq4k_version() == 100
+    assert lib.bpq4k_status_string(0) == b"ok"
+    assert b"256" in lib.bpq4k_status_string(2) or lib.bpq4k_status_string(2) == b"unsupported shape"
+    assert lib.bpq4k_status_string(99) == b"unknown status"
+
+
+def test_null_handle_is_rejected_not_crashing():
+    lib = _lib.load()
+    assert lib.bpq4k_destroy(None) == 1
+    assert lib.bpq4k_set_option(None, 1, 0) == 1
+    assert lib.bpq4k_matmul_f32(None, None, None, None, None, 1, 1, 256, 36, 0, None) == 1
+    assert lib.bpq4k_last_error_string(None) == b"null handle"
+    assert lib.bpq4k_create(0, None) == 1
+
+
+def test_strides_follow_pack_q4k():
+    lib = _lib.load()
+    for K, nb in [(256, 1), (512, 2), (4096, 16), (14336, 56), (300, 2)]:
+        assert lib.bpq4k_n_blocks(K) == nb
+        assert lib.bpq4k_row_stride_words(K) == nb * 36
+
+
+def test_pack_host_is_identity():
+    N, K = 9, 768
+    w = synth.make_q4k_weights(N, K, 2)
+    p = pack_q4k(w, N, K)
+    assert p.rowStrideWords == 108 and p.nBlocks == 3 and p.N == N and p.K == K
+    assert np.array_equal(p.data.view(np.uint8), w.reshape(-1))
+    empty = pack_q4k(np.zeros(0, np.uint8), 0, 256)
+    assert empty.data.size == 0

@@ -1,0 +1,278 @@
+"""GPU parity: the CUDA path through the C ABI against the CPU checker and the
+reference-generated golden vectors.  Dequantised weights must be bit-exact;
+matmul outputs must be within 1e-3 relative L2 and 2e-2 max absolute error of
+the reference computation (and within the reference's own test tolerance,
+atol = rtol = 2e-4, on its own fixtures)."""
+import numpy as np
+import pytest
+
+from backpack_b200 import pack_q4k, q4k, synth
+from conftest import GOLDEN_CASES, assert_close_ref, rel_l2
+from oracle import q4k_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+REL_L2_TOL = 1e-3     # stated tolerance of the path
+MAX_ABS_TOL = 2e-2
+
+VARIANTS = [q4k.GEMV_FP32, q4k.GEMV_STREAM, q4k.GEMV_AUTO]
+VARIANT_IDS = ["fp32", "stream", "auto"]
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+def dev(t, a):
+    return t.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def run_matmul(ctx, x, raw, bias, N, K, variant=q4k.GEMV_AUTO):
+    import torch
+
+    ctx.set_option(q4k.OPT_GEMV_VARIANT, variant)
+    try:
+        w = ctx.upload(pack_q4k(raw, N, K))
+        y = ctx.matmul(dev(torch, x.reshape(-1, K)), w, dev(torch, bias) if bias is not None else None)
+        torch.cuda.synchronize()
+        return y.cpu().numpy()
+    finally:
+        ctx.set_option(q4k.OPT_GEMV_VARIANT, q4k.GEMV_AUTO)
+
+
+def check(y, want):
+    assert y.shape == want.shape
+    assert np.isfinite(y).all()
+    assert rel_l2(y, want) <= REL_L2_TOL
+    assert float(np.abs(y - want).max()) <= MAX_ABS_TOL
+
+
+# ---------------------------------------------------------------- dequant
+
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_dequant_bit_exact_on_golden(ctx, golden, case):
+    import torch
+
+    M, N, K = (int(v) for v in golden[f"{case}.shape"])
+    w = ctx.upload(pack_q4k(golden[f"{case}.raw"], N, K))
+    out = ctx.dequant(w)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(out.cpu().numpy()), bits(golden[f"{case}.deq"]))
+
+
+@pytest.mark.parametrize("N,K,seed", [(1, 256, 1), (3, 768, 2), (257, 1024, 3), (4096, 4096, 0)])
+def test_dequant_bit_exact_on_synthetic(ctx, N, K, seed):
+    import torch
+
+    raw = synth.make_q4k_weights(N, K, seed)
+    out = ctx.dequant(ctx.upload(pack_q4k(raw, N, K)))
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(out.cpu().numpy()), bits(orc.dequant(raw, N, K)))
+
+
+def test_dequant_random_bytes_every_field_value(ctx):
+    """Arbitrary bytes: every scale/min/code value and many half patterns (finite ones compared)."""
+    import torch
+
+    N, K = 512, 512
+    raw = np.random.default_rng(11).integers(0, 256, (N, 2 * 144), dtype=np.uint8)
+    out = ctx.dequant(ctx.upload(pack_q4k(raw, N, K))).cpu().numpy()
+    torch.cuda.synchronize()
+    want = orc.dequant(raw, N, K)
+    ok = np.isfinite(want)
+    assert np.array_equal(bits(out[ok]), bits(want[ok]))
+    assert np.array_equal(np.isnan(out), np.isnan(want))
+
+
+def test_dequant_padded_row_stride(ctx):
+    import torch
+
+    N, K = 5, 512
+    raw = synth.make_q4k_weights(N, K, 4)
+    stride_words = 2 * 36 + 8
+    padded = np.full((N, stride_words * 4), 0xEE, np.uint8)
+    padded[:, : 2 * 144] = raw
+    w = q4k.Q4KWeight(dev(torch, padded.reshape(-1)), N, K, stride_words)
+    out = ctx.dequant(w).cpu().numpy()
+    assert np.array_equal(bits(out), bits(orc.dequant(raw, N, K)))
+
+
+# ---------------------------------------------------------------- matmul
+
+@pytest.mark.parametrize("variant", VARIANTS, ids=VARIANT_IDS)
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_matmul_golden(ctx, golden, case, variant):
+    M, N, K = (int(v) for v in golden[f"{case}.shape"])
+    y = run_matmul(ctx, golden[f"{case}.x"], golden[f"{case}.raw"], golden[f"{case}.bias"], N, K, variant)
+    want = golden[f"{case}.y"]
+    check(y, want)
+    if case.startswith("kt_"):
+        assert_close_ref(y, want, 2e-4, 2e-4)   # the reference's own bar on its fixtures
+
+
+@pytest.mark.parametrize("variant", VARIANTS, ids=VARIANT_IDS)
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 8, 9, 16, 17, 33])
+@pytest.mark.parametrize("N,K", [(1, 256), (7, 512), (8, 256), (9, 768), (17, 1024), (130, 2048)])
+def test_matmul_small_shapes(ctx, M, N, K, variant):
+    raw = synth.make_q4k_weights(N, K, 100 + N)
+    x = synth.make_activations(M, K, 200 + M)
+    bias = (np.arange(N) * 0.01).astype(np.float32)
+    y = run_matmul(ctx, x, raw, bias, N, K, variant)
+    check(y, orc.matmul(x, raw, bias, N, K))
+
+
+@pytest.mark.parametrize("variant", VARIANTS, ids=VARIANT_IDS)
+@pytest.mark.parametrize("M", [1, 8])
+@pytest.mark.parametrize("N,K", [(4096, 4096), (1024, 4096), (4096, 14336), (3000, 8192)])
+def test_matmul_projection_shapes(ctx, M, N, K, variant):
+    raw = synth.make_q4k_weights(N, K, 0)
+    x = synth.make_activations(M, K, 1)
+    y = run_matmul(ctx, x, raw, None, N, K, variant)
+    check(y, orc.matmul(x, raw, None, N, K, threads=8))
+
+
+@pytest.mark.parametrize("variant", VARIANTS, ids=VARIANT_IDS)
+def test_matmul_y_offset_and_canaries(ctx, variant):
+    """yOffset as q4k_matmul_128 uses it; nothing outside [yOffset, yOffset+M*N) may be written."""
+    import torch
+
+    N, K, M, yo = 20, 512, 1, 12
+    raw = synth.make_q4k_weights(N, K, 1)
+    x = synth.make_activations(M, K, 2)
+    ctx.set_option(q4k.OPT_GEMV_VARIANT, variant)
+    w = ctx.upload(pack_q4k(raw, N, K))
+    out = torch.full((64,), -777.0, dtype=torch.float32, device="cuda")
+    ctx.matmul(dev(torch, x), w, None, out=out, y_offset=yo)
+    ctx.set_option(q4k.OPT_GEMV_VARIANT, q4k.GEMV_AUTO)
+    got = out.cpu().numpy()
+    check(got[yo:yo + N].reshape(1, N), orc.matmul(x, raw, None, N, K))
+    assert (got[:yo] == -777.0).all() and (got[yo + N:] == -777.0).all()
+
+
+@pytest.mark.parametrize("variant", VARIANTS, ids=VARIANT_IDS)
+def test_matmul_extreme_activations(ctx, variant):
+    """Large, tiny and mixed-magnitude activations (the split-precision path must rescale)."""
+    N, K = 64, 1024
+    raw = synth.make_q4k_weights(N, K, 8)
+    base = synth.make_activations(4, K, 9)
+    x = base.copy()
+    x[0] *= 1e5
+    x[1] *= 1e-6
+    x[2, ::7] *= 3e4
+    x[3] = 0.0
+    y = run_matmul(ctx, x, raw, None, N, K, variant)
+    want = orc.matmul_f64(x, raw, None, N, K)
+    for m in range(4):
+        scale = max(float(np.abs(want[m]).max()), 1e-30)
+        assert float(np.abs(y[m] - want[m]).max()) / scale <= 2e-5 or float(np.abs(want[m]).max()) == 0.0
+    assert (y[3] == 0).all()
+
+
+@pytest.mark.parametrize("variant", VARIANTS, ids=VARIANT_IDS)
+def test_matmul_linearity_full_size(ctx, variant):
+    """Size-independent property at a full benchmark shape: f(a*x1 + x2) == a*f(x1) + f(x2)."""
+    import torch
+
+    N, K = 14336, 4096
+    raw = synth.make_q4k_weights(N, K, 3)
+    ctx.set_option(q4k.OPT_GEMV_VARIANT, variant)
+    w = ctx.upload(pack_q4k(raw, N, K))
+    x1 = dev(torch, synth.make_activations(1, K, 4))
+    x2 = dev(torch, synth.make_activations(1, K, 5))
+    y1, y2 = ctx.matmul(x1, w).double(), ctx.matmul(x2, w).double()
+    y12 = ctx.matmul(0.5 * x1 + x2, w).double()
+    ctx.set_option(q4k.OPT_GEMV_VARIANT, q4k.GEMV_AUTO)
+    err = (y12 - (0.5 * y1 + y2)).abs().max().item()
+    assert err <= 2e-3, err
+    # and the output equals X . dequant(W)^T computed from the library's own bit-exact dequant
+    deq = ctx.dequant(w).double()
+    ref = x1.double() @ deq.T
+    assert ((y1 - ref).abs().max().item()) <= MAX_ABS_TOL
+    assert ((y1 - ref).norm() / ref.norm()).item() <= REL_L2_TOL
+
+
+# ---------------------------------------------------------------- MoE indirect form
+
+@pytest.mark.parametrize("variant", VARIANTS, ids=VARIANT_IDS)
+def test_moe_indirect(ctx, variant):
+    import torch
+
+    E, N, K, T, topk = 16, 96, 512, 4, 3
+    raw = synth.make_q4k_weights(E * N, K, 21)
+    x = synth.make_activations(T, K, 22)
+    ids = synth.make_moe_routing(T, E, topk, 23)                  # [T, topk]
+    offsets = (ids.reshape(-1) * N).astype(np.int32)               # slot s = (token, k)
+    x_rows = np.repeat(np.arange(T), topk).astype(np.int32)
+    ctx.set_option(q4k.OPT_GEMV_VARIANT, variant)
+    w = ctx.upload(pack_q4k(raw, E * N, K))
+    y = ctx.matmul_moe(dev(torch, x), w, N, dev(torch, offsets), dev(torch, x_rows))
+    # per-slot activations (the "down" direction): row s of X belongs to slot s
+    xs = synth.make_activations(T * topk, K, 24)
+    y2 = ctx.matmul_moe(dev(torch, xs), w, N, dev(torch, offsets))
+    ctx.set_option(q4k.OPT_GEMV_VARIANT, q4k.GEMV_AUTO)
+    want = orc.matmul_moe(x[x_rows], raw, None, N, K, offsets.astype(np.uint32))
+    check(y.cpu().numpy(), want.reshape(T * topk, N))
+    want2 = orc.matmul_moe(xs, raw, None, N, K, offsets.astype(np.uint32))
+    check(y2.cpu().numpy(), want2.reshape(T * topk, N))
+
+
+# ---------------------------------------------------------------- host entry point
+
+def test_matmul_host_buffers(ctx):
+    N, K, M = 300, 1024, 2
+    raw = synth.make_q4k_weights(N, K, 31)
+    x = synth.make_activations(M, K, 32)
+    w = ctx.upload(pack_q4k(raw, N, K))
+    y = np.zeros((M, N), np.float32)
+    ctx.matmul_host(x, w, y)
+    check(y, orc.matmul(x, raw, None, N, K))
+    # a second, larger call re-sizes the staging buffers
+    M2 = 700
+    x2 = synth.make_activations(M2, K, 33)
+    y2 = np.zeros((M2, N), np.float32)
+    ctx.matmul_host(x2, w, y2)
+    check(y2, orc.matmul(x2, raw, None, N, K, threads=8))
+
+
+# ---------------------------------------------------------------- error behaviour
+
+def test_errors_are_statuses_not_faults(ctx):
+    import torch
+
+    N, K = 8, 512
+    w = ctx.upload(pack_q4k(synth.make_q4k_weights(N, K, 1), N, K))
+    x = torch.zeros(1, K, device="cuda")
+    with pytest.raises(q4k.Q4KError) as e:     # K not a multiple of 256
+        ctx.matmul(torch.zeros(1, 300, device="cuda"), q4k.Q4KWeight(w.buf, N, 300, 72))
+    assert e.value.status == 2 and "256" in str(e.value)
+    with pytest.raises(q4k.Q4KError) as e:     # stride shorter than a row
+        ctx.matmul(x, q4k.Q4KWeight(w.buf, N, K, 36))
+    assert e.value.status == 1
+    with pytest.raises(q4k.Q4KError) as e:     # stride not a multiple of 16 bytes
+        ctx.matmul(x, q4k.Q4KWeight(w.buf, N, K, 73))
+    assert e.value.status == 3
+    with pytest.raises(q4k.Q4KError) as e:     # misaligned activations
+        ctx.matmul(torch.zeros(K + 1, device="cuda")[1:].reshape(1, K), w)
+    assert e.value.status == 3
+    with pytest.raises(q4k.Q4KError) as e:     # misaligned weights
+        ctx.matmul(x, q4k.Q4KWeight(torch.zeros(w.buf.numel() + 4, dtype=torch.uint8, device="cuda")[4:], N, K, 72))
+    assert e.value.status == 3
+    with pytest.raises(q4k.Q4KError):
+        ctx.set_option(q4k.OPT_GEMV_VARIANT, 17)
+    # empty problems are no-ops
+    assert ctx.matmul(torch.zeros(0, K, device="cuda"), w).shape == (0, N)
+    # the context is still healthy
+    y = ctx.matmul(x, w)
+    torch.cuda.synchronize()
+    assert (y == 0).all()
+
+
+def test_launch_counter_counts_kernels(ctx):
+    import torch
+
+    N, K = 64, 512
+    w = ctx.upload(pack_q4k(synth.make_q4k_weights(N, K, 1), N, K))
+    ctx.launch_count(reset=True)
+    ctx.matmul(torch.zeros(1, K, device="cuda"), w)
+    ctx.dequant(w)
+    assert ctx.launch_count() >= 2
