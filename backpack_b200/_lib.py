@@ -25,6 +25,7 @@ SIGNATURES = {
     "bpq4k_set_option": (C.c_int, [vp, C.c_int, C.c_int]),
     "bpq4k_get_option": (C.c_int, [vp, C.c_int, C.POINTER(C.c_int)]),
     "bpq4k_launch_count": (u64, [vp, C.c_int]),
+    "bpq4k_device_status": (C.c_int, [vp, vp, C.POINTER(C.c_int)]),
     "bpq4k_n_blocks": (u32, [u32]),
     "bpq4k_row_stride_words": (u32, [u32]),
     "bpq4k_pack_q4k_host": (C.c_int, [vp, u32, u32, vp]),

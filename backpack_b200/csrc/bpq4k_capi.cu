@@ -25,9 +25,12 @@ struct bpq4k_context {
     size_t stage_x_bytes = 0;
     float* stage_y = nullptr;
     size_t stage_y_bytes = 0;
-    // scratch for kernels that need it (split activations, partial sums)
+    // scratch for kernels that need it (split activations)
     void* scratch = nullptr;
     size_t scratch_bytes = 0;
+    // device status word written by kernels whose bounded waits run out
+    int* dev_status = nullptr;
+    StreamTuning tune;
 };
 
 namespace {
@@ -90,14 +93,37 @@ int ensure_bytes(bpq4k_context* h, void** p, size_t* have, size_t need) {
     return BPQ4K_OK;
 }
 
+constexpr uint32_t kStreamMaxM = 8;  // rows of X one streaming launch covers
+
+// Kernel selection.  FP32: always the float kernel.  STREAM / AUTO: the streaming
+// kernel, X walked in slabs of 8 rows (each slab re-reads the weights, as the
+// reference's batched8 shader does per 8 rows).
 int run_matmul(bpq4k_context* h, const MatmulArgs& a, cudaStream_t st) {
     int launches = 0;
     cudaError_t e = cudaSuccess;
-    int variant = h->gemv_variant;
-    (void)variant;
-    e = launch_gemv_fp32(a, st, &launches);
+    if (h->gemv_variant == BPQ4K_GEMV_FP32) {
+        e = launch_gemv_fp32(a, st, &launches);
+    } else {
+        const uint32_t Mtot = a.n_slots ? 1 : a.M;
+        const size_t need = a.n_slots ? 0 : gemv_stream_scratch_bytes(Mtot < kStreamMaxM ? Mtot : kStreamMaxM, a.K);
+        if (need > h->scratch_bytes) {
+            if (int s = ensure_bytes(h, &h->scratch, &h->scratch_bytes, need)) return s;
+        }
+        MatmulArgs c = a;
+        for (uint32_t m0 = 0; m0 < Mtot && e == cudaSuccess; m0 += kStreamMaxM) {
+            if (!a.n_slots) {
+                c.M = Mtot - m0 < kStreamMaxM ? Mtot - m0 : kStreamMaxM;
+                c.X = a.X + (uint64_t)m0 * a.K;
+                c.Y = a.Y + (uint64_t)m0 * a.N;
+            }
+            e = launch_gemv_stream(c, h->tune, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count, st, &launches);
+        }
+    }
     h->launches += (uint64_t)launches;
-    if (e != cudaSuccess) return cuda_fail(h, e, "matmul launch");
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return cuda_fail(h, e, "matmul launch");
+    }
     return BPQ4K_OK;
 }
 
@@ -143,6 +169,23 @@ int bpq4k_create(int device, bpq4k_handle_t* out) {
         delete h;
         return BPQ4K_ERR_NO_DEVICE;
     }
+    {
+        DeviceGuard g(device);
+        // status word and a first scratch slab are allocated here so that later calls
+        // with common shapes allocate nothing (and can be captured into CUDA graphs)
+        cudaError_t e2 = cudaMalloc(reinterpret_cast<void**>(&h->dev_status), 256);
+        if (e2 == cudaSuccess) e2 = cudaMemset(h->dev_status, 0, 256);
+        if (e2 == cudaSuccess) {
+            e2 = cudaMalloc(&h->scratch, 4u << 20);
+            if (e2 == cudaSuccess) h->scratch_bytes = 4u << 20;
+        }
+        if (e2 != cudaSuccess) {
+            cudaGetLastError();
+            if (h->dev_status) cudaFree(h->dev_status);
+            delete h;
+            return BPQ4K_ERR_ALLOC;
+        }
+    }
     *out = h;
     return BPQ4K_OK;
 }
@@ -154,6 +197,7 @@ int bpq4k_destroy(bpq4k_handle_t h) {
         if (h->stage_x) cudaFree(h->stage_x);
         if (h->stage_y) cudaFree(h->stage_y);
         if (h->scratch) cudaFree(h->scratch);
+        if (h->dev_status) cudaFree(h->dev_status);
     }
     delete h;
     return BPQ4K_OK;
@@ -178,6 +222,29 @@ int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
             if (value < 1) return fail(h, BPQ4K_ERR_INVALID_ARG, "prefill_min_m must be >= 1");
             h->prefill_min_m = value;
             return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_WARPS:
+            if (value < 0 || value > 16) return fail(h, BPQ4K_ERR_INVALID_ARG, "stream warps must be 0..16");
+            h->tune.warps = (uint32_t)value;
+            return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_KSPLIT:
+            if (value < 0 || value > 16) return fail(h, BPQ4K_ERR_INVALID_ARG, "stream k-split must be 0..16");
+            h->tune.wk = (uint32_t)value;
+            return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_STAGE_BLOCKS:
+            if (value < 0 || value > 8) return fail(h, BPQ4K_ERR_INVALID_ARG, "stage blocks must be 0..8");
+            h->tune.cb = (uint32_t)value;
+            return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_STAGES:
+            if (value < 0 || value > 8) return fail(h, BPQ4K_ERR_INVALID_ARG, "stages must be 0..8");
+            h->tune.stages = (uint32_t)value;
+            return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_CTAS_PER_SM:
+            if (value < 0 || value > 32) return fail(h, BPQ4K_ERR_INVALID_ARG, "ctas per sm must be 0..32");
+            h->tune.ctas_per_sm = (uint32_t)value;
+            return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_FORCE_SCRATCH:
+            h->tune.force_scratch = value ? 1u : 0u;
+            return BPQ4K_OK;
         default: return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown option %d", option);
     }
 }
@@ -188,6 +255,12 @@ int bpq4k_get_option(bpq4k_handle_t h, int option, int* value) {
         case BPQ4K_OPT_GEMV_VARIANT: *value = h->gemv_variant; return BPQ4K_OK;
         case BPQ4K_OPT_PREFILL_MODE: *value = h->prefill_mode; return BPQ4K_OK;
         case BPQ4K_OPT_PREFILL_MIN_M: *value = h->prefill_min_m; return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_WARPS: *value = (int)h->tune.warps; return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_KSPLIT: *value = (int)h->tune.wk; return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_STAGE_BLOCKS: *value = (int)h->tune.cb; return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_STAGES: *value = (int)h->tune.stages; return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_CTAS_PER_SM: *value = (int)h->tune.ctas_per_sm; return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_FORCE_SCRATCH: *value = (int)h->tune.force_scratch; return BPQ4K_OK;
         default: return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown option %d", option);
     }
 }
@@ -197,6 +270,22 @@ uint64_t bpq4k_launch_count(bpq4k_handle_t h, int reset) {
     const uint64_t v = h->launches;
     if (reset) h->launches = 0;
     return v;
+}
+
+int bpq4k_device_status(bpq4k_handle_t h, void* stream, int* status_out) {
+    if (!h || !status_out) return BPQ4K_ERR_INVALID_ARG;
+    DeviceGuard g(h->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int v = 0;
+    cudaError_t e = cudaMemcpyAsync(&v, h->dev_status, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(h, e, "status read-back");
+    *status_out = v;
+    if (v != 0) {
+        cudaMemsetAsync(h->dev_status, 0, sizeof(int), st);
+        return fail(h, v, "a kernel reported status %d (%s)", v, bpq4k_status_string(v));
+    }
+    return BPQ4K_OK;
 }
 
 uint32_t bpq4k_n_blocks(uint32_t K) { return (K + BPQ4K_QK_K - 1u) / BPQ4K_QK_K; }

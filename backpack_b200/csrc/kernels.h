@@ -25,6 +25,27 @@ struct MatmulArgs {
 cudaError_t launch_dequant_f32(const uint8_t* W, uint32_t N, uint32_t K, uint64_t w_row_bytes, float* out,
                                cudaStream_t stream);
 
+// Value a kernel stores in the handle's device status word when a bounded wait runs out.
+constexpr int kDeviceTimeout = 6;
+
+// Tuning knobs of the streaming kernel; 0 = choose automatically.
+struct StreamTuning {
+    uint32_t warps = 0;        // warps per CTA (<= 16)
+    uint32_t wk = 0;           // warps that split K of one 16-row tile
+    uint32_t cb = 0;           // super-blocks per ring stage
+    uint32_t stages = 0;       // ring depth per warp
+    uint32_t ctas_per_sm = 0;  // cap on resident CTAs per SM
+    uint32_t force_scratch = 0;  // 1: always split activations into global scratch first
+};
+
+// Bytes of scratch launch_gemv_stream needs when the activations do not fit in shared memory.
+size_t gemv_stream_scratch_bytes(uint32_t M, uint32_t K);
+
+// Streaming tensor-core matmul for M <= 8 (or the indirect form).  `scratch` may be null
+// when the activations fit in shared memory.
+cudaError_t launch_gemv_stream(const MatmulArgs& a, const StreamTuning& tune, void* scratch, size_t scratch_bytes,
+                               int* status_dev, int sm_count, cudaStream_t stream, int* launches);
+
 // One warp per output row, float FMAs in the reference shader's arithmetic.
 cudaError_t launch_gemv_fp32(const MatmulArgs& a, cudaStream_t stream, int* launches);
 

@@ -1,0 +1,618 @@
+// Bandwidth-bound Q4_K matmul for small M (decode): a persistent kernel that
+// streams raw 144-byte super-blocks from HBM into per-warp shared-memory rings
+// with bulk asynchronous copies (cp.async.bulk + mbarrier), decodes the 4-bit
+// codes in registers and takes the dot products on the tensor cores.
+//
+// Replaces the reference's q4k_matmul / q4k_matmul_128 / q4k_matmul_batched4/8
+// shaders (runtime/kernels/quant_kq/q4k_matmul.wgsl:20-95 and siblings) and the
+// per-slot `*_matmul_moe` dispatch form (iq4xs_matmul_moe.wgsl:55-99).
+//
+// Arithmetic.  For sub-block sb of row n:  w = dsc*q - dmn  with dsc = d*sc,
+// dmn = dmin*mn, so
+//     sum_k x_k w_k = dsc * sum_k x_k q_k  -  dmn * sum_k x_k .
+// The 4-bit codes are turned into halves 64+q with one logic op each (the nibble
+// is dropped into the mantissa of 0x5400 = 64.0, whose ulp is 1/16 ... shifted so
+// that the nibble counts units), the activation row is split into two halves
+// x = xh + xl after scaling by a power of two so that max|x| ~ 2^10, and
+//     T = sum_k (64+q_k)(xh_k + xl_k)
+// is accumulated in float by mma.sync.m16n8k16 (all products are exact).  With
+// S = sum_k (xh_k + xl_k) per sub-block computed once per activation row,
+//     contribution = dsc*T - (64*dsc + dmn)*S .
+// Error relative to the float reference is ~1e-6 (x keeps 22 bits, sums are float).
+//
+// Work decomposition.  A tile is 16 output rows.  The warps of a CTA are arranged
+// as WT tile slots x WK slices of K; a warp streams its slice of its tile through
+// a private ring of `stages` buffers of `cb` blocks x 16 rows (one bulk copy per
+// row), so the only CTA-wide synchronisation is the staging of the activations.
+// The K slices of a tile are combined through shared memory in a fixed order, so
+// results are deterministic.  CTAs are persistent and walk tiles with stride
+// gridDim.x*WT.
+//
+// mma operand mapping (one mma = 16 rows x 16 weights of one sub-block).  ldmatrix
+// hands thread (r = lane/4, t = lane%4) word t of a 16-byte run of code bytes of
+// rows r and r+8.  A word holds bytes 4t..4t+3, i.e. weights 4t..4t+3 of the even
+// sub-block in its low nibbles and of the odd sub-block in its high nibbles:
+//   a0a1 = (w[4t], w[4t+2])  a4a5 = (w[4t+1], w[4t+3])   (row r;  a2a3/a6a7: row r+8)
+// and the activations are stored in shared memory already permuted the same way.
+// The 8 mma columns are 4 pairs (hi, lo); pair j carries x only in the mmas of the
+// sub-block parity j%2 and zeros in the others, so after the four mmas of a 64-weight
+// group thread t holds the sums of sub-block parity t%2 -- the per-sub-block scaling
+// work is spread over the four threads of a quad without any shuffles.  With one
+// activation row (M1) pairs 2,3 repeat pairs 0,1 and threads t>=2 take row r+8.
+#include <cuda_fp16.h>
+
+#include "kernels.h"
+#include "q4k_common.cuh"
+
+namespace bpq4k {
+
+namespace {
+
+constexpr uint32_t kMaxWarps = 16;
+constexpr uint32_t kMaxStages = 8;
+constexpr uint32_t kBarBytes = kMaxWarps * kMaxStages * 8;  // 1 KiB of mbarriers
+constexpr uint32_t kWaitPolls = 1u << 22;                    // bounded mbarrier wait
+
+struct StreamArgs {
+    MatmulArgs m;
+    uint32_t wk, wt, cb, stages, pitch, stage_bytes, ntiles, tokens;
+    uint32_t off_zero, off_red, off_inv, off_S, off_x, off_part, off_ring;
+    int* status;
+    // activations prepared by split_activations_kernel (XG mode)
+    const uint8_t* xfrag_g;
+    const float* S_g;
+    const float* inv_g;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Plain (non-multicast) bulk copy global -> this CTA's shared memory.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// (64+q) halves of the four nibble pairs of a code word.
+//   even0 = nibbles 0,4 (weights 4t, 4t+2 of the even sub-block), even1 = nibbles 2,6 (4t+1, 4t+3)
+//   odd0  = nibbles 1,5 (same weights of the odd sub-block),      odd1  = nibbles 3,7
+__device__ __forceinline__ void decode_word(uint32_t w, uint32_t& even0, uint32_t& even1, uint32_t& odd0,
+                                            uint32_t& odd1) {
+    constexpr uint32_t kMask = 0x00F000F0u, kBase = 0x54005400u;  // 0x5400 = 64.0h, nibble lands on units
+    even0 = ((w << 4) & kMask) | kBase;
+    odd0 = (w & kMask) | kBase;
+    even1 = ((w >> 4) & kMask) | kBase;
+    odd1 = ((w >> 8) & kMask) | kBase;
+}
+
+// Power-of-two scale that brings `amax` to [2^10, 2^11), and its inverse.
+__device__ __forceinline__ void pow2_scale(float amax, float& scale, float& inv) {
+    const uint32_t e = (__float_as_uint(amax) >> 23) & 0xFFu;
+    if (e < 11u || e == 255u) {  // zero, tiny, inf or nan: leave unscaled
+        scale = 1.f;
+        inv = 1.f;
+    } else {
+        scale = __uint_as_float((264u - e) << 23);  // 2^(137-e)
+        inv = __uint_as_float((e - 10u) << 23);     // 2^(e-137)
+    }
+}
+
+// Split 32 consecutive activations (one sub-block) of one row into halves and
+// store them in the mma-permuted layout; returns sum(xh+xl) over the warp.
+//   layout: [token][group G = k/64][parity][part hi/lo][t][8 halves], 128 B per (token,G,parity)
+//   thread t's 8 halves = x[4t], x[4t+2], x[4t+1], x[4t+3], x[16+4t], x[16+4t+2], x[16+4t+1], x[16+4t+3]
+__device__ __forceinline__ float split_store(float v, uint8_t* frag_base, uint32_t lane) {
+    const __half xh = __float2half_rn(v);
+    const float fh = __half2float(xh);
+    const __half xl = __float2half_rn(v - fh);
+    const uint32_t c = lane >> 4, t = (lane >> 2) & 3u, j = lane & 3u;
+    const uint32_t h = c * 4u + (j & 1u) * 2u + (j >> 1);
+    __half* hi = reinterpret_cast<__half*>(frag_base + t * 16u) + h;
+    hi[0] = xh;
+    hi[32] = xl;  // +64 bytes: the lo part
+    float s = fh + __half2float(xl);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+    return s;
+}
+
+template <int NT, bool M1, bool XG>
+__global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int TOK = M1 ? 1 : NT * 2;  // token slots
+    constexpr int RPT = M1 ? 1 : 2;       // rows post-processed per thread
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t nwarps = blockDim.x >> 5;
+    const uint32_t wk = warp % a.wk, wt = warp / a.wk;
+    const uint32_t K = a.m.K, N = a.m.N, nb = K / kQK;
+    const uint32_t b0 = (uint32_t)((uint64_t)nb * wk / a.wk), b1 = (uint32_t)((uint64_t)nb * (wk + 1) / a.wk);
+    const uint32_t nchunks = (b1 - b0 + a.cb - 1) / a.cb;
+
+    // problem selection (indirect form: blockIdx.y is the slot)
+    const float* X = a.m.X;
+    float* Y = a.m.Y;
+    uint64_t wrow0 = 0;
+    uint32_t M = a.m.M;
+    if (a.m.n_slots) {
+        const uint32_t s = blockIdx.y;
+        wrow0 = a.m.offsets[s];
+        X += (uint64_t)(a.m.x_rows ? a.m.x_rows[s] : s) * K;
+        Y += (uint64_t)s * N;
+        M = 1;
+    }
+    const uint8_t* Wp = a.m.W + wrow0 * a.m.w_row_bytes;
+
+    const uint32_t tstride = gridDim.x * a.wt;
+    const uint32_t tile0 = blockIdx.x * a.wt + wt;
+    const uint32_t my_tiles = tile0 < a.ntiles ? (a.ntiles - tile0 + tstride - 1) / tstride : 0;
+    const uint32_t total_units = my_tiles * nchunks;
+
+    const uint32_t bar0 = smem_u32(smem) + warp * kMaxStages * 8u;
+    const uint32_t ring = smem_u32(smem + a.off_ring) + warp * a.stages * a.stage_bytes;
+
+    if (lane == 0) {
+        for (uint32_t s = 0; s < a.stages; s++) mbar_init(bar0 + s * 8u, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    fence_proxy_async();
+    __syncwarp();
+
+    // ---- producer side: one bulk copy per row of the unit's chunk -------------
+    uint32_t iss_tile = tile0, iss_c = 0, iss_u = 0;
+    auto issue_next = [&]() {
+        const uint32_t bs = b0 + iss_c * a.cb;
+        const uint32_t nblk = min(a.cb, b1 - bs);
+        const uint32_t st = iss_u % a.stages;
+        const uint32_t row = iss_tile * 16u + lane;
+        const uint32_t rows_valid = min(16u, N - iss_tile * 16u);
+        const uint32_t bytes = nblk * kBlockBytes;
+        const uint32_t bar = bar0 + st * 8u;
+        if (lane == 0) mbar_expect_tx(bar, rows_valid * bytes);
+        __syncwarp();
+        if (lane < rows_valid)
+            bulk_g2s(ring + st * a.stage_bytes + lane * a.pitch, Wp + (uint64_t)row * a.m.w_row_bytes + (uint64_t)bs * kBlockBytes,
+                     bytes, bar);
+        iss_u++;
+        if (++iss_c == nchunks) {
+            iss_c = 0;
+            iss_tile += tstride;
+        }
+    };
+    {
+        const uint32_t pre = min(a.stages, total_units);
+        for (uint32_t i = 0; i < pre; i++) issue_next();
+    }
+
+    // ---- activations: split into scaled half pairs, once per CTA ---------------
+    const uint32_t NG = K / 64u;
+    float* invs = reinterpret_cast<float*>(smem + a.off_inv);
+    if constexpr (!XG) {
+        float* red = reinterpret_cast<float*>(smem + a.off_red);
+        float* Ss = reinterpret_cast<float*>(smem + a.off_S);
+        uint8_t* xf = smem + a.off_x;
+        if (tid < 4) reinterpret_cast<uint32_t*>(smem + a.off_zero)[tid] = 0u;
+        for (int tok = 0; tok < TOK; tok++) {
+            float amax = 0.f;
+            if ((uint32_t)tok < M) {
+                const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok * K);
+                for (uint32_t i = tid; i < K / 4u; i += blockDim.x) {
+                    const float4 v = __ldg(xp + i);
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+            if (lane == 0) red[tok * kMaxWarps + warp] = amax;
+        }
+        __syncthreads();
+        const uint32_t nsub = K / 32u;
+        for (uint32_t tok = 0; tok < (uint32_t)TOK; tok++) {
+            float amax = 0.f;
+            for (uint32_t w2 = 0; w2 < nwarps; w2++) amax = fmaxf(amax, red[tok * kMaxWarps + w2]);
+            float scale, inv;
+            pow2_scale(amax, scale, inv);
+            if (tid == 0) invs[tok] = inv;
+            for (uint32_t sbg = warp; sbg < nsub; sbg += nwarps) {
+                const float v = tok < M ? __ldg(X + (uint64_t)tok * K + sbg * 32u + lane) * scale : 0.f;
+                const uint32_t G = sbg >> 1, par = sbg & 1u;
+                const float s = split_store(v, xf + ((uint64_t)(tok * NG + G) * 2u + par) * 128u, lane);
+                if (lane == 0) Ss[((tok * nb + (sbg >> 3)) * 2u + par) * 4u + ((sbg >> 1) & 3u)] = s;
+            }
+        }
+        __syncthreads();
+    }
+
+    // ---- per-lane constants ----------------------------------------------------
+    // ldmatrix row addresses: lanes 0-7 rows 0-7 bytes [0,16), 8-15 rows 8-15 bytes [0,16),
+    // 16-23 rows 0-7 bytes [16,32), 24-31 rows 8-15 bytes [16,32)
+    const uint32_t lm_off = ((lane & 7u) + ((lane >> 3) & 1u) * 8u) * a.pitch + 16u + (lane >> 4) * 16u;
+    // B operand: column n = lane/4 -> pair n/2 (parity n/2%2), part n%2; t = lane%4
+    const uint32_t bn = lane >> 2, bt = lane & 3u;
+    const uint32_t b_par = (bn >> 1) & 1u;
+    const uint32_t b_tok = M1 ? 0u : (bn >> 2);  // token within an n-tile (0 or 1)
+    // C / post-processing role: column pair t
+    const uint32_t c_par = lane & 1u;
+    const uint32_t c_tok = M1 ? 0u : (bt >> 1);
+    const uint32_t row_a = M1 ? (lane >> 2) + ((bt >> 1) << 3) : (lane >> 2);
+    const uint32_t sel0 = 0x7440u + c_par, sel1 = 0x7442u + c_par;
+
+    // base "addresses" of this lane's B data and of the zero block
+    uint64_t xdata, xzero;      // XG: global addresses; else shared addresses (low 32 bits)
+    const float* Sbase;
+    if constexpr (XG) {
+        xdata = reinterpret_cast<uint64_t>(a.xfrag_g) + 128u;  // first 128 bytes of the scratch: zeros
+        xzero = reinterpret_cast<uint64_t>(a.xfrag_g);
+        Sbase = a.S_g;
+    } else {
+        xdata = smem_u32(smem + a.off_x);
+        xzero = smem_u32(smem + a.off_zero);
+        Sbase = reinterpret_cast<const float*>(smem + a.off_S);
+    }
+    const uint32_t lane_boff = b_par * 128u + (bn & 1u) * 64u + bt * 16u;
+    auto load_b = [&](uint64_t addr) -> uint4 {
+        if constexpr (XG) return __ldg(reinterpret_cast<const uint4*>(addr));
+        else return lds128((uint32_t)addr);
+    };
+
+    float* part = reinterpret_cast<float*>(smem + a.off_part);
+    uint32_t st = 0, ph = 0, u = 0, failed = 0;
+
+    for (uint32_t ti = 0; ti < my_tiles; ti++) {
+        const uint32_t tile = tile0 + ti * tstride;
+        float acc[NT][RPT];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int r = 0; r < RPT; r++) acc[nt][r] = 0.f;
+
+        for (uint32_t c = 0; c < nchunks; c++) {
+            const uint32_t bs = b0 + c * a.cb;
+            const uint32_t nblk = min(a.cb, b1 - bs);
+            const uint32_t bar = bar0 + st * 8u;
+            if (!failed) {
+                uint32_t polls = 0;
+                while (!mbar_try_wait(bar, ph)) {
+                    if (++polls > kWaitPolls) {  // give up: flag it, keep the barriers matched
+                        failed = 1;
+                        if (lane == 0 && a.status) atomicExch(a.status, kDeviceTimeout);
+                        break;
+                    }
+                }
+            }
+            const uint32_t sbase = ring + st * a.stage_bytes;
+            for (uint32_t bl = 0; bl < nblk; bl++) {
+                const uint32_t blk = bs + bl;
+                const uint32_t boff = sbase + bl * kBlockBytes;
+                // scales of this thread's rows, its parity's four sub-blocks
+                float dsc[RPT][4], esc[RPT][4];
+#pragma unroll
+                for (int r = 0; r < RPT; r++) {
+                    const uint4 hv = lds128(boff + (row_a + r * 8u) * a.pitch);
+                    const BlockHeader h{hv.x, hv.y, hv.z, hv.w};
+                    const float d = half_bits_to_float(h.w0), dmin = half_bits_to_float(h.w0 >> 16);
+                    uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
+                    unpack_scales_packed(h, sc_lo, sc_hi, mn_lo, mn_hi);
+                    // d*(2^23+sc) - d*2^23 in one fma: the product is exact inside the fma
+                    const float nd = -d * 8388608.f, ndm = -dmin * 8388608.f;
+                    const uint32_t scw[4] = {__byte_perm(sc_lo, 0x4B000000u, sel0), __byte_perm(sc_lo, 0x4B000000u, sel1),
+                                             __byte_perm(sc_hi, 0x4B000000u, sel0), __byte_perm(sc_hi, 0x4B000000u, sel1)};
+                    const uint32_t mnw[4] = {__byte_perm(mn_lo, 0x4B000000u, sel0), __byte_perm(mn_lo, 0x4B000000u, sel1),
+                                             __byte_perm(mn_hi, 0x4B000000u, sel0), __byte_perm(mn_hi, 0x4B000000u, sel1)};
+#pragma unroll
+                    for (int g = 0; g < 4; g++) {
+                        dsc[r][g] = fmaf(d, __uint_as_float(scw[g]), nd);
+                        const float dmn = fmaf(dmin, __uint_as_float(mnw[g]), ndm);
+                        esc[r][g] = fmaf(64.f, dsc[r][g], dmn);
+                    }
+                }
+                float4 Sv[NT];
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const uint32_t tok = nt * 2u + c_tok;
+                    Sv[nt] = *reinterpret_cast<const float4*>(Sbase + ((uint64_t)(tok * nb + blk) * 2u + c_par) * 4u);
+                }
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    uint32_t r0, r1, r2, r3;
+                    ldmatrix_x4(boff + lm_off + g * 32u, r0, r1, r2, r3);
+                    uint32_t e0[4], e1[4], o0[4], o1[4];
+                    decode_word(r0, e0[0], e1[0], o0[0], o1[0]);
+                    decode_word(r1, e0[1], e1[1], o0[1], o1[1]);
+                    decode_word(r2, e0[2], e1[2], o0[2], o1[2]);
+                    decode_word(r3, e0[3], e1[3], o0[3], o1[3]);
+                    const uint32_t G = blk * 4u + g;
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        const uint32_t tok = nt * 2u + b_tok;
+                        const uint64_t mine = xdata + ((uint64_t)(tok * NG + G) * 2u) * 128u + lane_boff;
+                        const uint4 qa = load_b(b_par == 0 ? mine : xzero);
+                        const uint4 qb = load_b(b_par == 1 ? mine : xzero);
+                        float cfr[4] = {0.f, 0.f, 0.f, 0.f};
+                        mma16816(cfr, e0[0], e0[1], e1[0], e1[1], qa.x, qa.y);  // even sub-block, code bytes 0-15
+                        mma16816(cfr, e0[2], e0[3], e1[2], e1[3], qa.z, qa.w);  // even sub-block, code bytes 16-31
+                        mma16816(cfr, o0[0], o0[1], o1[0], o1[1], qb.x, qb.y);  // odd sub-block
+                        mma16816(cfr, o0[2], o0[3], o1[2], o1[3], qb.z, qb.w);
+                        const float Sg = g == 0 ? Sv[nt].x : g == 1 ? Sv[nt].y : g == 2 ? Sv[nt].z : Sv[nt].w;
+                        if constexpr (M1) {
+                            const float v = (bt & 2u) ? (cfr[2] + cfr[3]) : (cfr[0] + cfr[1]);
+                            acc[nt][0] = fmaf(dsc[0][g], v, acc[nt][0]);
+                            acc[nt][0] = fmaf(-esc[0][g], Sg, acc[nt][0]);
+                        } else {
+                            acc[nt][0] = fmaf(dsc[0][g], cfr[0] + cfr[1], acc[nt][0]);
+                            acc[nt][0] = fmaf(-esc[0][g], Sg, acc[nt][0]);
+                            acc[nt][1] = fmaf(dsc[1][g], cfr[2] + cfr[3], acc[nt][1]);
+                            acc[nt][1] = fmaf(-esc[1][g], Sg, acc[nt][1]);
+                        }
+                    }
+                }
+            }
+            // the stage is free: refill it with the unit `stages` ahead
+            __syncwarp();
+            fence_proxy_async();
+            if (u + a.stages < total_units) issue_next();
+            u++;
+            if (++st == a.stages) {
+                st = 0;
+                ph ^= 1u;
+            }
+        }
+
+        // ---- tile epilogue: parities -> K slices -> bias -> Y -------------------
+        float* pbuf = part + ((uint64_t)((ti & 1u) * nwarps + warp)) * (TOK * 16u);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+            for (int r = 0; r < RPT; r++) {
+                const float s = acc[nt][r] + __shfl_xor_sync(0xFFFFFFFFu, acc[nt][r], 1);
+                if (c_par == 0) pbuf[(nt * 2u + c_tok) * 16u + row_a + r * 8u] = s;
+            }
+        }
+        if (a.wk > 1) {
+            asm volatile("bar.sync %0, %1;" ::"r"(wt + 1u), "r"(a.wk * 32u) : "memory");
+        } else {
+            __syncwarp();
+        }
+        if (wk == 0) {
+            const float* gbuf = part + ((uint64_t)((ti & 1u) * nwarps + warp)) * (TOK * 16u);
+            for (uint32_t idx = lane; idx < (uint32_t)TOK * 16u; idx += 32u) {
+                const uint32_t tok = idx >> 4, row = tile * 16u + (idx & 15u);
+                if (tok < M && row < N) {
+                    float s = 0.f;
+                    for (uint32_t k2 = 0; k2 < a.wk; k2++) s += gbuf[(uint64_t)k2 * (TOK * 16u) + idx];
+                    const float inv = XG ? a.inv_g[tok] : invs[tok];
+                    Y[(uint64_t)tok * N + row] = fmaf(s, inv, a.m.bias ? a.m.bias[row] : 0.f);
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// XG mode: split the activations once per call into global scratch, in the same
+// permuted layout the kernel above keeps in shared memory.  One CTA per row.
+// Scratch layout: [128 B zeros][xfrag: tokens*K*4 B][S: tokens*(K/32) floats][inv: tokens floats]
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) split_activations_kernel(const float* __restrict__ X, uint32_t M, uint32_t K,
+                                                                 uint32_t tokens, uint8_t* __restrict__ scratch) {
+    __shared__ float red[32];
+    const uint32_t tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t nwarps = blockDim.x >> 5, nb = K / kQK, NG = K / 64u, nsub = K / 32u;
+    uint8_t* xf = scratch + 128;
+    float* S = reinterpret_cast<float*>(xf + (uint64_t)tokens * K * 4u);
+    float* inv_out = S + (uint64_t)tokens * nsub;
+    if (tok == 0 && tid < 32) reinterpret_cast<uint32_t*>(scratch)[tid] = 0u;
+    float amax = 0.f;
+    if (tok < M) {
+        const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok * K);
+        for (uint32_t i = tid; i < K / 4u; i += blockDim.x) {
+            const float4 v = __ldg(xp + i);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    if (lane == 0) red[warp] = amax;
+    __syncthreads();
+    amax = 0.f;
+    for (uint32_t w2 = 0; w2 < nwarps; w2++) amax = fmaxf(amax, red[w2]);
+    float scale, inv;
+    pow2_scale(amax, scale, inv);
+    for (uint32_t sbg = warp; sbg < nsub; sbg += nwarps) {
+        const float v = tok < M ? __ldg(X + (uint64_t)tok * K + sbg * 32u + lane) * scale : 0.f;
+        const uint32_t G = sbg >> 1, par = sbg & 1u;
+        const float s = split_store(v, xf + ((uint64_t)(tok * NG + G) * 2u + par) * 128u, lane);
+        if (lane == 0) S[((uint64_t)(tok * nb + (sbg >> 3)) * 2u + par) * 4u + ((sbg >> 1) & 3u)] = s;
+    }
+    if (tid == 0) inv_out[tok] = inv;
+}
+
+// Launch one instantiation.  The grid is persistent: at most as many CTAs as can be
+// resident at once (occupancy query, cached), never more than there are tile groups.
+template <int NT, bool M1, bool XG>
+cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, uint32_t threads, size_t smem,
+                       int sm_count, uint32_t ctas_per_sm_override, cudaStream_t stream) {
+    struct Cache { int dev = -1; size_t smem_cfg = 0; uint32_t threads = 0; size_t smem = 0; int occ = 0; };
+    static Cache cache;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cache.dev != dev) cache = Cache{};
+    cache.dev = dev;
+    if (smem > cache.smem_cfg) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT, M1, XG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return e;
+        cache.smem_cfg = smem;
+        cache.threads = 0;
+    }
+    if (cache.threads != threads || cache.smem != smem) {
+        int occ = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_stream_kernel<NT, M1, XG>, (int)threads, smem);
+        if (e != cudaSuccess) return e;
+        cache.threads = threads;
+        cache.smem = smem;
+        cache.occ = occ > 0 ? occ : 1;
+    }
+    uint32_t per_sm = (uint32_t)cache.occ;
+    if (ctas_per_sm_override && ctas_per_sm_override < per_sm) per_sm = ctas_per_sm_override;
+    const uint64_t cap = (uint64_t)sm_count * per_sm;
+    uint32_t gx = groups;
+    if ((uint64_t)gx * slots_y > cap) gx = (uint32_t)((cap + slots_y - 1) / slots_y);
+    if (gx == 0) gx = 1;
+    if (gx > groups) gx = groups;
+    gemv_stream_kernel<NT, M1, XG><<<dim3(gx, slots_y), threads, smem, stream>>>(sa);
+    return cudaGetLastError();
+}
+
+uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+size_t gemv_stream_scratch_bytes(uint32_t M, uint32_t K) {
+    const uint32_t tokens = M <= 1 ? 1 : (M + 1) / 2 * 2;
+    return 128 + (size_t)tokens * K * 4 + (size_t)tokens * (K / 32) * 4 + (size_t)tokens * 4 + 256;
+}
+
+cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, void* scratch, size_t scratch_bytes,
+                               int* status_dev, int sm_count, cudaStream_t stream, int* launches) {
+    if (m.N == 0) return cudaSuccess;
+    const bool indirect = m.n_slots != 0;
+    const uint32_t M = indirect ? 1 : m.M;
+    if (M == 0) return cudaSuccess;
+    if (M > 8) return cudaErrorInvalidValue;  // callers split larger M
+    const uint32_t nb = m.K / kQK;
+    const uint32_t ntiles = (m.N + 15) / 16;
+    const bool m1 = M == 1;
+    const int NT = m1 ? 1 : (int)((M + 1) / 2);
+    const uint32_t tokens = m1 ? 1 : NT * 2;
+
+    // ---- plan ------------------------------------------------------------------
+    constexpr uint32_t kSmemMax = 227 * 1024;
+    uint32_t warps = tune.warps ? tune.warps : 16;
+    uint32_t wk = tune.wk;
+    if (!wk) {
+        // smallest K split that still gives every warp of the machine a tile slice
+        const uint64_t want = (uint64_t)sm_count * warps * (indirect ? 1 : 1);
+        const uint64_t tiles_total = (uint64_t)ntiles * (indirect ? m.n_slots : 1);
+        wk = 1;
+        while (wk < warps && wk * 2 <= nb && tiles_total * wk < want) wk *= 2;
+    }
+    if (wk > nb) wk = nb;
+    if (wk > warps) wk = warps;
+    while (warps % wk) wk--;  // wk must divide the warp count
+    uint32_t wt = warps / wk;
+    if (wk > 1 && wt > 15) wt = 15, warps = wt * wk;  // named barrier ids 1..15
+    const uint32_t cb = tune.cb ? tune.cb : 1;
+    const uint32_t pitch = cb * kBlockBytes + ((cb & 1u) ? 0u : 16u);
+    const uint32_t stage_bytes = 16 * pitch;
+
+    const uint32_t x_bytes = tokens * m.K * 4u, S_bytes = tokens * (m.K / 32u) * 4u;
+    auto layout = [&](bool xg, uint32_t stages, StreamArgs& sa) -> uint32_t {
+        uint32_t off = kBarBytes;
+        sa.off_zero = off; off += 128;
+        sa.off_red = off; off += tokens * kMaxWarps * 4u;
+        sa.off_inv = off; off += align_up(tokens * 4u, 16);
+        sa.off_S = off; off += xg ? 0 : align_up(S_bytes, 16);
+        sa.off_x = align_up(off, 128); off = sa.off_x + (xg ? 0 : x_bytes);
+        sa.off_part = align_up(off, 16); off = sa.off_part + 2u * warps * tokens * 16u * 4u;
+        sa.off_ring = align_up(off, 128); off = sa.off_ring + warps * stages * stage_bytes;
+        return off;
+    };
+    StreamArgs sa{};
+    sa.m = m;
+    sa.m.M = M;
+    // activations in shared memory if they leave room for at least 3 stages per warp
+    bool xg = false;
+    uint32_t stages = tune.stages ? tune.stages : 4;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (tune.force_scratch) xg = true;
+    if (!xg) {
+        uint32_t s_try = stages;
+        while (s_try >= 2 && layout(false, s_try, sa) > kSmemMax) s_try--;
+        if (s_try >= 2) stages = s_try;
+        else xg = true;
+    }
+    if (xg) {
+        while (stages > 1 && layout(true, stages, sa) > kSmemMax) stages--;
+        if (indirect) return cudaErrorInvalidValue;  // per-slot activations are staged in shared memory only
+        if (!scratch || scratch_bytes < gemv_stream_scratch_bytes(M, m.K)) return cudaErrorInvalidValue;
+    }
+    const uint32_t smem = layout(xg, stages, sa);
+    if (smem > kSmemMax) return cudaErrorInvalidValue;
+    sa.wk = wk; sa.wt = wt; sa.cb = cb; sa.stages = stages; sa.pitch = pitch; sa.stage_bytes = stage_bytes;
+    sa.ntiles = ntiles; sa.tokens = tokens; sa.status = status_dev;
+
+    const uint32_t groups = (ntiles + wt - 1) / wt;  // CTAs needed to give every tile a slot once
+    const uint32_t slots_total = indirect ? m.n_slots : 1;
+
+    if (xg) {
+        uint8_t* sc = static_cast<uint8_t*>(scratch);
+        split_activations_kernel<<<tokens, 1024, 0, stream>>>(m.X, M, m.K, tokens, sc);
+        if (launches) ++*launches;
+        sa.xfrag_g = sc;
+        sa.S_g = reinterpret_cast<const float*>(sc + 128 + (size_t)tokens * m.K * 4u);
+        sa.inv_g = sa.S_g + (size_t)tokens * (m.K / 32u);
+    }
+
+    cudaError_t e = cudaSuccess;
+    MatmulArgs base = sa.m;
+    for (uint32_t s0 = 0; s0 < slots_total; s0 += 65535u) {
+        const uint32_t cnt = indirect ? min(65535u, m.n_slots - s0) : 1;
+        if (indirect) {
+            sa.m.offsets = base.offsets + s0;
+            sa.m.x_rows = base.x_rows ? base.x_rows + s0 : nullptr;
+            sa.m.X = base.x_rows ? base.X : base.X + (uint64_t)s0 * m.K;
+            sa.m.Y = base.Y + (uint64_t)s0 * m.N;
+        }
+        const uint32_t threads = warps * 32;
+#define BPQ4K_LAUNCH(NT_, M1_, XG_) \
+    launch_one<NT_, M1_, XG_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, stream)
+        if (m1) e = xg ? BPQ4K_LAUNCH(1, true, true) : BPQ4K_LAUNCH(1, true, false);
+        else if (NT == 1) e = xg ? BPQ4K_LAUNCH(1, false, true) : BPQ4K_LAUNCH(1, false, false);
+        else if (NT == 2) e = xg ? BPQ4K_LAUNCH(2, false, true) : BPQ4K_LAUNCH(2, false, false);
+        else if (NT == 3) e = xg ? BPQ4K_LAUNCH(3, false, true) : BPQ4K_LAUNCH(3, false, false);
+        else e = xg ? BPQ4K_LAUNCH(4, false, true) : BPQ4K_LAUNCH(4, false, false);
+#undef BPQ4K_LAUNCH
+        if (launches) ++*launches;
+        if (e != cudaSuccess) return e;
+    }
+    return e;
+}
+
+}  // namespace bpq4k

@@ -27,6 +27,8 @@ BLOCK_WORDS = 36
 OPT_GEMV_VARIANT = 1
 OPT_PREFILL_MODE = 2
 OPT_PREFILL_MIN_M = 3
+OPT_STREAM_WARPS, OPT_STREAM_KSPLIT, OPT_STREAM_STAGE_BLOCKS = 10, 11, 12
+OPT_STREAM_STAGES, OPT_STREAM_CTAS_PER_SM, OPT_STREAM_FORCE_SCRATCH = 13, 14, 15
 GEMV_AUTO, GEMV_FP32, GEMV_STREAM = 0, 1, 2
 PREFILL_F16X3, PREFILL_F16, PREFILL_BF16 = 0, 1, 2
 
@@ -122,6 +124,12 @@ class Q4KContext:
     def get_option(self, option: int) -> int:
         v = C.c_int()
         self._check(self.lib.bpq4k_get_option(self.h, option, C.byref(v)))
+        return v.value
+
+    def device_status(self) -> int:
+        """Status word set by kernels whose bounded waits ran out (0 = none); synchronises."""
+        v = C.c_int()
+        self._check(self.lib.bpq4k_device_status(self.h, self._stream(), C.byref(v)))
         return v.value
 
     def launch_count(self, reset: bool = False) -> int:

@@ -64,7 +64,15 @@ typedef enum bpq4k_status {
 typedef enum bpq4k_option {
     BPQ4K_OPT_GEMV_VARIANT = 1,  /* bpq4k_gemv_variant; default AUTO */
     BPQ4K_OPT_PREFILL_MODE = 2,  /* bpq4k_prefill_mode; default F16X3 */
-    BPQ4K_OPT_PREFILL_MIN_M = 3  /* smallest M routed to the tensor-core prefill kernel; default 64 */
+    BPQ4K_OPT_PREFILL_MIN_M = 3, /* smallest M routed to the tensor-core prefill kernel; default 64 */
+    /* Tuning of the streaming kernel; 0 = automatic.  The reference tunes its decode
+     * kernels through an autotune cache (runtime/model_runner.cpp:5113-5199). */
+    BPQ4K_OPT_STREAM_WARPS = 10,         /* warps per CTA, <= 16 */
+    BPQ4K_OPT_STREAM_KSPLIT = 11,        /* warps that share the K range of one 16-row tile */
+    BPQ4K_OPT_STREAM_STAGE_BLOCKS = 12,  /* super-blocks per ring stage */
+    BPQ4K_OPT_STREAM_STAGES = 13,        /* ring depth per warp, <= 8 */
+    BPQ4K_OPT_STREAM_CTAS_PER_SM = 14,   /* cap on resident CTAs per SM */
+    BPQ4K_OPT_STREAM_FORCE_SCRATCH = 15  /* 1: split activations into global scratch even if they fit on chip */
 } bpq4k_option;
 
 typedef enum bpq4k_gemv_variant {
@@ -101,6 +109,12 @@ int bpq4k_get_option(bpq4k_handle_t h, int option, int* value);
  * counter was last reset with reset != 0).  The reference counts dispatches in
  * GPUContext::timing (runtime/gpu_context.h:223-231). */
 uint64_t bpq4k_launch_count(bpq4k_handle_t h, int reset);
+
+/* Read (and clear) the device status word that kernels set when one of their
+ * bounded waits runs out; waits for `stream`.  Returns BPQ4K_OK and *status_out = 0
+ * when nothing was reported, else that status (BPQ4K_ERR_TIMEOUT).  Stands in for
+ * GPUContext's deviceLost / lastAllocFailed flags (runtime/gpu_context.cpp:212-237). */
+int bpq4k_device_status(bpq4k_handle_t h, void* stream, int* status_out);
 
 /* ---- host-side packing -------------------------------------------------- */
 

@@ -105,9 +105,13 @@ def test_matmul_golden(ctx, golden, case, variant):
     M, N, K = (int(v) for v in golden[f"{case}.shape"])
     y = run_matmul(ctx, golden[f"{case}.x"], golden[f"{case}.raw"], golden[f"{case}.bias"], N, K, variant)
     want = golden[f"{case}.y"]
-    check(y, want)
-    if case.startswith("kt_"):
-        assert_close_ref(y, want, 2e-4, 2e-4)   # the reference's own bar on its fixtures
+    assert rel_l2(y, want) <= REL_L2_TOL
+    if case != "synthetic":
+        # the reference's own bar on its fixtures; the hand-made corner blocks reach 3.6e5 in
+        # magnitude (d = 65504), where only a relative bound is meaningful
+        assert_close_ref(y, want, 2e-4, 2e-4)
+    if case != "corner":
+        check(y, want)
 
 
 @pytest.mark.parametrize("variant", VARIANTS, ids=VARIANT_IDS)
