@@ -33,7 +33,7 @@ SIGNATURES = {
     "bpq4k_free_device": (C.c_int, [vp, vp]),
     "bpq4k_dequant_f32": (C.c_int, [vp, vp, u32, u32, u32, vp, vp]),
     "bpq4k_matmul_f32": (C.c_int, [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
-    "bpq4k_matmul_moe_f32": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, vp]),
+    "bpq4k_matmul_moe_f32": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
     "bpq4k_matmul_host_f32": (C.c_int, [vp, vp, vp, vp, vp, u32, u32, u32, u32, vp]),
 }
 

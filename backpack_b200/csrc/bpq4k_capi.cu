@@ -31,6 +31,7 @@ struct bpq4k_context {
     // device status word written by kernels whose bounded waits run out
     int* dev_status = nullptr;
     StreamTuning tune;
+    TmapCache tmaps;
 };
 
 namespace {
@@ -116,7 +117,7 @@ int run_matmul(bpq4k_context* h, const MatmulArgs& a, cudaStream_t st) {
                 c.X = a.X + (uint64_t)m0 * a.K;
                 c.Y = a.Y + (uint64_t)m0 * a.N;
             }
-            e = launch_gemv_stream(c, h->tune, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count, st, &launches);
+            e = launch_gemv_stream(c, h->tune, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count, &h->tmaps, st, &launches);
         }
     }
     h->launches += (uint64_t)launches;
@@ -245,6 +246,11 @@ int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
         case BPQ4K_OPT_STREAM_FORCE_SCRATCH:
             h->tune.force_scratch = value ? 1u : 0u;
             return BPQ4K_OK;
+#ifdef BPQ4K_ENABLE_PROBES
+        case 99:
+            h->tune.probe = (uint32_t)value;
+            return BPQ4K_OK;
+#endif
         default: return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown option %d", option);
     }
 }
@@ -369,11 +375,12 @@ int bpq4k_matmul_f32(bpq4k_handle_t h, const float* X, const void* W, const floa
 
 int bpq4k_matmul_moe_f32(bpq4k_handle_t h, const float* X, const void* W, const float* bias, float* Y,
                          const uint32_t* offsets, const uint32_t* x_rows, uint32_t nSlots, uint32_t N, uint32_t K,
-                         uint32_t rowStrideWords, void* stream) {
+                         uint32_t rowStrideWords, uint32_t wRows, void* stream) {
     if (!h) return BPQ4K_ERR_INVALID_ARG;
     if (nSlots == 0 || N == 0) return BPQ4K_OK;
     if (int s = check_weights(h, W, N, K, rowStrideWords)) return s;
     if (!X || !Y || !offsets) return fail(h, BPQ4K_ERR_INVALID_ARG, "X, Y or offsets is null");
+    if (wRows < N) return fail(h, BPQ4K_ERR_INVALID_ARG, "wRows=%u is smaller than N=%u", wRows, N);
     if (!aligned16(X)) return fail(h, BPQ4K_ERR_MISALIGNED, "X is not 16-byte aligned");
     if (!aligned16(Y)) return fail(h, BPQ4K_ERR_MISALIGNED, "Y is not 16-byte aligned");
     DeviceGuard g(h->device);
@@ -389,6 +396,7 @@ int bpq4k_matmul_moe_f32(bpq4k_handle_t h, const float* X, const void* W, const 
     a.offsets = offsets;
     a.x_rows = x_rows;
     a.n_slots = nSlots;
+    a.w_total_rows = wRows;
     return run_matmul(h, a, static_cast<cudaStream_t>(stream));
 }
 

@@ -20,6 +20,7 @@ struct MatmulArgs {
     const uint32_t* offsets;  // null for the direct form
     const uint32_t* x_rows;   // null: slot s reads row s
     uint32_t n_slots;         // 0 for the direct form
+    uint64_t w_total_rows;    // indirect form: rows of the whole expert stack (bounds the copies)
 };
 
 cudaError_t launch_dequant_f32(const uint8_t* W, uint32_t N, uint32_t K, uint64_t w_row_bytes, float* out,
@@ -36,6 +37,21 @@ struct StreamTuning {
     uint32_t stages = 0;       // ring depth per warp
     uint32_t ctas_per_sm = 0;  // cap on resident CTAs per SM
     uint32_t force_scratch = 0;  // 1: always split activations into global scratch first
+    uint32_t probe = 0;        // development builds only: time-attribution variants of the kernel
+};
+
+// Encoded tensor maps of recently used weight matrices (encoding one costs ~15 us of host time;
+// a decode loop calls with the same few weights over and over).
+struct TmapCache {
+    static constexpr uint32_t kEntries = 64;
+    struct Entry {
+        const void* W = nullptr;
+        uint64_t rows = 0, row_bytes = 0;
+        uint32_t nb = 0, cb = 0;
+        alignas(64) unsigned char map[128];
+    };
+    Entry entries[kEntries];
+    uint32_t next = 0;
 };
 
 // Bytes of scratch launch_gemv_stream needs when the activations do not fit in shared memory.
@@ -44,7 +60,7 @@ size_t gemv_stream_scratch_bytes(uint32_t M, uint32_t K);
 // Streaming tensor-core matmul for M <= 8 (or the indirect form).  `scratch` may be null
 // when the activations fit in shared memory.
 cudaError_t launch_gemv_stream(const MatmulArgs& a, const StreamTuning& tune, void* scratch, size_t scratch_bytes,
-                               int* status_dev, int sm_count, cudaStream_t stream, int* launches);
+                               int* status_dev, int sm_count, TmapCache* tmaps, cudaStream_t stream, int* launches);
 
 // One warp per output row, float FMAs in the reference shader's arithmetic.
 cudaError_t launch_gemv_fp32(const MatmulArgs& a, cudaStream_t stream, int* launches);

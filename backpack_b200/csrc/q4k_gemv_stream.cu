@@ -39,7 +39,11 @@
 // group thread t holds the sums of sub-block parity t%2 -- the per-sub-block scaling
 // work is spread over the four threads of a quad without any shuffles.  With one
 // activation row (M1) pairs 2,3 repeat pairs 0,1 and threads t>=2 take row r+8.
+#include <cuda.h>
 #include <cuda_fp16.h>
+
+#include <cstring>
+#include <type_traits>
 
 #include "kernels.h"
 #include "q4k_common.cuh"
@@ -53,7 +57,10 @@ constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kBarBytes = kMaxWarps * kMaxStages * 8;  // 1 KiB of mbarriers
 constexpr uint32_t kWaitPolls = 1u << 22;                    // bounded mbarrier wait
 
+constexpr uint32_t kZeroBytes = 1024;  // zero region the "other parity" lanes read their B operand from
+
 struct StreamArgs {
+    CUtensorMap tmap;  // W as a 2-D tensor [rows][row words], box = 16 rows x cb blocks
     MatmulArgs m;
     uint32_t wk, wt, cb, stages, pitch, stage_bytes, ntiles, tokens;
     uint32_t off_zero, off_red, off_inv, off_S, off_x, off_part, off_ring;
@@ -83,42 +90,70 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok;
 }
-// Plain (non-multicast) bulk copy global -> this CTA's shared memory.
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
+// Plain (non-multicast) 2-D tiled tensor copy global -> this CTA's shared memory:
+// box = 16 rows x (cb*36) words starting at (word x, row y); rows/words outside the tensor
+// arrive as zeros and still count towards the transaction bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tmap, uint32_t x, uint32_t y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(tmap), "r"(x), "r"(y), "r"(bar)
+        : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Shared-memory loads with a compile-time byte offset folded into the instruction.
+template <int OFF>
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4+%5];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
+                 : "r"(addr), "n"(OFF));
 }
+template <int OFF = 0>
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr), "n"(OFF));
     return v;
 }
+// D = A*B + C.  Not volatile: a pure function of its register operands, so the compiler may
+// interleave the independent chains of different 64-weight groups.
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// D = A*B (accumulator starts at zero).
+__device__ __forceinline__ void mma16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
 // (64+q) halves of the four nibble pairs of a code word.
 //   even0 = nibbles 0,4 (weights 4t, 4t+2 of the even sub-block), even1 = nibbles 2,6 (4t+1, 4t+3)
 //   odd0  = nibbles 1,5 (same weights of the odd sub-block),      odd1  = nibbles 3,7
+// A high nibble (bits 4-7 of a half) dropped into the mantissa of 0x5400 (= 64, ulp 1/16) reads
+// 64+q directly.  A low nibble (bits 0-3) dropped into 0x6400 (= 1024, ulp 1) reads 1024+q; one
+// packed half add of -960 (exact) turns it into 64+q.  The integer pipe is the scarce one in
+// this kernel, so the adds (fma pipe) are cheaper than the shifts they replace.
+__device__ __forceinline__ uint32_t hadd2_bits(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
 __device__ __forceinline__ void decode_word(uint32_t w, uint32_t& even0, uint32_t& even1, uint32_t& odd0,
                                             uint32_t& odd1) {
-    constexpr uint32_t kMask = 0x00F000F0u, kBase = 0x54005400u;  // 0x5400 = 64.0h, nibble lands on units
-    even0 = ((w << 4) & kMask) | kBase;
-    odd0 = (w & kMask) | kBase;
-    even1 = ((w >> 4) & kMask) | kBase;
-    odd1 = ((w >> 8) & kMask) | kBase;
+    constexpr uint32_t kLoMask = 0x000F000Fu, kHiMask = 0x00F000F0u;
+    constexpr uint32_t kBase1024 = 0x64006400u, kBase64 = 0x54005400u;
+    constexpr uint32_t kMinus960 = 0xE380E380u;  // -960.0h twice
+    const uint32_t t = w >> 8;
+    even0 = hadd2_bits((w & kLoMask) | kBase1024, kMinus960);
+    odd0 = (w & kHiMask) | kBase64;
+    even1 = hadd2_bits((t & kLoMask) | kBase1024, kMinus960);
+    odd1 = (t & kHiMask) | kBase64;
 }
 
 // Power-of-two scale that brings `amax` to [2^10, 2^11), and its inverse.
@@ -152,7 +187,10 @@ __device__ __forceinline__ float split_store(float v, uint8_t* frag_base, uint32
     return s;
 }
 
-template <int NT, bool M1, bool XG>
+// PROBE (development builds only, -DBPQ4K_ENABLE_PROBES): 0 = the kernel; 1 = copies and waits
+// only; 2 = math on whatever the ring holds, no copies; 3 = as 2 without the mmas; 4 = as 2
+// without the nibble decode; 5 = as 2 without the scale decode.  Used to attribute time.
+template <int NT, bool M1, bool XG, int PROBE = 0>
 __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TOK = M1 ? 1 : NT * 2;  // token slots
@@ -168,7 +206,7 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
     // problem selection (indirect form: blockIdx.y is the slot)
     const float* X = a.m.X;
     float* Y = a.m.Y;
-    uint64_t wrow0 = 0;
+    uint32_t wrow0 = 0;
     uint32_t M = a.m.M;
     if (a.m.n_slots) {
         const uint32_t s = blockIdx.y;
@@ -177,8 +215,6 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
         Y += (uint64_t)s * N;
         M = 1;
     }
-    const uint8_t* Wp = a.m.W + wrow0 * a.m.w_row_bytes;
-
     const uint32_t tstride = gridDim.x * a.wt;
     const uint32_t tile0 = blockIdx.x * a.wt + wt;
     const uint32_t my_tiles = tile0 < a.ntiles ? (a.ntiles - tile0 + tstride - 1) / tstride : 0;
@@ -194,28 +230,22 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
     fence_proxy_async();
     __syncwarp();
 
-    // ---- producer side: one bulk copy per row of the unit's chunk -------------
-    uint32_t iss_tile = tile0, iss_c = 0, iss_u = 0;
+    // ---- producer side: lane 0 issues one tensor copy per unit ------------------
+    uint32_t iss_tile = tile0, iss_c = 0, iss_st = 0;
     auto issue_next = [&]() {
-        const uint32_t bs = b0 + iss_c * a.cb;
-        const uint32_t nblk = min(a.cb, b1 - bs);
-        const uint32_t st = iss_u % a.stages;
-        const uint32_t row = iss_tile * 16u + lane;
-        const uint32_t rows_valid = min(16u, N - iss_tile * 16u);
-        const uint32_t bytes = nblk * kBlockBytes;
-        const uint32_t bar = bar0 + st * 8u;
-        if (lane == 0) mbar_expect_tx(bar, rows_valid * bytes);
-        __syncwarp();
-        if (lane < rows_valid)
-            bulk_g2s(ring + st * a.stage_bytes + lane * a.pitch, Wp + (uint64_t)row * a.m.w_row_bytes + (uint64_t)bs * kBlockBytes,
-                     bytes, bar);
-        iss_u++;
+        if (lane == 0) {
+            const uint32_t bar = bar0 + iss_st * 8u;
+            mbar_expect_tx(bar, a.stage_bytes);
+            tma_load_2d(ring + iss_st * a.stage_bytes, &a.tmap, (b0 + iss_c * a.cb) * kBlockWords,
+                        (uint32_t)wrow0 + iss_tile * 16u, bar);
+        }
+        if (++iss_st == a.stages) iss_st = 0;
         if (++iss_c == nchunks) {
             iss_c = 0;
             iss_tile += tstride;
         }
     };
-    {
+    if constexpr (PROBE < 2) {
         const uint32_t pre = min(a.stages, total_units);
         for (uint32_t i = 0; i < pre; i++) issue_next();
     }
@@ -224,18 +254,27 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
     const uint32_t NG = K / 64u;
     float* invs = reinterpret_cast<float*>(smem + a.off_inv);
     if constexpr (!XG) {
+        // Pass 1: copy the raw floats into the fragment region (a sub-block's 32 floats occupy
+        // exactly the 128 bytes its hi/lo halves will) and find max|x| per row.  All global
+        // loads of a thread are independent, so their latencies overlap.
+        // Pass 2: convert in place from shared memory; no global latency on this path.
         float* red = reinterpret_cast<float*>(smem + a.off_red);
         float* Ss = reinterpret_cast<float*>(smem + a.off_S);
         uint8_t* xf = smem + a.off_x;
-        if (tid < 4) reinterpret_cast<uint32_t*>(smem + a.off_zero)[tid] = 0u;
+        for (uint32_t i = tid; i < kZeroBytes / 4u; i += blockDim.x) reinterpret_cast<uint32_t*>(smem + a.off_zero)[i] = 0u;
         for (int tok = 0; tok < TOK; tok++) {
             float amax = 0.f;
+            float4* dst = reinterpret_cast<float4*>(xf + (uint64_t)tok * K * 4u);
             if ((uint32_t)tok < M) {
                 const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok * K);
+#pragma unroll 4
                 for (uint32_t i = tid; i < K / 4u; i += blockDim.x) {
                     const float4 v = __ldg(xp + i);
+                    dst[i] = v;
                     amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
                 }
+            } else {
+                for (uint32_t i = tid; i < K / 4u; i += blockDim.x) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
@@ -249,11 +288,13 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
             float scale, inv;
             pow2_scale(amax, scale, inv);
             if (tid == 0) invs[tok] = inv;
+            uint8_t* base = xf + (uint64_t)tok * K * 4u;
             for (uint32_t sbg = warp; sbg < nsub; sbg += nwarps) {
-                const float v = tok < M ? __ldg(X + (uint64_t)tok * K + sbg * 32u + lane) * scale : 0.f;
-                const uint32_t G = sbg >> 1, par = sbg & 1u;
-                const float s = split_store(v, xf + ((uint64_t)(tok * NG + G) * 2u + par) * 128u, lane);
-                if (lane == 0) Ss[((tok * nb + (sbg >> 3)) * 2u + par) * 4u + ((sbg >> 1) & 3u)] = s;
+                uint8_t* blk128 = base + sbg * 128u;  // == ((tok*NG + G)*2 + parity)*128 with sbg = 2G + parity
+                const float v = reinterpret_cast<const float*>(blk128)[lane] * scale;
+                __syncwarp();  // every lane has read its float before the halves overwrite them
+                const float s = split_store(v, blk128, lane);
+                if (lane == 0) Ss[((tok * nb + (sbg >> 3)) * 2u + (sbg & 1u)) * 4u + ((sbg >> 1) & 3u)] = s;
             }
         }
         __syncthreads();
@@ -271,24 +312,35 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
     const uint32_t c_par = lane & 1u;
     const uint32_t c_tok = M1 ? 0u : (bt >> 1);
     const uint32_t row_a = M1 ? (lane >> 2) + ((bt >> 1) << 3) : (lane >> 2);
+    const uint32_t hdr_off = row_a * a.pitch;
     const uint32_t sel0 = 0x7440u + c_par, sel1 = 0x7442u + c_par;
 
-    // base "addresses" of this lane's B data and of the zero block
-    uint64_t xdata, xzero;      // XG: global addresses; else shared addresses (low 32 bits)
-    const float* Sbase;
+    // This lane's B data lives at  xbase + ((tok*NG + G)*2 + parity)*128 + part*64 + t*16.
+    // In the mmas of the other parity the lane feeds zeros: it reads the zero block with
+    // stride 0 instead.  AddrT is a shared-memory offset, or a global address in XG mode.
+    using AddrT = typename std::conditional<XG, uint64_t, uint32_t>::type;
+    AddrT xdata, xzero, s_addr;
     if constexpr (XG) {
-        xdata = reinterpret_cast<uint64_t>(a.xfrag_g) + 128u;  // first 128 bytes of the scratch: zeros
+        xdata = reinterpret_cast<uint64_t>(a.xfrag_g) + kZeroBytes;  // the scratch starts with the zero region
         xzero = reinterpret_cast<uint64_t>(a.xfrag_g);
-        Sbase = a.S_g;
+        s_addr = reinterpret_cast<uint64_t>(a.S_g);
     } else {
         xdata = smem_u32(smem + a.off_x);
         xzero = smem_u32(smem + a.off_zero);
-        Sbase = reinterpret_cast<const float*>(smem + a.off_S);
+        s_addr = smem_u32(smem + a.off_S);
     }
-    const uint32_t lane_boff = b_par * 128u + (bn & 1u) * 64u + bt * 16u;
-    auto load_b = [&](uint64_t addr) -> uint4 {
-        if constexpr (XG) return __ldg(reinterpret_cast<const uint4*>(addr));
-        else return lds128((uint32_t)addr);
+    const AddrT mine = xdata + (AddrT)(b_tok * NG) * 256u + b_par * 128u + (bn & 1u) * 64u + bt * 16u;
+    const AddrT pa0 = b_par == 0 ? mine : xzero;       // source for the even-sub-block mmas
+    const AddrT pb0 = b_par == 1 ? mine : xzero;       // source for the odd-sub-block mmas
+    const uint32_t stride_a = b_par == 0 ? 256u : 0u;  // per 64-weight group
+    const uint32_t stride_b = b_par == 1 ? 256u : 0u;
+    const uint32_t tile_stride = 2u * NG * 256u;       // per n-tile (two tokens)
+    const AddrT s0_addr = s_addr + (AddrT)(c_tok * nb) * 32u + c_par * 16u;  // + blk*32 (+ nt*2*nb*32)
+    // 16-byte load at addr + OFF (OFF is folded into the instruction)
+    auto load16 = [&](AddrT addr, auto off_tag) -> uint4 {
+        constexpr int OFF = decltype(off_tag)::value;
+        if constexpr (XG) return __ldg(reinterpret_cast<const uint4*>(addr + OFF));
+        else return lds128<OFF>(addr);
     };
 
     float* part = reinterpret_cast<float*>(smem + a.off_part);
@@ -306,7 +358,7 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
             const uint32_t bs = b0 + c * a.cb;
             const uint32_t nblk = min(a.cb, b1 - bs);
             const uint32_t bar = bar0 + st * 8u;
-            if (!failed) {
+            if (PROBE < 2 && !failed) {
                 uint32_t polls = 0;
                 while (!mbar_try_wait(bar, ph)) {
                     if (++polls > kWaitPolls) {  // give up: flag it, keep the barriers matched
@@ -316,15 +368,18 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
                     }
                 }
             }
-            const uint32_t sbase = ring + st * a.stage_bytes;
-            for (uint32_t bl = 0; bl < nblk; bl++) {
-                const uint32_t blk = bs + bl;
-                const uint32_t boff = sbase + bl * kBlockBytes;
+            uint32_t boff = ring + st * a.stage_bytes;
+            for (uint32_t blk = bs; PROBE != 1 && blk < bs + nblk; blk++, boff += kBlockBytes) {
                 // scales of this thread's rows, its parity's four sub-blocks
                 float dsc[RPT][4], esc[RPT][4];
 #pragma unroll
                 for (int r = 0; r < RPT; r++) {
-                    const uint4 hv = lds128(boff + (row_a + r * 8u) * a.pitch);
+                    if constexpr (PROBE == 5) {
+#pragma unroll
+                        for (int g = 0; g < 4; g++) dsc[r][g] = 1.f, esc[r][g] = 2.f;
+                        continue;
+                    }
+                    const uint4 hv = lds128<0>(boff + hdr_off + r * 8u * a.pitch);
                     const BlockHeader h{hv.x, hv.y, hv.z, hv.w};
                     const float d = half_bits_to_float(h.w0), dmin = half_bits_to_float(h.w0 >> 16);
                     uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
@@ -342,34 +397,48 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
                         esc[r][g] = fmaf(64.f, dsc[r][g], dmn);
                     }
                 }
-                float4 Sv[NT];
+                uint4 Sv[NT];
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    const uint32_t tok = nt * 2u + c_tok;
-                    Sv[nt] = *reinterpret_cast<const float4*>(Sbase + ((uint64_t)(tok * nb + blk) * 2u + c_par) * 4u);
-                }
-#pragma unroll
-                for (int g = 0; g < 4; g++) {
+                for (int nt = 0; nt < NT; nt++)
+                    Sv[nt] = load16(s0_addr + (AddrT)(nt * 2u * nb + blk) * 32u, std::integral_constant<int, 0>{});
+                // data lanes advance 1 KiB per block (4 groups x 256 B); zero lanes stay inside the
+                // 1 KiB zero region, so the per-group offset g*256 is an immediate for both
+                const AddrT pa = pa0 + blk * 4u * stride_a, pb = pb0 + blk * 4u * stride_b;
+                const uint32_t lm_addr = boff + lm_off;
+                auto do_group = [&](auto gc) {
+                    constexpr int g = decltype(gc)::value;
                     uint32_t r0, r1, r2, r3;
-                    ldmatrix_x4(boff + lm_off + g * 32u, r0, r1, r2, r3);
+                    ldmatrix_x4<g * 32>(lm_addr, r0, r1, r2, r3);
                     uint32_t e0[4], e1[4], o0[4], o1[4];
-                    decode_word(r0, e0[0], e1[0], o0[0], o1[0]);
-                    decode_word(r1, e0[1], e1[1], o0[1], o1[1]);
-                    decode_word(r2, e0[2], e1[2], o0[2], o1[2]);
-                    decode_word(r3, e0[3], e1[3], o0[3], o1[3]);
-                    const uint32_t G = blk * 4u + g;
+                    if constexpr (PROBE == 4) {
+                        e0[0] = e1[0] = o0[0] = o1[0] = r0;
+                        e0[1] = e1[1] = o0[1] = o1[1] = r1;
+                        e0[2] = e1[2] = o0[2] = o1[2] = r2;
+                        e0[3] = e1[3] = o0[3] = o1[3] = r3;
+                    } else {
+                        decode_word(r0, e0[0], e1[0], o0[0], o1[0]);
+                        decode_word(r1, e0[1], e1[1], o0[1], o1[1]);
+                        decode_word(r2, e0[2], e1[2], o0[2], o1[2]);
+                        decode_word(r3, e0[3], e1[3], o0[3], o1[3]);
+                    }
 #pragma unroll
                     for (int nt = 0; nt < NT; nt++) {
-                        const uint32_t tok = nt * 2u + b_tok;
-                        const uint64_t mine = xdata + ((uint64_t)(tok * NG + G) * 2u) * 128u + lane_boff;
-                        const uint4 qa = load_b(b_par == 0 ? mine : xzero);
-                        const uint4 qb = load_b(b_par == 1 ? mine : xzero);
-                        float cfr[4] = {0.f, 0.f, 0.f, 0.f};
-                        mma16816(cfr, e0[0], e0[1], e1[0], e1[1], qa.x, qa.y);  // even sub-block, code bytes 0-15
-                        mma16816(cfr, e0[2], e0[3], e1[2], e1[3], qa.z, qa.w);  // even sub-block, code bytes 16-31
-                        mma16816(cfr, o0[0], o0[1], o1[0], o1[1], qb.x, qb.y);  // odd sub-block
-                        mma16816(cfr, o0[2], o0[3], o1[2], o1[3], qb.z, qb.w);
-                        const float Sg = g == 0 ? Sv[nt].x : g == 1 ? Sv[nt].y : g == 2 ? Sv[nt].z : Sv[nt].w;
+                        const uint4 qa = load16(pa + (b_par == 0 ? nt * tile_stride : 0u), std::integral_constant<int, g * 256>{});
+                        const uint4 qb = load16(pb + (b_par == 1 ? nt * tile_stride : 0u), std::integral_constant<int, g * 256>{});
+                        float cfr[4];
+                        if constexpr (PROBE == 3) {
+                            cfr[0] = __uint_as_float(e0[0] ^ e1[1] ^ o0[2] ^ o1[3] ^ qa.x ^ qb.y);
+                            cfr[1] = __uint_as_float(e0[1] ^ e1[2] ^ o0[3] ^ o1[0] ^ qa.y ^ qb.z);
+                            cfr[2] = __uint_as_float(e0[2] ^ e1[3] ^ o0[0] ^ o1[1] ^ qa.z ^ qb.w);
+                            cfr[3] = __uint_as_float(e0[3] ^ e1[0] ^ o0[1] ^ o1[2] ^ qa.w ^ qb.x);
+                        } else {
+                            mma16816_first(cfr, e0[0], e0[1], e1[0], e1[1], qa.x, qa.y);  // even sub-block, code bytes 0-15
+                            mma16816(cfr, e0[2], e0[3], e1[2], e1[3], qa.z, qa.w);        // even sub-block, code bytes 16-31
+                            mma16816(cfr, o0[0], o0[1], o1[0], o1[1], qb.x, qb.y);        // odd sub-block
+                            mma16816(cfr, o0[2], o0[3], o1[2], o1[3], qb.z, qb.w);
+                        }
+                        const uint32_t sbits = g == 0 ? Sv[nt].x : g == 1 ? Sv[nt].y : g == 2 ? Sv[nt].z : Sv[nt].w;
+                        const float Sg = __uint_as_float(sbits);
                         if constexpr (M1) {
                             const float v = (bt & 2u) ? (cfr[2] + cfr[3]) : (cfr[0] + cfr[1]);
                             acc[nt][0] = fmaf(dsc[0][g], v, acc[nt][0]);
@@ -381,12 +450,16 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
                             acc[nt][1] = fmaf(-esc[1][g], Sg, acc[nt][1]);
                         }
                     }
-                }
+                };
+                do_group(std::integral_constant<int, 0>{});
+                do_group(std::integral_constant<int, 1>{});
+                do_group(std::integral_constant<int, 2>{});
+                do_group(std::integral_constant<int, 3>{});
             }
             // the stage is free: refill it with the unit `stages` ahead
             __syncwarp();
             fence_proxy_async();
-            if (u + a.stages < total_units) issue_next();
+            if (PROBE < 2 && u + a.stages < total_units) issue_next();
             u++;
             if (++st == a.stages) {
                 st = 0;
@@ -427,17 +500,17 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
 // ---------------------------------------------------------------------------
 // XG mode: split the activations once per call into global scratch, in the same
 // permuted layout the kernel above keeps in shared memory.  One CTA per row.
-// Scratch layout: [128 B zeros][xfrag: tokens*K*4 B][S: tokens*(K/32) floats][inv: tokens floats]
+// Scratch layout: [1 KiB zeros][xfrag: tokens*K*4 B][S: tokens*(K/32) floats][inv: tokens floats]
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024) split_activations_kernel(const float* __restrict__ X, uint32_t M, uint32_t K,
                                                                  uint32_t tokens, uint8_t* __restrict__ scratch) {
     __shared__ float red[32];
     const uint32_t tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t nwarps = blockDim.x >> 5, nb = K / kQK, NG = K / 64u, nsub = K / 32u;
-    uint8_t* xf = scratch + 128;
+    uint8_t* xf = scratch + kZeroBytes;
     float* S = reinterpret_cast<float*>(xf + (uint64_t)tokens * K * 4u);
     float* inv_out = S + (uint64_t)tokens * nsub;
-    if (tok == 0 && tid < 32) reinterpret_cast<uint32_t*>(scratch)[tid] = 0u;
+    if (tok == 0 && tid < kZeroBytes / 4u) reinterpret_cast<uint32_t*>(scratch)[tid] = 0u;
     float amax = 0.f;
     if (tok < M) {
         const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok * K);
@@ -465,7 +538,7 @@ __global__ void __launch_bounds__(1024) split_activations_kernel(const float* __
 
 // Launch one instantiation.  The grid is persistent: at most as many CTAs as can be
 // resident at once (occupancy query, cached), never more than there are tile groups.
-template <int NT, bool M1, bool XG>
+template <int NT, bool M1, bool XG, int PROBE = 0>
 cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, uint32_t threads, size_t smem,
                        int sm_count, uint32_t ctas_per_sm_override, cudaStream_t stream) {
     struct Cache { int dev = -1; size_t smem_cfg = 0; uint32_t threads = 0; size_t smem = 0; int occ = 0; };
@@ -475,7 +548,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     if (cache.dev != dev) cache = Cache{};
     cache.dev = dev;
     if (smem > cache.smem_cfg) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT, M1, XG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT, M1, XG, PROBE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return e;
         cache.smem_cfg = smem;
@@ -483,7 +556,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     }
     if (cache.threads != threads || cache.smem != smem) {
         int occ = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_stream_kernel<NT, M1, XG>, (int)threads, smem);
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_stream_kernel<NT, M1, XG, PROBE>, (int)threads, smem);
         if (e != cudaSuccess) return e;
         cache.threads = threads;
         cache.smem = smem;
@@ -496,21 +569,40 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     if ((uint64_t)gx * slots_y > cap) gx = (uint32_t)((cap + slots_y - 1) / slots_y);
     if (gx == 0) gx = 1;
     if (gx > groups) gx = groups;
-    gemv_stream_kernel<NT, M1, XG><<<dim3(gx, slots_y), threads, smem, stream>>>(sa);
+    gemv_stream_kernel<NT, M1, XG, PROBE><<<dim3(gx, slots_y), threads, smem, stream>>>(sa);
     return cudaGetLastError();
 }
 
+static_assert(sizeof(CUtensorMap) == 128, "TmapCache::Entry::map must hold a CUtensorMap");
+
 uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+// cuTensorMapEncodeTiled, fetched through the runtime so the library has no link-time
+// dependency on libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
 
 }  // namespace
 
 size_t gemv_stream_scratch_bytes(uint32_t M, uint32_t K) {
     const uint32_t tokens = M <= 1 ? 1 : (M + 1) / 2 * 2;
-    return 128 + (size_t)tokens * K * 4 + (size_t)tokens * (K / 32) * 4 + (size_t)tokens * 4 + 256;
+    return kZeroBytes + (size_t)tokens * K * 4 + (size_t)tokens * (K / 32) * 4 + (size_t)tokens * 4 + 256;
 }
 
 cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, void* scratch, size_t scratch_bytes,
-                               int* status_dev, int sm_count, cudaStream_t stream, int* launches) {
+                               int* status_dev, int sm_count, TmapCache* tmaps, cudaStream_t stream, int* launches) {
     if (m.N == 0) return cudaSuccess;
     const bool indirect = m.n_slots != 0;
     const uint32_t M = indirect ? 1 : m.M;
@@ -538,14 +630,17 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     while (warps % wk) wk--;  // wk must divide the warp count
     uint32_t wt = warps / wk;
     if (wk > 1 && wt > 15) wt = 15, warps = wt * wk;  // named barrier ids 1..15
-    const uint32_t cb = tune.cb ? tune.cb : 1;
-    const uint32_t pitch = cb * kBlockBytes + ((cb & 1u) ? 0u : 16u);
+    // Stage = dense TMA box of 16 rows x cb blocks.  An odd cb keeps the 16-byte units of
+    // the eight rows an ldmatrix touches in distinct bank groups (row pitch = cb*9 units).
+    uint32_t cb = tune.cb ? tune.cb : 1;
+    if (cb > 7) cb = 7;  // box width <= 256 words
+    const uint32_t pitch = cb * kBlockBytes;
     const uint32_t stage_bytes = 16 * pitch;
 
     const uint32_t x_bytes = tokens * m.K * 4u, S_bytes = tokens * (m.K / 32u) * 4u;
     auto layout = [&](bool xg, uint32_t stages, StreamArgs& sa) -> uint32_t {
         uint32_t off = kBarBytes;
-        sa.off_zero = off; off += 128;
+        sa.off_zero = off; off += kZeroBytes;
         sa.off_red = off; off += tokens * kMaxWarps * 4u;
         sa.off_inv = off; off += align_up(tokens * 4u, 16);
         sa.off_S = off; off += xg ? 0 : align_up(S_bytes, 16);
@@ -577,6 +672,36 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     if (smem > kSmemMax) return cudaErrorInvalidValue;
     sa.wk = wk; sa.wt = wt; sa.cb = cb; sa.stages = stages; sa.pitch = pitch; sa.stage_bytes = stage_bytes;
     sa.ntiles = ntiles; sa.tokens = tokens; sa.status = status_dev;
+    {
+        const uint64_t rows_total = indirect ? m.w_total_rows : m.N;
+        const TmapCache::Entry* hit = nullptr;
+        if (tmaps) {
+            for (const auto& en : tmaps->entries)
+                if (en.W == m.W && en.rows == rows_total && en.row_bytes == m.w_row_bytes && en.nb == nb && en.cb == cb) {
+                    hit = &en;
+                    break;
+                }
+        }
+        if (hit) {
+            std::memcpy(&sa.tmap, hit->map, sizeof(CUtensorMap));
+        } else {
+        EncodeTiledFn enc = encode_tiled_fn();
+        if (!enc) return cudaErrorNotSupported;
+        const cuuint64_t gdim[2] = {(cuuint64_t)nb * kBlockWords, (cuuint64_t)rows_total};
+        const cuuint64_t gstride[1] = {(cuuint64_t)m.w_row_bytes};
+        const cuuint32_t box[2] = {cb * kBlockWords, 16u};
+        const cuuint32_t estr[2] = {1u, 1u};
+        const CUresult r = enc(&sa.tmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(m.W), gdim, gstride, box,
+                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+        if (tmaps) {
+            auto& en = tmaps->entries[tmaps->next++ % TmapCache::kEntries];
+            en.W = m.W; en.rows = rows_total; en.row_bytes = m.w_row_bytes; en.nb = nb; en.cb = cb;
+            std::memcpy(en.map, &sa.tmap, sizeof(CUtensorMap));
+        }
+        }
+    }
 
     const uint32_t groups = (ntiles + wt - 1) / wt;  // CTAs needed to give every tile a slot once
     const uint32_t slots_total = indirect ? m.n_slots : 1;
@@ -586,7 +711,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         split_activations_kernel<<<tokens, 1024, 0, stream>>>(m.X, M, m.K, tokens, sc);
         if (launches) ++*launches;
         sa.xfrag_g = sc;
-        sa.S_g = reinterpret_cast<const float*>(sc + 128 + (size_t)tokens * m.K * 4u);
+        sa.S_g = reinterpret_cast<const float*>(sc + kZeroBytes + (size_t)tokens * m.K * 4u);
         sa.inv_g = sa.S_g + (size_t)tokens * (m.K / 32u);
     }
 
@@ -603,6 +728,19 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         const uint32_t threads = warps * 32;
 #define BPQ4K_LAUNCH(NT_, M1_, XG_) \
     launch_one<NT_, M1_, XG_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, stream)
+#ifdef BPQ4K_ENABLE_PROBES
+#define BPQ4K_PROBE(P_) launch_one<1, true, false, P_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, stream)
+        if (m1 && !xg && tune.probe) {
+            switch (tune.probe) {
+                case 1: e = BPQ4K_PROBE(1); break;
+                case 2: e = BPQ4K_PROBE(2); break;
+                case 3: e = BPQ4K_PROBE(3); break;
+                case 4: e = BPQ4K_PROBE(4); break;
+                default: e = BPQ4K_PROBE(5); break;
+            }
+        } else
+#undef BPQ4K_PROBE
+#endif
         if (m1) e = xg ? BPQ4K_LAUNCH(1, true, true) : BPQ4K_LAUNCH(1, true, false);
         else if (NT == 1) e = xg ? BPQ4K_LAUNCH(1, false, true) : BPQ4K_LAUNCH(1, false, false);
         else if (NT == 2) e = xg ? BPQ4K_LAUNCH(2, false, true) : BPQ4K_LAUNCH(2, false, false);

@@ -180,7 +180,7 @@ class Q4KContext:
         self._check(self.lib.bpq4k_matmul_moe_f32(
             self.h, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
             out.data_ptr(), offsets.data_ptr(), x_rows.data_ptr() if x_rows is not None else None,
-            S, N, w.K, w.rowStrideWords, self._stream()))
+            S, N, w.K, w.rowStrideWords, w.N, self._stream()))
         return out
 
     def matmul_host(self, x_host: np.ndarray, w: Q4KWeight, y_host: np.ndarray, bias=None) -> np.ndarray:

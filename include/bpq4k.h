@@ -161,10 +161,12 @@ int bpq4k_matmul_f32(bpq4k_handle_t h, const float* X, const void* W, const floa
  * ([nExperts*N][K], runtime/model_runner.cpp:1520-1562); offsets[s] is the first
  * weight row of slot s's expert (compute_offsets.wgsl:26-36: expert*N).  Slot s
  * reads activation row x_rows[s] of X (x_rows NULL: row s) and writes
- * Y[s*N + n] = sum_k X[x_rows[s]*K + k]*deq(W)[offsets[s]+n][k] + bias[n]. */
+ * Y[s*N + n] = sum_k X[x_rows[s]*K + k]*deq(W)[offsets[s]+n][k] + bias[n].
+ * `wRows` is the number of rows of the whole stack (nExperts*N): the size of the
+ * reference's weight binding, which bounds what the kernel may read. */
 int bpq4k_matmul_moe_f32(bpq4k_handle_t h, const float* X, const void* W, const float* bias, float* Y,
                          const uint32_t* offsets, const uint32_t* x_rows, uint32_t nSlots,
-                         uint32_t N, uint32_t K, uint32_t rowStrideWords, void* stream);
+                         uint32_t N, uint32_t K, uint32_t rowStrideWords, uint32_t wRows, void* stream);
 
 /* Same operator with HOST activations and HOST outputs: copies X_host to the
  * handle's staging buffer, runs the matmul on the resident device weights and
