@@ -10,15 +10,17 @@
 // Arithmetic.  For sub-block sb of row n:  w = dsc*q - dmn  with dsc = d*sc,
 // dmn = dmin*mn, so
 //     sum_k x_k w_k = dsc * sum_k x_k q_k  -  dmn * sum_k x_k .
-// The 4-bit codes are turned into halves 64+q with one logic op each (the nibble
-// is dropped into the mantissa of 0x5400 = 64.0, whose ulp is 1/16 ... shifted so
-// that the nibble counts units), the activation row is split into two halves
-// x = xh + xl after scaling by a power of two so that max|x| ~ 2^10, and
-//     T = sum_k (64+q_k)(xh_k + xl_k)
-// is accumulated in float by mma.sync.m16n8k16 (all products are exact).  With
-// S = sum_k (xh_k + xl_k) per sub-block computed once per activation row,
-//     contribution = dsc*T - (64*dsc + dmn)*S .
-// Error relative to the float reference is ~1e-6 (x keeps 22 bits, sums are float).
+// sum_k x_k q_k is taken EXACTLY in integers on the tensor cores (mma.sync m16n8k32,
+// u8 x s8 -> s32): the activation row is scaled so that max|x| maps to 2080000 (< 2^21),
+// rounded to an integer xi and written as three signed base-128 digits
+// xi = d0*2^14 + d1*2^7 + d2 (|d| <= 64).  The 4-bit codes need almost no decoding: a
+// code word masked with 0x0F0F0F0F is four u8 weights of the even sub-block, masked with
+// 0xF0F0F0F0 it is four weights of the odd sub-block times 16 (the 1/16 goes into dsc).
+// Per sub-block   T = 2^14*sum(q d0) + 2^7*sum(q d1) + sum(q d2)   (exact: the two low
+// digit sums are combined in int32, the top one joins in float where it is exact), then
+//     contribution = dsc*float(T) - dmn*float(sum xi)
+// in float.  x keeps 22 bits relative to its row maximum; everything else is float, so the
+// result differs from the float reference by ~1e-6 relative.
 //
 // Work decomposition.  A tile is 16 output rows.  The warps of a CTA are arranged
 // as WT tile slots x WK slices of K; a warp streams its slice of its tile through
@@ -28,17 +30,16 @@
 // results are deterministic.  CTAs are persistent and walk tiles with stride
 // gridDim.x*WT.
 //
-// mma operand mapping (one mma = 16 rows x 16 weights of one sub-block).  ldmatrix
-// hands thread (r = lane/4, t = lane%4) word t of a 16-byte run of code bytes of
-// rows r and r+8.  A word holds bytes 4t..4t+3, i.e. weights 4t..4t+3 of the even
-// sub-block in its low nibbles and of the odd sub-block in its high nibbles:
-//   a0a1 = (w[4t], w[4t+2])  a4a5 = (w[4t+1], w[4t+3])   (row r;  a2a3/a6a7: row r+8)
-// and the activations are stored in shared memory already permuted the same way.
-// The 8 mma columns are 4 pairs (hi, lo); pair j carries x only in the mmas of the
-// sub-block parity j%2 and zeros in the others, so after the four mmas of a 64-weight
-// group thread t holds the sums of sub-block parity t%2 -- the per-sub-block scaling
-// work is spread over the four threads of a quad without any shuffles.  With one
-// activation row (M1) pairs 2,3 repeat pairs 0,1 and threads t>=2 take row r+8.
+// mma operand mapping (one mma = 16 rows x the 32 weights of one sub-block).  ldmatrix hands
+// thread (r = lane/4, t = lane%4) word t of a 16-byte run of code bytes of rows r and r+8:
+// exactly the A fragment of m16n8k32 (a0: row r, k = 4t..4t+3; a1: row r+8; a2, a3: k+16),
+// in natural k order, so the activation digits are stored in natural order too.
+// The 8 mma columns are 4 pairs; a pair's two columns carry digits (d0, d1) in the first
+// mma of a sub-block and (d2, 0) in the second.  Pair j carries digits only in the mmas of
+// sub-block parity j%2 and zeros in the others, so after the four mmas of a 64-weight group
+// thread t holds the sums of sub-block parity t%2 -- the per-sub-block scaling work is
+// spread over the four threads of a quad without any shuffles.  With one activation row
+// (M1) pairs 2,3 repeat pairs 0,1 and threads t>=2 take row r+8.
 #include <cuda.h>
 #include <cuda_fp16.h>
 
@@ -116,72 +117,55 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
                  : "r"(addr), "n"(OFF));
     return v;
 }
-// D = A*B + C.  Not volatile: a pure function of its register operands, so the compiler may
-// interleave the independent chains of different 64-weight groups.
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+// D = A*B + C on u8 x s8 -> s32.  Not volatile: a pure function of its register operands, so
+// the compiler may interleave the independent chains of different 64-weight groups.
+__device__ __forceinline__ void imma16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 // D = A*B (accumulator starts at zero).
-__device__ __forceinline__ void mma16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+__device__ __forceinline__ void imma16832_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-// (64+q) halves of the four nibble pairs of a code word.
-//   even0 = nibbles 0,4 (weights 4t, 4t+2 of the even sub-block), even1 = nibbles 2,6 (4t+1, 4t+3)
-//   odd0  = nibbles 1,5 (same weights of the odd sub-block),      odd1  = nibbles 3,7
-// A high nibble (bits 4-7 of a half) dropped into the mantissa of 0x5400 (= 64, ulp 1/16) reads
-// 64+q directly.  A low nibble (bits 0-3) dropped into 0x6400 (= 1024, ulp 1) reads 1024+q; one
-// packed half add of -960 (exact) turns it into 64+q.  The integer pipe is the scarce one in
-// this kernel, so the adds (fma pipe) are cheaper than the shifts they replace.
-__device__ __forceinline__ uint32_t hadd2_bits(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ void decode_word(uint32_t w, uint32_t& even0, uint32_t& even1, uint32_t& odd0,
-                                            uint32_t& odd1) {
-    constexpr uint32_t kLoMask = 0x000F000Fu, kHiMask = 0x00F000F0u;
-    constexpr uint32_t kBase1024 = 0x64006400u, kBase64 = 0x54005400u;
-    constexpr uint32_t kMinus960 = 0xE380E380u;  // -960.0h twice
-    const uint32_t t = w >> 8;
-    even0 = hadd2_bits((w & kLoMask) | kBase1024, kMinus960);
-    odd0 = (w & kHiMask) | kBase64;
-    even1 = hadd2_bits((t & kLoMask) | kBase1024, kMinus960);
-    odd1 = (t & kHiMask) | kBase64;
-}
-
-// Power-of-two scale that brings `amax` to [2^10, 2^11), and its inverse.
-__device__ __forceinline__ void pow2_scale(float amax, float& scale, float& inv) {
-    const uint32_t e = (__float_as_uint(amax) >> 23) & 0xFFu;
-    if (e < 11u || e == 255u) {  // zero, tiny, inf or nan: leave unscaled
+// Scale that maps `amax` to kXiMax (and its inverse): the largest |xi| whose top base-128
+// digit still fits a signed byte, with 32*15*kXiMax < 2^31.
+constexpr float kXiMax = 2080000.f;
+__device__ __forceinline__ void row_scale(float amax, float& scale, float& inv) {
+    if (!(amax > 1e-30f) || !(amax < 3e38f)) {  // zero, tiny, inf or nan: leave unscaled
         scale = 1.f;
         inv = 1.f;
     } else {
-        scale = __uint_as_float((264u - e) << 23);  // 2^(137-e)
-        inv = __uint_as_float((e - 10u) << 23);     // 2^(e-137)
+        scale = kXiMax / amax;
+        inv = amax / kXiMax;
     }
 }
 
-// Split 32 consecutive activations (one sub-block) of one row into halves and
-// store them in the mma-permuted layout; returns sum(xh+xl) over the warp.
-//   layout: [token][group G = k/64][parity][part hi/lo][t][8 halves], 128 B per (token,G,parity)
-//   thread t's 8 halves = x[4t], x[4t+2], x[4t+1], x[4t+3], x[16+4t], x[16+4t+2], x[16+4t+1], x[16+4t+3]
-__device__ __forceinline__ float split_store(float v, uint8_t* frag_base, uint32_t lane) {
-    const __half xh = __float2half_rn(v);
-    const float fh = __half2float(xh);
-    const __half xl = __float2half_rn(v - fh);
-    const uint32_t c = lane >> 4, t = (lane >> 2) & 3u, j = lane & 3u;
-    const uint32_t h = c * 4u + (j & 1u) * 2u + (j >> 1);
-    __half* hi = reinterpret_cast<__half*>(frag_base + t * 16u) + h;
-    hi[0] = xh;
-    hi[32] = xl;  // +64 bytes: the lo part
-    float s = fh + __half2float(xl);
+// Quantise 32 consecutive scaled activations (one sub-block) of one row to 21-bit integers,
+// store their base-128 digits in the mma B layout, return sum(xi) over the warp.
+//   layout per (token, 64-weight group, parity): 128 B = [c: 0,1][t: 0..3][16 B]
+//   16 B of (c, t): c = 0: d0[4t..4t+3], d0[16+4t..], d2[4t..], d2[16+4t..]
+//                   c = 1: d1[4t..4t+3], d1[16+4t..], 0, 0
+// `blk128` may alias the 32 floats being converted (the caller separates reads from writes).
+__device__ __forceinline__ int digits_store(float v, uint8_t* blk128, uint32_t lane) {
+    const float vc = fminf(fmaxf(v, -kXiMax), kXiMax);  // rounding of x*scale can overshoot by an ulp
+    const int xi = __float2int_rn(vc);
+    const int d2 = ((xi + 64) & 127) - 64;
+    const int r1 = (xi - d2) >> 7;
+    const int d1 = ((r1 + 64) & 127) - 64;
+    const int d0 = (r1 - d1) >> 7;
+    const uint32_t half = lane >> 4, t = (lane >> 2) & 3u, j = lane & 3u;
+    int8_t* p = reinterpret_cast<int8_t*>(blk128) + t * 16u + half * 4u + j;
+    p[0] = (int8_t)d0;
+    p[8] = (int8_t)d2;
+    p[64] = (int8_t)d1;
+    p[72] = 0;
+    int s = xi;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
     return s;
@@ -286,15 +270,15 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
             float amax = 0.f;
             for (uint32_t w2 = 0; w2 < nwarps; w2++) amax = fmaxf(amax, red[tok * kMaxWarps + w2]);
             float scale, inv;
-            pow2_scale(amax, scale, inv);
+            row_scale(amax, scale, inv);
             if (tid == 0) invs[tok] = inv;
             uint8_t* base = xf + (uint64_t)tok * K * 4u;
             for (uint32_t sbg = warp; sbg < nsub; sbg += nwarps) {
                 uint8_t* blk128 = base + sbg * 128u;  // == ((tok*NG + G)*2 + parity)*128 with sbg = 2G + parity
                 const float v = reinterpret_cast<const float*>(blk128)[lane] * scale;
                 __syncwarp();  // every lane has read its float before the halves overwrite them
-                const float s = split_store(v, blk128, lane);
-                if (lane == 0) Ss[((tok * nb + (sbg >> 3)) * 2u + (sbg & 1u)) * 4u + ((sbg >> 1) & 3u)] = s;
+                const int s = digits_store(v, blk128, lane);
+                if (lane == 0) Ss[((tok * nb + (sbg >> 3)) * 2u + (sbg & 1u)) * 4u + ((sbg >> 1) & 3u)] = (float)s;
             }
         }
         __syncthreads();
@@ -314,8 +298,9 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
     const uint32_t row_a = M1 ? (lane >> 2) + ((bt >> 1) << 3) : (lane >> 2);
     const uint32_t hdr_off = row_a * a.pitch;
     const uint32_t sel0 = 0x7440u + c_par, sel1 = 0x7442u + c_par;
+    const float par_scale = c_par ? 0.0625f : 1.f;  // odd sub-blocks arrive as 16*q
 
-    // This lane's B data lives at  xbase + ((tok*NG + G)*2 + parity)*128 + part*64 + t*16.
+    // This lane's B data lives at  xbase + ((tok*NG + G)*2 + parity)*128 + c*64 + t*16  (c = n%2).
     // In the mmas of the other parity the lane feeds zeros: it reads the zero block with
     // stride 0 instead.  AddrT is a shared-memory offset, or a global address in XG mode.
     using AddrT = typename std::conditional<XG, uint64_t, uint32_t>::type;
@@ -370,18 +355,19 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
             }
             uint32_t boff = ring + st * a.stage_bytes;
             for (uint32_t blk = bs; PROBE != 1 && blk < bs + nblk; blk++, boff += kBlockBytes) {
-                // scales of this thread's rows, its parity's four sub-blocks
-                float dsc[RPT][4], esc[RPT][4];
+                // scales of this thread's rows, its parity's four sub-blocks; the odd sub-block's
+                // weights reach the mma as 16*q, so its scale carries the 1/16
+                float dsc[RPT][4], dmn[RPT][4];
 #pragma unroll
                 for (int r = 0; r < RPT; r++) {
                     if constexpr (PROBE == 5) {
 #pragma unroll
-                        for (int g = 0; g < 4; g++) dsc[r][g] = 1.f, esc[r][g] = 2.f;
+                        for (int g = 0; g < 4; g++) dsc[r][g] = 1.f, dmn[r][g] = 2.f;
                         continue;
                     }
                     const uint4 hv = lds128<0>(boff + hdr_off + r * 8u * a.pitch);
                     const BlockHeader h{hv.x, hv.y, hv.z, hv.w};
-                    const float d = half_bits_to_float(h.w0), dmin = half_bits_to_float(h.w0 >> 16);
+                    const float d = half_bits_to_float(h.w0) * par_scale, dmin = half_bits_to_float(h.w0 >> 16);
                     uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
                     unpack_scales_packed(h, sc_lo, sc_hi, mn_lo, mn_hi);
                     // d*(2^23+sc) - d*2^23 in one fma: the product is exact inside the fma
@@ -393,8 +379,7 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
 #pragma unroll
                     for (int g = 0; g < 4; g++) {
                         dsc[r][g] = fmaf(d, __uint_as_float(scw[g]), nd);
-                        const float dmn = fmaf(dmin, __uint_as_float(mnw[g]), ndm);
-                        esc[r][g] = fmaf(64.f, dsc[r][g], dmn);
+                        dmn[r][g] = fmaf(dmin, __uint_as_float(mnw[g]), ndm);
                     }
                 }
                 uint4 Sv[NT];
@@ -409,45 +394,47 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
                     constexpr int g = decltype(gc)::value;
                     uint32_t r0, r1, r2, r3;
                     ldmatrix_x4<g * 32>(lm_addr, r0, r1, r2, r3);
-                    uint32_t e0[4], e1[4], o0[4], o1[4];
+                    constexpr uint32_t kLo = 0x0F0F0F0Fu, kHi = 0xF0F0F0F0u;
+                    uint32_t e[4], o[4];
                     if constexpr (PROBE == 4) {
-                        e0[0] = e1[0] = o0[0] = o1[0] = r0;
-                        e0[1] = e1[1] = o0[1] = o1[1] = r1;
-                        e0[2] = e1[2] = o0[2] = o1[2] = r2;
-                        e0[3] = e1[3] = o0[3] = o1[3] = r3;
+                        e[0] = o[0] = r0; e[1] = o[1] = r1; e[2] = o[2] = r2; e[3] = o[3] = r3;
                     } else {
-                        decode_word(r0, e0[0], e1[0], o0[0], o1[0]);
-                        decode_word(r1, e0[1], e1[1], o0[1], o1[1]);
-                        decode_word(r2, e0[2], e1[2], o0[2], o1[2]);
-                        decode_word(r3, e0[3], e1[3], o0[3], o1[3]);
+                        e[0] = r0 & kLo; e[1] = r1 & kLo; e[2] = r2 & kLo; e[3] = r3 & kLo;  // q   (even sub-block)
+                        o[0] = r0 & kHi; o[1] = r1 & kHi; o[2] = r2 & kHi; o[3] = r3 & kHi;  // 16q (odd sub-block)
                     }
 #pragma unroll
                     for (int nt = 0; nt < NT; nt++) {
                         const uint4 qa = load16(pa + (b_par == 0 ? nt * tile_stride : 0u), std::integral_constant<int, g * 256>{});
                         const uint4 qb = load16(pb + (b_par == 1 ? nt * tile_stride : 0u), std::integral_constant<int, g * 256>{});
-                        float cfr[4];
+                        int c01[4], c2[4];  // column pair = digits (d0, d1) resp. (d2, 0)
                         if constexpr (PROBE == 3) {
-                            cfr[0] = __uint_as_float(e0[0] ^ e1[1] ^ o0[2] ^ o1[3] ^ qa.x ^ qb.y);
-                            cfr[1] = __uint_as_float(e0[1] ^ e1[2] ^ o0[3] ^ o1[0] ^ qa.y ^ qb.z);
-                            cfr[2] = __uint_as_float(e0[2] ^ e1[3] ^ o0[0] ^ o1[1] ^ qa.z ^ qb.w);
-                            cfr[3] = __uint_as_float(e0[3] ^ e1[0] ^ o0[1] ^ o1[2] ^ qa.w ^ qb.x);
+                            c01[0] = e[0] ^ o[1] ^ qa.x ^ qb.y; c01[1] = e[1] ^ o[2] ^ qa.y ^ qb.z;
+                            c01[2] = e[2] ^ o[3] ^ qa.z ^ qb.w; c01[3] = e[3] ^ o[0] ^ qa.w ^ qb.x;
+                            c2[0] = c01[1]; c2[2] = c01[3];
                         } else {
-                            mma16816_first(cfr, e0[0], e0[1], e1[0], e1[1], qa.x, qa.y);  // even sub-block, code bytes 0-15
-                            mma16816(cfr, e0[2], e0[3], e1[2], e1[3], qa.z, qa.w);        // even sub-block, code bytes 16-31
-                            mma16816(cfr, o0[0], o0[1], o1[0], o1[1], qb.x, qb.y);        // odd sub-block
-                            mma16816(cfr, o0[2], o0[3], o1[2], o1[3], qb.z, qb.w);
+                            imma16832_first(c01, e[0], e[1], e[2], e[3], qa.x, qa.y);
+                            imma16832_first(c2, e[0], e[1], e[2], e[3], qa.z, qa.w);
+                            imma16832(c01, o[0], o[1], o[2], o[3], qb.x, qb.y);
+                            imma16832(c2, o[0], o[1], o[2], o[3], qb.z, qb.w);
                         }
                         const uint32_t sbits = g == 0 ? Sv[nt].x : g == 1 ? Sv[nt].y : g == 2 ? Sv[nt].z : Sv[nt].w;
                         const float Sg = __uint_as_float(sbits);
+                        // T = 2^14*sum(a d0) + (2^7*sum(a d1) + sum(a d2)) with a = q or 16q.  The
+                        // bracket fits int32 (< 2^26); the whole of T need not (16q weights), so
+                        // the top digit joins in float: its sum (< 2^19) times 2^14 is exact.
+                        const int u_lo = c01[1] * 128 + c2[0], u_hi = c01[3] * 128 + c2[2];  // rows r, r+8
                         if constexpr (M1) {
-                            const float v = (bt & 2u) ? (cfr[2] + cfr[3]) : (cfr[0] + cfr[1]);
+                            const bool hi = (bt & 2u) != 0;
+                            const float v = fmaf((float)(hi ? c01[2] : c01[0]), 16384.f, (float)(hi ? u_hi : u_lo));
                             acc[nt][0] = fmaf(dsc[0][g], v, acc[nt][0]);
-                            acc[nt][0] = fmaf(-esc[0][g], Sg, acc[nt][0]);
+                            acc[nt][0] = fmaf(-dmn[0][g], Sg, acc[nt][0]);
                         } else {
-                            acc[nt][0] = fmaf(dsc[0][g], cfr[0] + cfr[1], acc[nt][0]);
-                            acc[nt][0] = fmaf(-esc[0][g], Sg, acc[nt][0]);
-                            acc[nt][1] = fmaf(dsc[1][g], cfr[2] + cfr[3], acc[nt][1]);
-                            acc[nt][1] = fmaf(-esc[1][g], Sg, acc[nt][1]);
+                            const float v_lo = fmaf((float)c01[0], 16384.f, (float)u_lo);
+                            const float v_hi = fmaf((float)c01[2], 16384.f, (float)u_hi);
+                            acc[nt][0] = fmaf(dsc[0][g], v_lo, acc[nt][0]);
+                            acc[nt][0] = fmaf(-dmn[0][g], Sg, acc[nt][0]);
+                            acc[nt][1] = fmaf(dsc[1][g], v_hi, acc[nt][1]);
+                            acc[nt][1] = fmaf(-dmn[1][g], Sg, acc[nt][1]);
                         }
                     }
                 };
@@ -526,12 +513,12 @@ __global__ void __launch_bounds__(1024) split_activations_kernel(const float* __
     amax = 0.f;
     for (uint32_t w2 = 0; w2 < nwarps; w2++) amax = fmaxf(amax, red[w2]);
     float scale, inv;
-    pow2_scale(amax, scale, inv);
+    row_scale(amax, scale, inv);
     for (uint32_t sbg = warp; sbg < nsub; sbg += nwarps) {
         const float v = tok < M ? __ldg(X + (uint64_t)tok * K + sbg * 32u + lane) * scale : 0.f;
         const uint32_t G = sbg >> 1, par = sbg & 1u;
-        const float s = split_store(v, xf + ((uint64_t)(tok * NG + G) * 2u + par) * 128u, lane);
-        if (lane == 0) S[((uint64_t)(tok * nb + (sbg >> 3)) * 2u + par) * 4u + ((sbg >> 1) & 3u)] = s;
+        const int s = digits_store(v, xf + ((uint64_t)(tok * NG + G) * 2u + par) * 128u, lane);
+        if (lane == 0) S[((uint64_t)(tok * nb + (sbg >> 3)) * 2u + par) * 4u + ((sbg >> 1) & 3u)] = (float)s;
     }
     if (tid == 0) inv_out[tok] = inv;
 }

@@ -187,7 +187,8 @@ def test_matmul_linearity_full_size(ctx, variant):
     y12 = ctx.matmul(0.5 * x1 + x2, w).double()
     ctx.set_option(q4k.OPT_GEMV_VARIANT, q4k.GEMV_AUTO)
     err = (y12 - (0.5 * y1 + y2)).abs().max().item()
-    assert err <= 2e-3, err
+    # three evaluations, each within a few 1e-4 of exact at |y| ~ 250: a quarter of the 2e-2 bound
+    assert err <= 5e-3, err
     # and the output equals X . dequant(W)^T computed from the library's own bit-exact dequant
     deq = ctx.dequant(w).double()
     ref = x1.double() @ deq.T
