@@ -246,6 +246,9 @@ int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
         case BPQ4K_OPT_STREAM_FORCE_SCRATCH:
             h->tune.force_scratch = value ? 1u : 0u;
             return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_NO_PDL:
+            h->tune.no_pdl = value ? 1u : 0u;
+            return BPQ4K_OK;
 #ifdef BPQ4K_ENABLE_PROBES
         case 99:
             h->tune.probe = (uint32_t)value;
@@ -267,6 +270,7 @@ int bpq4k_get_option(bpq4k_handle_t h, int option, int* value) {
         case BPQ4K_OPT_STREAM_STAGES: *value = (int)h->tune.stages; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_CTAS_PER_SM: *value = (int)h->tune.ctas_per_sm; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_FORCE_SCRATCH: *value = (int)h->tune.force_scratch; return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_NO_PDL: *value = (int)h->tune.no_pdl; return BPQ4K_OK;
         default: return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown option %d", option);
     }
 }

@@ -37,6 +37,7 @@ struct StreamTuning {
     uint32_t stages = 0;       // ring depth per warp
     uint32_t ctas_per_sm = 0;  // cap on resident CTAs per SM
     uint32_t force_scratch = 0;  // 1: always split activations into global scratch first
+    uint32_t no_pdl = 0;       // 1: launch without programmatic dependent launch
     uint32_t probe = 0;        // development builds only: time-attribution variants of the kernel
 };
 

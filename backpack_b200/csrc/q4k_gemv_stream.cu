@@ -64,12 +64,11 @@ struct StreamArgs {
     CUtensorMap tmap;  // W as a 2-D tensor [rows][row words], box = 16 rows x cb blocks
     MatmulArgs m;
     uint32_t wk, wt, cb, stages, pitch, stage_bytes, ntiles, tokens;
-    uint32_t off_zero, off_red, off_inv, off_S, off_x, off_part, off_ring;
+    uint32_t off_zero, off_S, off_x, off_part, off_ring;
     int* status;
-    // activations prepared by split_activations_kernel (XG mode)
+    // activations prepared by quantize_activations_kernel (XG mode)
     const uint8_t* xfrag_g;
     const float* S_g;
-    const float* inv_g;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -133,49 +132,82 @@ __device__ __forceinline__ void imma16832_first(int (&c)[4], uint32_t a0, uint32
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-// Scale that maps `amax` to kXiMax (and its inverse): the largest |xi| whose top base-128
-// digit still fits a signed byte, with 32*15*kXiMax < 2^31.
+// Largest |xi|: its top base-128 digit still fits a signed byte.
 constexpr float kXiMax = 2080000.f;
-__device__ __forceinline__ void row_scale(float amax, float& scale, float& inv) {
-    if (!(amax > 1e-30f) || !(amax < 3e38f)) {  // zero, tiny, inf or nan: leave unscaled
-        scale = 1.f;
-        inv = 1.f;
-    } else {
+
+// Quantise the activations.  Work item `item` covers 8 consecutive floats of row `tok`; the four
+// items of a 32-float sub-block sit in four adjacent lanes, which agree on the sub-block's
+// max|x| with two shuffles.  Each sub-block gets its own scale kXiMax/max|x| (block floating
+// point), xi = rint(x*scale), and the three base-128 digits of xi are stored in the mma B
+// layout:
+//   per (token, 64-weight group G, parity): 128 B = [c: 0,1][t: 0..3][16 B]
+//   16 B of (c, t): c = 0: d0[4t..4t+3], d0[16+4t..], d2[4t..], d2[16+4t..]
+//                   c = 1: d1[4t..4t+3], d1[16+4t..], 0, 0
+// and per sub-block the two floats the kernel needs: inv = max|x|/kXiMax and sum(xi)*inv,
+//   SI[((tok*nb + blk)*2 + parity)*8 + {0: sum*inv, 4: inv} + g].
+// All 32 lanes of a warp must call this together (idle lanes pass valid = false).
+__device__ __forceinline__ void quantize_item(const float* __restrict__ X, uint32_t M, uint32_t K, uint32_t tok,
+                                              uint32_t c8, bool valid, uint8_t* frag, float* SI) {
+    float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+    if (valid && tok < M) {
+        const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok * K + (uint64_t)c8 * 8u);
+        v0 = __ldg(xp);
+        v1 = __ldg(xp + 1);
+    }
+    float amax = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
+                       fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    float scale = 1.f, inv = 1.f;
+    if (amax > 1e-30f && amax < 3e38f) {  // zero, tiny, inf or nan: leave unscaled
         scale = kXiMax / amax;
         inv = amax / kXiMax;
     }
-}
-
-// Quantise 32 consecutive scaled activations (one sub-block) of one row to 21-bit integers,
-// store their base-128 digits in the mma B layout, return sum(xi) over the warp.
-//   layout per (token, 64-weight group, parity): 128 B = [c: 0,1][t: 0..3][16 B]
-//   16 B of (c, t): c = 0: d0[4t..4t+3], d0[16+4t..], d2[4t..], d2[16+4t..]
-//                   c = 1: d1[4t..4t+3], d1[16+4t..], 0, 0
-// `blk128` may alias the 32 floats being converted (the caller separates reads from writes).
-__device__ __forceinline__ int digits_store(float v, uint8_t* blk128, uint32_t lane) {
-    const float vc = fminf(fmaxf(v, -kXiMax), kXiMax);  // rounding of x*scale can overshoot by an ulp
-    const int xi = __float2int_rn(vc);
-    const int d2 = ((xi + 64) & 127) - 64;
-    const int r1 = (xi - d2) >> 7;
-    const int d1 = ((r1 + 64) & 127) - 64;
-    const int d0 = (r1 - d1) >> 7;
-    const uint32_t half = lane >> 4, t = (lane >> 2) & 3u, j = lane & 3u;
-    int8_t* p = reinterpret_cast<int8_t*>(blk128) + t * 16u + half * 4u + j;
-    p[0] = (int8_t)d0;
-    p[8] = (int8_t)d2;
-    p[64] = (int8_t)d1;
-    p[72] = 0;
-    int s = xi;
+    const float xs[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    uint32_t w0[2] = {0, 0}, w1[2] = {0, 0}, w2[2] = {0, 0};
+    int sum = 0;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
-    return s;
+    for (int i = 0; i < 8; i++) {
+        const float vc = fminf(fmaxf(xs[i] * scale, -kXiMax), kXiMax);  // x*scale may overshoot by an ulp
+        const int xi = __float2int_rn(vc);
+        const int d2 = ((xi + 64) & 127) - 64;
+        const int r1 = (xi - d2) >> 7;
+        const int d1 = ((r1 + 64) & 127) - 64;
+        const int d0 = (r1 - d1) >> 7;
+        sum += xi;
+        w0[i >> 2] |= (uint32_t)(d0 & 255) << (8 * (i & 3));
+        w1[i >> 2] |= (uint32_t)(d1 & 255) << (8 * (i & 3));
+        w2[i >> 2] |= (uint32_t)(d2 & 255) << (8 * (i & 3));
+    }
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    if (!valid) return;
+    const uint32_t nb = K / kQK, NG = K / 64u;
+    const uint32_t sbg = c8 >> 2, j8 = c8 & 3u;  // sub-block in the row, 8-float piece in the sub-block
+    const uint32_t G = sbg >> 1, par = sbg & 1u;
+    uint8_t* base = frag + ((uint64_t)(tok * NG + G) * 2u + par) * 128u;
+    const uint32_t half = j8 >> 1;  // k < 16 -> first word pair (b0), else second (b1)
+#pragma unroll
+    for (int m2 = 0; m2 < 2; m2++) {
+        const uint32_t t = 2u * (j8 & 1u) + m2;
+        uint32_t* p = reinterpret_cast<uint32_t*>(base + t * 16u + half * 4u);
+        p[0] = w0[m2];    // c = 0: d0
+        p[2] = w2[m2];    //        d2
+        p[16] = w1[m2];   // c = 1: d1
+        p[18] = 0u;       //        zeros
+    }
+    if (j8 == 0) {
+        float* si = SI + ((uint64_t)(tok * nb + (sbg >> 3)) * 2u + par) * 8u + ((sbg >> 1) & 3u);
+        si[0] = (float)sum * inv;
+        si[4] = inv;
+    }
 }
 
 // PROBE (development builds only, -DBPQ4K_ENABLE_PROBES): 0 = the kernel; 1 = copies and waits
 // only; 2 = math on whatever the ring holds, no copies; 3 = as 2 without the mmas; 4 = as 2
 // without the nibble decode; 5 = as 2 without the scale decode.  Used to attribute time.
 template <int NT, bool M1, bool XG, int PROBE = 0>
-__global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
+__global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TOK = M1 ? 1 : NT * 2;  // token slots
     constexpr int RPT = M1 ? 1 : 2;       // rows post-processed per thread
@@ -233,53 +265,25 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
         const uint32_t pre = min(a.stages, total_units);
         for (uint32_t i = 0; i < pre; i++) issue_next();
     }
+    // Programmatic dependent launch: everything above touches only this CTA's shared memory
+    // and READS the weights, so it may overlap the tail of the preceding kernel in the stream.
+    // Let the next kernel start its own prologue, then wait for the preceding kernel (which may
+    // have produced X, or may still read Y) before reading X or writing anything.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    // ---- activations: split into scaled half pairs, once per CTA ---------------
+    // ---- activations: quantise to base-128 digits, once per CTA ---------------------
     const uint32_t NG = K / 64u;
-    float* invs = reinterpret_cast<float*>(smem + a.off_inv);
     if constexpr (!XG) {
-        // Pass 1: copy the raw floats into the fragment region (a sub-block's 32 floats occupy
-        // exactly the 128 bytes its hi/lo halves will) and find max|x| per row.  All global
-        // loads of a thread are independent, so their latencies overlap.
-        // Pass 2: convert in place from shared memory; no global latency on this path.
-        float* red = reinterpret_cast<float*>(smem + a.off_red);
-        float* Ss = reinterpret_cast<float*>(smem + a.off_S);
-        uint8_t* xf = smem + a.off_x;
+        // one pass: every thread quantises 8-float items straight from global memory
         for (uint32_t i = tid; i < kZeroBytes / 4u; i += blockDim.x) reinterpret_cast<uint32_t*>(smem + a.off_zero)[i] = 0u;
-        for (int tok = 0; tok < TOK; tok++) {
-            float amax = 0.f;
-            float4* dst = reinterpret_cast<float4*>(xf + (uint64_t)tok * K * 4u);
-            if ((uint32_t)tok < M) {
-                const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok * K);
-#pragma unroll 4
-                for (uint32_t i = tid; i < K / 4u; i += blockDim.x) {
-                    const float4 v = __ldg(xp + i);
-                    dst[i] = v;
-                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-                }
-            } else {
-                for (uint32_t i = tid; i < K / 4u; i += blockDim.x) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-            if (lane == 0) red[tok * kMaxWarps + warp] = amax;
-        }
-        __syncthreads();
-        const uint32_t nsub = K / 32u;
-        for (uint32_t tok = 0; tok < (uint32_t)TOK; tok++) {
-            float amax = 0.f;
-            for (uint32_t w2 = 0; w2 < nwarps; w2++) amax = fmaxf(amax, red[tok * kMaxWarps + w2]);
-            float scale, inv;
-            row_scale(amax, scale, inv);
-            if (tid == 0) invs[tok] = inv;
-            uint8_t* base = xf + (uint64_t)tok * K * 4u;
-            for (uint32_t sbg = warp; sbg < nsub; sbg += nwarps) {
-                uint8_t* blk128 = base + sbg * 128u;  // == ((tok*NG + G)*2 + parity)*128 with sbg = 2G + parity
-                const float v = reinterpret_cast<const float*>(blk128)[lane] * scale;
-                __syncwarp();  // every lane has read its float before the halves overwrite them
-                const int s = digits_store(v, blk128, lane);
-                if (lane == 0) Ss[((tok * nb + (sbg >> 3)) * 2u + (sbg & 1u)) * 4u + ((sbg >> 1) & 3u)] = (float)s;
-            }
+        const uint32_t per_row = K / 8u, items = (uint32_t)TOK * per_row;
+        for (uint32_t base = 0; base < items; base += blockDim.x) {
+            const uint32_t it = base + tid;
+            const bool valid = it < items;
+            const uint32_t tok = valid ? it / per_row : 0u;
+            quantize_item(X, M, K, tok, valid ? it - tok * per_row : 0u, valid, smem + a.off_x,
+                          reinterpret_cast<float*>(smem + a.off_S));
         }
         __syncthreads();
     }
@@ -320,7 +324,7 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
     const uint32_t stride_a = b_par == 0 ? 256u : 0u;  // per 64-weight group
     const uint32_t stride_b = b_par == 1 ? 256u : 0u;
     const uint32_t tile_stride = 2u * NG * 256u;       // per n-tile (two tokens)
-    const AddrT s0_addr = s_addr + (AddrT)(c_tok * nb) * 32u + c_par * 16u;  // + blk*32 (+ nt*2*nb*32)
+    const AddrT s0_addr = s_addr + (AddrT)(c_tok * nb) * 64u + c_par * 32u;  // + blk*64 (+ nt*2*nb*64)
     // 16-byte load at addr + OFF (OFF is folded into the instruction)
     auto load16 = [&](AddrT addr, auto off_tag) -> uint4 {
         constexpr int OFF = decltype(off_tag)::value;
@@ -382,10 +386,12 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
                         dmn[r][g] = fmaf(dmin, __uint_as_float(mnw[g]), ndm);
                     }
                 }
-                uint4 Sv[NT];
+                uint4 Sv[NT], Iv[NT];  // per group: sum(xi)*inv and inv of this parity's sub-block
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++)
-                    Sv[nt] = load16(s0_addr + (AddrT)(nt * 2u * nb + blk) * 32u, std::integral_constant<int, 0>{});
+                for (int nt = 0; nt < NT; nt++) {
+                    Sv[nt] = load16(s0_addr + (AddrT)(nt * 2u * nb + blk) * 64u, std::integral_constant<int, 0>{});
+                    Iv[nt] = load16(s0_addr + (AddrT)(nt * 2u * nb + blk) * 64u, std::integral_constant<int, 16>{});
+                }
                 // data lanes advance 1 KiB per block (4 groups x 256 B); zero lanes stay inside the
                 // 1 KiB zero region, so the per-group offset g*256 is an immediate for both
                 const AddrT pa = pa0 + blk * 4u * stride_a, pb = pb0 + blk * 4u * stride_b;
@@ -419,18 +425,19 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
                         }
                         const uint32_t sbits = g == 0 ? Sv[nt].x : g == 1 ? Sv[nt].y : g == 2 ? Sv[nt].z : Sv[nt].w;
                         const float Sg = __uint_as_float(sbits);
+                        const float Ig = __uint_as_float(g == 0 ? Iv[nt].x : g == 1 ? Iv[nt].y : g == 2 ? Iv[nt].z : Iv[nt].w);
                         // T = 2^14*sum(a d0) + (2^7*sum(a d1) + sum(a d2)) with a = q or 16q.  The
                         // bracket fits int32 (< 2^26); the whole of T need not (16q weights), so
                         // the top digit joins in float: its sum (< 2^19) times 2^14 is exact.
                         const int u_lo = c01[1] * 128 + c2[0], u_hi = c01[3] * 128 + c2[2];  // rows r, r+8
                         if constexpr (M1) {
                             const bool hi = (bt & 2u) != 0;
-                            const float v = fmaf((float)(hi ? c01[2] : c01[0]), 16384.f, (float)(hi ? u_hi : u_lo));
+                            const float v = fmaf((float)(hi ? c01[2] : c01[0]), 16384.f, (float)(hi ? u_hi : u_lo)) * Ig;
                             acc[nt][0] = fmaf(dsc[0][g], v, acc[nt][0]);
                             acc[nt][0] = fmaf(-dmn[0][g], Sg, acc[nt][0]);
                         } else {
-                            const float v_lo = fmaf((float)c01[0], 16384.f, (float)u_lo);
-                            const float v_hi = fmaf((float)c01[2], 16384.f, (float)u_hi);
+                            const float v_lo = fmaf((float)c01[0], 16384.f, (float)u_lo) * Ig;
+                            const float v_hi = fmaf((float)c01[2], 16384.f, (float)u_hi) * Ig;
                             acc[nt][0] = fmaf(dsc[0][g], v_lo, acc[nt][0]);
                             acc[nt][0] = fmaf(-dmn[0][g], Sg, acc[nt][0]);
                             acc[nt][1] = fmaf(dsc[1][g], v_hi, acc[nt][1]);
@@ -476,8 +483,7 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
                 if (tok < M && row < N) {
                     float s = 0.f;
                     for (uint32_t k2 = 0; k2 < a.wk; k2++) s += gbuf[(uint64_t)k2 * (TOK * 16u) + idx];
-                    const float inv = XG ? a.inv_g[tok] : invs[tok];
-                    Y[(uint64_t)tok * N + row] = fmaf(s, inv, a.m.bias ? a.m.bias[row] : 0.f);
+                    Y[(uint64_t)tok * N + row] = s + (a.m.bias ? a.m.bias[row] : 0.f);
                 }
             }
         }
@@ -485,49 +491,30 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const __grid_consta
 }
 
 // ---------------------------------------------------------------------------
-// XG mode: split the activations once per call into global scratch, in the same
-// permuted layout the kernel above keeps in shared memory.  One CTA per row.
-// Scratch layout: [1 KiB zeros][xfrag: tokens*K*4 B][S: tokens*(K/32) floats][inv: tokens floats]
+// XG mode: quantise the activations once per call into global scratch, in the same layout
+// the kernel above keeps in shared memory.
+// Scratch layout: [1 KiB zeros][digits: tokens*K*4 B][SI: tokens*(K/32)*2 floats]
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) split_activations_kernel(const float* __restrict__ X, uint32_t M, uint32_t K,
-                                                                 uint32_t tokens, uint8_t* __restrict__ scratch) {
-    __shared__ float red[32];
-    const uint32_t tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t nwarps = blockDim.x >> 5, nb = K / kQK, NG = K / 64u, nsub = K / 32u;
-    uint8_t* xf = scratch + kZeroBytes;
-    float* S = reinterpret_cast<float*>(xf + (uint64_t)tokens * K * 4u);
-    float* inv_out = S + (uint64_t)tokens * nsub;
-    if (tok == 0 && tid < kZeroBytes / 4u) reinterpret_cast<uint32_t*>(scratch)[tid] = 0u;
-    float amax = 0.f;
-    if (tok < M) {
-        const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok * K);
-        for (uint32_t i = tid; i < K / 4u; i += blockDim.x) {
-            const float4 v = __ldg(xp + i);
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-        }
+__global__ void __launch_bounds__(256) quantize_activations_kernel(const float* __restrict__ X, uint32_t M, uint32_t K,
+                                                                   uint32_t tokens, uint8_t* __restrict__ scratch) {
+    uint8_t* frag = scratch + kZeroBytes;
+    float* SI = reinterpret_cast<float*>(frag + (uint64_t)tokens * K * 4u);
+    const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (gtid < kZeroBytes / 4u) reinterpret_cast<uint32_t*>(scratch)[gtid] = 0u;
+    const uint32_t per_row = K / 8u, items = tokens * per_row;
+    for (uint32_t base = blockIdx.x * blockDim.x; base < items; base += gridDim.x * blockDim.x) {
+        const uint32_t it = base + threadIdx.x;
+        const bool valid = it < items;
+        const uint32_t tok = valid ? it / per_row : 0u;
+        quantize_item(X, M, K, tok, valid ? it - tok * per_row : 0u, valid, frag, SI);
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    if (lane == 0) red[warp] = amax;
-    __syncthreads();
-    amax = 0.f;
-    for (uint32_t w2 = 0; w2 < nwarps; w2++) amax = fmaxf(amax, red[w2]);
-    float scale, inv;
-    row_scale(amax, scale, inv);
-    for (uint32_t sbg = warp; sbg < nsub; sbg += nwarps) {
-        const float v = tok < M ? __ldg(X + (uint64_t)tok * K + sbg * 32u + lane) * scale : 0.f;
-        const uint32_t G = sbg >> 1, par = sbg & 1u;
-        const int s = digits_store(v, xf + ((uint64_t)(tok * NG + G) * 2u + par) * 128u, lane);
-        if (lane == 0) S[((uint64_t)(tok * nb + (sbg >> 3)) * 2u + par) * 4u + ((sbg >> 1) & 3u)] = (float)s;
-    }
-    if (tid == 0) inv_out[tok] = inv;
 }
 
 // Launch one instantiation.  The grid is persistent: at most as many CTAs as can be
 // resident at once (occupancy query, cached), never more than there are tile groups.
 template <int NT, bool M1, bool XG, int PROBE = 0>
 cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, uint32_t threads, size_t smem,
-                       int sm_count, uint32_t ctas_per_sm_override, cudaStream_t stream) {
+                       int sm_count, uint32_t ctas_per_sm_override, bool pdl, cudaStream_t stream) {
     struct Cache { int dev = -1; size_t smem_cfg = 0; uint32_t threads = 0; size_t smem = 0; int occ = 0; };
     static Cache cache;
     int dev = 0;
@@ -556,8 +543,17 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     if ((uint64_t)gx * slots_y > cap) gx = (uint32_t)((cap + slots_y - 1) / slots_y);
     if (gx == 0) gx = 1;
     if (gx > groups) gx = groups;
-    gemv_stream_kernel<NT, M1, XG, PROBE><<<dim3(gx, slots_y), threads, smem, stream>>>(sa);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(gx, slots_y);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, PROBE>, sa);
 }
 
 static_assert(sizeof(CUtensorMap) == 128, "TmapCache::Entry::map must hold a CUtensorMap");
@@ -585,7 +581,7 @@ EncodeTiledFn encode_tiled_fn() {
 
 size_t gemv_stream_scratch_bytes(uint32_t M, uint32_t K) {
     const uint32_t tokens = M <= 1 ? 1 : (M + 1) / 2 * 2;
-    return kZeroBytes + (size_t)tokens * K * 4 + (size_t)tokens * (K / 32) * 4 + (size_t)tokens * 4 + 256;
+    return kZeroBytes + (size_t)tokens * K * 4 + (size_t)tokens * (K / 32) * 8 + 256;
 }
 
 cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, void* scratch, size_t scratch_bytes,
@@ -603,15 +599,12 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
 
     // ---- plan ------------------------------------------------------------------
     constexpr uint32_t kSmemMax = 227 * 1024;
-    uint32_t warps = tune.warps ? tune.warps : 16;
-    uint32_t wk = tune.wk;
-    if (!wk) {
-        // smallest K split that still gives every warp of the machine a tile slice
-        const uint64_t want = (uint64_t)sm_count * warps * (indirect ? 1 : 1);
-        const uint64_t tiles_total = (uint64_t)ntiles * (indirect ? m.n_slots : 1);
-        wk = 1;
-        while (wk < warps && wk * 2 <= nb && tiles_total * wk < want) wk *= 2;
-    }
+    // Defaults from tuning sweeps on B200 (Llama-3 shapes): 12 warps, K split 6 ways, stages of
+    // 3 blocks, 4 deep; problems with fewer tiles than SMs spread every tile over a whole CTA.
+    const bool tiny = (uint64_t)ntiles * (indirect ? m.n_slots : 1) < (uint64_t)sm_count;
+    uint32_t warps = tune.warps ? tune.warps : (m1 ? (tiny ? 16 : 12) : 8);
+    if (!m1 && warps > 8) warps = 8;  // the multi-row kernels are built for 256 threads (more registers each)
+    uint32_t wk = tune.wk ? tune.wk : (tiny ? warps : (m1 ? 6 : 4));
     if (wk > nb) wk = nb;
     if (wk > warps) wk = warps;
     while (warps % wk) wk--;  // wk must divide the warp count
@@ -619,17 +612,15 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     if (wk > 1 && wt > 15) wt = 15, warps = wt * wk;  // named barrier ids 1..15
     // Stage = dense TMA box of 16 rows x cb blocks.  An odd cb keeps the 16-byte units of
     // the eight rows an ldmatrix touches in distinct bank groups (row pitch = cb*9 units).
-    uint32_t cb = tune.cb ? tune.cb : 1;
+    uint32_t cb = tune.cb ? tune.cb : (tiny ? 1 : 3);
     if (cb > 7) cb = 7;  // box width <= 256 words
     const uint32_t pitch = cb * kBlockBytes;
     const uint32_t stage_bytes = 16 * pitch;
 
-    const uint32_t x_bytes = tokens * m.K * 4u, S_bytes = tokens * (m.K / 32u) * 4u;
+    const uint32_t x_bytes = tokens * m.K * 4u, S_bytes = tokens * (m.K / 32u) * 8u;
     auto layout = [&](bool xg, uint32_t stages, StreamArgs& sa) -> uint32_t {
         uint32_t off = kBarBytes;
         sa.off_zero = off; off += kZeroBytes;
-        sa.off_red = off; off += tokens * kMaxWarps * 4u;
-        sa.off_inv = off; off += align_up(tokens * 4u, 16);
         sa.off_S = off; off += xg ? 0 : align_up(S_bytes, 16);
         sa.off_x = align_up(off, 128); off = sa.off_x + (xg ? 0 : x_bytes);
         sa.off_part = align_up(off, 16); off = sa.off_part + 2u * warps * tokens * 16u * 4u;
@@ -641,7 +632,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     sa.m.M = M;
     // activations in shared memory if they leave room for at least 3 stages per warp
     bool xg = false;
-    uint32_t stages = tune.stages ? tune.stages : 4;
+    uint32_t stages = tune.stages ? tune.stages : (tiny ? 2 : 4);
     if (stages > kMaxStages) stages = kMaxStages;
     if (tune.force_scratch) xg = true;
     if (!xg) {
@@ -695,11 +686,13 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
 
     if (xg) {
         uint8_t* sc = static_cast<uint8_t*>(scratch);
-        split_activations_kernel<<<tokens, 1024, 0, stream>>>(m.X, M, m.K, tokens, sc);
+        const uint32_t items = tokens * (m.K / 8u);
+        uint32_t qgrid = (items + 255) / 256;
+        if (qgrid < 4) qgrid = 4;  // the first 256 threads also clear the zero region
+        quantize_activations_kernel<<<qgrid, 256, 0, stream>>>(m.X, M, m.K, tokens, sc);
         if (launches) ++*launches;
         sa.xfrag_g = sc;
         sa.S_g = reinterpret_cast<const float*>(sc + kZeroBytes + (size_t)tokens * m.K * 4u);
-        sa.inv_g = sa.S_g + (size_t)tokens * (m.K / 32u);
     }
 
     cudaError_t e = cudaSuccess;
@@ -714,9 +707,9 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         }
         const uint32_t threads = warps * 32;
 #define BPQ4K_LAUNCH(NT_, M1_, XG_) \
-    launch_one<NT_, M1_, XG_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, stream)
+    launch_one<NT_, M1_, XG_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream)
 #ifdef BPQ4K_ENABLE_PROBES
-#define BPQ4K_PROBE(P_) launch_one<1, true, false, P_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, stream)
+#define BPQ4K_PROBE(P_) launch_one<1, true, false, P_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream)
         if (m1 && !xg && tune.probe) {
             switch (tune.probe) {
                 case 1: e = BPQ4K_PROBE(1); break;

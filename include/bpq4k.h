@@ -72,7 +72,12 @@ typedef enum bpq4k_option {
     BPQ4K_OPT_STREAM_STAGE_BLOCKS = 12,  /* super-blocks per ring stage */
     BPQ4K_OPT_STREAM_STAGES = 13,        /* ring depth per warp, <= 8 */
     BPQ4K_OPT_STREAM_CTAS_PER_SM = 14,   /* cap on resident CTAs per SM */
-    BPQ4K_OPT_STREAM_FORCE_SCRATCH = 15  /* 1: split activations into global scratch even if they fit on chip */
+    BPQ4K_OPT_STREAM_FORCE_SCRATCH = 15, /* 1: split activations into global scratch even if they fit on chip */
+    /* The streaming kernel is launched with programmatic dependent launch: it prefetches
+     * WEIGHTS while the preceding kernel of the stream drains, and reads X / writes Y only
+     * after that kernel has completed.  Set to 1 if a preceding kernel in the same stream
+     * writes the weight buffer itself. */
+    BPQ4K_OPT_STREAM_NO_PDL = 16
 } bpq4k_option;
 
 typedef enum bpq4k_gemv_variant {
