@@ -61,9 +61,10 @@ constexpr uint32_t kWaitPolls = 1u << 22;                    // bounded mbarrier
 constexpr uint32_t kZeroBytes = 1024;  // zero region the "other parity" lanes read their B operand from
 
 struct StreamArgs {
-    CUtensorMap tmap;  // W as a 2-D tensor [rows][row words], box = 16 rows x cb blocks
+    CUtensorMap tmap;      // W as a 2-D tensor [rows][row words], box = 16 rows x cb blocks
+    CUtensorMap tmap_rem;  // same tensor, box = 16 rows x rem blocks (tail of a warp's K range)
     MatmulArgs m;
-    uint32_t wk, wt, cb, stages, pitch, stage_bytes, ntiles, tokens;
+    uint32_t wk, wt, cb, rem, bpw, stages, stage_bytes, ntiles, tokens;  // bpw: blocks per warp per tile
     uint32_t off_zero, off_S, off_x, off_part, off_ring;
     int* status;
     // activations prepared by quantize_activations_kernel (XG mode)
@@ -216,8 +217,10 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
     const uint32_t nwarps = blockDim.x >> 5;
     const uint32_t wk = warp % a.wk, wt = warp / a.wk;
     const uint32_t K = a.m.K, N = a.m.N, nb = K / kQK;
-    const uint32_t b0 = (uint32_t)((uint64_t)nb * wk / a.wk), b1 = (uint32_t)((uint64_t)nb * (wk + 1) / a.wk);
-    const uint32_t nchunks = (b1 - b0 + a.cb - 1) / a.cb;
+    // every warp of a tile takes the same number of blocks: full stages of cb, then one of rem
+    const uint32_t b0 = wk * a.bpw;
+    const uint32_t nfull = a.bpw / a.cb;
+    const uint32_t nchunks = nfull + (a.rem ? 1u : 0u);
 
     // problem selection (indirect form: blockIdx.y is the slot)
     const float* X = a.m.X;
@@ -251,8 +254,9 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
     auto issue_next = [&]() {
         if (lane == 0) {
             const uint32_t bar = bar0 + iss_st * 8u;
-            mbar_expect_tx(bar, a.stage_bytes);
-            tma_load_2d(ring + iss_st * a.stage_bytes, &a.tmap, (b0 + iss_c * a.cb) * kBlockWords,
+            const bool full = iss_c < nfull;
+            mbar_expect_tx(bar, 16u * kBlockBytes * (full ? a.cb : a.rem));
+            tma_load_2d(ring + iss_st * a.stage_bytes, full ? &a.tmap : &a.tmap_rem, (b0 + iss_c * a.cb) * kBlockWords,
                         (uint32_t)wrow0 + iss_tile * 16u, bar);
         }
         if (++iss_st == a.stages) iss_st = 0;
@@ -291,7 +295,8 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
     // ---- per-lane constants ----------------------------------------------------
     // ldmatrix row addresses: lanes 0-7 rows 0-7 bytes [0,16), 8-15 rows 8-15 bytes [0,16),
     // 16-23 rows 0-7 bytes [16,32), 24-31 rows 8-15 bytes [16,32)
-    const uint32_t lm_off = ((lane & 7u) + ((lane >> 3) & 1u) * 8u) * a.pitch + 16u + (lane >> 4) * 16u;
+    // (row pitch = bytes of the stage's box row: cb or rem blocks)
+    const uint32_t lm_row = (lane & 7u) + ((lane >> 3) & 1u) * 8u, lm_col = 16u + (lane >> 4) * 16u;
     // B operand: column n = lane/4 -> pair n/2 (parity n/2%2), part n%2; t = lane%4
     const uint32_t bn = lane >> 2, bt = lane & 3u;
     const uint32_t b_par = (bn >> 1) & 1u;
@@ -300,7 +305,6 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
     const uint32_t c_par = lane & 1u;
     const uint32_t c_tok = M1 ? 0u : (bt >> 1);
     const uint32_t row_a = M1 ? (lane >> 2) + ((bt >> 1) << 3) : (lane >> 2);
-    const uint32_t hdr_off = row_a * a.pitch;
     const uint32_t sel0 = 0x7440u + c_par, sel1 = 0x7442u + c_par;
     const float par_scale = c_par ? 0.0625f : 1.f;  // odd sub-blocks arrive as 16*q
 
@@ -345,7 +349,9 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
 
         for (uint32_t c = 0; c < nchunks; c++) {
             const uint32_t bs = b0 + c * a.cb;
-            const uint32_t nblk = min(a.cb, b1 - bs);
+            const uint32_t nblk = c < nfull ? a.cb : a.rem;
+            const uint32_t pitch = nblk * kBlockBytes;
+            const uint32_t lm_off = lm_row * pitch + lm_col, hdr_off = row_a * pitch;
             const uint32_t bar = bar0 + st * 8u;
             if (PROBE < 2 && !failed) {
                 uint32_t polls = 0;
@@ -369,7 +375,7 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
                         for (int g = 0; g < 4; g++) dsc[r][g] = 1.f, dmn[r][g] = 2.f;
                         continue;
                     }
-                    const uint4 hv = lds128<0>(boff + hdr_off + r * 8u * a.pitch);
+                    const uint4 hv = lds128<0>(boff + hdr_off + r * 8u * pitch);
                     const BlockHeader h{hv.x, hv.y, hv.z, hv.w};
                     const float d = half_bits_to_float(h.w0) * par_scale, dmin = half_bits_to_float(h.w0 >> 16);
                     uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
@@ -538,11 +544,17 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     }
     uint32_t per_sm = (uint32_t)cache.occ;
     if (ctas_per_sm_override && ctas_per_sm_override < per_sm) per_sm = ctas_per_sm_override;
+    // Every CTA walks ceil(groups/gx) tile groups.  Pick the smallest grid that needs no more
+    // rounds than the full machine would, so that all CTAs carry (almost) the same load:
+    // 448 groups on 148 SMs -> 4 rounds -> 112 CTAs of exactly 4, not 148 CTAs of 3 or 4.
     const uint64_t cap = (uint64_t)sm_count * per_sm;
     uint32_t gx = groups;
-    if ((uint64_t)gx * slots_y > cap) gx = (uint32_t)((cap + slots_y - 1) / slots_y);
+    if ((uint64_t)gx * slots_y > cap) {
+        const uint32_t cap_x = (uint32_t)((cap + slots_y - 1) / slots_y);
+        const uint32_t rounds = (groups + cap_x - 1) / cap_x;
+        gx = (groups + rounds - 1) / rounds;
+    }
     if (gx == 0) gx = 1;
-    if (gx > groups) gx = groups;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(gx, slots_y);
     cfg.blockDim = dim3(threads);
@@ -599,23 +611,30 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
 
     // ---- plan ------------------------------------------------------------------
     constexpr uint32_t kSmemMax = 227 * 1024;
-    // Defaults from tuning sweeps on B200 (Llama-3 shapes): 12 warps, K split 6 ways, stages of
-    // 3 blocks, 4 deep; problems with fewer tiles than SMs spread every tile over a whole CTA.
-    const bool tiny = (uint64_t)ntiles * (indirect ? m.n_slots : 1) < (uint64_t)sm_count;
-    uint32_t warps = tune.warps ? tune.warps : (m1 ? (tiny ? 16 : 12) : 8);
+    // Defaults from tuning sweeps on B200 over the Llama-3 projection shapes:
+    //   fewer tiles than SMs      16 warps, every warp a K slice of the CTA's one tile, 1-block stages
+    //   up to two tiles per SM    16 warps, K split 8 ways, one stage holds a warp's whole slice if small
+    //   more                      8 warps, wide stages (5 blocks), little or no K split
+    const uint64_t tiles_total = (uint64_t)ntiles * (indirect ? m.n_slots : 1);
+    const bool tiny = tiles_total < (uint64_t)sm_count;
+    const bool small = !tiny && tiles_total <= 2ull * sm_count;
+    uint32_t warps = tune.warps ? tune.warps : (m1 ? ((tiny || small) ? 16 : 8) : 8);
     if (!m1 && warps > 8) warps = 8;  // the multi-row kernels are built for 256 threads (more registers each)
-    uint32_t wk = tune.wk ? tune.wk : (tiny ? warps : (m1 ? 6 : 4));
+    uint32_t wk = tune.wk ? tune.wk : (tiny ? warps : small ? 8 : (tiles_total >= 16ull * sm_count ? 2 : 1));
     if (wk > nb) wk = nb;
     if (wk > warps) wk = warps;
-    while (warps % wk) wk--;  // wk must divide the warp count
+    while (wk > 1 && (warps % wk || nb % wk)) wk--;
     uint32_t wt = warps / wk;
     if (wk > 1 && wt > 15) wt = 15, warps = wt * wk;  // named barrier ids 1..15
-    // Stage = dense TMA box of 16 rows x cb blocks.  An odd cb keeps the 16-byte units of
-    // the eight rows an ldmatrix touches in distinct bank groups (row pitch = cb*9 units).
-    uint32_t cb = tune.cb ? tune.cb : (tiny ? 1 : 3);
+    const uint32_t bpw = nb / wk;  // blocks per warp per tile
+    // Stage = dense TMA box of 16 rows x cb blocks, then one box of rem blocks for the tail of
+    // the warp's K range.  An odd cb keeps the 16-byte units of the eight rows an ldmatrix
+    // touches in distinct bank groups (row pitch = cb*9 units).
+    uint32_t cb = tune.cb ? tune.cb : (tiny ? 1 : small ? (bpw <= 3 ? bpw : 1) : 5);
     if (cb > 7) cb = 7;  // box width <= 256 words
-    const uint32_t pitch = cb * kBlockBytes;
-    const uint32_t stage_bytes = 16 * pitch;
+    if (cb > bpw) cb = bpw;
+    const uint32_t rem = bpw % cb;
+    const uint32_t stage_bytes = 16 * cb * kBlockBytes;
 
     const uint32_t x_bytes = tokens * m.K * 4u, S_bytes = tokens * (m.K / 32u) * 8u;
     auto layout = [&](bool xg, uint32_t stages, StreamArgs& sa) -> uint32_t {
@@ -632,7 +651,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     sa.m.M = M;
     // activations in shared memory if they leave room for at least 3 stages per warp
     bool xg = false;
-    uint32_t stages = tune.stages ? tune.stages : (tiny ? 2 : 4);
+    uint32_t stages = tune.stages ? tune.stages : ((tiny || small) ? 2 : 4);
     if (stages > kMaxStages) stages = kMaxStages;
     if (tune.force_scratch) xg = true;
     if (!xg) {
@@ -648,36 +667,41 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     }
     const uint32_t smem = layout(xg, stages, sa);
     if (smem > kSmemMax) return cudaErrorInvalidValue;
-    sa.wk = wk; sa.wt = wt; sa.cb = cb; sa.stages = stages; sa.pitch = pitch; sa.stage_bytes = stage_bytes;
+    sa.wk = wk; sa.wt = wt; sa.cb = cb; sa.rem = rem; sa.bpw = bpw; sa.stages = stages; sa.stage_bytes = stage_bytes;
     sa.ntiles = ntiles; sa.tokens = tokens; sa.status = status_dev;
     {
         const uint64_t rows_total = indirect ? m.w_total_rows : m.N;
-        const TmapCache::Entry* hit = nullptr;
-        if (tmaps) {
-            for (const auto& en : tmaps->entries)
-                if (en.W == m.W && en.rows == rows_total && en.row_bytes == m.w_row_bytes && en.nb == nb && en.cb == cb) {
-                    hit = &en;
-                    break;
-                }
-        }
-        if (hit) {
-            std::memcpy(&sa.tmap, hit->map, sizeof(CUtensorMap));
+        auto get_map = [&](uint32_t width_blocks, CUtensorMap* out) -> cudaError_t {
+            if (tmaps) {
+                for (const auto& en : tmaps->entries)
+                    if (en.W == m.W && en.rows == rows_total && en.row_bytes == m.w_row_bytes && en.nb == nb &&
+                        en.cb == width_blocks) {
+                        std::memcpy(out, en.map, sizeof(CUtensorMap));
+                        return cudaSuccess;
+                    }
+            }
+            EncodeTiledFn enc = encode_tiled_fn();
+            if (!enc) return cudaErrorNotSupported;
+            const cuuint64_t gdim[2] = {(cuuint64_t)nb * kBlockWords, (cuuint64_t)rows_total};
+            const cuuint64_t gstride[1] = {(cuuint64_t)m.w_row_bytes};
+            const cuuint32_t box[2] = {width_blocks * kBlockWords, 16u};
+            const cuuint32_t estr[2] = {1u, 1u};
+            const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(m.W), gdim, gstride, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+            if (tmaps) {
+                auto& en = tmaps->entries[tmaps->next++ % TmapCache::kEntries];
+                en.W = m.W; en.rows = rows_total; en.row_bytes = m.w_row_bytes; en.nb = nb; en.cb = width_blocks;
+                std::memcpy(en.map, out, sizeof(CUtensorMap));
+            }
+            return cudaSuccess;
+        };
+        if (cudaError_t e = get_map(cb, &sa.tmap)) return e;
+        if (rem) {
+            if (cudaError_t e = get_map(rem, &sa.tmap_rem)) return e;
         } else {
-        EncodeTiledFn enc = encode_tiled_fn();
-        if (!enc) return cudaErrorNotSupported;
-        const cuuint64_t gdim[2] = {(cuuint64_t)nb * kBlockWords, (cuuint64_t)rows_total};
-        const cuuint64_t gstride[1] = {(cuuint64_t)m.w_row_bytes};
-        const cuuint32_t box[2] = {cb * kBlockWords, 16u};
-        const cuuint32_t estr[2] = {1u, 1u};
-        const CUresult r = enc(&sa.tmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(m.W), gdim, gstride, box,
-                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-        if (tmaps) {
-            auto& en = tmaps->entries[tmaps->next++ % TmapCache::kEntries];
-            en.W = m.W; en.rows = rows_total; en.row_bytes = m.w_row_bytes; en.nb = nb; en.cb = cb;
-            std::memcpy(en.map, &sa.tmap, sizeof(CUtensorMap));
-        }
+            sa.tmap_rem = sa.tmap;
         }
     }
 

@@ -1,0 +1,77 @@
+// The Q4_K operators, registered the way the reference registers its ONNX ops
+// (REGISTER_OP at the end of runtime/ops/matmul.cpp:582-585).  The reference has no
+// ONNX op for Q4_K -- its Q4_K kernels are driven by ModelRunner -- so the op carries
+// a custom name and follows MatMulNBits' conventions (runtime/ops/matmul.cpp:205-335):
+// attributes K and N, M = product of the leading dims of X, the op allocates its output,
+// and on bad input it returns early leaving the output invalid.
+//
+//   MatMulQ4K   inputs  X float32[..., K], W uint8[N, K/256*144] (raw GGUF super-blocks),
+//                       optional Bias float32[N];  attrs K, N;  output Y float32[..., N]
+//   DequantQ4K  input   W uint8[N, K/256*144];  attrs K, N;  output float32[N, K]
+//               (dequant_kquant, runtime/gguf_loader.cpp:455-496)
+#include <cstdio>
+
+#include "bp_runtime.h"
+
+static bool weight_ok(const GpuTensor* W, uint32_t N, uint32_t K) {
+    return W && W->IsValid() && W->dtype == TensorDtype::UInt8 && K % 256 == 0 &&
+           (uint64_t)W->ElementCount() >= (uint64_t)N * (K / 256) * 144;
+}
+
+static void opMatMulQ4K(OpContext& ex, const OnnxGraphNode& n, const std::vector<GpuTensor*>& in,
+                        std::vector<GpuTensor*>& out) {
+    if (in.size() < 2 || out.empty()) return;
+    GpuTensor* X = in[0];
+    GpuTensor* W = in[1];
+    GpuTensor* B = in.size() > 2 && in[2] && in[2]->IsValid() ? in[2] : nullptr;
+    if (!X || !X->IsValid() || X->dtype != TensorDtype::Float32 || X->shape.empty()) return;
+    const uint32_t N = (uint32_t)n.GetInt("N"), K = (uint32_t)n.GetInt("K");
+    if (!N || !K || X->shape.back() != (int64_t)K || !weight_ok(W, N, K)) {
+        fprintf(stderr, "[MatMulQ4K] %s: bad shapes (N=%u K=%u)\n", n.name.c_str(), N, K);
+        return;
+    }
+    if (B && (B->dtype != TensorDtype::Float32 || B->ElementCount() < (int64_t)N)) return;
+    ex.EnsureGpu(*X);
+    ex.EnsureGpu(*W);
+    if (B) ex.EnsureGpu(*B);
+    int64_t M = 1;
+    for (size_t i = 0; i + 1 < X->shape.size(); i++) M *= X->shape[i];
+    auto outShape = X->shape;
+    outShape.back() = N;
+    GpuTensor y = ex.AllocTensor(outShape, TensorDtype::Float32);
+    if (!y.buffer.handle) return;
+    GPUContext* gpu = ex.getGpu();
+    const int st = bpq4k_matmul_f32(gpu->q4k(), static_cast<const float*>(X->buffer.handle), W->buffer.handle,
+                                    B ? static_cast<const float*>(B->buffer.handle) : nullptr,
+                                    static_cast<float*>(y.buffer.handle), (uint32_t)M, N, K,
+                                    bpq4k_row_stride_words(K), 0, gpu->stream());
+    if (st != BPQ4K_OK) {
+        fprintf(stderr, "[MatMulQ4K] %s: %s\n", n.name.c_str(), bpq4k_last_error_string(gpu->q4k()));
+        gpu->releaseBuffer(y.buffer);
+        return;  // output stays invalid
+    }
+    *out[0] = std::move(y);
+}
+
+static void opDequantQ4K(OpContext& ex, const OnnxGraphNode& n, const std::vector<GpuTensor*>& in,
+                         std::vector<GpuTensor*>& out) {
+    if (in.empty() || out.empty()) return;
+    GpuTensor* W = in[0];
+    const uint32_t N = (uint32_t)n.GetInt("N"), K = (uint32_t)n.GetInt("K");
+    if (!N || !K || !weight_ok(W, N, K)) return;
+    ex.EnsureGpu(*W);
+    GpuTensor y = ex.AllocTensor({(int64_t)N, (int64_t)K}, TensorDtype::Float32);
+    if (!y.buffer.handle) return;
+    GPUContext* gpu = ex.getGpu();
+    const int st = bpq4k_dequant_f32(gpu->q4k(), W->buffer.handle, N, K, bpq4k_row_stride_words(K),
+                                     static_cast<float*>(y.buffer.handle), gpu->stream());
+    if (st != BPQ4K_OK) {
+        fprintf(stderr, "[DequantQ4K] %s: %s\n", n.name.c_str(), bpq4k_last_error_string(gpu->q4k()));
+        gpu->releaseBuffer(y.buffer);
+        return;
+    }
+    *out[0] = std::move(y);
+}
+
+REGISTER_OP(MatMulQ4K, opMatMulQ4K)
+REGISTER_OP(DequantQ4K, opDequantQ4K)
