@@ -37,6 +37,16 @@ SIGNATURES = {
     "bpq4k_matmul_host_f32": (C.c_int, [vp, vp, vp, vp, vp, u32, u32, u32, u32, vp]),
 }
 
+
+
+class HostMatmul(C.Structure):
+    """bpq4k_host_matmul of include/bpq4k.h."""
+    _fields_ = [("X_host", vp), ("W_dev", vp), ("bias_dev", vp), ("Y_host", vp),
+                ("M", u32), ("N", u32), ("K", u32), ("rowStrideWords", u32)]
+
+
+SIGNATURES["bpq4k_matmul_host_batch_f32"] = (C.c_int, [vp, C.POINTER(HostMatmul), u32, vp])
+
 _lib = None
 
 

@@ -435,5 +435,64 @@ int bpq4k_matmul_host_f32(bpq4k_handle_t h, const float* X_host, const void* W_d
     return BPQ4K_OK;
 }
 
+int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items, uint32_t count, void* stream) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (count == 0) return BPQ4K_OK;
+    if (!items) return fail(h, BPQ4K_ERR_INVALID_ARG, "items is null");
+    size_t xb = 0, yb = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        const bpq4k_host_matmul& it = items[i];
+        if (it.M == 0 || it.N == 0) continue;
+        if (!it.X_host || !it.Y_host) return fail(h, BPQ4K_ERR_INVALID_ARG, "item %u: X_host or Y_host is null", i);
+        if (int s = check_weights(h, it.W_dev, it.N, it.K, it.rowStrideWords)) return s;
+        xb += ((size_t)it.M * it.K * 4u + 255u) & ~(size_t)255u;  // keep every slice 256-byte aligned
+        yb += ((size_t)it.M * it.N * 4u + 255u) & ~(size_t)255u;
+    }
+    DeviceGuard g(h->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (int s = ensure_bytes(h, reinterpret_cast<void**>(&h->stage_x), &h->stage_x_bytes, xb)) return s;
+    if (int s = ensure_bytes(h, reinterpret_cast<void**>(&h->stage_y), &h->stage_y_bytes, yb)) return s;
+    cudaError_t e = cudaSuccess;
+    size_t xo = 0;
+    for (uint32_t i = 0; i < count && e == cudaSuccess; i++) {
+        const bpq4k_host_matmul& it = items[i];
+        if (it.M == 0 || it.N == 0) continue;
+        const size_t bytes = (size_t)it.M * it.K * 4u;
+        e = cudaMemcpyAsync(reinterpret_cast<uint8_t*>(h->stage_x) + xo, it.X_host, bytes, cudaMemcpyHostToDevice, st);
+        xo += (bytes + 255u) & ~(size_t)255u;
+    }
+    if (e != cudaSuccess) return cuda_fail(h, e, "activation upload");
+    xo = 0;
+    size_t yo = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        const bpq4k_host_matmul& it = items[i];
+        if (it.M == 0 || it.N == 0) continue;
+        MatmulArgs a{};
+        a.X = reinterpret_cast<const float*>(reinterpret_cast<uint8_t*>(h->stage_x) + xo);
+        a.W = static_cast<const uint8_t*>(it.W_dev);
+        a.bias = it.bias_dev;
+        a.Y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(h->stage_y) + yo);
+        a.M = it.M;
+        a.N = it.N;
+        a.K = it.K;
+        a.w_row_bytes = (uint64_t)it.rowStrideWords * 4u;
+        if (int s = run_matmul(h, a, st)) return s;
+        xo += ((size_t)it.M * it.K * 4u + 255u) & ~(size_t)255u;
+        yo += ((size_t)it.M * it.N * 4u + 255u) & ~(size_t)255u;
+    }
+    yo = 0;
+    for (uint32_t i = 0; i < count && e == cudaSuccess; i++) {
+        const bpq4k_host_matmul& it = items[i];
+        if (it.M == 0 || it.N == 0) continue;
+        const size_t bytes = (size_t)it.M * it.N * 4u;
+        e = cudaMemcpyAsync(it.Y_host, reinterpret_cast<uint8_t*>(h->stage_y) + yo, bytes, cudaMemcpyDeviceToHost, st);
+        yo += (bytes + 255u) & ~(size_t)255u;
+    }
+    if (e != cudaSuccess) return cuda_fail(h, e, "result read-back");
+    e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(h, e, "stream synchronize");
+    return BPQ4K_OK;
+}
+
 }  // extern "C"
 #pragma GCC visibility pop

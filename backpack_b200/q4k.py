@@ -193,3 +193,17 @@ class Q4KContext:
             self.h, x_host.ctypes.data, w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
             y_host.ctypes.data, M, w.N, w.K, w.rowStrideWords, self._stream()))
         return y_host
+
+    def make_host_batch(self, items):
+        """Pre-build the dispatch list for matmul_host_batch: items = [(x_host, weight, y_host, bias|None)]."""
+        arr = (_lib.HostMatmul * len(items))()
+        for i, (x, w, y, bias) in enumerate(items):
+            assert x.dtype == np.float32 and y.dtype == np.float32 and x.flags.c_contiguous and y.flags.c_contiguous
+            arr[i] = _lib.HostMatmul(x.ctypes.data, w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                     y.ctypes.data, x.size // w.K, w.N, w.K, w.rowStrideWords)
+        return arr, list(items)   # keep the arrays alive alongside the descriptors
+
+    def matmul_host_batch(self, batch) -> None:
+        """One call: upload every X, run every matmul, read every Y back, wait once."""
+        arr, _keep = batch
+        self._check(self.lib.bpq4k_matmul_host_batch_f32(self.h, arr, len(arr), self._stream()))

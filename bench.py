@@ -14,9 +14,10 @@ launch streams its weights from HBM.
 ``value``     whole-job algorithmic GB/s (weights + activations + outputs moved
               once) with everything resident in HBM, the step replayed from a
               CUDA graph, timed with CUDA events; max over ranks.
-``e2e``       the same metric through the host-buffer C-ABI call: every step
-              copies the activations from pinned host memory, runs the kernels
-              on the resident weights and reads the outputs back.
+``e2e``       the same metric through the host-buffer C-ABI call
+              (bpq4k_matmul_host_batch_f32, one call per step): every step copies
+              the activations from pinned host memory, runs the kernels on the
+              resident weights, reads the outputs back and waits.
 ``roofline``  the dominant kernel (the streaming matmul kernel) against the
               measured HBM copy bandwidth.
 ``cpu_baseline`` the reference's own CPU code for the path (dequant_kquant +
@@ -305,11 +306,22 @@ def run_gpu_arm(args, rank, world, local_rank):
         xs_np = {n: xs_pin[n].numpy() for n in xs_pin}
         ys_np = {n: ys_pin[n].numpy() for n in ys_pin}
 
-        def e2e_pass():
-            for name, N, K in shapes:
-                ctx.matmul_host(xs_np[name], W[name], ys_np[name])
-                if world > 1:
+        if world == 1:
+            # the user-facing call: one dispatch list on host buffers (uploads, kernels, read-backs, one wait)
+            batch = ctx.make_host_batch([(xs_np[n], W[n], ys_np[n], None) for n, _, _ in shapes])
+
+            def e2e_pass():
+                ctx.matmul_host_batch(batch)
+        else:
+            yall_pin = {n: torch.zeros(world * N, dtype=torch.float32).pin_memory() for n, N, _ in shapes}
+
+            def e2e_pass():
+                for name, N, K in shapes:
+                    X[name].copy_(xs_pin[name], non_blocking=True)
+                    ctx.matmul(X[name], W[name], out=Y[name])
                     dist.all_gather_into_tensor(Yall[name], Y[name])
+                    yall_pin[name].copy_(Yall[name], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
 
         for _ in range(3):
             e2e_pass()

@@ -183,6 +183,21 @@ int bpq4k_matmul_host_f32(bpq4k_handle_t h, const float* X_host, const void* W_d
                           const float* bias_dev, float* Y_host, uint32_t M, uint32_t N, uint32_t K,
                           uint32_t rowStrideWords, void* stream);
 
+/* A list of matmuls on host buffers served by ONE call: all activations go up, all kernels
+ * run, all outputs come back, one wait.  This is how the reference runs a decode step -- a
+ * pre-recorded list of Dispatch structs replayed by one queue submit, one small write before
+ * and one read-back after (runtime/gpu_context.h:36-44, runtime/model_runner.cpp:4839,
+ * 5725-5764).  Entries are independent of each other (no entry reads another's output). */
+typedef struct bpq4k_host_matmul {
+    const float* X_host;      /* M*K floats; pinned host memory makes the copies asynchronous */
+    const void* W_dev;        /* resident weights */
+    const float* bias_dev;    /* may be NULL */
+    float* Y_host;            /* M*N floats */
+    uint32_t M, N, K, rowStrideWords;
+} bpq4k_host_matmul;
+
+int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items, uint32_t count, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -239,6 +239,24 @@ def test_matmul_host_buffers(ctx):
     check(y2, orc.matmul(x2, raw, None, N, K, threads=8))
 
 
+def test_matmul_host_batch(ctx):
+    """A dispatch list of independent matmuls on host buffers, one call."""
+    shapes = [(1, 300, 1024), (2, 64, 512), (1, 1024, 4096), (0, 8, 256)]
+    items, wants = [], []
+    for i, (M, N, K) in enumerate(shapes):
+        raw = synth.make_q4k_weights(N, K, 40 + i)
+        x = synth.make_activations(M, K, 50 + i)
+        y = np.full((M, N), np.nan, np.float32)
+        items.append((x, ctx.upload(pack_q4k(raw, N, K)), y, None))
+        wants.append(orc.matmul(x, raw, None, N, K))
+    batch = ctx.make_host_batch(items)
+    for _ in range(2):          # the second call reuses the staging buffers
+        ctx.matmul_host_batch(batch)
+        for (x, w, y, b), want in zip(items, wants):
+            if want.size:
+                check(y, want)
+
+
 # ---------------------------------------------------------------- error behaviour
 
 def test_errors_are_statuses_not_faults(ctx):
