@@ -1,0 +1,50 @@
+"""Run one Q4_K matmul shape on cuda:0 a few times and report its time.
+
+    python -m backpack_b200.run_case N K M [--reps R] [--variant auto|fp32|stream]
+
+A small driver for profilers and quick checks: seeded synthetic weights and
+activations (backpack_b200.synth), `reps` back-to-back calls through the C ABI,
+CUDA-event timing of the last `reps - 1` calls.
+"""
+from __future__ import annotations
+
+import argparse
+
+import numpy as np
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("N", type=int)
+    ap.add_argument("K", type=int)
+    ap.add_argument("M", type=int)
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--variant", default="auto", choices=["auto", "fp32", "stream"])
+    args = ap.parse_args()
+
+    import torch
+
+    import backpack_b200 as bp
+    from backpack_b200 import q4k, synth
+
+    ctx = bp.Q4KContext(0)
+    ctx.set_option(q4k.OPT_GEMV_VARIANT, {"auto": q4k.GEMV_AUTO, "fp32": q4k.GEMV_FP32, "stream": q4k.GEMV_STREAM}[args.variant])
+    w = ctx.upload(bp.pack_q4k(synth.make_q4k_weights(args.N, args.K, 0), args.N, args.K))
+    x = torch.from_numpy(synth.make_activations(args.M, args.K, 1)).cuda()
+    y = torch.zeros(args.M, args.N, device="cuda")
+    ctx.matmul(x, w, out=y)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(max(args.reps - 1, 1)):
+        ctx.matmul(x, w, out=y)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / max(args.reps - 1, 1)
+    nbytes = synth.algorithmic_bytes(args.M, args.N, args.K)
+    print(f"N={args.N} K={args.K} M={args.M}: {us:.2f} us/call, {nbytes / us / 1e3:.1f} GB/s algorithmic "
+          f"(back-to-back calls on one weight: L2-warm if it fits), checksum {float(y.double().abs().sum()):.6e}")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,103 @@
+"""Row-sharded Q4_K matmul over several GPUs, one process per GPU.
+
+The reference is single-GPU; this layer is what the multi-GPU configurations add.  Output
+rows are independent and a row range of the packed weight is a contiguous byte range
+(rows are `rowStrideWords*4` bytes apart, runtime/gguf_loader.cpp:367-378), so rank g keeps
+rows [g*Ns, (g+1)*Ns) resident, every rank holds the (small) activations, and the output
+slices are exchanged with one all-gather (`torch.distributed`, NCCL on GPUs).
+
+    M = 1   slices are contiguous pieces of Y[N]: all-gather straight into Y.
+    M > 1   slices are column blocks of row-major Y[M, N]: all-gather into [G][M][Ns],
+            then one strided copy into [M][N].
+
+When N is not a multiple of the world size every rank takes ceil(N/G) rows and the last
+rank's shard is zero-padded (a padded row decodes to weight 0 and is cut off after the gather).
+
+`matmul_fn(x, shard) -> y` does the local product.  By default it is the CUDA path of this
+package; tests of the partitioning logic on CPU ranks pass their own.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import numpy as np
+
+from .synth import BLOCK_BYTES, QK_K
+
+
+def shard_rows(N: int, world: int) -> int:
+    """Rows per rank (the last rank may own fewer real rows)."""
+    return (N + world - 1) // world
+
+
+def shard_range(N: int, world: int, rank: int) -> tuple[int, int]:
+    ns = shard_rows(N, world)
+    return min(rank * ns, N), min((rank + 1) * ns, N)
+
+
+def shard_raw(raw: np.ndarray, N: int, K: int, world: int, rank: int) -> np.ndarray:
+    """This rank's rows of a raw [N, K/256*144] weight, zero-padded to shard_rows(N, world) rows."""
+    rb = (K // QK_K) * BLOCK_BYTES
+    raw = np.ascontiguousarray(raw).view(np.uint8).reshape(N, rb)
+    n0, n1 = shard_range(N, world, rank)
+    ns = shard_rows(N, world)
+    out = np.zeros((ns, rb), np.uint8)
+    out[: n1 - n0] = raw[n0:n1]
+    return out
+
+
+@dataclass
+class ShardedQ4KLinear:
+    """One projection, N-sharded.  `shard` is whatever `matmul_fn` understands as a weight."""
+    N: int
+    K: int
+    world: int
+    rank: int
+    shard: object
+    matmul_fn: Callable
+    group: Optional[object] = None
+
+    @property
+    def Ns(self) -> int:
+        return shard_rows(self.N, self.world)
+
+    def local(self, x, out=None):
+        """This rank's slice Y[:, n0:n0+Ns] (padded rows included)."""
+        return self.matmul_fn(x, self.shard, out)
+
+    def forward(self, x, gathered=None):
+        """Full Y[M, N] on every rank.  x: [M, K] float32, replicated."""
+        import torch
+        import torch.distributed as dist
+
+        M = x.shape[0]
+        Ns, G = self.Ns, self.world
+        if G == 1:
+            return self.local(x)[:, : self.N]
+        if gathered is None:
+            gathered = torch.empty((G, M, Ns), dtype=torch.float32, device=x.device)
+        # the local product is written straight into this rank's slot of the gather buffer
+        self.local(x, gathered[self.rank])
+        dist.all_gather_into_tensor(gathered.view(-1), gathered[self.rank].reshape(-1), group=self.group)
+        if M == 1:
+            return gathered.view(1, G * Ns)[:, : self.N]
+        return gathered.permute(1, 0, 2).reshape(M, G * Ns)[:, : self.N]
+
+
+def make_cuda_linear(ctx, raw: np.ndarray, N: int, K: int, world: int, rank: int, group=None) -> ShardedQ4KLinear:
+    """Upload this rank's rows and bind the CUDA matmul of `ctx` (a Q4KContext)."""
+    from . import pack_q4k
+
+    ns = shard_rows(N, world)
+    w = ctx.upload(pack_q4k(shard_raw(raw, N, K, world, rank), ns, K))
+
+    def fn(x, shard, out=None):
+        import torch
+
+        if out is None:
+            out = torch.empty((x.shape[0], shard.N), dtype=torch.float32, device=x.device)
+        ctx.matmul(x, shard, out=out)
+        return out
+
+    return ShardedQ4KLinear(N, K, world, rank, w, fn, group)

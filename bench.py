@@ -220,21 +220,28 @@ def run_gpu_arm(args, rank, world, local_rank):
     shapes = synth.LLAMA3_8B
     weights_h, xs_h = make_host_inputs(shapes, "config1", rank)
     dev = f"cuda:{local_rank}"
-    W, X, Y, Yall = {}, {}, {}, {}
+    from backpack_b200 import sharded
+
+    W, X, Y, Yall, lin = {}, {}, {}, {}, {}
     for name, N, K in shapes:
         W[name] = ctx.upload(bp.pack_q4k(weights_h[name], N, K))
         X[name] = torch.from_numpy(xs_h[name]).to(dev)
         if world > 1:
-            Yall[name] = torch.zeros(world * N, dtype=torch.float32, device=dev)
-            Y[name] = Yall[name][rank * N:(rank + 1) * N]      # the rank's slice, written in place
+            # weak scaling: this rank's shard has the single-GPU shape, the global matrix has world*N rows
+            Yall[name] = torch.zeros((world, 1, N), dtype=torch.float32, device=dev)
+            Y[name] = Yall[name][rank]                          # the rank's slice, written in place
+            lin[name] = sharded.ShardedQ4KLinear(
+                world * N, K, world, rank, W[name],
+                lambda x, shard, out=None: ctx.matmul(x, shard, out=out))
         else:
             Y[name] = torch.zeros(1, N, dtype=torch.float32, device=dev)
 
     def one_pass():
         for name, N, K in shapes:
-            ctx.matmul(X[name], W[name], out=Y[name])
             if world > 1:
-                dist.all_gather_into_tensor(Yall[name], Y[name])
+                lin[name].forward(X[name], Yall[name])          # local product + all-gather of the slices
+            else:
+                ctx.matmul(X[name], W[name], out=Y[name])
 
     # correctness spot-check before timing (one projection against the CPU checker)
     from oracle import q4k_oracle as orc
@@ -318,9 +325,8 @@ def run_gpu_arm(args, rank, world, local_rank):
             def e2e_pass():
                 for name, N, K in shapes:
                     X[name].copy_(xs_pin[name], non_blocking=True)
-                    ctx.matmul(X[name], W[name], out=Y[name])
-                    dist.all_gather_into_tensor(Yall[name], Y[name])
-                    yall_pin[name].copy_(Yall[name], non_blocking=True)
+                    lin[name].forward(X[name], Yall[name])
+                    yall_pin[name].copy_(Yall[name].view(-1), non_blocking=True)
                 torch.cuda.current_stream().synchronize()
 
         for _ in range(3):
