@@ -363,7 +363,7 @@ int bpq4k_matmul_f32(bpq4k_handle_t h, const float* X, const void* W, const floa
     if (int s = check_weights(h, W, N, K, rowStrideWords)) return s;
     if (!X || !Y) return fail(h, BPQ4K_ERR_INVALID_ARG, "X or Y is null");
     if (!aligned16(X)) return fail(h, BPQ4K_ERR_MISALIGNED, "X is not 16-byte aligned");
-    if (!aligned16(Y)) return fail(h, BPQ4K_ERR_MISALIGNED, "Y is not 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(Y) & 3u) return fail(h, BPQ4K_ERR_MISALIGNED, "Y is not 4-byte aligned");
     DeviceGuard g(h->device);
     MatmulArgs a{};
     a.X = X;
@@ -386,7 +386,7 @@ int bpq4k_matmul_moe_f32(bpq4k_handle_t h, const float* X, const void* W, const 
     if (!X || !Y || !offsets) return fail(h, BPQ4K_ERR_INVALID_ARG, "X, Y or offsets is null");
     if (wRows < N) return fail(h, BPQ4K_ERR_INVALID_ARG, "wRows=%u is smaller than N=%u", wRows, N);
     if (!aligned16(X)) return fail(h, BPQ4K_ERR_MISALIGNED, "X is not 16-byte aligned");
-    if (!aligned16(Y)) return fail(h, BPQ4K_ERR_MISALIGNED, "Y is not 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(Y) & 3u) return fail(h, BPQ4K_ERR_MISALIGNED, "Y is not 4-byte aligned");
     DeviceGuard g(h->device);
     MatmulArgs a{};
     a.X = X;

@@ -152,8 +152,8 @@ int bpq4k_dequant_f32(bpq4k_handle_t h, const void* W, uint32_t N, uint32_t K,
  * q4k_matmul_128.wgsl:8-17 (yOffset), q4k_matmul_batched4/8.wgsl:9-23; bindings
  * X, W, Bias, Y and params {K, N, nBlocks, rowStrideWords, yOffset}
  * (runtime/model_runner.cpp:2404-2413).  Grid and tile choices are internal.
- * `bias` may be NULL (the reference always binds a zero buffer).  X, W and Y
- * must be 16-byte aligned.  M >= the PREFILL_MIN_M option goes to the
+ * `bias` may be NULL (the reference always binds a zero buffer).  X and W must be
+ * 16-byte aligned; Y (outputs are written one float at a time) 4-byte aligned.  M >= the PREFILL_MIN_M option goes to the
  * tensor-core kernel in the PREFILL_MODE option's precision. */
 int bpq4k_matmul_f32(bpq4k_handle_t h, const float* X, const void* W, const float* bias, float* Y,
                      uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords,
