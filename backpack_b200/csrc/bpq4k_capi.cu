@@ -104,6 +104,13 @@ int run_matmul(bpq4k_context* h, const MatmulArgs& a, cudaStream_t st) {
     cudaError_t e = cudaSuccess;
     if (h->gemv_variant == BPQ4K_GEMV_FP32) {
         e = launch_gemv_fp32(a, st, &launches);
+    } else if (!a.n_slots && a.M >= (uint32_t)h->prefill_min_m && h->gemv_variant == BPQ4K_GEMV_AUTO) {
+        // prefill: tensor-core kernel; its 16-bit copy of the activations lives in the handle's scratch
+        const size_t need = prefill_scratch_bytes(a.M, a.N, a.K, h->prefill_mode, h->sm_count);
+        if (need > h->scratch_bytes) {
+            if (int s = ensure_bytes(h, &h->scratch, &h->scratch_bytes, need)) return s;
+        }
+        e = launch_prefill_tc(a, h->prefill_mode, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count, st, &launches);
     } else {
         const uint32_t Mtot = a.n_slots ? 1 : a.M;
         const size_t need = a.n_slots ? 0 : gemv_stream_scratch_bytes(Mtot < kStreamMaxM ? Mtot : kStreamMaxM, a.K);

@@ -63,6 +63,12 @@ size_t gemv_stream_scratch_bytes(uint32_t M, uint32_t K);
 cudaError_t launch_gemv_stream(const MatmulArgs& a, const StreamTuning& tune, void* scratch, size_t scratch_bytes,
                                int* status_dev, int sm_count, TmapCache* tmaps, cudaStream_t stream, int* launches);
 
+// Tensor-core prefill matmul (tcgen05 + TMEM).  mode follows bpq4k_prefill_mode: 0 three-pass half
+// split, 1 one pass half, 2 one pass bfloat16.  `scratch` holds the 16-bit activations.
+size_t prefill_scratch_bytes(uint32_t M, uint32_t N, uint32_t K, int mode, int sm_count);
+cudaError_t launch_prefill_tc(const MatmulArgs& a, int mode, void* scratch, size_t scratch_bytes, int* status_dev,
+                              int sm_count, cudaStream_t stream, int* launches);
+
 // One warp per output row, float FMAs in the reference shader's arithmetic.
 cudaError_t launch_gemv_fp32(const MatmulArgs& a, cudaStream_t stream, int* launches);
 

@@ -1,0 +1,533 @@
+// Prefill Q4_K matmul (M >= 64) on the 5th-generation tensor cores: weights are dequantised
+// on chip into 16-bit tiles, multiplied with tcgen05.mma, accumulated in TMEM.
+//
+// The reference has no tensor-core path for Q4_K: its "prefill" is q4k_matmul_batched8
+// (runtime/kernels/quant_kq/q4k_matmul_batched8.wgsl:9-23, picked at
+// runtime/model_runner.cpp:5841-5845), scalar FMAs that re-read the weights M/8 times, or
+// serial decode (runtime/model_runner.cpp:4447-4471).  This kernel reads each weight once per
+// 256 activation rows.
+//
+//   Y[m][n] = sum_k X[m][k] * deq(W)[n][k] + bias[n]
+//
+// MMA orientation: D[weight row][activation row] = A[weight row][k] * B[activation row][k]^T, so
+// the 128 TMEM lanes are weight rows and the accumulator columns are activation rows (N_mma = 256).
+// A CTA owns ROWS weight rows (ROWS/128 accumulators of 256 columns) x 256 activation rows and
+// walks K in steps of 64 (one 64-weight group of a super-block = one 128-byte swizzle row).
+//
+// Roles (warp-specialised, all hand-offs through mbarriers):
+//   warp 0        one lane issues the TMA loads of the activation tile (16-bit, K-major,
+//                 SWIZZLE_128B; plain loads, no multicast)
+//   warp 1        allocates TMEM; one lane issues tcgen05.mma and tcgen05.commit
+//   warps 2..     thread r dequantises weight row r: raw super-block (144 B, prefetched into
+//                 registers one block ahead) -> w = (d*sc)*q - dmin*mn in float -> 16-bit ->
+//                 the K-major 128-byte-swizzled A tile; afterwards the same warps drain TMEM
+//                 (tcgen05.ld), add the bias and store Y.
+//
+// Precision modes: one pass in half or bfloat16 (weights and activations rounded to 16 bits), or
+// three passes with W = Wh + Wl, X = Xh + Xl in half (Wh*Xh + Wh*Xl + Wl*Xh, all into the same
+// accumulator), which meets the float tolerance of the path.
+//
+// Every wait is bounded: on a time-out the role raises the CTA's abort flag and the device status
+// word, every role leaves its loop, TMEM is freed and the kernel returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstring>
+
+#include "kernels.h"
+#include "q4k_common.cuh"
+
+namespace bpq4k {
+
+namespace {
+
+constexpr uint32_t kTokTile = 256;   // activation rows per CTA tile (= mma N)
+constexpr uint32_t kKStep = 64;      // k per pipeline stage
+constexpr uint32_t kWaitLimit = 1u << 24;
+
+struct PrefillArgs {
+    CUtensorMap tmap_x[2];  // [0]: X (or its high part), [1]: low part (three-pass mode)
+    const uint8_t* W;
+    const float* bias;
+    float* Y;
+    uint32_t M, N, K;
+    uint64_t w_row_bytes;
+    int* status;
+    // split-K: blockIdx.z takes super-blocks [z*bps, (z+1)*bps) and writes Ypart[z] (no bias);
+    // splitk_reduce_kernel adds the slices in a fixed order.  ksplit == 1: the kernel writes Y.
+    uint32_t ksplit, bps;
+    float* Ypart;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait.  Returns false if the CTA is aborting (this wait or another role's timed out).
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    for (uint32_t i = 0; i < kWaitLimit; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    if (status) atomicExch(status, kDeviceTimeout);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tmap, uint32_t x, uint32_t y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(tmap), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, rows 128 B apart, 8-row groups
+// 1024 B apart (SBO), version 1 (sm_100), LBO unused (1).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: D = f32, A/B = f16 (0) or bf16 (1), both K-major, M = 128, N = 256.
+__device__ __forceinline__ constexpr uint32_t umma_idesc(bool bf16) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((kTokTile >> 3) << 17) | ((128u >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    if constexpr (BF16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    } else {
+        const __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+}
+// low part of a half split: half(x - float(half(x)))
+__device__ __forceinline__ uint32_t pack2_lo(float a, float b, uint32_t hi_bits) {
+    const __half2 hi = *reinterpret_cast<const __half2*>(&hi_bits);
+    const float2 hf = __half22float2(hi);
+    const __half2 v = __floats2half2_rn(a - hf.x, b - hf.y);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Shared-memory plan (all tiles 1024-byte aligned for the 128-byte swizzle):
+//   per stage: NV versions (1, or hi+lo) of the A tile [ROWS x 128 B] and of the B tile [256 x 128 B]
+template <int ROWS, int PASSES>
+struct Plan {
+    static constexpr uint32_t NV = PASSES == 3 ? 2 : 1;
+    static constexpr uint32_t A_BYTES = ROWS * 128u, B_BYTES = kTokTile * 128u;
+    static constexpr uint32_t STAGE_BYTES = NV * (A_BYTES + B_BYTES);
+    static constexpr uint32_t STAGES = (200u * 1024u) / STAGE_BYTES;
+    static constexpr uint32_t DEQ_WARPS = ROWS / 32;
+    static constexpr uint32_t THREADS = (2 + DEQ_WARPS) * 32;
+    // three-pass mode: a second accumulator takes the two small cross terms (see the mma issuer)
+    static constexpr uint32_t TMEM_COLS = (PASSES == 3 ? 2 : ROWS / 128) * kTokTile;
+    static constexpr uint32_t SMEM_BYTES = 1024 /*align slack*/ + STAGES * STAGE_BYTES + 256 /*barriers*/;
+};
+
+template <int ROWS, int PASSES, bool BF16>
+__global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_kernel(const __grid_constant__ PrefillArgs a) {
+    using P = Plan<ROWS, PASSES>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bar_base = base + P::STAGES * P::STAGE_BYTES;
+    // barriers: full[s] (dequant warps + TMA producer), empty[s] (mma commit), acc_full
+    auto full_bar = [&](uint32_t s) { return bar_base + s * 8u; };
+    auto empty_bar = [&](uint32_t s) { return bar_base + (P::STAGES + s) * 8u; };
+    const uint32_t acc_bar = bar_base + 2u * P::STAGES * 8u;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + P::STAGES * P::STAGE_BYTES + 2u * P::STAGES * 8u + 16u);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + P::STAGES * P::STAGE_BYTES + 2u * P::STAGES * 8u + 32u);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t n0 = blockIdx.x * ROWS, tok0 = blockIdx.y * kTokTile;
+    const uint32_t blk0 = blockIdx.z * a.bps;                          // first super-block of this K slice
+    const uint32_t blk1 = min(a.K / kQK, blk0 + a.bps);
+    const uint32_t nkb = (blk1 - blk0) * 4u;                           // pipeline iterations (64 k each)
+    const uint32_t kbase = blk0 * kQK;                                 // first k of the slice
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < P::STAGES; s++) {
+            mbar_init(full_bar(s), P::DEQ_WARPS + 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(acc_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {  // TMEM allocation by one whole warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(P::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    auto a_tile = [&](uint32_t s, uint32_t v) { return base + s * P::STAGE_BYTES + v * P::A_BYTES; };
+    auto b_tile = [&](uint32_t s, uint32_t v) { return base + s * P::STAGE_BYTES + P::NV * P::A_BYTES + v * P::B_BYTES; };
+
+    if (warp == 0) {
+        // ---------------- TMA producer: activation tiles ----------------
+        if (lane == 0) {
+            for (uint32_t kb = 0; kb < nkb; kb++) {
+                const uint32_t s = kb % P::STAGES, it = kb / P::STAGES;
+                if (it > 0 && !wait_bar(empty_bar(s), (it - 1) & 1u, abort_flag, a.status)) break;
+                mbar_expect_tx(full_bar(s), P::NV * P::B_BYTES);
+                for (uint32_t v = 0; v < P::NV; v++) tma_load_2d(b_tile(s, v), &a.tmap_x[v], kbase + kb * kKStep, tok0, full_bar(s));
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(BF16);
+            bool ok = true;
+            for (uint32_t kb = 0; kb < nkb && ok; kb++) {
+                const uint32_t s = kb % P::STAGES, it = kb / P::STAGES;
+                ok = wait_bar(full_bar(s), it & 1u, abort_flag, a.status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (uint32_t ks = 0; ks < kKStep / 16; ks++) {
+                    const uint32_t acc = (kb | ks) ? 1u : 0u;
+#pragma unroll
+                    for (uint32_t r = 0; r < (uint32_t)ROWS / 128; r++) {
+                        // a 128-row half of the A tile is 16 KiB further on; a k-step of 16 is 32 B inside the swizzle row
+                        const uint64_t da_h = umma_desc(a_tile(s, 0) + r * 16384u + ks * 32u);
+                        const uint64_t db_h = umma_desc(b_tile(s, 0) + ks * 32u);
+                        const uint32_t d = tmem_base + r * kTokTile;
+                        umma_f16(d, da_h, db_h, idesc, acc);
+                        if constexpr (PASSES == 3) {
+                            // The tensor core truncates when it adds into a float accumulator, so the error
+                            // of a long K grows with the number of accumulations times the accumulator's
+                            // magnitude.  The cross terms Wh*Xl + Wl*Xh are 2^-11 of the main term: they get
+                            // an accumulator of their own (columns 256..511) and are added in the epilogue,
+                            // which leaves the large accumulator with a third of the accumulations.
+                            const uint64_t da_l = umma_desc(a_tile(s, 1) + r * 16384u + ks * 32u);
+                            const uint64_t db_l = umma_desc(b_tile(s, 1) + ks * 32u);
+                            umma_f16(d + kTokTile, da_h, db_l, idesc, acc);
+                            umma_f16(d + kTokTile, da_l, db_h, idesc, 1u);
+                        }
+                    }
+                }
+                umma_commit(empty_bar(s));  // the stage's smem may be overwritten once these mmas retire
+            }
+            if (ok) umma_commit(acc_bar);
+        }
+    } else {
+        // ---------------- dequantise (thread = weight row), then drain TMEM ----------------
+        const uint32_t dw = warp - 2;              // 0 .. DEQ_WARPS-1
+        const uint32_t r = dw * 32u + lane;        // row inside the tile
+        const uint32_t n = n0 + r;
+        const bool row_ok = n < a.N;
+        const uint4* wrow = reinterpret_cast<const uint4*>(a.W + (uint64_t)(row_ok ? n : 0) * a.w_row_bytes);
+        const uint32_t nblocks = blk1 - blk0;
+        wrow += (uint64_t)blk0 * 9u;
+        uint4 raw[9], nxt[9];
+#pragma unroll
+        for (int i = 0; i < 9; i++) nxt[i] = (row_ok && nblocks) ? __ldg(wrow + i) : make_uint4(0, 0, 0, 0);
+        bool ok = true;
+        // swizzled address of 16-byte chunk c of row r: 8-row group base + row*128 + ((c ^ (r&7)) * 16)
+        const uint32_t row_off = (r >> 3) * 1024u + (r & 7u) * 128u;
+        const uint32_t sw = r & 7u;
+        for (uint32_t b = 0; b < nblocks && ok; b++) {
+#pragma unroll
+            for (int i = 0; i < 9; i++) raw[i] = nxt[i];
+            if (b + 1 < nblocks && row_ok) {
+#pragma unroll
+                for (int i = 0; i < 9; i++) nxt[i] = __ldg(wrow + (uint64_t)(b + 1) * 9u + i);
+            }
+            const BlockHeader h{raw[0].x, raw[0].y, raw[0].z, raw[0].w};
+            const float d = half_bits_to_float(h.w0), dmin = half_bits_to_float(h.w0 >> 16);
+            uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
+            unpack_scales_packed(h, sc_lo, sc_hi, mn_lo, mn_hi);
+#pragma unroll
+            for (uint32_t g = 0; g < 4; g++) {
+                const uint32_t kb = b * 4u + g;
+                const uint32_t s = kb % P::STAGES, it = kb / P::STAGES;
+                if (it > 0 && !wait_bar(empty_bar(s), (it - 1) & 1u, abort_flag, a.status)) {
+                    ok = false;
+                    break;
+                }
+                // w = (d*sc)*q - dmin*mn in float, rounded to 16 bits afterwards
+                const float dsc_e = d * (float)byte_of(sc_lo, sc_hi, 2 * g), dmn_e = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g);
+                const float dsc_o = d * (float)byte_of(sc_lo, sc_hi, 2 * g + 1), dmn_o = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g + 1);
+                const uint4 c0 = raw[1 + 2 * g], c1 = raw[2 + 2 * g];  // the group's 32 code bytes
+                const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                const uint32_t ta = a_tile(s, 0) + row_off;
+#pragma unroll
+                for (uint32_t c = 0; c < 4; c++) {  // chunk c: weights 8c..8c+7 of the even sub-block, chunk c+4: of the odd one
+                    uint32_t lo_bits[4], hi_bits[4], lo_l[4], hi_l[4];
+#pragma unroll
+                    for (uint32_t j = 0; j < 2; j++) {
+                        const uint32_t w = words[2 * c + j];
+                        float e[4], o[4];
+#pragma unroll
+                        for (uint32_t q = 0; q < 4; q++) {
+                            // 0x4B000000 | q is the float 2^23 + q: one subtraction gives q without the
+                            // (slow) integer-to-float unit; w = dsc*q - dmn as one fma (the rounding to
+                            // 16 bits that follows is 2^13 times coarser than the fma/mul+sub difference)
+                            const float qe = __uint_as_float(((w >> (8 * q)) & 15u) | 0x4B000000u) - 8388608.f;
+                            const float qo = __uint_as_float(((w >> (8 * q + 4)) & 15u) | 0x4B000000u) - 8388608.f;
+                            e[q] = fmaf(dsc_e, qe, -dmn_e);
+                            o[q] = fmaf(dsc_o, qo, -dmn_o);
+                        }
+                        lo_bits[2 * j] = pack2<BF16>(e[0], e[1]);
+                        lo_bits[2 * j + 1] = pack2<BF16>(e[2], e[3]);
+                        hi_bits[2 * j] = pack2<BF16>(o[0], o[1]);
+                        hi_bits[2 * j + 1] = pack2<BF16>(o[2], o[3]);
+                        if constexpr (PASSES == 3) {
+                            lo_l[2 * j] = pack2_lo(e[0], e[1], lo_bits[2 * j]);
+                            lo_l[2 * j + 1] = pack2_lo(e[2], e[3], lo_bits[2 * j + 1]);
+                            hi_l[2 * j] = pack2_lo(o[0], o[1], hi_bits[2 * j]);
+                            hi_l[2 * j + 1] = pack2_lo(o[2], o[3], hi_bits[2 * j + 1]);
+                        }
+                    }
+                    if (!row_ok) {
+#pragma unroll
+                        for (int q = 0; q < 4; q++) lo_bits[q] = hi_bits[q] = lo_l[q] = hi_l[q] = 0u;
+                    }
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + ((c ^ sw) << 4)), "r"(lo_bits[0]),
+                                 "r"(lo_bits[1]), "r"(lo_bits[2]), "r"(lo_bits[3])
+                                 : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + (((c + 4u) ^ sw) << 4)), "r"(hi_bits[0]),
+                                 "r"(hi_bits[1]), "r"(hi_bits[2]), "r"(hi_bits[3])
+                                 : "memory");
+                    if constexpr (PASSES == 3) {
+                        const uint32_t tl = a_tile(s, 1) + row_off;
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tl + ((c ^ sw) << 4)), "r"(lo_l[0]),
+                                     "r"(lo_l[1]), "r"(lo_l[2]), "r"(lo_l[3])
+                                     : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tl + (((c + 4u) ^ sw) << 4)), "r"(hi_l[0]),
+                                     "r"(hi_l[1]), "r"(hi_l[2]), "r"(hi_l[3])
+                                     : "memory");
+                    }
+                }
+                // make the generic-proxy stores visible to the tensor core, then one arrival per warp
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_bar(s));
+            }
+        }
+        // ---------------- epilogue: TMEM -> registers -> Y ----------------
+        if (ok && wait_bar(acc_bar, 0, abort_flag, a.status)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t quad = warp & 3u;               // the TMEM lanes this warp may read
+            const uint32_t accum = dw / 4u;                // which 128-row accumulator
+            const uint32_t row = n0 + accum * 128u + quad * 32u + lane;
+            const float bias = (a.ksplit == 1 && a.bias && row < a.N) ? a.bias[row] : 0.f;
+            float* Yout = a.ksplit == 1 ? a.Y : a.Ypart + (uint64_t)blockIdx.z * a.M * a.N;
+            for (uint32_t c0 = 0; c0 < kTokTile; c0 += 32) {
+                if (tok0 + c0 >= a.M) break;
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((quad * 32u) << 16) + accum * kTokTile + c0, v);
+                if constexpr (PASSES == 3) {  // add the cross-term accumulator
+                    uint32_t v2[32];
+                    tmem_ld32(tmem_base + ((quad * 32u) << 16) + kTokTile + c0, v2);
+#pragma unroll
+                    for (uint32_t t = 0; t < 32; t++) v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(v2[t]));
+                }
+                if (row < a.N) {
+#pragma unroll
+                    for (uint32_t t = 0; t < 32; t++) {
+                        const uint32_t tok = tok0 + c0 + t;
+                        if (tok < a.M) Yout[(uint64_t)tok * a.N + row] = __uint_as_float(v[t]) + bias;
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P::TMEM_COLS) : "memory");
+    }
+}
+
+// X float32 [M][K] -> 16-bit [M][K] (and, for the three-pass mode, the low part of the half split)
+template <bool BF16, bool SPLIT>
+__global__ void __launch_bounds__(256) cast_activations_kernel(const float* __restrict__ X, uint64_t count4,
+                                                               uint2* __restrict__ hi, uint2* __restrict__ lo) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count4; i += (uint64_t)gridDim.x * blockDim.x) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(X) + i);
+        uint2 h;
+        h.x = pack2<BF16>(v.x, v.y);
+        h.y = pack2<BF16>(v.z, v.w);
+        hi[i] = h;
+        if constexpr (SPLIT) {
+            uint2 l;
+            l.x = pack2_lo(v.x, v.y, h.x);
+            l.y = pack2_lo(v.z, v.w, h.y);
+            lo[i] = l;
+        }
+    }
+}
+
+// Y = bias + sum_z Ypart[z], slices added in ascending z (deterministic)
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, uint32_t Z, uint64_t MN, uint32_t N,
+                                                            const float* __restrict__ bias, float* __restrict__ Y) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < MN; i += (uint64_t)gridDim.x * blockDim.x) {
+        float s = bias ? bias[i % N] : 0.f;
+        for (uint32_t z = 0; z < Z; z++) s += part[(uint64_t)z * MN + i];
+        Y[i] = s;
+    }
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+template <int ROWS, int PASSES, bool BF16>
+cudaError_t launch_tc(const PrefillArgs& pa, cudaStream_t stream) {
+    using P = Plan<ROWS, PASSES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<ROWS, PASSES, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)P::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const dim3 grid((pa.N + ROWS - 1) / ROWS, (pa.M + kTokTile - 1) / kTokTile, pa.ksplit);
+    prefill_tc_kernel<ROWS, PASSES, BF16><<<grid, P::THREADS, P::SMEM_BYTES, stream>>>(pa);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// K slices per problem: enough CTAs to occupy the machine when there are few output tiles, slices
+// of at least 1024 k, and (three-pass mode) at most 4096 k per slice so that the accumulation
+// error of the tensor core stays inside the tolerance of the path.
+static uint32_t choose_ksplit(uint32_t M, uint32_t N, uint32_t K, int mode, int sm_count) {
+    const uint32_t rows = mode == 0 ? 128u : 256u;
+    const uint32_t tiles = ((N + rows - 1) / rows) * ((M + kTokTile - 1) / kTokTile);
+    const uint32_t nblk = K / kQK;
+    uint32_t z = tiles >= (uint32_t)sm_count ? 1u : (uint32_t)sm_count / tiles;  // stay within one wave of CTAs
+    const uint32_t zmax = nblk / 4u ? nblk / 4u : 1u;  // >= 1024 k per slice
+    if (z > zmax) z = zmax;
+    if (mode == 0 && nblk > 16u * z) z = (nblk + 15u) / 16u;
+    if (z > 16u) z = 16u;
+    if (z < 1u) z = 1u;
+    const uint32_t bps = (nblk + z - 1) / z;  // super-blocks per slice
+    return (nblk + bps - 1) / bps;            // no empty slice
+}
+
+size_t prefill_scratch_bytes(uint32_t M, uint32_t N, uint32_t K, int mode, int sm_count) {
+    const size_t one = ((size_t)M * K * 2u + 255u) & ~(size_t)255u;
+    const uint32_t z = choose_ksplit(M, N, K, mode, sm_count);
+    return (mode == 0 ? 2 * one : one) + (z > 1 ? (size_t)z * M * N * 4u : 0);
+}
+
+// mode: 0 = three-pass half split, 1 = one pass half, 2 = one pass bfloat16 (the values of bpq4k_prefill_mode)
+cudaError_t launch_prefill_tc(const MatmulArgs& m, int mode, void* scratch, size_t scratch_bytes, int* status_dev,
+                              int sm_count, cudaStream_t stream, int* launches) {
+    if (m.M == 0 || m.N == 0) return cudaSuccess;
+    if (m.n_slots) return cudaErrorInvalidValue;
+    if (!scratch || scratch_bytes < prefill_scratch_bytes(m.M, m.N, m.K, mode, sm_count)) return cudaErrorInvalidValue;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return cudaErrorNotSupported;
+    uint8_t* hi = static_cast<uint8_t*>(scratch);
+    uint8_t* lo = hi + (((size_t)m.M * m.K * 2u + 255u) & ~(size_t)255u);
+    const uint64_t count4 = (uint64_t)m.M * m.K / 4u;
+    const unsigned cgrid = (unsigned)((count4 + 255) / 256 < 148u * 16u ? (count4 + 255) / 256 : 148u * 16u);
+    if (mode == 0)
+        cast_activations_kernel<false, true><<<cgrid, 256, 0, stream>>>(m.X, count4, reinterpret_cast<uint2*>(hi), reinterpret_cast<uint2*>(lo));
+    else if (mode == 1)
+        cast_activations_kernel<false, false><<<cgrid, 256, 0, stream>>>(m.X, count4, reinterpret_cast<uint2*>(hi), nullptr);
+    else
+        cast_activations_kernel<true, false><<<cgrid, 256, 0, stream>>>(m.X, count4, reinterpret_cast<uint2*>(hi), nullptr);
+    if (launches) ++*launches;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+
+    PrefillArgs pa{};
+    pa.W = m.W;
+    pa.bias = m.bias;
+    pa.Y = m.Y;
+    pa.M = m.M;
+    pa.N = m.N;
+    pa.K = m.K;
+    pa.w_row_bytes = m.w_row_bytes;
+    pa.status = status_dev;
+    pa.ksplit = choose_ksplit(m.M, m.N, m.K, mode, sm_count);
+    pa.bps = (m.K / kQK + pa.ksplit - 1) / pa.ksplit;
+    pa.Ypart = reinterpret_cast<float*>(lo + (mode == 0 ? (((size_t)m.M * m.K * 2u + 255u) & ~(size_t)255u) : 0));
+    for (int v = 0; v < (mode == 0 ? 2 : 1); v++) {
+        const cuuint64_t gdim[2] = {(cuuint64_t)m.K, (cuuint64_t)m.M};
+        const cuuint64_t gstride[1] = {(cuuint64_t)m.K * 2u};
+        const cuuint32_t box[2] = {kKStep, kTokTile};
+        const cuuint32_t estr[2] = {1u, 1u};
+        const CUresult r = enc(&pa.tmap_x[v], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, v == 0 ? hi : lo, gdim, gstride, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    }
+    if (mode != 0) pa.tmap_x[1] = pa.tmap_x[0];
+    if (mode == 0) e = launch_tc<128, 3, false>(pa, stream);
+    else if (mode == 1) e = launch_tc<256, 1, false>(pa, stream);
+    else e = launch_tc<256, 1, true>(pa, stream);
+    if (launches) ++*launches;
+    if (e != cudaSuccess) return e;
+    if (pa.ksplit > 1) {
+        const uint64_t MN = (uint64_t)m.M * m.N;
+        const unsigned rgrid = (unsigned)((MN + 255) / 256 < (uint64_t)sm_count * 8u ? (MN + 255) / 256 : (uint64_t)sm_count * 8u);
+        splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(pa.Ypart, pa.ksplit, MN, m.N, m.bias, m.Y);
+        if (launches) ++*launches;
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
+}  // namespace bpq4k

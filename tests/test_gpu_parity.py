@@ -196,6 +196,64 @@ def test_matmul_linearity_full_size(ctx, variant):
     assert ((y1 - ref).norm() / ref.norm()).item() <= REL_L2_TOL
 
 
+# ---------------------------------------------------------------- prefill (tensor-core kernel)
+
+PREFILL_MODES = [(q4k.PREFILL_F16X3, "f16x3"), (q4k.PREFILL_F16, "f16"), (q4k.PREFILL_BF16, "bf16")]
+
+
+@pytest.mark.parametrize("mode,name", PREFILL_MODES, ids=[m[1] for m in PREFILL_MODES])
+@pytest.mark.parametrize("M,N,K", [(64, 256, 256), (100, 130, 512), (256, 300, 1024), (300, 1024, 2048),
+                                   (512, 4096, 4096), (512, 1000, 14336)])
+def test_prefill_tensor_core(ctx, M, N, K, mode, name):
+    """M >= 64 goes to the tcgen05 kernel.  The three-pass half split must meet the float tolerance
+    of the path; the single-pass modes round weights and activations to 16 bits and are held to the
+    error that rounding implies (half: 2^-11 per operand, bfloat16: 2^-8)."""
+    import torch
+
+    raw = synth.make_q4k_weights(N, K, 60)
+    x = synth.make_activations(M, K, 61)
+    bias = np.linspace(-1, 1, N).astype(np.float32)
+    ctx.set_option(q4k.OPT_PREFILL_MODE, mode)
+    try:
+        w = ctx.upload(pack_q4k(raw, N, K))
+        ctx.launch_count(reset=True)
+        y = ctx.matmul(dev(torch, x), w, dev(torch, bias))
+        torch.cuda.synchronize()
+        assert ctx.launch_count() in (2, 3)     # activation cast + tensor-core kernel (+ split-K reduction)
+        assert ctx.device_status() == 0
+    finally:
+        ctx.set_option(q4k.OPT_PREFILL_MODE, q4k.PREFILL_F16X3)
+    y = y.cpu().numpy()
+    want = orc.matmul(x, raw, bias, N, K, threads=8)
+    assert np.isfinite(y).all()
+    if mode == q4k.PREFILL_F16X3:
+        check(y, want)
+    else:
+        tol = 1e-3 if mode == q4k.PREFILL_F16 else 8e-3
+        assert rel_l2(y, want) <= tol
+
+
+def test_prefill_threshold_option(ctx):
+    """BPQ4K_OPT_PREFILL_MIN_M moves the hand-over point between the streaming and the tensor-core kernel."""
+    import torch
+
+    N, K, M = 128, 512, 64
+    raw = synth.make_q4k_weights(N, K, 62)
+    x = synth.make_activations(M, K, 63)
+    w = ctx.upload(pack_q4k(raw, N, K))
+    want = orc.matmul(x, raw, None, N, K)
+    ctx.set_option(q4k.OPT_PREFILL_MIN_M, 65)
+    ctx.launch_count(reset=True)
+    y_stream = ctx.matmul(dev(torch, x), w).cpu().numpy()
+    n_stream = ctx.launch_count(reset=True)
+    ctx.set_option(q4k.OPT_PREFILL_MIN_M, 64)
+    y_tc = ctx.matmul(dev(torch, x), w).cpu().numpy()
+    n_tc = ctx.launch_count()
+    assert n_stream == 8 and n_tc in (2, 3)     # eight slabs of 8 rows vs. cast + tensor-core launch (+ reduction)
+    check(y_stream, want)
+    check(y_tc, want)
+
+
 # ---------------------------------------------------------------- MoE indirect form
 
 @pytest.mark.parametrize("variant", VARIANTS, ids=VARIANT_IDS)
