@@ -198,6 +198,34 @@ typedef struct bpq4k_host_matmul {
 
 int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items, uint32_t count, void* stream);
 
+/* The small-M matmul for callers that must not allocate device memory.  It has no counterpart
+ * in the reference.
+ *
+ * Such callers exist: a serving process that has handed all free device memory to its own pool
+ * (an allocation made by a library would fail or eat into that pool's budget), and any path
+ * that cannot afford the device-wide synchronisation inside cudaMalloc/cudaFree, such as a
+ * decode loop with other streams in flight.  They cannot create a handle either (bpq4k_create
+ * allocates), so this entry point takes none.
+ *
+ * Same arguments and result as bpq4k_matmul_f32 for M <= 8.  Its working memory (the
+ * activations re-coded for the tensor cores) is a fixed array inside the library, present on
+ * every device that loads it, so:
+ *   - sizes are limited: M <= 8 and (M rounded up to an even number) * K <= BPQ4K_NOALLOC_MAX_MK,
+ *     otherwise BPQ4K_ERR_UNSUPPORTED and a message in bpq4k_noalloc_last_error();
+ *   - all calls on a device share that array: calls that may overlap on the GPU (different
+ *     streams without an ordering between them, or different threads) race and must be
+ *     serialised by the caller; the array keeps the last call's contents, and each call
+ *     rewrites everything it will read, so no clearing is needed between calls;
+ *   - the first call on each device looks up the array's address on that device and should be
+ *     made before any stream capture begins.
+ * No cudaMalloc, cudaFree or allocating library routine is called.  Errors are reported per
+ * thread by bpq4k_noalloc_last_error(). */
+#define BPQ4K_NOALLOC_MAX_MK 131072u
+int bpq4k_matmul_noalloc_f32(const float* X, const void* W, const float* bias, float* Y,
+                             uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords,
+                             uint32_t yOffset, void* stream);
+const char* bpq4k_noalloc_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif
