@@ -550,7 +550,9 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     const uint64_t cap = (uint64_t)sm_count * per_sm;
     uint32_t gx = groups;
     if ((uint64_t)gx * slots_y > cap) {
-        const uint32_t cap_x = (uint32_t)((cap + slots_y - 1) / slots_y);
+        // CTAs per slot such that the whole 2-D grid fits the machine at once (never a partial second wave)
+        uint32_t cap_x = (uint32_t)(cap / slots_y);
+        if (cap_x == 0) cap_x = 1;
         const uint32_t rounds = (groups + cap_x - 1) / cap_x;
         gx = (groups + rounds - 1) / rounds;
     }

@@ -344,6 +344,10 @@ def run_gpu_arm(args, rank, world, local_rank):
         e2e_s = time.perf_counter() - t0
         sampler.stop()
 
+    prefill = None
+    if world == 1 and not args.no_prefill:
+        prefill = measure_prefill(ctx, torch, shapes, W, dev)
+
     times = torch.tensor([ms, kernel_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
     if dist:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -379,11 +383,56 @@ def run_gpu_arm(args, rank, world, local_rank):
             "cpu_baseline": cpu,
             "clocks": sampler.summary(),
         }
+        if prefill is not None:
+            line["prefill"] = prefill
         print(json.dumps(line), flush=True)
     if dist:
         dist.barrier()
         dist.destroy_process_group()
     _ = launches_eager
+
+
+def measure_prefill(ctx, torch, shapes, W, dev, M=512, reps=5):
+    """Config 2: the same projections at M = 512 through the tensor-core kernel; useful TFLOP/s
+    (2*M*N*K, extra passes not counted) per precision mode, summed over the eight projections."""
+    from backpack_b200 import q4k
+
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        peaks = {"bf16_tflops": p.get("bf16_tflops"), "bf16_tflops_sustained": p.get("bf16_tflops_sustained"),
+                 "peak_source": "measured"}
+    except Exception:
+        peaks = {"bf16_tflops": FALLBACK_PEAKS["bf16_tflops"], "bf16_tflops_sustained": None, "peak_source": "fallback"}
+    xs = {K: torch.randn(M, K, device=dev, generator=torch.Generator(device=dev).manual_seed(7)) for K in {k for _, _, k in shapes}}
+    ys = {n: torch.empty(M, N, device=dev) for n, N, _ in shapes}
+    flops = sum(2.0 * M * N * K for _, N, K in shapes)
+    out = {"workload": "llama3-8b prefill projections, M=512, Q4_K (config 2)", "M": M, "flops_per_pass": flops, **peaks,
+           "modes": {}}
+    for mode, name in ((q4k.PREFILL_F16X3, "f16x3"), (q4k.PREFILL_F16, "f16"), (q4k.PREFILL_BF16, "bf16")):
+        ctx.set_option(q4k.OPT_PREFILL_MODE, mode)
+
+        def one_pass():
+            for n, N, K in shapes:
+                ctx.matmul(xs[K], W[n], out=ys[n])
+
+        for _ in range(2):
+            one_pass()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            one_pass()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        tf = flops / (ms * 1e-3) / 1e12
+        out["modes"][name] = {"ms_per_pass": ms, "tflops": tf,
+                              "frac_of_burst_peak": tf / peaks["bf16_tflops"] if peaks.get("bf16_tflops") else None,
+                              "meets_float_tolerance": name == "f16x3"}
+    ctx.set_option(q4k.OPT_PREFILL_MODE, q4k.PREFILL_F16X3)
+    return out
 
 
 def main():
@@ -394,6 +443,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
     ap.add_argument("--ref-budget", type=float, default=120.0, help="seconds the --impl reference run may take")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the M=512 (config 2) measurement")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

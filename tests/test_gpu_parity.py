@@ -357,3 +357,42 @@ def test_launch_counter_counts_kernels(ctx):
     ctx.matmul(torch.zeros(1, K, device="cuda"), w)
     ctx.dequant(w)
     assert ctx.launch_count() >= 2
+
+
+# ---------------------------------------------------------------- benchmark configurations 3 and 4
+
+def test_moe_config3_shapes(ctx):
+    """128 experts, hidden 2048, expert FFN 768, 8 rows x 8 routed experts: gate/up share the row's
+    activations, down takes one activation row per (row, expert) pair."""
+    import torch
+
+    E, H, F, T, topk = 128, 2048, 768, 8, 8
+    ids = synth.make_moe_routing(T, E, topk, 5).reshape(-1)
+    x_rows = np.repeat(np.arange(T), topk).astype(np.int32)
+    # gate / up direction: [E*F, H]
+    raw_gate = synth.make_q4k_weights(E * F, H, 70)
+    wg = ctx.upload(pack_q4k(raw_gate, E * F, H))
+    x = synth.make_activations(T, H, 71)
+    off_g = (ids * F).astype(np.int32)
+    y = ctx.matmul_moe(dev(torch, x), wg, F, dev(torch, off_g), dev(torch, x_rows)).cpu().numpy()
+    want = orc.matmul_moe(x[x_rows], raw_gate, None, F, H, off_g.astype(np.uint32)).reshape(T * topk, F)
+    check(y, want)
+    # down direction: [E*H, F], K = 768 (three super-blocks per row)
+    raw_down = synth.make_q4k_weights(E * H, F, 72)
+    wd = ctx.upload(pack_q4k(raw_down, E * H, F))
+    xs = synth.make_activations(T * topk, F, 73)
+    off_d = (ids * H).astype(np.int32)
+    y = ctx.matmul_moe(dev(torch, xs), wd, H, dev(torch, off_d)).cpu().numpy()
+    want = orc.matmul_moe(xs, raw_down, None, H, F, off_d.astype(np.uint32)).reshape(T * topk, H)
+    check(y, want)
+
+
+@pytest.mark.parametrize("M", [1, 8])
+@pytest.mark.parametrize("N,K", [(8192, 8192), (1024, 8192), (3584, 8192), (1024, 28672)])
+def test_llama70b_shard_shapes(ctx, M, N, K):
+    """Config 4 shapes as one rank of an 8-way row split sees them (28672/8 = 3584 rows of gate/up,
+    8192/8 = 1024 rows of down with K = 28672), plus the unsplit q/k."""
+    raw = synth.make_q4k_weights(N, K, 80)
+    x = synth.make_activations(M, K, 81)
+    y = run_matmul(ctx, x, raw, None, N, K)
+    check(y, orc.matmul(x, raw, None, N, K, threads=8))
