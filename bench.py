@@ -217,6 +217,10 @@ def run_gpu_arm(args, rank, world, local_rank):
 
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     ctx = bp.Q4KContext(local_rank)
+    if args.no_pdl:
+        from backpack_b200 import q4k as _q4k
+
+        ctx.set_option(_q4k.OPT_STREAM_NO_PDL, 1)
     shapes = synth.LLAMA3_8B
     weights_h, xs_h = make_host_inputs(shapes, "config1", rank)
     dev = f"cuda:{local_rank}"
@@ -260,12 +264,13 @@ def run_gpu_arm(args, rank, world, local_rank):
         for _ in range(3):
             one_pass()
         stream.synchronize()
-        if world == 1:
+        if world == 1 or args.graph_multi:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 one_pass()
-        # (with several ranks the step is timed as eager launches: capturing the NCCL all-gathers
-        # together with the dependent-launch kernels into one graph did not complete on this pool)
+        # (with several ranks the step is timed as eager launches unless --graph-multi is given:
+        # capturing the NCCL all-gathers together with the dependent-launch kernels into one graph
+        # did not complete on this pool)
         run_step = graph.replay if graph is not None else one_pass
         for _ in range(max(args.warmup, 3)):
             run_step()
@@ -444,6 +449,8 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
     ap.add_argument("--ref-budget", type=float, default=120.0, help="seconds the --impl reference run may take")
     ap.add_argument("--no-prefill", action="store_true", help="skip the M=512 (config 2) measurement")
+    ap.add_argument("--graph-multi", action="store_true", help="with several ranks, replay the step from a CUDA graph too")
+    ap.add_argument("--no-pdl", action="store_true", help="launch the streaming kernel without programmatic dependent launch")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
