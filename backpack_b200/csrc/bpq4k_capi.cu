@@ -442,6 +442,62 @@ int bpq4k_matmul_host_f32(bpq4k_handle_t h, const float* X_host, const void* W_d
     return BPQ4K_OK;
 }
 
+int bpq4k_matmul_allgather_f32(bpq4k_handle_t h, const float* X, const void* W, const float* bias, float* const* slot_ptrs,
+                               uint32_t nPeers, uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords, void* stream) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return BPQ4K_OK;
+    if (int s = check_weights(h, W, N, K, rowStrideWords)) return s;
+    if (!X || !slot_ptrs) return fail(h, BPQ4K_ERR_INVALID_ARG, "X or slot_ptrs is null");
+    if (nPeers == 0 || nPeers > 8) return fail(h, BPQ4K_ERR_UNSUPPORTED, "nPeers=%u: 1..8 GPUs are supported", nPeers);
+    if (M > kStreamMaxM) return fail(h, BPQ4K_ERR_UNSUPPORTED, "the fused gather covers M <= %u (M=%u)", kStreamMaxM, M);
+    if (!aligned16(X)) return fail(h, BPQ4K_ERR_MISALIGNED, "X is not 16-byte aligned");
+    for (uint32_t p = 0; p < nPeers; p++)
+        if (!slot_ptrs[p] || (reinterpret_cast<uintptr_t>(slot_ptrs[p]) & 3u))
+            return fail(h, BPQ4K_ERR_INVALID_ARG, "slot_ptrs[%u] is null or misaligned", p);
+    DeviceGuard g(h->device);
+    MatmulArgs a{};
+    a.X = X;
+    a.W = static_cast<const uint8_t*>(W);
+    a.bias = bias;
+    a.Y = slot_ptrs[0];
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
+    a.n_peers = nPeers - 1;
+    for (uint32_t p = 1; p < nPeers; p++) a.peer_Y[p - 1] = slot_ptrs[p];
+    const size_t need = gemv_stream_scratch_bytes(M, K);
+    if (need > h->scratch_bytes) {
+        if (int s = ensure_bytes(h, &h->scratch, &h->scratch_bytes, need)) return s;
+    }
+    int launches = 0;
+    const cudaError_t e = launch_gemv_stream(a, h->tune, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count, &h->tmaps,
+                                             static_cast<cudaStream_t>(stream), &launches);
+    h->launches += (uint64_t)launches;
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return cuda_fail(h, e, "matmul launch");
+    }
+    return BPQ4K_OK;
+}
+
+int bpq4k_peer_barrier(bpq4k_handle_t h, uint32_t* const* flag_ptrs, uint32_t nPeers, uint32_t rank, uint32_t epoch,
+                       uint32_t timeout_ms, void* stream) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (!flag_ptrs || nPeers == 0 || nPeers > 8 || rank >= nPeers) return fail(h, BPQ4K_ERR_INVALID_ARG, "bad peer arguments");
+    for (uint32_t p = 0; p < nPeers; p++)
+        if (!flag_ptrs[p]) return fail(h, BPQ4K_ERR_INVALID_ARG, "flag_ptrs[%u] is null", p);
+    DeviceGuard g(h->device);
+    int khz = 0;
+    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, h->device);
+    if (khz <= 0) khz = 1900000;
+    const uint64_t cycles = (uint64_t)(timeout_ms ? timeout_ms : 1000u) * (uint64_t)khz;
+    const cudaError_t e = launch_peer_barrier(flag_ptrs, nPeers, rank, epoch, cycles, h->dev_status, static_cast<cudaStream_t>(stream));
+    h->launches += 1;
+    if (e != cudaSuccess) return cuda_fail(h, e, "barrier launch");
+    return BPQ4K_OK;
+}
+
 int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items, uint32_t count, void* stream) {
     if (!h) return BPQ4K_ERR_INVALID_ARG;
     if (count == 0) return BPQ4K_OK;

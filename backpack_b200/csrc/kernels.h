@@ -21,6 +21,9 @@ struct MatmulArgs {
     const uint32_t* x_rows;   // null: slot s reads row s
     uint32_t n_slots;         // 0 for the direct form
     uint64_t w_total_rows;    // indirect form: rows of the whole expert stack (bounds the copies)
+    // fused all-gather: every output is also stored to these buffers (other GPUs' memory, plain stores)
+    float* peer_Y[8];
+    uint32_t n_peers;
 };
 
 cudaError_t launch_dequant_f32(const uint8_t* W, uint32_t N, uint32_t K, uint64_t w_row_bytes, float* out,
@@ -68,6 +71,12 @@ cudaError_t launch_gemv_stream(const MatmulArgs& a, const StreamTuning& tune, vo
 size_t prefill_scratch_bytes(uint32_t M, uint32_t N, uint32_t K, int mode, int sm_count);
 cudaError_t launch_prefill_tc(const MatmulArgs& a, int mode, void* scratch, size_t scratch_bytes, int* status_dev,
                               int sm_count, cudaStream_t stream, int* launches);
+
+// Cross-GPU barrier on flag words in peer memory (one process per GPU): store `epoch` into slot
+// `rank` of every peer's flag array, then wait -- at most timeout_cycles -- until every slot of the
+// own array has reached `epoch`.  On a time-out the kernel stores kDeviceTimeout to *status.
+cudaError_t launch_peer_barrier(uint32_t* const* flag_ptrs_host, uint32_t n_peers, uint32_t rank, uint32_t epoch,
+                                uint64_t timeout_cycles, int* status_dev, cudaStream_t stream);
 
 // One warp per output row, float FMAs in the reference shader's arithmetic.
 cudaError_t launch_gemv_fp32(const MatmulArgs& a, cudaStream_t stream, int* launches);

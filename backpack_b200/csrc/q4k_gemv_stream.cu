@@ -489,7 +489,10 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
                 if (tok < M && row < N) {
                     float s = 0.f;
                     for (uint32_t k2 = 0; k2 < a.wk; k2++) s += gbuf[(uint64_t)k2 * (TOK * 16u) + idx];
-                    Y[(uint64_t)tok * N + row] = s + (a.m.bias ? a.m.bias[row] : 0.f);
+                    const float yv = s + (a.m.bias ? a.m.bias[row] : 0.f);
+                    Y[(uint64_t)tok * N + row] = yv;
+                    // fused all-gather: the same value goes straight into every peer's gather buffer
+                    for (uint32_t p = 0; p < a.m.n_peers; p++) a.m.peer_Y[p][(uint64_t)tok * N + row] = yv;
                 }
             }
         }

@@ -207,3 +207,18 @@ class Q4KContext:
         """One call: upload every X, run every matmul, read every Y back, wait once."""
         arr, _keep = batch
         self._check(self.lib.bpq4k_matmul_host_batch_f32(self.h, arr, len(arr), self._stream()))
+
+    # -- several GPUs (one process per GPU) ---------------------------------
+    def matmul_allgather(self, x, w: Q4KWeight, slot_ptrs, bias=None) -> None:
+        """Local product of this rank's row shard, stored straight into every rank's gather buffer.
+        slot_ptrs: ctypes array of device addresses, own slot first (see bpq4k_matmul_allgather_f32)."""
+        K = x.shape[-1]
+        M = x.numel() // K
+        self._check(self.lib.bpq4k_matmul_allgather_f32(
+            self.h, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
+            slot_ptrs, len(slot_ptrs), M, w.N, K, w.rowStrideWords, self._stream()))
+
+    def peer_barrier(self, flag_ptrs, rank: int, epoch: int, timeout_ms: int = 1000) -> None:
+        """Bounded cross-GPU barrier on this stream (bpq4k_peer_barrier)."""
+        self._check(self.lib.bpq4k_peer_barrier(self.h, flag_ptrs, len(flag_ptrs), rank, epoch, timeout_ms,
+                                                self._stream()))

@@ -101,3 +101,58 @@ def make_cuda_linear(ctx, raw: np.ndarray, N: int, K: int, world: int, rank: int
         return out
 
     return ShardedQ4KLinear(N, K, world, rank, w, fn, group)
+
+
+class PeerGather:
+    """Fused all-gather over peer-mapped memory for a set of projections.
+
+    One symmetric allocation per rank holds, for every projection, the gather buffer
+    [world][M][Ns]; the matmul kernel of rank g stores its slice into slot g of EVERY rank's
+    buffer (plain stores over NVLink), and one bounded flag barrier per step makes the slices
+    visible.  Replaces the per-projection NCCL all-gather of `ShardedQ4KLinear.forward`.
+    """
+
+    def __init__(self, ctx, world: int, rank: int, slots: dict, group=None, timeout_ms: int = 1000):
+        import ctypes as C
+
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        self.ctx, self.world, self.rank, self.timeout_ms = ctx, world, rank, timeout_ms
+        group = group or dist.group.WORLD
+        dev = torch.device(f"cuda:{ctx.device}")
+        self.offsets, total = {}, 0
+        for name, (M, Ns) in slots.items():
+            self.offsets[name] = (total, M, Ns)
+            total += world * M * Ns
+            total = (total + 63) // 64 * 64
+        self.buf = symm.empty(max(total, 64), dtype=torch.float32, device=dev)
+        self.flags = symm.empty(64, dtype=torch.int32, device=dev)
+        self.buf.zero_()
+        self.flags.zero_()
+        hb = symm.rendezvous(self.buf, group.group_name)
+        hf = symm.rendezvous(self.flags, group.group_name)
+        torch.cuda.synchronize()
+        dist.barrier(group=group)          # every rank's flags are zero before anyone signals
+        order = [rank] + [p for p in range(world) if p != rank]
+        self.slot_ptrs = {}
+        for name, (off, M, Ns) in self.offsets.items():
+            arr = (C.c_void_p * world)(*[int(hb.buffer_ptrs[p]) + (off + rank * M * Ns) * 4 for p in order])
+            self.slot_ptrs[name] = arr
+        self.flag_ptrs = (C.c_void_p * world)(*[int(hf.buffer_ptrs[p]) for p in range(world)])
+        self._handles = (hb, hf)
+        self.epoch = 0
+
+    def gathered(self, name: str):
+        """[world, M, Ns] view of this rank's gather buffer for one projection."""
+        off, M, Ns = self.offsets[name]
+        return self.buf[off: off + self.world * M * Ns].view(self.world, M, Ns)
+
+    def matmul(self, name: str, x, shard, bias=None) -> None:
+        self.ctx.matmul_allgather(x, shard, self.slot_ptrs[name], bias)
+
+    def barrier(self) -> None:
+        """Epoch 0 = self-advancing (the count lives in the flag array), so this call can be captured
+        into a CUDA graph and replayed."""
+        self.ctx.peer_barrier(self.flag_ptrs, self.rank, 0, self.timeout_ms)

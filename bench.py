@@ -227,6 +227,10 @@ def run_gpu_arm(args, rank, world, local_rank):
     from backpack_b200 import sharded
 
     W, X, Y, Yall, lin = {}, {}, {}, {}, {}
+    pg = None
+    if world > 1 and args.gather == "peer":
+        # fused all-gather: the matmul epilogue stores every slice into all ranks' gather buffers
+        pg = sharded.PeerGather(ctx, world, rank, {name: (1, N) for name, N, _ in shapes})
     for name, N, K in shapes:
         W[name] = ctx.upload(bp.pack_q4k(weights_h[name], N, K))
         X[name] = torch.from_numpy(xs_h[name]).to(dev)
@@ -242,10 +246,14 @@ def run_gpu_arm(args, rank, world, local_rank):
 
     def one_pass():
         for name, N, K in shapes:
-            if world > 1:
-                lin[name].forward(X[name], Yall[name])          # local product + all-gather of the slices
+            if pg is not None:
+                pg.matmul(name, X[name], W[name])               # local product, slices stored to every rank
+            elif world > 1:
+                lin[name].forward(X[name], Yall[name])          # local product + NCCL all-gather of the slices
             else:
                 ctx.matmul(X[name], W[name], out=Y[name])
+        if pg is not None:
+            pg.barrier()                                        # one bounded flag barrier per step
 
     # correctness spot-check before timing (one projection against the CPU checker)
     from oracle import q4k_oracle as orc
@@ -253,7 +261,7 @@ def run_gpu_arm(args, rank, world, local_rank):
     one_pass()
     torch.cuda.synchronize()
     want = orc.matmul(xs_h["k"], weights_h["k"], None, 1024, 4096)
-    got = Y["k"].reshape(1, -1).cpu().numpy()
+    got = (pg.gathered("k")[rank] if pg is not None else Y["k"]).reshape(1, -1).cpu().numpy()
     rel = float(np.linalg.norm(got - want) / np.linalg.norm(want))
     assert rel < 1e-3, f"parity check failed before timing: rel_l2={rel}"
 
@@ -264,7 +272,7 @@ def run_gpu_arm(args, rank, world, local_rank):
         for _ in range(3):
             one_pass()
         stream.synchronize()
-        if world == 1 or args.graph_multi:
+        if world == 1 or args.graph_multi or pg is not None:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 one_pass()
@@ -332,8 +340,15 @@ def run_gpu_arm(args, rank, world, local_rank):
             def e2e_pass():
                 for name, N, K in shapes:
                     X[name].copy_(xs_pin[name], non_blocking=True)
-                    lin[name].forward(X[name], Yall[name])
-                    yall_pin[name].copy_(Yall[name].view(-1), non_blocking=True)
+                    if pg is not None:
+                        pg.matmul(name, X[name], W[name])
+                    else:
+                        lin[name].forward(X[name], Yall[name])
+                        yall_pin[name].copy_(Yall[name].view(-1), non_blocking=True)
+                if pg is not None:
+                    pg.barrier()
+                    for name, N, K in shapes:
+                        yall_pin[name].copy_(pg.gathered(name).reshape(-1), non_blocking=True)
                 torch.cuda.current_stream().synchronize()
 
         for _ in range(3):
@@ -376,8 +391,11 @@ def run_gpu_arm(args, rank, world, local_rank):
             "config": {"workload": WORKLOAD, "M": 1, "projections": [list(s) for s in shapes],
                        "bytes_per_step_per_gpu": sb, "weight_bytes_per_step_per_gpu": weight_bytes_total(),
                        "l2": "inputs larger than L2 (418 MB of weights per pass vs 126 MB L2)",
-                       "replay": "cuda graph" if graph is not None else "eager + nccl all-gather",
-                       "sharding": "rows (N) per rank, output slices all-gathered" if world > 1 else "none"},
+                       "replay": "cuda graph" if graph is not None else "eager launches",
+                       "sharding": ("none" if world == 1 else
+                                    "rows (N) per rank; slices stored into every rank's gather buffer by the matmul "
+                                    "epilogue (peer memory), one flag barrier per step" if pg is not None else
+                                    "rows (N) per rank; NCCL all-gather per projection")},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": int(launches_per_step * args.steps),
@@ -449,6 +467,8 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
     ap.add_argument("--ref-budget", type=float, default=120.0, help="seconds the --impl reference run may take")
     ap.add_argument("--no-prefill", action="store_true", help="skip the M=512 (config 2) measurement")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="several ranks: fused peer-store all-gather (default) or one NCCL all-gather per projection")
     ap.add_argument("--graph-multi", action="store_true", help="with several ranks, replay the step from a CUDA graph too")
     ap.add_argument("--no-pdl", action="store_true", help="launch the streaming kernel without programmatic dependent launch")
     args = ap.parse_args()

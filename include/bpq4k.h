@@ -183,6 +183,29 @@ int bpq4k_matmul_host_f32(bpq4k_handle_t h, const float* X_host, const void* W_d
                           const float* bias_dev, float* Y_host, uint32_t M, uint32_t N, uint32_t K,
                           uint32_t rowStrideWords, void* stream);
 
+/* ---- several GPUs, one process per GPU ------------------------------------ */
+
+/* N-sharded matmul with the all-gather of the output slices fused into the kernel.  The
+ * reference is single-GPU; this is what the multi-GPU configurations add.  This rank owns N
+ * rows of the global matrix (W is its shard) and computes Y_slice[M][N]; the epilogue stores
+ * every value to slot_ptrs[0] (normally the rank's slot in its own gather buffer) and to
+ * slot_ptrs[1..nPeers-1] (the same slot in the other ranks' gather buffers, peer-mapped
+ * memory: plain stores over NVLink, nothing is loaded from a peer).  M <= 8.  The data is
+ * visible to a peer after that peer's next bpq4k_peer_barrier with this rank. */
+int bpq4k_matmul_allgather_f32(bpq4k_handle_t h, const float* X, const void* W, const float* bias,
+                               float* const* slot_ptrs, uint32_t nPeers, uint32_t M, uint32_t N, uint32_t K,
+                               uint32_t rowStrideWords, void* stream);
+
+/* Barrier between the ranks' streams over flag words in peer-mapped memory: writes `epoch` to
+ * flag_ptrs[p][rank] for every p, then waits until flag_ptrs[rank][p] >= epoch for every p.
+ * flag_ptrs[p] is rank p's flag array (64 words, zero-initialised); epochs must grow.  epoch 0
+ * means "the next one": the count is kept in word 63 of the rank's own array, which lets a
+ * barrier that is replayed from a CUDA graph advance by itself.  The
+ * wait is bounded: after timeout_ms (0: one second) the kernel gives up and sets the device
+ * status word (bpq4k_device_status then reports BPQ4K_ERR_TIMEOUT); it never traps. */
+int bpq4k_peer_barrier(bpq4k_handle_t h, uint32_t* const* flag_ptrs, uint32_t nPeers, uint32_t rank,
+                       uint32_t epoch, uint32_t timeout_ms, void* stream);
+
 /* A list of matmuls on host buffers served by ONE call: all activations go up, all kernels
  * run, all outputs come back, one wait.  This is how the reference runs a decode step -- a
  * pre-recorded list of Dispatch structs replayed by one queue submit, one small write before

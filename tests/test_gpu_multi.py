@@ -48,3 +48,86 @@ def test_two_gpu_sharded_matches_checker():
     ret = mgr.dict()
     mp.spawn(_worker, args=(2, 29650 + os.getpid() % 300, ret), nprocs=2, join=True)
     assert ret[0] and ret[1]
+
+
+def _peer_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+
+    import backpack_b200 as bp
+    from backpack_b200 import sharded, synth
+    from oracle import q4k_oracle as orc
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    ctx = bp.Q4KContext(rank)
+    cases = {"a": (1, 8192, 4096), "b": (8, 1024, 8192), "c": (3, 128, 512)}
+    pg = sharded.PeerGather(ctx, world, rank, {n: (M, sharded.shard_rows(N, world)) for n, (M, N, K) in cases.items()})
+    ok = True
+    for rep in range(2):                       # a second step reuses buffers and flags (epoch 2)
+        xs, raws = {}, {}
+        for n, (M, N, K) in cases.items():
+            raws[n] = synth.make_q4k_weights(N, K, 5 + rep)
+            xs[n] = synth.make_activations(M, K, 6 + rep)
+            ns = sharded.shard_rows(N, world)
+            w = ctx.upload(bp.pack_q4k(sharded.shard_raw(raws[n], N, K, world, rank), ns, K))
+            pg.matmul(n, torch.from_numpy(xs[n]).cuda(), w)
+        pg.barrier()
+        torch.cuda.synchronize()
+        ok = ok and ctx.device_status() == 0
+        for n, (M, N, K) in cases.items():
+            g = pg.gathered(n)                                     # [world, M, Ns]
+            y = g.permute(1, 0, 2).reshape(M, -1)[:, :N].cpu().numpy()
+            want = orc.matmul(xs[n], raws[n], None, N, K, threads=4)
+            rel = np.linalg.norm(y - want) / np.linalg.norm(want)
+            ok = ok and rel <= 1e-3 and np.abs(y - want).max() <= 2e-2
+        pg.barrier()                                               # nobody overwrites slots others still read
+        torch.cuda.synchronize()
+    ret[rank] = bool(ok)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_fused_peer_gather():
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_peer_worker, args=(2, 29950 + os.getpid() % 300, ret), nprocs=2, join=True)
+    assert ret[0] and ret[1]
+
+
+def test_peer_barrier_wait_is_bounded(ctx):
+    """A flag nothing ever sets: the barrier kernel must give up after its limit, report
+    BPQ4K_ERR_TIMEOUT through the device status word, and leave the context usable."""
+    import ctypes as C
+    import time
+
+    import torch
+
+    mine = torch.zeros(8, dtype=torch.int32, device="cuda")      # this GPU's flag array: slot 1 stays 0
+    other = torch.zeros(8, dtype=torch.int32, device="cuda")     # stands in for the absent peer's array
+    ptrs = (C.c_void_p * 2)(mine.data_ptr(), other.data_ptr())
+    t0 = time.time()
+    ctx.peer_barrier(ptrs, rank=0, epoch=1, timeout_ms=200)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0
+    from backpack_b200 import q4k
+
+    with pytest.raises(q4k.Q4KError) as e:
+        ctx.device_status()
+    assert e.value.status == 6
+    assert ctx.device_status() == 0                                # cleared by the read
+    assert int(other[0]) == 1 and int(mine[0]) == 1 and int(mine[1]) == 0
+    # satisfied barrier: both slots already at the epoch
+    mine[1] = 2
+    ctx.peer_barrier(ptrs, rank=0, epoch=2, timeout_ms=200)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
