@@ -14,7 +14,8 @@
 // process exits.
 //
 // Rules that follow from the shared, fixed scratch:
-//   * M <= 8 and (M rounded up to even) * K <= kNoAllocMaxMK, else BPQ4K_ERR_UNSUPPORTED.
+//   * M <= 8 and R * K <= kNoAllocMaxMK, where R = 1 for M = 1 and M rounded up to a multiple of 4
+//     otherwise; else BPQ4K_ERR_UNSUPPORTED.
 //   * The array keeps the previous call's contents.  Nothing in it has to start at zero for
 //     the next call: the quantising kernel rewrites the zero region, the digits and the
 //     per-sub-block sums of every activation row it is given, and rows beyond M are written as
@@ -68,10 +69,10 @@ int bpq4k_matmul_noalloc_f32(const float* X, const void* W, const float* bias, f
     if ((reinterpret_cast<uintptr_t>(X) & 15u) || (reinterpret_cast<uintptr_t>(W) & 15u))
         return fail(BPQ4K_ERR_MISALIGNED, "X or W is not 16-byte aligned");
     if (reinterpret_cast<uintptr_t>(Y) & 3u) return fail(BPQ4K_ERR_MISALIGNED, "Y is not 4-byte aligned");
-    const uint64_t rows_even = M <= 1 ? 1 : (uint64_t)(M + 1) / 2 * 2;
-    if (M > 8 || rows_even * K > kNoAllocMaxMK) {
+    const uint64_t rows_padded = M <= 1 ? 1 : (uint64_t)(M + 3) / 4 * 4;  // the kernel works on 4-row slots
+    if (M > 8 || rows_padded * K > kNoAllocMaxMK) {
         snprintf(g_error, sizeof(g_error),
-                 "M=%u, K=%u is beyond the fixed scratch: need M <= 8 and (M rounded up to even)*K <= %u", M, K,
+                 "M=%u, K=%u is beyond the fixed scratch: need M <= 8 and (M rounded up to a multiple of 4, or 1)*K <= %u", M, K,
                  kNoAllocMaxMK);
         return BPQ4K_ERR_UNSUPPORTED;
     }

@@ -38,8 +38,10 @@
 // mma of a sub-block and (d2, 0) in the second.  Pair j carries digits only in the mmas of
 // sub-block parity j%2 and zeros in the others, so after the four mmas of a 64-weight group
 // thread t holds the sums of sub-block parity t%2 -- the per-sub-block scaling work is
-// spread over the four threads of a quad without any shuffles.  With one activation row
-// (M1) pairs 2,3 repeat pairs 0,1 and threads t>=2 take row r+8.
+// spread over the four threads of a quad without any shuffles; pairs 2,3 repeat pairs 0,1 and
+// threads t>=2 take row r+8.  That is the single-row kernel (M1).  With several activation rows
+// the four pairs are four activation rows instead: every mma is one sub-block x four rows of X,
+// no zero columns, and thread t finishes activation row t for rows r and r+8 of the tile.
 #include <cuda.h>
 #include <cuda_fp16.h>
 
@@ -210,8 +212,7 @@ __device__ __forceinline__ void quantize_item(const float* __restrict__ X, uint3
 template <int NT, bool M1, bool XG, int PROBE = 0>
 __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int TOK = M1 ? 1 : NT * 2;  // token slots
-    constexpr int RPT = M1 ? 1 : 2;       // rows post-processed per thread
+    constexpr int TOK = M1 ? 1 : NT * 4;  // activation-row slots (four per 8-column mma tile)
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t nwarps = blockDim.x >> 5;
@@ -300,10 +301,9 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
     // B operand: column n = lane/4 -> pair n/2 (parity n/2%2), part n%2; t = lane%4
     const uint32_t bn = lane >> 2, bt = lane & 3u;
     const uint32_t b_par = (bn >> 1) & 1u;
-    const uint32_t b_tok = M1 ? 0u : (bn >> 2);  // token within an n-tile (0 or 1)
-    // C / post-processing role: column pair t
+    // C / post-processing role: column pair t.  M1: sub-block parity t%2 of row r (t < 2) or r+8.
+    // Otherwise: activation row t of the mma tile, both rows r and r+8, both parities.
     const uint32_t c_par = lane & 1u;
-    const uint32_t c_tok = M1 ? 0u : (bt >> 1);
     const uint32_t row_a = M1 ? (lane >> 2) + ((bt >> 1) << 3) : (lane >> 2);
     const uint32_t sel0 = 0x7440u + c_par, sel1 = 0x7442u + c_par;
     const float par_scale = c_par ? 0.0625f : 1.f;  // odd sub-blocks arrive as 16*q
@@ -322,13 +322,17 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
         xzero = smem_u32(smem + a.off_zero);
         s_addr = smem_u32(smem + a.off_S);
     }
-    const AddrT mine = xdata + (AddrT)(b_tok * NG) * 256u + b_par * 128u + (bn & 1u) * 64u + bt * 16u;
+    // M1: the lane's own parity block, or the zero region for the mmas of the other parity.
+    const AddrT mine = xdata + b_par * 128u + (bn & 1u) * 64u + bt * 16u;
     const AddrT pa0 = b_par == 0 ? mine : xzero;       // source for the even-sub-block mmas
     const AddrT pb0 = b_par == 1 ? mine : xzero;       // source for the odd-sub-block mmas
     const uint32_t stride_a = b_par == 0 ? 256u : 0u;  // per 64-weight group
     const uint32_t stride_b = b_par == 1 ? 256u : 0u;
-    const uint32_t tile_stride = 2u * NG * 256u;       // per n-tile (two tokens)
-    const AddrT s0_addr = s_addr + (AddrT)(c_tok * nb) * 64u + c_par * 32u;  // + blk*64 (+ nt*2*nb*64)
+    const AddrT s0_addr = s_addr + c_par * 32u;        // + blk*64
+    // several rows: column n carries activation row n/2 of the mma tile (digit column n%2); the even
+    // and the odd sub-block's 128-byte blocks follow each other
+    const AddrT gx_addr = xdata + (AddrT)((bn >> 1) * NG) * 256u + (bn & 1u) * 64u + bt * 16u;  // + nt*4*NG*256 + G*256 (+128)
+    const AddrT gs_addr = s_addr + (AddrT)(bt * nb) * 64u;                                         // + (nt*4*nb + blk)*64
     // 16-byte load at addr + OFF (OFF is folded into the instruction)
     auto load16 = [&](AddrT addr, auto off_tag) -> uint4 {
         constexpr int OFF = decltype(off_tag)::value;
@@ -341,11 +345,9 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
 
     for (uint32_t ti = 0; ti < my_tiles; ti++) {
         const uint32_t tile = tile0 + ti * tstride;
-        float acc[NT][RPT];
+        float acc[NT][2];
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-            for (int r = 0; r < RPT; r++) acc[nt][r] = 0.f;
+        for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = 0.f;
 
         for (uint32_t c = 0; c < nchunks; c++) {
             const uint32_t bs = b0 + c * a.cb;
@@ -365,11 +367,12 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
             }
             uint32_t boff = ring + st * a.stage_bytes;
             for (uint32_t blk = bs; PROBE != 1 && blk < bs + nblk; blk++, boff += kBlockBytes) {
+                if constexpr (M1) {
                 // scales of this thread's rows, its parity's four sub-blocks; the odd sub-block's
                 // weights reach the mma as 16*q, so its scale carries the 1/16
-                float dsc[RPT][4], dmn[RPT][4];
+                float dsc[1][4], dmn[1][4];
 #pragma unroll
-                for (int r = 0; r < RPT; r++) {
+                for (int r = 0; r < 1; r++) {
                     if constexpr (PROBE == 5) {
 #pragma unroll
                         for (int g = 0; g < 4; g++) dsc[r][g] = 1.f, dmn[r][g] = 2.f;
@@ -395,8 +398,8 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
                 uint4 Sv[NT], Iv[NT];  // per group: sum(xi)*inv and inv of this parity's sub-block
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
-                    Sv[nt] = load16(s0_addr + (AddrT)(nt * 2u * nb + blk) * 64u, std::integral_constant<int, 0>{});
-                    Iv[nt] = load16(s0_addr + (AddrT)(nt * 2u * nb + blk) * 64u, std::integral_constant<int, 16>{});
+                    Sv[nt] = load16(s0_addr + (AddrT)blk * 64u, std::integral_constant<int, 0>{});
+                    Iv[nt] = load16(s0_addr + (AddrT)blk * 64u, std::integral_constant<int, 16>{});
                 }
                 // data lanes advance 1 KiB per block (4 groups x 256 B); zero lanes stay inside the
                 // 1 KiB zero region, so the per-group offset g*256 is an immediate for both
@@ -416,8 +419,8 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
                     }
 #pragma unroll
                     for (int nt = 0; nt < NT; nt++) {
-                        const uint4 qa = load16(pa + (b_par == 0 ? nt * tile_stride : 0u), std::integral_constant<int, g * 256>{});
-                        const uint4 qb = load16(pb + (b_par == 1 ? nt * tile_stride : 0u), std::integral_constant<int, g * 256>{});
+                        const uint4 qa = load16(pa, std::integral_constant<int, g * 256>{});
+                        const uint4 qb = load16(pb, std::integral_constant<int, g * 256>{});
                         int c01[4], c2[4];  // column pair = digits (d0, d1) resp. (d2, 0)
                         if constexpr (PROBE == 3) {
                             c01[0] = e[0] ^ o[1] ^ qa.x ^ qb.y; c01[1] = e[1] ^ o[2] ^ qa.y ^ qb.z;
@@ -436,18 +439,81 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
                         // bracket fits int32 (< 2^26); the whole of T need not (16q weights), so
                         // the top digit joins in float: its sum (< 2^19) times 2^14 is exact.
                         const int u_lo = c01[1] * 128 + c2[0], u_hi = c01[3] * 128 + c2[2];  // rows r, r+8
-                        if constexpr (M1) {
-                            const bool hi = (bt & 2u) != 0;
-                            const float v = fmaf((float)(hi ? c01[2] : c01[0]), 16384.f, (float)(hi ? u_hi : u_lo)) * Ig;
-                            acc[nt][0] = fmaf(dsc[0][g], v, acc[nt][0]);
-                            acc[nt][0] = fmaf(-dmn[0][g], Sg, acc[nt][0]);
-                        } else {
-                            const float v_lo = fmaf((float)c01[0], 16384.f, (float)u_lo) * Ig;
-                            const float v_hi = fmaf((float)c01[2], 16384.f, (float)u_hi) * Ig;
-                            acc[nt][0] = fmaf(dsc[0][g], v_lo, acc[nt][0]);
-                            acc[nt][0] = fmaf(-dmn[0][g], Sg, acc[nt][0]);
-                            acc[nt][1] = fmaf(dsc[1][g], v_hi, acc[nt][1]);
-                            acc[nt][1] = fmaf(-dmn[1][g], Sg, acc[nt][1]);
+                        const bool hi = (bt & 2u) != 0;
+                        const float v = fmaf((float)(hi ? c01[2] : c01[0]), 16384.f, (float)(hi ? u_hi : u_lo)) * Ig;
+                        acc[nt][0] = fmaf(dsc[0][g], v, acc[nt][0]);
+                        acc[nt][0] = fmaf(-dmn[0][g], Sg, acc[nt][0]);
+                    }
+                };
+                do_group(std::integral_constant<int, 0>{});
+                do_group(std::integral_constant<int, 1>{});
+                do_group(std::integral_constant<int, 2>{});
+                do_group(std::integral_constant<int, 3>{});
+                } else {
+                // ---- several activation rows: every mma is one sub-block x four activation rows ----
+                // scales of rows r and r+8, all eight sub-blocks (odd ones carry the 1/16 of the 16q weights)
+                float dsc[2][8], dmn[2][8];
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    const uint4 hv = lds128<0>(boff + hdr_off + r * 8u * pitch);
+                    const BlockHeader h{hv.x, hv.y, hv.z, hv.w};
+                    const float d = half_bits_to_float(h.w0), dmin = half_bits_to_float(h.w0 >> 16);
+                    uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
+                    unpack_scales_packed(h, sc_lo, sc_hi, mn_lo, mn_hi);
+                    const float d16 = d * 0.0625f;
+                    const float nd = -d * 8388608.f, nd16 = -d16 * 8388608.f, ndm = -dmin * 8388608.f;
+#pragma unroll
+                    for (int sb = 0; sb < 8; sb++) {
+                        const uint32_t scw = __byte_perm(sb < 4 ? sc_lo : sc_hi, 0x4B000000u, 0x7440u + (sb & 3));
+                        const uint32_t mnw = __byte_perm(sb < 4 ? mn_lo : mn_hi, 0x4B000000u, 0x7440u + (sb & 3));
+                        dsc[r][sb] = (sb & 1) ? fmaf(d16, __uint_as_float(scw), nd16) : fmaf(d, __uint_as_float(scw), nd);
+                        dmn[r][sb] = fmaf(dmin, __uint_as_float(mnw), ndm);
+                    }
+                }
+                // per activation row of this thread (row t of each mma tile): sum(xi)*inv and inv, 8 sub-blocks
+                uint4 SIv[NT][4];  // [even: S', inv][odd: S', inv], four groups each
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const AddrT sa = gs_addr + (AddrT)(nt * 4u * nb + blk) * 64u;
+                    SIv[nt][0] = load16(sa, std::integral_constant<int, 0>{});
+                    SIv[nt][1] = load16(sa, std::integral_constant<int, 16>{});
+                    SIv[nt][2] = load16(sa, std::integral_constant<int, 32>{});
+                    SIv[nt][3] = load16(sa, std::integral_constant<int, 48>{});
+                }
+                const uint32_t lm_addr = boff + lm_off;
+                const AddrT gx_blk = gx_addr + (AddrT)blk * 1024u;
+                auto do_group = [&](auto gc) {
+                    constexpr int g = decltype(gc)::value;
+                    uint32_t r0, r1, r2, r3;
+                    ldmatrix_x4<g * 32>(lm_addr, r0, r1, r2, r3);
+                    constexpr uint32_t kLo = 0x0F0F0F0Fu, kHi = 0xF0F0F0F0u;
+                    const uint32_t e[4] = {r0 & kLo, r1 & kLo, r2 & kLo, r3 & kLo};  // q   (even sub-block)
+                    const uint32_t o[4] = {r0 & kHi, r1 & kHi, r2 & kHi, r3 & kHi};  // 16q (odd sub-block)
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        const AddrT xa = gx_blk + (AddrT)(nt * 4u * NG) * 256u;
+                        const uint4 qa = load16(xa, std::integral_constant<int, g * 256>{});        // even sub-block digits
+                        const uint4 qb = load16(xa, std::integral_constant<int, g * 256 + 128>{});  // odd sub-block digits
+                        int ce01[4], ce2[4], co01[4], co2[4];  // column pair = digits (d0, d1) resp. (d2, 0)
+                        imma16832_first(ce01, e[0], e[1], e[2], e[3], qa.x, qa.y);
+                        imma16832_first(ce2, e[0], e[1], e[2], e[3], qa.z, qa.w);
+                        imma16832_first(co01, o[0], o[1], o[2], o[3], qb.x, qb.y);
+                        imma16832_first(co2, o[0], o[1], o[2], o[3], qb.z, qb.w);
+                        auto pick = [](const uint4& v) { return g == 0 ? v.x : g == 1 ? v.y : g == 2 ? v.z : v.w; };
+                        const float Se = __uint_as_float(pick(SIv[nt][0])), Ie = __uint_as_float(pick(SIv[nt][1]));
+                        const float So = __uint_as_float(pick(SIv[nt][2])), Io = __uint_as_float(pick(SIv[nt][3]));
+                        // T = 2^14*sum(a d0) + (2^7*sum(a d1) + sum(a d2)); the bracket is exact in int32, the
+                        // top digit's sum (< 2^19) times 2^14 is exact in float
+#pragma unroll
+                        for (int r = 0; r < 2; r++) {
+                            const float te = fmaf((float)ce01[2 * r], 16384.f, (float)(ce01[2 * r + 1] * 128 + ce2[2 * r])) * Ie;
+                            const float to = fmaf((float)co01[2 * r], 16384.f, (float)(co01[2 * r + 1] * 128 + co2[2 * r])) * Io;
+                            float s2 = acc[nt][r];
+                            s2 = fmaf(dsc[r][2 * g], te, s2);
+                            s2 = fmaf(-dmn[r][2 * g], Se, s2);
+                            s2 = fmaf(dsc[r][2 * g + 1], to, s2);
+                            s2 = fmaf(-dmn[r][2 * g + 1], So, s2);
+                            acc[nt][r] = s2;
                         }
                     }
                 };
@@ -455,6 +521,7 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
                 do_group(std::integral_constant<int, 1>{});
                 do_group(std::integral_constant<int, 2>{});
                 do_group(std::integral_constant<int, 3>{});
+                }
             }
             // the stage is free: refill it with the unit `stages` ahead
             __syncwarp();
@@ -469,12 +536,15 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
 
         // ---- tile epilogue: parities -> K slices -> bias -> Y -------------------
         float* pbuf = part + ((uint64_t)((ti & 1u) * nwarps + warp)) * (TOK * 16u);
+        if constexpr (M1) {
+            // the two sub-block parities of a row sit in neighbouring lanes
+            const float s = acc[0][0] + __shfl_xor_sync(0xFFFFFFFFu, acc[0][0], 1);
+            if (c_par == 0) pbuf[row_a] = s;
+        } else {
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-#pragma unroll
-            for (int r = 0; r < RPT; r++) {
-                const float s = acc[nt][r] + __shfl_xor_sync(0xFFFFFFFFu, acc[nt][r], 1);
-                if (c_par == 0) pbuf[(nt * 2u + c_tok) * 16u + row_a + r * 8u] = s;
+            for (int nt = 0; nt < NT; nt++) {
+                pbuf[(nt * 4u + bt) * 16u + row_a] = acc[nt][0];
+                pbuf[(nt * 4u + bt) * 16u + row_a + 8u] = acc[nt][1];
             }
         }
         if (a.wk > 1) {
@@ -597,7 +667,7 @@ EncodeTiledFn encode_tiled_fn() {
 }  // namespace
 
 size_t gemv_stream_scratch_bytes(uint32_t M, uint32_t K) {
-    const uint32_t tokens = M <= 1 ? 1 : (M + 1) / 2 * 2;
+    const uint32_t tokens = M <= 1 ? 1 : (M + 3) / 4 * 4;
     return kZeroBytes + (size_t)tokens * K * 4 + (size_t)tokens * (K / 32) * 8 + 256;
 }
 
@@ -611,21 +681,29 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     const uint32_t nb = m.K / kQK;
     const uint32_t ntiles = (m.N + 15) / 16;
     const bool m1 = M == 1;
-    const int NT = m1 ? 1 : (int)((M + 1) / 2);
-    const uint32_t tokens = m1 ? 1 : NT * 2;
+    const int NT = m1 ? 1 : (int)((M + 3) / 4);
+    const uint32_t tokens = m1 ? 1 : NT * 4;
 
     // ---- plan ------------------------------------------------------------------
     constexpr uint32_t kSmemMax = 227 * 1024;
-    // Defaults from tuning sweeps on B200 over the Llama-3 projection shapes:
-    //   fewer tiles than SMs      16 warps, every warp a K slice of the CTA's one tile, 1-block stages
-    //   up to two tiles per SM    16 warps, K split 8 ways, one stage holds a warp's whole slice if small
-    //   more                      8 warps, wide stages (5 blocks), little or no K split
+    // Defaults from tuning sweeps on B200 over the Llama-3 8B and 70B projection shapes:
+    //   up to 1024 tiles   all warps the kernel allows (16 with one activation row), K split as far
+    //                      as possible while every tile group still gets its own resident CTA (one
+    //                      round, everything in flight at once), 1-block stages, 2 deep
+    //   more               8 warps, about 8 super-blocks per warp and tile, 5-block stages, 4 deep
     const uint64_t tiles_total = (uint64_t)ntiles * (indirect ? m.n_slots : 1);
-    const bool tiny = tiles_total < (uint64_t)sm_count;
-    const bool small = !tiny && tiles_total <= 2ull * sm_count;
-    uint32_t warps = tune.warps ? tune.warps : (m1 ? ((tiny || small) ? 16 : 8) : 8);
+    const bool small = tiles_total <= 1024;
+    uint32_t warps = tune.warps ? tune.warps : (m1 && small ? 16 : 8);
     if (!m1 && warps > 8) warps = 8;  // the multi-row kernels are built for 256 threads (more registers each)
-    uint32_t wk = tune.wk ? tune.wk : (tiny ? warps : small ? 8 : (tiles_total >= 16ull * sm_count ? 2 : 1));
+    uint32_t wk = tune.wk;
+    if (!wk) {
+        if (small) {
+            wk = 1;
+            while (wk * 2 <= warps && nb % (wk * 2) == 0 && tiles_total * (wk * 2) <= (uint64_t)sm_count * warps) wk *= 2;
+        } else {
+            wk = nb >= 64 ? 8 : nb >= 32 ? 4 : nb >= 16 ? 2 : 1;
+        }
+    }
     if (wk > nb) wk = nb;
     if (wk > warps) wk = warps;
     while (wk > 1 && (warps % wk || nb % wk)) wk--;
@@ -635,7 +713,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     // Stage = dense TMA box of 16 rows x cb blocks, then one box of rem blocks for the tail of
     // the warp's K range.  An odd cb keeps the 16-byte units of the eight rows an ldmatrix
     // touches in distinct bank groups (row pitch = cb*9 units).
-    uint32_t cb = tune.cb ? tune.cb : (tiny ? 1 : small ? (bpw <= 3 ? bpw : 1) : 5);
+    uint32_t cb = tune.cb ? tune.cb : (small ? 1 : 5);
     if (cb > 7) cb = 7;  // box width <= 256 words
     if (cb > bpw) cb = bpw;
     const uint32_t rem = bpw % cb;
@@ -656,7 +734,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     sa.m.M = M;
     // activations in shared memory if they leave room for at least 3 stages per warp
     bool xg = false;
-    uint32_t stages = tune.stages ? tune.stages : ((tiny || small) ? 2 : 4);
+    uint32_t stages = tune.stages ? tune.stages : (small ? 2 : 4);
     if (stages > kMaxStages) stages = kMaxStages;
     if (tune.force_scratch) xg = true;
     if (!xg) {
@@ -752,9 +830,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
 #endif
         if (m1) e = xg ? BPQ4K_LAUNCH(1, true, true) : BPQ4K_LAUNCH(1, true, false);
         else if (NT == 1) e = xg ? BPQ4K_LAUNCH(1, false, true) : BPQ4K_LAUNCH(1, false, false);
-        else if (NT == 2) e = xg ? BPQ4K_LAUNCH(2, false, true) : BPQ4K_LAUNCH(2, false, false);
-        else if (NT == 3) e = xg ? BPQ4K_LAUNCH(3, false, true) : BPQ4K_LAUNCH(3, false, false);
-        else e = xg ? BPQ4K_LAUNCH(4, false, true) : BPQ4K_LAUNCH(4, false, false);
+        else e = xg ? BPQ4K_LAUNCH(2, false, true) : BPQ4K_LAUNCH(2, false, false);
 #undef BPQ4K_LAUNCH
         if (launches) ++*launches;
         if (e != cudaSuccess) return e;

@@ -233,7 +233,8 @@ int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items
  * Same arguments and result as bpq4k_matmul_f32 for M <= 8.  Its working memory (the
  * activations re-coded for the tensor cores) is a fixed array inside the library, present on
  * every device that loads it, so:
- *   - sizes are limited: M <= 8 and (M rounded up to an even number) * K <= BPQ4K_NOALLOC_MAX_MK,
+ *   - sizes are limited: M <= 8 and R * K <= BPQ4K_NOALLOC_MAX_MK with R = 1 for M = 1, else M rounded
+ *     up to a multiple of 4,
  *     otherwise BPQ4K_ERR_UNSUPPORTED and a message in bpq4k_noalloc_last_error();
  *   - all calls on a device share that array: calls that may overlap on the GPU (different
  *     streams without an ordering between them, or different threads) race and must be
