@@ -687,12 +687,12 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     // ---- plan ------------------------------------------------------------------
     constexpr uint32_t kSmemMax = 227 * 1024;
     // Defaults from tuning sweeps on B200 over the Llama-3 8B and 70B projection shapes:
-    //   up to 1024 tiles   all warps the kernel allows (16 with one activation row), K split as far
+    //   up to 640 tiles    all warps the kernel allows (16 with one activation row), K split as far
     //                      as possible while every tile group still gets its own resident CTA (one
     //                      round, everything in flight at once), 1-block stages, 2 deep
     //   more               8 warps, about 8 super-blocks per warp and tile, 5-block stages, 4 deep
     const uint64_t tiles_total = (uint64_t)ntiles * (indirect ? m.n_slots : 1);
-    const bool small = tiles_total <= 1024;
+    const bool small = tiles_total <= 640;
     uint32_t warps = tune.warps ? tune.warps : (m1 && small ? 16 : 8);
     if (!m1 && warps > 8) warps = 8;  // the multi-row kernels are built for 256 threads (more registers each)
     uint32_t wk = tune.wk;
@@ -713,7 +713,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     // Stage = dense TMA box of 16 rows x cb blocks, then one box of rem blocks for the tail of
     // the warp's K range.  An odd cb keeps the 16-byte units of the eight rows an ldmatrix
     // touches in distinct bank groups (row pitch = cb*9 units).
-    uint32_t cb = tune.cb ? tune.cb : (small ? 1 : 5);
+    uint32_t cb = tune.cb ? tune.cb : (small ? (bpw <= 2 ? bpw : 1) : 5);
     if (cb > 7) cb = 7;  // box width <= 256 words
     if (cb > bpw) cb = bpw;
     const uint32_t rem = bpw % cb;

@@ -65,6 +65,15 @@ def pack_q4k(raw, N: int, K: int) -> KQuantPacked:
     return KQuantPacked(words, N, K, rs, nb)
 
 
+def fuse_kq(a: KQuantPacked, b: KQuantPacked) -> KQuantPacked:
+    """Vertical fusion of two packed tensors (rows of `b` after rows of `a`), as the reference's
+    loader fuses Q+K+V and gate+up so that one dispatch covers them
+    (`fuseKQ`, runtime/model_runner.cpp:1002-1012)."""
+    if a.K != b.K or a.rowStrideWords != b.rowStrideWords:
+        raise ValueError("fuse_kq needs equal K and row stride")
+    return KQuantPacked(np.concatenate([a.data, b.data]), a.N + b.N, a.K, a.rowStrideWords, a.nBlocks)
+
+
 @dataclass
 class Q4KWeight:
     """A packed weight resident on the device (a torch uint8 tensor owns the bytes)."""

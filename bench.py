@@ -50,6 +50,10 @@ METRIC = "q4k_matmul_m1_algorithmic_bandwidth"
 UNIT = "GB/s"
 WORKLOAD = "llama3-8b decode projections, M=1, Q4_K (config 1)"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+# DRAM read+write bytes of the streaming kernel divided by its algorithmic bytes, from one ncu capture
+# on a 151 MB case (65536 x 4096, M = 1); traffic grows with the rows, so a launch's traffic is this
+# ratio times its algorithmic bytes.
+TRAFFIC_RATIO = 1.026
 
 
 def load_peaks():
@@ -364,6 +368,47 @@ def run_gpu_arm(args, rank, world, local_rank):
         e2e_s = time.perf_counter() - t0
         sampler.stop()
 
+    fused = None
+    if world == 1:
+        # the same bytes with Q+K+V and gate+up fused by rows, as the reference's loader fuses them
+        # (fuseKQ): five launches instead of eight
+        groups = [("qkv", ["q", "k", "v"]), ("o", ["o"]), ("gate_up", ["gate", "up"]), ("down", ["down"]),
+                  ("lm_head", ["lm_head"])]
+        dims = {n: (N, K) for n, N, K in shapes}
+        FW, FX, FY = {}, {}, {}
+        for gname, members in groups:
+            packed = None
+            for mname in members:
+                pk = bp.pack_q4k(weights_h[mname], *dims[mname])
+                packed = pk if packed is None else bp.fuse_kq(packed, pk)
+            FW[gname] = ctx.upload(packed)
+            FX[gname] = X[members[0]]
+            FY[gname] = torch.zeros(1, packed.N, dtype=torch.float32, device=dev)
+
+        def fused_pass():
+            for gname, _ in groups:
+                ctx.matmul(FX[gname], FW[gname], out=FY[gname])
+
+        with torch.cuda.stream(stream):
+            fused_pass()
+            stream.synchronize()
+            fg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(fg, stream=stream):
+                fused_pass()
+            for _ in range(3):
+                fg.replay()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record(stream)
+            for _ in range(args.steps):
+                fg.replay()
+            f1.record(stream)
+            stream.synchronize()
+        fms = f0.elapsed_time(f1) / args.steps
+        fbytes = sum(synth.algorithmic_bytes(1, FW[g].N, FW[g].K) for g, _ in groups)
+        fused = {"what": "same weights, Q+K+V and gate+up fused by rows as the reference's loader does: 5 launches",
+                 "ms_per_step": fms, "value": fbytes / (fms * 1e-3) / 1e9, "unit": UNIT}
+        del FW, FY
+
     prefill = None
     if world == 1 and not args.no_prefill:
         prefill = measure_prefill(ctx, torch, shapes, W, dev)
@@ -400,7 +445,9 @@ def run_gpu_arm(args, rank, world, local_rank):
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": int(launches_per_step * args.steps),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "frac": achieved / peak, "traffic": per_launch_bytes * TRAFFIC_RATIO,
+                         "traffic_note": "ncu dram read+write of a 151 MB launch, scaled to the average launch by bytes",
+                         "peak_source": peak_src,
                          "kernel": "q4k matmul (M=1)", "launches_per_step": launches_per_step,
                          "avg_launch_us": per_launch_s * 1e6, "alg_bytes_per_launch": per_launch_bytes},
             "cpu_baseline": cpu,
@@ -408,6 +455,8 @@ def run_gpu_arm(args, rank, world, local_rank):
         }
         if prefill is not None:
             line["prefill"] = prefill
+        if fused is not None:
+            line["fused_projections"] = fused
         print(json.dumps(line), flush=True)
     if dist:
         dist.barrier()

@@ -58,3 +58,15 @@ def test_pack_host_is_identity():
     assert np.array_equal(p.data.view(np.uint8), w.reshape(-1))
     empty = pack_q4k(np.zeros(0, np.uint8), 0, 256)
     assert empty.data.size == 0
+
+
+def test_fuse_kq_concatenates_rows():
+    from backpack_b200 import fuse_kq
+    from oracle import q4k_oracle as orc
+
+    K = 512
+    q, k = synth.make_q4k_weights(6, K, 1), synth.make_q4k_weights(3, K, 2)
+    f = fuse_kq(pack_q4k(q, 6, K), pack_q4k(k, 3, K))
+    assert (f.N, f.K, f.rowStrideWords, f.nBlocks) == (9, K, 72, 2)
+    want = np.concatenate([orc.dequant(q, 6, K), orc.dequant(k, 3, K)])
+    assert np.array_equal(orc.dequant(f.data.view(np.uint8), 9, K), want)
