@@ -20,6 +20,8 @@ def main() -> None:
     ap.add_argument("M", type=int)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--variant", default="auto", choices=["auto", "fp32", "stream"])
+    ap.add_argument("--prefill-mode", default="f16x3", choices=["f16x3", "f16", "bf16"],
+                    help="precision mode of the tensor-core kernel (M >= 64)")
     args = ap.parse_args()
 
     import torch
@@ -29,6 +31,7 @@ def main() -> None:
 
     ctx = bp.Q4KContext(0)
     ctx.set_option(q4k.OPT_GEMV_VARIANT, {"auto": q4k.GEMV_AUTO, "fp32": q4k.GEMV_FP32, "stream": q4k.GEMV_STREAM}[args.variant])
+    ctx.set_option(q4k.OPT_PREFILL_MODE, {"f16x3": q4k.PREFILL_F16X3, "f16": q4k.PREFILL_F16, "bf16": q4k.PREFILL_BF16}[args.prefill_mode])
     w = ctx.upload(bp.pack_q4k(synth.make_q4k_weights(args.N, args.K, 0), args.N, args.K))
     x = torch.from_numpy(synth.make_activations(args.M, args.K, 1)).cuda()
     y = torch.zeros(args.M, args.N, device="cuda")
