@@ -149,14 +149,8 @@ constexpr float kXiMax = 2080000.f;
 // and per sub-block the two floats the kernel needs: inv = max|x|/kXiMax and sum(xi)*inv,
 //   SI[((tok*nb + blk)*2 + parity)*8 + {0: sum*inv, 4: inv} + g].
 // All 32 lanes of a warp must call this together (idle lanes pass valid = false).
-__device__ __forceinline__ void quantize_item(const float* __restrict__ X, uint32_t M, uint32_t K, uint32_t tok,
-                                              uint32_t c8, bool valid, uint8_t* frag, float* SI) {
-    float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
-    if (valid && tok < M) {
-        const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok * K + (uint64_t)c8 * 8u);
-        v0 = __ldg(xp);
-        v1 = __ldg(xp + 1);
-    }
+__device__ __forceinline__ void quantize_loaded(float4 v0, float4 v1, uint32_t K, uint32_t tok, uint32_t c8, bool valid,
+                                                uint8_t* frag, float* SI) {
     float amax = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
                        fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
@@ -205,12 +199,23 @@ __device__ __forceinline__ void quantize_item(const float* __restrict__ X, uint3
         si[4] = inv;
     }
 }
+// Load the 8 floats of an item (zeros for rows past M or an idle lane), then quantise them.
+__device__ __forceinline__ void quantize_item(const float* __restrict__ X, uint32_t M, uint32_t K, uint32_t tok,
+                                              uint32_t c8, bool valid, uint8_t* frag, float* SI) {
+    float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+    if (valid && tok < M) {
+        const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok * K + (uint64_t)c8 * 8u);
+        v0 = __ldg(xp);
+        v1 = __ldg(xp + 1);
+    }
+    quantize_loaded(v0, v1, K, tok, c8, valid, frag, SI);
+}
 
 // PROBE (development builds only, -DBPQ4K_ENABLE_PROBES): 0 = the kernel; 1 = copies and waits
 // only; 2 = math on whatever the ring holds, no copies; 3 = as 2 without the mmas; 4 = as 2
 // without the nibble decode; 5 = as 2 without the scale decode.  Used to attribute time.
 template <int NT, bool M1, bool XG, int PROBE = 0>
-__global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
+__global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TOK = M1 ? 1 : NT * 4;  // activation-row slots (four per 8-column mma tile)
 
@@ -282,13 +287,43 @@ __global__ void __launch_bounds__(M1 ? 512 : 256, 1) gemv_stream_kernel(const __
     if constexpr (!XG) {
         // one pass: every thread quantises 8-float items straight from global memory
         for (uint32_t i = tid; i < kZeroBytes / 4u; i += blockDim.x) reinterpret_cast<uint32_t*>(smem + a.off_zero)[i] = 0u;
-        const uint32_t per_row = K / 8u, items = (uint32_t)TOK * per_row;
-        for (uint32_t base = 0; base < items; base += blockDim.x) {
-            const uint32_t it = base + tid;
-            const bool valid = it < items;
-            const uint32_t tok = valid ? it / per_row : 0u;
-            quantize_item(X, M, K, tok, valid ? it - tok * per_row : 0u, valid, smem + a.off_x,
-                          reinterpret_cast<float*>(smem + a.off_S));
+        const uint32_t per_row = K / 8u;
+        uint8_t* frag = smem + a.off_x;
+        float* SI = reinterpret_cast<float*>(smem + a.off_S);
+        if constexpr (M1) {
+            for (uint32_t base = 0; base < per_row; base += blockDim.x) {
+                const uint32_t it = base + tid;
+                const bool valid = it < per_row;
+                quantize_item(X, M, K, 0u, valid ? it : 0u, valid, frag, SI);
+            }
+        } else {
+            // rows past M carry zeros: clear their digits and scales instead of quantising zeros
+            const uint32_t mrows = min(M, (uint32_t)TOK);
+            for (uint32_t i = mrows * K + tid; i < (uint32_t)TOK * K; i += blockDim.x) reinterpret_cast<uint32_t*>(frag)[i] = 0u;
+            for (uint32_t i = mrows * nb * 16u + tid; i < (uint32_t)TOK * nb * 16u; i += blockDim.x) SI[i] = 0.f;
+            // four items per thread and round, all loads issued before the first use
+            constexpr int U = 4;
+            const uint32_t items = mrows * per_row;
+            for (uint32_t base = 0; base < items; base += blockDim.x * U) {
+                float4 v[U][2];
+                uint32_t tok[U], c8[U];
+                bool valid[U];
+#pragma unroll
+                for (int j = 0; j < U; j++) {
+                    const uint32_t it = base + j * blockDim.x + tid;
+                    valid[j] = it < items;
+                    tok[j] = valid[j] ? it / per_row : 0u;
+                    c8[j] = valid[j] ? it - tok[j] * per_row : 0u;
+                    v[j][0] = v[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (valid[j]) {
+                        const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok[j] * K + (uint64_t)c8[j] * 8u);
+                        v[j][0] = __ldg(xp);
+                        v[j][1] = __ldg(xp + 1);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < U; j++) quantize_loaded(v[j][0], v[j][1], K, tok[j], c8[j], valid[j], frag, SI);
+            }
         }
         __syncthreads();
     }
@@ -693,15 +728,21 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     //   more               8 warps, about 8 super-blocks per warp and tile, 5-block stages, 4 deep
     const uint64_t tiles_total = (uint64_t)ntiles * (indirect ? m.n_slots : 1);
     const bool small = tiles_total <= 640;
-    uint32_t warps = tune.warps ? tune.warps : (m1 && small ? 16 : 8);
-    if (!m1 && warps > 8) warps = 8;  // the multi-row kernels are built for 256 threads (more registers each)
+    // Several activation rows (sweeps over the same shapes, M = 2, 4, 8): the digits of all rows
+    // should stay in shared memory, so the rings are narrower; with K > 4096 they do not fit
+    // next to any ring and more warps hide the latency of reading them through L1/L2 instead.
+    const bool wide_k = m.K > 4096;
+    uint32_t warps = tune.warps ? tune.warps : m1 ? (small ? 16 : 8) : NT == 1 ? (small || wide_k ? 16 : 8) : (!small && wide_k ? 12 : 8);
+    if (!m1 && NT > 1 && warps > 12) warps = 12;  // the eight-row kernel is built for 384 threads (more registers each)
     uint32_t wk = tune.wk;
     if (!wk) {
         if (small) {
             wk = 1;
             while (wk * 2 <= warps && nb % (wk * 2) == 0 && tiles_total * (wk * 2) <= (uint64_t)sm_count * warps) wk *= 2;
-        } else {
+        } else if (m1) {
             wk = nb >= 64 ? 8 : nb >= 32 ? 4 : nb >= 16 ? 2 : 1;
+        } else {
+            wk = !wide_k ? 1 : NT == 1 ? 8 : 4;
         }
     }
     if (wk > nb) wk = nb;
@@ -713,13 +754,11 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     // Stage = dense TMA box of 16 rows x cb blocks, then one box of rem blocks for the tail of
     // the warp's K range.  An odd cb keeps the 16-byte units of the eight rows an ldmatrix
     // touches in distinct bank groups (row pitch = cb*9 units).
-    uint32_t cb = tune.cb ? tune.cb : (small ? (bpw <= 2 ? bpw : 1) : 5);
+    uint32_t cb = tune.cb ? tune.cb : m1 ? (small ? (bpw <= 2 ? bpw : 1) : 5) : 3;
     if (cb > 7) cb = 7;  // box width <= 256 words
     if (cb > bpw) cb = bpw;
-    const uint32_t rem = bpw % cb;
-    const uint32_t stage_bytes = 16 * cb * kBlockBytes;
-
     const uint32_t x_bytes = tokens * m.K * 4u, S_bytes = tokens * (m.K / 32u) * 8u;
+    uint32_t stage_bytes = 0;
     auto layout = [&](bool xg, uint32_t stages, StreamArgs& sa) -> uint32_t {
         uint32_t off = kBarBytes;
         sa.off_zero = off; off += kZeroBytes;
@@ -732,17 +771,29 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     StreamArgs sa{};
     sa.m = m;
     sa.m.M = M;
-    // activations in shared memory if they leave room for at least 3 stages per warp
+    // activations in shared memory if they leave room for at least 2 stages per warp; with several
+    // activation rows a narrower stage (down to 2 blocks) is tried before giving up on that
     bool xg = false;
     uint32_t stages = tune.stages ? tune.stages : (small ? 2 : 4);
     if (stages > kMaxStages) stages = kMaxStages;
     if (tune.force_scratch) xg = true;
     if (!xg) {
-        uint32_t s_try = stages;
-        while (s_try >= 2 && layout(false, s_try, sa) > kSmemMax) s_try--;
-        if (s_try >= 2) stages = s_try;
-        else xg = true;
+        const uint32_t cb_min = (m1 || tune.cb || cb < 2) ? cb : 2;
+        bool fits = false;
+        for (uint32_t cb_try = cb; cb_try >= cb_min && !fits; cb_try--) {
+            stage_bytes = 16 * cb_try * kBlockBytes;
+            uint32_t s_try = stages;
+            while (s_try >= 2 && layout(false, s_try, sa) > kSmemMax) s_try--;
+            if (s_try >= 2) {
+                stages = s_try;
+                cb = cb_try;
+                fits = true;
+            }
+        }
+        if (!fits) xg = true;
     }
+    const uint32_t rem = bpw % cb;
+    stage_bytes = 16 * cb * kBlockBytes;
     if (xg) {
         while (stages > 1 && layout(true, stages, sa) > kSmemMax) stages--;
         if (indirect) return cudaErrorInvalidValue;  // per-slot activations are staged in shared memory only

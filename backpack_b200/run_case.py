@@ -1,6 +1,7 @@
 """Run one Q4_K matmul shape on cuda:0 a few times and report its time.
 
     python -m backpack_b200.run_case N K M [--reps R] [--variant auto|fp32|stream]
+                                           [--prefill-mode f16x3|f16|bf16] [--opt ID=VALUE ...]
 
 A small driver for profilers and quick checks: seeded synthetic weights and
 activations (backpack_b200.synth), `reps` back-to-back calls through the C ABI,
@@ -22,6 +23,8 @@ def main() -> None:
     ap.add_argument("--variant", default="auto", choices=["auto", "fp32", "stream"])
     ap.add_argument("--prefill-mode", default="f16x3", choices=["f16x3", "f16", "bf16"],
                     help="precision mode of the tensor-core kernel (M >= 64)")
+    ap.add_argument("--opt", action="append", default=[], metavar="ID=VALUE",
+                    help="set a numbered library option (see include/bpq4k.h), e.g. --opt 10=8 for 8 warps")
     args = ap.parse_args()
 
     import torch
@@ -32,6 +35,9 @@ def main() -> None:
     ctx = bp.Q4KContext(0)
     ctx.set_option(q4k.OPT_GEMV_VARIANT, {"auto": q4k.GEMV_AUTO, "fp32": q4k.GEMV_FP32, "stream": q4k.GEMV_STREAM}[args.variant])
     ctx.set_option(q4k.OPT_PREFILL_MODE, {"f16x3": q4k.PREFILL_F16X3, "f16": q4k.PREFILL_F16, "bf16": q4k.PREFILL_BF16}[args.prefill_mode])
+    for kv in args.opt:
+        k, v = kv.split("=")
+        ctx.set_option(int(k), int(v))
     w = ctx.upload(bp.pack_q4k(synth.make_q4k_weights(args.N, args.K, 0), args.N, args.K))
     x = torch.from_numpy(synth.make_activations(args.M, args.K, 1)).cuda()
     y = torch.zeros(args.M, args.N, device="cuda")
