@@ -18,7 +18,7 @@ struct bpq4k_context {
     char err[512] = "no error";
     int gemv_variant = BPQ4K_GEMV_AUTO;
     int prefill_mode = BPQ4K_PREFILL_F16X3;
-    int prefill_min_m = 64;
+    int prefill_min_m = 25;  // four 8-row slabs of the streaming kernel cost as much as one tensor-core pass
     uint64_t launches = 0;
     // staging for the *_host entry point
     float* stage_x = nullptr;

@@ -1,4 +1,4 @@
-// Prefill Q4_K matmul (M >= 64) on the 5th-generation tensor cores: weights are dequantised
+// Prefill Q4_K matmul (M >= 25 by default) on the 5th-generation tensor cores: weights are dequantised
 // on chip into 16-bit tiles, multiplied with tcgen05.mma, accumulated in TMEM.
 //
 // The reference has no tensor-core path for Q4_K: its "prefill" is q4k_matmul_batched8

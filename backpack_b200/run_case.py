@@ -22,7 +22,7 @@ def main() -> None:
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--variant", default="auto", choices=["auto", "fp32", "stream"])
     ap.add_argument("--prefill-mode", default="f16x3", choices=["f16x3", "f16", "bf16"],
-                    help="precision mode of the tensor-core kernel (M >= 64)")
+                    help="precision mode of the tensor-core kernel (large M)")
     ap.add_argument("--opt", action="append", default=[], metavar="ID=VALUE",
                     help="set a numbered library option (see include/bpq4k.h), e.g. --opt 10=8 for 8 warps")
     args = ap.parse_args()

@@ -47,6 +47,54 @@ def make_q4k_weights(N: int, K: int, seed: int = 0) -> np.ndarray:
     return blk.reshape(N, nb * BLOCK_BYTES)
 
 
+# Sibling K-quant formats (reference GGUFType numbers, runtime/gguf_loader.h:27-30).
+Q4_K, Q5_K, Q6_K = 12, 13, 14
+KQ_BLOCK_BYTES = {Q4_K: 144, Q5_K: 176, Q6_K: 210}
+
+
+def make_kq_weights(qtype: int, N: int, K: int, seed: int = 0) -> np.ndarray:
+    """uint8 [N, K/256*block_bytes] raw super-blocks of a K-quant type, GGUF layout, no padding.
+
+    Q5_K: d, dmin and scale bytes as for Q4_K, 32 fifth-bit bytes and 128 nibble bytes uniform.
+    Q6_K: 128 + 64 code bytes uniform (6-bit codes uniform 0..63), 16 signed scales uniform
+    -128..127, fp16 d ~ U(1e-4, 2e-3) (so that weights have a spread of order 1).
+    """
+    if qtype == Q4_K:
+        return make_q4k_weights(N, K, seed)
+    if K % QK_K:
+        raise ValueError(f"K={K} is not a multiple of {QK_K}")
+    nb = K // QK_K
+    rng = np.random.default_rng(seed)
+    nblk = N * nb
+    bb = KQ_BLOCK_BYTES[qtype]
+    blk = np.empty((nblk, bb), np.uint8)
+    if qtype == Q5_K:
+        d = rng.uniform(1e-3, 2e-2, nblk).astype(np.float16)
+        dmin = rng.uniform(0.0, 1e-2, nblk).astype(np.float16)
+        blk[:, 0:2] = d.view(np.uint8).reshape(nblk, 2)
+        blk[:, 2:4] = dmin.view(np.uint8).reshape(nblk, 2)
+        blk[:, 4:16] = rng.integers(0, 256, (nblk, 12), dtype=np.uint8)
+        blk[:, 16:48] = rng.integers(0, 256, (nblk, 32), dtype=np.uint8)
+        blk[:, 48:] = rng.integers(0, 256, (nblk, 128), dtype=np.uint8)
+    elif qtype == Q6_K:
+        d = rng.uniform(1e-4, 2e-3, nblk).astype(np.float16)
+        blk[:, 0:192] = rng.integers(0, 256, (nblk, 192), dtype=np.uint8)
+        blk[:, 192:208] = rng.integers(0, 256, (nblk, 16), dtype=np.uint8)
+        blk[:, 208:210] = d.view(np.uint8).reshape(nblk, 2)
+    else:
+        raise ValueError(f"unknown K-quant type {qtype}")
+    return blk.reshape(N, nb * bb)
+
+
+def kq_weight_bytes(qtype: int, N: int, K: int) -> int:
+    return N * (K // QK_K) * KQ_BLOCK_BYTES[qtype]
+
+
+def kq_algorithmic_bytes(qtype: int, M: int, N: int, K: int, bias: bool = False) -> int:
+    """As algorithmic_bytes, with the file-format block size of the type (no padding counted)."""
+    return kq_weight_bytes(qtype, N, K) + M * K * 4 + M * N * 4 + (N * 4 if bias else 0)
+
+
 def make_activations(M: int, K: int, seed: int = 0) -> np.ndarray:
     """float32 [M, K] ~ N(0, 1)."""
     return np.random.default_rng(seed).standard_normal((M, K), dtype=np.float32)

@@ -64,7 +64,7 @@ typedef enum bpq4k_status {
 typedef enum bpq4k_option {
     BPQ4K_OPT_GEMV_VARIANT = 1,  /* bpq4k_gemv_variant; default AUTO */
     BPQ4K_OPT_PREFILL_MODE = 2,  /* bpq4k_prefill_mode; default F16X3 */
-    BPQ4K_OPT_PREFILL_MIN_M = 3, /* smallest M routed to the tensor-core prefill kernel; default 64 */
+    BPQ4K_OPT_PREFILL_MIN_M = 3, /* smallest M routed to the tensor-core prefill kernel; default 25 */
     /* Tuning of the streaming kernel; 0 = automatic.  The reference tunes its decode
      * kernels through an autotune cache (runtime/model_runner.cpp:5113-5199). */
     BPQ4K_OPT_STREAM_WARPS = 10,         /* warps per CTA, <= 16 */
@@ -153,8 +153,9 @@ int bpq4k_dequant_f32(bpq4k_handle_t h, const void* W, uint32_t N, uint32_t K,
  * X, W, Bias, Y and params {K, N, nBlocks, rowStrideWords, yOffset}
  * (runtime/model_runner.cpp:2404-2413).  Grid and tile choices are internal.
  * `bias` may be NULL (the reference always binds a zero buffer).  X and W must be
- * 16-byte aligned; Y (outputs are written one float at a time) 4-byte aligned.  M >= the PREFILL_MIN_M option goes to the
- * tensor-core kernel in the PREFILL_MODE option's precision. */
+ * 16-byte aligned; Y (outputs are written one float at a time) 4-byte aligned.
+ * M >= the PREFILL_MIN_M option goes to the tensor-core kernel in the PREFILL_MODE
+ * option's precision; smaller M runs the streaming kernel in slabs of 8 rows. */
 int bpq4k_matmul_f32(bpq4k_handle_t h, const float* X, const void* W, const float* bias, float* Y,
                      uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords,
                      uint32_t yOffset, void* stream);

@@ -1,4 +1,4 @@
-"""Python doorway to the CPU checker for the Q4_K path.
+"""Python doorway to the CPU checker for the Q4_K path and its Q5_K / Q6_K siblings.
 
 TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the
 benchmark's CPU-baseline leg; never by the shipped package.
@@ -57,6 +57,11 @@ def lib() -> C.CDLL:
         L.oracle_q4k_matmul_moe_slot.argtypes = [_fp, C.c_void_p, _fp, _fp, _u32, _u32, _u32,
                                                  C.POINTER(_u32), _u32, _u32]
         L.oracle_q4k_matmul_f64.argtypes = [_fp, C.c_void_p, _fp, C.POINTER(C.c_double), _u32, _u32, _u32]
+        L.oracle_kq_block_bytes.restype = _u32
+        L.oracle_kq_block_bytes.argtypes = [_u32]
+        L.oracle_kq_dequant.argtypes = [_u32, C.c_void_p, _fp, _u32, _u32]
+        L.oracle_kq_pack.argtypes = [_u32, C.c_void_p, _u32, _u32, C.c_void_p, C.POINTER(_u32), C.POINTER(_u32)]
+        L.oracle_kq_matmul.argtypes = [_u32, _fp, C.c_void_p, _fp, _fp, _u32, _u32, _u32, _u32]
         _lib = L
     return _lib
 
@@ -73,6 +78,9 @@ def ref_lib() -> C.CDLL:
         L.ref_q4k_dequant.argtypes = [C.c_void_p, _fp, _u32, _u32]
         L.ref_pack_q4k.argtypes = [C.c_void_p, _u32, _u32, C.c_void_p, C.POINTER(_u32), C.POINTER(_u32)]
         L.ref_q4k_matmul.argtypes = [_fp, C.c_void_p, _fp, _fp, _u32, _u32, _u32, _u32]
+        L.ref_kq_dequant.argtypes = [_u32, C.c_void_p, _fp, _u32, _u32]
+        L.ref_kq_pack.argtypes = [_u32, C.c_void_p, _u32, _u32, C.c_void_p, C.POINTER(_u32), C.POINTER(_u32)]
+        L.ref_kq_matmul.argtypes = [_u32, _fp, C.c_void_p, _fp, _fp, _u32, _u32, _u32, _u32]
         _ref = L
     return _ref
 
@@ -166,6 +174,100 @@ def pack(raw: np.ndarray, N: int, K: int, use_ref: bool = False):
     if words.size:
         fn(raw.ctypes.data, N, K, words.ctypes.data, C.byref(rs), C.byref(nb))
     return words, rs.value, nb.value
+
+
+# --------------------------------------------------------------------------
+# The K-quant family by type number (reference GGUFType: Q4_K 12, Q5_K 13, Q6_K 14)
+# --------------------------------------------------------------------------
+
+Q4_K, Q5_K, Q6_K = 12, 13, 14
+KQ_BLOCK_BYTES = {Q4_K: 144, Q5_K: 176, Q6_K: 210}
+
+
+def kq_dequant(qtype: int, raw: np.ndarray, N: int, K: int, use_ref: bool = False) -> np.ndarray:
+    """float32 [N, K] weights from N rows of K/256 raw super-blocks of the given type."""
+    raw = _raw(raw)
+    assert raw.size >= N * (K // QK_K) * KQ_BLOCK_BYTES[qtype]
+    out = np.zeros((N, K), np.float32)
+    if N and K:
+        fn = ref_lib().ref_kq_dequant if use_ref else lib().oracle_kq_dequant
+        fn(qtype, raw.ctypes.data, _f(out), N, K)
+    return out
+
+
+def kq_matmul(qtype: int, x: np.ndarray, raw: np.ndarray, bias: np.ndarray | None, N: int, K: int,
+              threads: int = 1, use_ref: bool = False) -> np.ndarray:
+    """Y[M, N] = bias + X[M, K] . deq(W)[N, K]^T, float32, k ascending, for any K-quant type."""
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, K)
+    M = x.shape[0]
+    raw = _raw(raw)
+    y = np.zeros((M, N), np.float32)
+    b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    if M == 0 or N == 0:
+        return y
+    fn = ref_lib().ref_kq_matmul if use_ref else lib().oracle_kq_matmul
+    fn(qtype, _f(x), raw.ctypes.data, _f(b) if b is not None else None, _f(y), M, N, K, threads)
+    return y
+
+
+def kq_pack(qtype: int, raw: np.ndarray, N: int, K: int, use_ref: bool = False):
+    """(words u32[N*rowStrideWords], rowStrideWords, nBlocks) as pack_q4k/q5k/q6k return them."""
+    raw = _raw(raw)
+    rs, nb = _u32(0), _u32(0)
+    fn = ref_lib().ref_kq_pack if use_ref else lib().oracle_kq_pack
+    fn(qtype, raw.ctypes.data, N, K, None, C.byref(rs), C.byref(nb))
+    words = np.zeros(N * rs.value, np.uint32)
+    if words.size:
+        fn(qtype, raw.ctypes.data, N, K, words.ctypes.data, C.byref(rs), C.byref(nb))
+    return words, rs.value, nb.value
+
+
+def kq_dequant_numpy(qtype: int, raw: np.ndarray, N: int, K: int) -> np.ndarray:
+    """Independent vectorised restatement of the Q5_K / Q6_K branches of dequant_kquant
+    (runtime/gguf_loader.cpp:497-573); Q4_K goes to dequant_numpy."""
+    if qtype == Q4_K:
+        return dequant_numpy(raw, N, K)
+    nb = K // QK_K
+    bb = KQ_BLOCK_BYTES[qtype]
+    blk = _raw(raw)[: N * nb * bb].reshape(N * nb, bb)
+    out = np.zeros((N, K), np.float32)
+    if qtype == Q5_K:
+        d = blk[:, 0:2].copy().view(np.float16).astype(np.float32)
+        dmin = blk[:, 2:4].copy().view(np.float16).astype(np.float32)
+        p = blk[:, 4:16].astype(np.uint32)
+        sc = np.empty((N * nb, 8), np.uint32)
+        mn = np.empty((N * nb, 8), np.uint32)
+        sc[:, :4] = p[:, 0:4] & 63
+        mn[:, :4] = p[:, 4:8] & 63
+        sc[:, 4:] = (p[:, 8:12] & 15) | ((p[:, 0:4] >> 2) & 0x30)
+        mn[:, 4:] = (p[:, 8:12] >> 4) | ((p[:, 4:8] >> 2) & 0x30)
+        qh = blk[:, 16:48].astype(np.uint32)                               # [B, 32]
+        codes = blk[:, 48:].reshape(N * nb, 4, 32).astype(np.uint32)
+        q = np.empty((N * nb, 8, 32), np.uint32)
+        q[:, 0::2] = codes & 15
+        q[:, 1::2] = codes >> 4
+        for sb in range(8):
+            q[:, sb] |= ((qh >> sb) & 1) << 4
+        s = (d * sc.astype(np.float32)).astype(np.float32)
+        m = (dmin * mn.astype(np.float32)).astype(np.float32)
+        w = (s[:, :, None] * q.astype(np.float32)).astype(np.float32) - m[:, :, None]
+        out[:, : nb * QK_K] = w.astype(np.float32).reshape(N, nb * QK_K)
+        return out
+    # Q6_K
+    d = blk[:, 208:210].copy().view(np.float16).astype(np.float32)         # [B, 1]
+    sc = blk[:, 192:208].copy().view(np.int8).astype(np.float32)           # [B, 16]
+    ql = blk[:, 0:128].reshape(N * nb, 2, 2, 32).astype(np.int32)          # [B, half, byte group (l, l+32), l]
+    qh = blk[:, 128:192].reshape(N * nb, 2, 32).astype(np.int32)           # [B, half, l]
+    q = np.empty((N * nb, 2, 4, 32), np.int32)                             # [B, half, group of 32, l]
+    q[:, :, 0] = (ql[:, :, 0] & 15) | (((qh >> 0) & 3) << 4)
+    q[:, :, 1] = (ql[:, :, 1] & 15) | (((qh >> 2) & 3) << 4)
+    q[:, :, 2] = (ql[:, :, 0] >> 4) | (((qh >> 4) & 3) << 4)
+    q[:, :, 3] = (ql[:, :, 1] >> 4) | (((qh >> 6) & 3) << 4)
+    q -= 32
+    ds = (d * sc).astype(np.float32).reshape(N * nb, 2, 4, 2)              # scale index = half*8 + group*2 + l//16
+    w = (np.repeat(ds, 16, axis=3) * q.astype(np.float32)).astype(np.float32)
+    out[:, : nb * QK_K] = w.reshape(N, nb * QK_K)
+    return out
 
 
 # --------------------------------------------------------------------------

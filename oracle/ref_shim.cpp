@@ -1,5 +1,5 @@
 // ref_shim.cpp -- C-callable doorway into the reference's own CPU code for the
-// Q4_K path, so the restatement in q4k_oracle.c can be checked against it and
+// Q4_K path (and its Q5_K / Q6_K siblings), so the restatement in q4k_oracle.c can be checked against it and
 // so the benchmark can time the reference itself on the host cores.
 //
 // TEST INFRASTRUCTURE ONLY.  This file contains no reference code: it includes
@@ -66,6 +66,60 @@ void ref_q4k_matmul(const float* X, const void* raw, const float* bias, float* Y
         uint32_t n0 = (uint32_t)((uint64_t)N * t / threads);
         uint32_t n1 = (uint32_t)((uint64_t)N * (t + 1) / threads);
         pool.emplace_back([=]() { rows(X, src, bias, Y, M, N, K, n0, n1); });
+    }
+    for (auto& th : pool) th.join();
+}
+
+// ---- any K-quant type the reference's dequant_kquant knows (Q4_K = 12, Q5_K = 13, Q6_K = 14) ----
+
+static uint32_t block_bytes(uint32_t type) { return type == 12 ? 144u : type == 13 ? 176u : type == 14 ? 210u : 0u; }
+
+// dequant_kquant -- runtime/gguf_loader.cpp:455-573
+void ref_kq_dequant(uint32_t type, const void* raw, float* out, uint32_t N, uint32_t K) {
+    dequant_kquant(raw, out, N, K, (GGUFType)type);
+}
+
+// pack_q4k / pack_q5k / pack_q6k -- runtime/gguf_loader.cpp:359-424
+void ref_kq_pack(uint32_t type, const void* raw, uint32_t N, uint32_t K, uint32_t* words,
+                 uint32_t* rowStrideWords, uint32_t* nBlocks) {
+    KQuantPacked p = type == 13 ? pack_q5k(raw, N, K) : type == 14 ? pack_q6k(raw, N, K) : pack_q4k(raw, N, K);
+    if (rowStrideWords) *rowStrideWords = p.rowStrideWords;
+    if (nBlocks) *nBlocks = p.nBlocks;
+    if (words) std::memcpy(words, p.data.data(), p.data.size() * sizeof(uint32_t));
+}
+
+// Expected-value computation of the Q5_K / Q6_K kernel tests (runtime/tests/kernel_test.cpp:
+// 1669-1676, 1691-1698, 1732-1742): same loops as above, any type.
+static void kq_rows(uint32_t type, const float* X, const uint8_t* raw, const float* bias, float* Y,
+                    uint32_t M, uint32_t N, uint32_t K, uint32_t n0, uint32_t n1) {
+    const uint32_t nb = K / 256, SLAB = 64, bb = block_bytes(type);
+    std::vector<float> deq((size_t)SLAB * K);
+    for (uint32_t s0 = n0; s0 < n1; s0 += SLAB) {
+        const uint32_t cnt = (n1 - s0 < SLAB) ? n1 - s0 : SLAB;
+        dequant_kquant(raw + (size_t)s0 * nb * bb, deq.data(), cnt, K, (GGUFType)type);
+        for (uint32_t m = 0; m < M; m++)
+            for (uint32_t r = 0; r < cnt; r++) {
+                const uint32_t n = s0 + r;
+                float a = bias ? bias[n] : 0.0f;
+                for (uint32_t k = 0; k < K; k++) a += X[(size_t)m * K + k] * deq[(size_t)r * K + k];
+                Y[(size_t)m * N + n] = a;
+            }
+    }
+}
+
+void ref_kq_matmul(uint32_t type, const float* X, const void* raw, const float* bias, float* Y,
+                   uint32_t M, uint32_t N, uint32_t K, uint32_t threads) {
+    const uint8_t* src = (const uint8_t*)raw;
+    if (!block_bytes(type)) return;
+    if (threads <= 1 || N < threads) {
+        kq_rows(type, X, src, bias, Y, M, N, K, 0, N);
+        return;
+    }
+    std::vector<std::thread> pool;
+    for (uint32_t t = 0; t < threads; t++) {
+        uint32_t n0 = (uint32_t)((uint64_t)N * t / threads);
+        uint32_t n1 = (uint32_t)((uint64_t)N * (t + 1) / threads);
+        pool.emplace_back([=]() { kq_rows(type, X, src, bias, Y, M, N, K, n0, n1); });
     }
     for (auto& th : pool) th.join();
 }

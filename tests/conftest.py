@@ -19,6 +19,16 @@ def golden():
     return dict(np.load(path))
 
 
+@pytest.fixture(scope="session")
+def kq_golden():
+    """Reference-generated vectors for the Q5_K / Q6_K siblings (tests/golden/make_golden_kq.py)."""
+    return dict(np.load(os.path.join(ROOT, "tests", "golden", "kq_golden.npz")))
+
+
+KQ_GOLDEN_MATMUL = ["kt_q5k_matmul", "kt_q6k_matmul", "kt_q6k_matmul_wide", "kt_q5k_matmul_batched4",
+                    "kt_q6k_matmul_batched4", "corner_q5k", "corner_q6k", "synthetic_q5k", "synthetic_q6k"]
+KQ_GOLDEN_GATHER = ["kt_q6k_gather", "kt_q6k_gather_batched"]
+
 GOLDEN_CASES = ["kt_q4k_matmul", "kt_q4k_matmul_128", "kt_q4k_matmul_batched4", "kt_q4k_matmul_batched8",
                 "corner", "synthetic"]
 
