@@ -51,6 +51,13 @@ SIGNATURES["bpq4k_matmul_allgather_f32"] = (C.c_int, [vp, vp, vp, vp, C.POINTER(
 SIGNATURES["bpq4k_peer_barrier"] = (C.c_int, [vp, C.POINTER(vp), u32, u32, u32, u32, vp])
 SIGNATURES["bpq4k_matmul_host_batch_f32"] = (C.c_int, [vp, C.POINTER(HostMatmul), u32, vp])
 
+SIGNATURES["bpq4k_kq_block_bytes"] = (u32, [C.c_int])
+SIGNATURES["bpq4k_kq_row_stride_words"] = (u32, [C.c_int, u32])
+SIGNATURES["bpq4k_kq_pack_host"] = (C.c_int, [C.c_int, vp, u32, u32, vp])
+SIGNATURES["bpq4k_kq_dequant_f32"] = (C.c_int, [vp, C.c_int, vp, u32, u32, u32, vp, vp])
+SIGNATURES["bpq4k_kq_gather_f32"] = (C.c_int, [vp, C.c_int, vp, u32, u32, u32, vp, u32, vp, vp])
+SIGNATURES["bpq4k_kq_matmul_f32"] = (C.c_int, [vp, C.c_int, vp, vp, vp, vp, u32, u32, u32, u32, u32, vp])
+
 _lib = None
 
 

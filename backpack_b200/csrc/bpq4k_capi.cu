@@ -384,6 +384,113 @@ int bpq4k_matmul_f32(bpq4k_handle_t h, const float* X, const void* W, const floa
     return run_matmul(h, a, static_cast<cudaStream_t>(stream));
 }
 
+// ---- Q5_K / Q6_K siblings ----------------------------------------------------
+
+uint32_t bpq4k_kq_block_bytes(int qtype) {
+    return qtype == BPQ4K_TYPE_Q4_K ? 144u : qtype == BPQ4K_TYPE_Q5_K ? 176u : qtype == BPQ4K_TYPE_Q6_K ? 210u : 0u;
+}
+
+uint32_t bpq4k_kq_row_stride_words(int qtype, uint32_t K) {
+    return (bpq4k_n_blocks(K) * bpq4k_kq_block_bytes(qtype) + 3u) / 4u;
+}
+
+int bpq4k_kq_pack_host(int qtype, const void* raw_host, uint32_t N, uint32_t K, uint32_t* words_host) {
+    const uint32_t bb = bpq4k_kq_block_bytes(qtype);
+    if (!bb) return BPQ4K_ERR_UNSUPPORTED;
+    if ((!raw_host || !words_host) && N != 0 && K != 0) return BPQ4K_ERR_INVALID_ARG;
+    const uint64_t row_bytes = (uint64_t)bpq4k_n_blocks(K) * bb;
+    const uint64_t stride = bpq4k_kq_row_stride_words(qtype, K);
+    const uint8_t* src = static_cast<const uint8_t*>(raw_host);
+    for (uint32_t r = 0; r < N; r++) {
+        uint8_t* dst = reinterpret_cast<uint8_t*>(words_host + r * stride);
+        std::memcpy(dst, src + r * row_bytes, row_bytes);
+        std::memset(dst + row_bytes, 0, stride * 4u - row_bytes);
+    }
+    return BPQ4K_OK;
+}
+
+namespace {
+int check_kq_weights(bpq4k_context* h, int qtype, const void* W, uint32_t K, uint32_t rowStrideWords) {
+    const uint32_t bb = bpq4k_kq_block_bytes(qtype);
+    if (!bb) return fail(h, BPQ4K_ERR_UNSUPPORTED, "quantisation type %d is not Q4_K (12), Q5_K (13) or Q6_K (14)", qtype);
+    if (K == 0 || K % BPQ4K_QK_K != 0)
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "K=%u is not a positive multiple of 256", K);
+    if (!W) return fail(h, BPQ4K_ERR_INVALID_ARG, "W is null");
+    const uint32_t need = bpq4k_kq_row_stride_words(qtype, K);
+    if (rowStrideWords < need)
+        return fail(h, BPQ4K_ERR_INVALID_ARG, "rowStrideWords=%u is smaller than the %u words a row of K=%u needs", rowStrideWords, need, K);
+    if (qtype == BPQ4K_TYPE_Q6_K) {
+        if (reinterpret_cast<uintptr_t>(W) & 3u) return fail(h, BPQ4K_ERR_MISALIGNED, "W is not 4-byte aligned");
+    } else {
+        if (rowStrideWords % 4u != 0)
+            return fail(h, BPQ4K_ERR_MISALIGNED, "rowStrideWords=%u is not a multiple of 4 words (16 bytes)", rowStrideWords);
+        if (!aligned16(W)) return fail(h, BPQ4K_ERR_MISALIGNED, "W is not 16-byte aligned");
+    }
+    return BPQ4K_OK;
+}
+}  // namespace
+
+int bpq4k_kq_dequant_f32(bpq4k_handle_t h, int qtype, const void* W, uint32_t N, uint32_t K, uint32_t rowStrideWords,
+                         float* out, void* stream) {
+    if (qtype == BPQ4K_TYPE_Q4_K) return bpq4k_dequant_f32(h, W, N, K, rowStrideWords, out, stream);
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (N == 0) return BPQ4K_OK;
+    if (int s = check_kq_weights(h, qtype, W, K, rowStrideWords)) return s;
+    if (!out) return fail(h, BPQ4K_ERR_INVALID_ARG, "out is null");
+    if (!aligned16(out)) return fail(h, BPQ4K_ERR_MISALIGNED, "out is not 16-byte aligned");
+    DeviceGuard g(h->device);
+    cudaError_t e = launch_kq_dequant_f32(qtype, static_cast<const uint8_t*>(W), nullptr, N, N, K, (uint64_t)rowStrideWords * 4u,
+                                          out, static_cast<cudaStream_t>(stream));
+    h->launches += 1;
+    if (e != cudaSuccess) return cuda_fail(h, e, "dequant launch");
+    return BPQ4K_OK;
+}
+
+int bpq4k_kq_gather_f32(bpq4k_handle_t h, int qtype, const void* W, uint32_t nRows, uint32_t K, uint32_t rowStrideWords,
+                        const uint32_t* tokens, uint32_t nTokens, float* out, void* stream) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (nTokens == 0) return BPQ4K_OK;
+    if (qtype == BPQ4K_TYPE_Q4_K) return fail(h, BPQ4K_ERR_UNSUPPORTED, "the embedding gather covers Q5_K and Q6_K tables");
+    if (int s = check_kq_weights(h, qtype, W, K, rowStrideWords)) return s;
+    if (!out || !tokens) return fail(h, BPQ4K_ERR_INVALID_ARG, "out or tokens is null");
+    if (!aligned16(out)) return fail(h, BPQ4K_ERR_MISALIGNED, "out is not 16-byte aligned");
+    DeviceGuard g(h->device);
+    cudaError_t e = launch_kq_dequant_f32(qtype, static_cast<const uint8_t*>(W), tokens, nRows, nTokens, K,
+                                          (uint64_t)rowStrideWords * 4u, out, static_cast<cudaStream_t>(stream));
+    h->launches += 1;
+    if (e != cudaSuccess) return cuda_fail(h, e, "gather launch");
+    return BPQ4K_OK;
+}
+
+int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W, const float* bias, float* Y,
+                        uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords, uint32_t yOffset, void* stream) {
+    if (qtype == BPQ4K_TYPE_Q4_K) return bpq4k_matmul_f32(h, X, W, bias, Y, M, N, K, rowStrideWords, yOffset, stream);
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return BPQ4K_OK;
+    if (int s = check_kq_weights(h, qtype, W, K, rowStrideWords)) return s;
+    if (!X || !Y) return fail(h, BPQ4K_ERR_INVALID_ARG, "X or Y is null");
+    if (reinterpret_cast<uintptr_t>(X) & 3u) return fail(h, BPQ4K_ERR_MISALIGNED, "X is not 4-byte aligned");
+    if (reinterpret_cast<uintptr_t>(Y) & 3u) return fail(h, BPQ4K_ERR_MISALIGNED, "Y is not 4-byte aligned");
+    DeviceGuard g(h->device);
+    MatmulArgs a{};
+    a.X = X;
+    a.W = static_cast<const uint8_t*>(W);
+    a.bias = bias;
+    a.Y = Y + yOffset;
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
+    int launches = 0;
+    const cudaError_t e = launch_kq_gemv_fp32(qtype, a, static_cast<cudaStream_t>(stream), &launches);
+    h->launches += (uint64_t)launches;
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return cuda_fail(h, e, "matmul launch");
+    }
+    return BPQ4K_OK;
+}
+
 int bpq4k_matmul_moe_f32(bpq4k_handle_t h, const float* X, const void* W, const float* bias, float* Y,
                          const uint32_t* offsets, const uint32_t* x_rows, uint32_t nSlots, uint32_t N, uint32_t K,
                          uint32_t rowStrideWords, uint32_t wRows, void* stream) {

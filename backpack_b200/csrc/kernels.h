@@ -81,4 +81,10 @@ cudaError_t launch_peer_barrier(uint32_t* const* flag_ptrs_host, uint32_t n_peer
 // One warp per output row, float FMAs in the reference shader's arithmetic.
 cudaError_t launch_gemv_fp32(const MatmulArgs& a, cudaStream_t stream, int* launches);
 
+// Q5_K (qtype 13) and Q6_K (qtype 14) on the reference's packed layout: bit-exact dequantiser
+// (source row r = rows[r] when `rows` is given, zeros for ids >= n_src_rows) and float-FMA matmul.
+cudaError_t launch_kq_dequant_f32(int qtype, const uint8_t* W, const uint32_t* rows, uint32_t n_src_rows, uint32_t N,
+                                  uint32_t K, uint64_t w_row_bytes, float* out, cudaStream_t stream);
+cudaError_t launch_kq_gemv_fp32(int qtype, const MatmulArgs& a, cudaStream_t stream, int* launches);
+
 }  // namespace bpq4k

@@ -23,6 +23,8 @@ from . import _lib
 QK_K = 256
 BLOCK_BYTES = 144
 BLOCK_WORDS = 36
+# the reference's GGUFType numbers (runtime/gguf_loader.h:27-30)
+Q4_K, Q5_K, Q6_K = 12, 13, 14
 
 OPT_GEMV_VARIANT = 1
 OPT_PREFILL_MODE = 2
@@ -48,6 +50,34 @@ class KQuantPacked:
     K: int
     rowStrideWords: int
     nBlocks: int
+    qtype: int = Q4_K
+
+
+def pack_kq(qtype: int, raw, N: int, K: int) -> KQuantPacked:
+    """pack_q4k / pack_q5k / pack_q6k (runtime/gguf_loader.cpp:359-424): rows of raw blocks copied
+    into u32 words; Q6_K rows (210-byte blocks) are padded with zeros to a whole word."""
+    lib = _lib.load()
+    bb = lib.bpq4k_kq_block_bytes(qtype)
+    if not bb:
+        raise ValueError(f"unknown K-quant type {qtype}")
+    raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+    nb = lib.bpq4k_n_blocks(K)
+    rs = lib.bpq4k_kq_row_stride_words(qtype, K)
+    if raw.size < N * nb * bb:
+        raise ValueError(f"raw has {raw.size} bytes, need {N * nb * bb}")
+    words = np.zeros(N * rs, np.uint32)
+    st = lib.bpq4k_kq_pack_host(qtype, raw.ctypes.data, N, K, words.ctypes.data)
+    if st:
+        raise Q4KError(st, "pack_kq")
+    return KQuantPacked(words, N, K, rs, nb, qtype)
+
+
+def pack_q5k(raw, N: int, K: int) -> KQuantPacked:
+    return pack_kq(Q5_K, raw, N, K)
+
+
+def pack_q6k(raw, N: int, K: int) -> KQuantPacked:
+    return pack_kq(Q6_K, raw, N, K)
 
 
 def pack_q4k(raw, N: int, K: int) -> KQuantPacked:
@@ -69,9 +99,9 @@ def fuse_kq(a: KQuantPacked, b: KQuantPacked) -> KQuantPacked:
     """Vertical fusion of two packed tensors (rows of `b` after rows of `a`), as the reference's
     loader fuses Q+K+V and gate+up so that one dispatch covers them
     (`fuseKQ`, runtime/model_runner.cpp:1002-1012)."""
-    if a.K != b.K or a.rowStrideWords != b.rowStrideWords:
-        raise ValueError("fuse_kq needs equal K and row stride")
-    return KQuantPacked(np.concatenate([a.data, b.data]), a.N + b.N, a.K, a.rowStrideWords, a.nBlocks)
+    if a.K != b.K or a.rowStrideWords != b.rowStrideWords or a.qtype != b.qtype:
+        raise ValueError("fuse_kq needs equal K, row stride and type")
+    return KQuantPacked(np.concatenate([a.data, b.data]), a.N + b.N, a.K, a.rowStrideWords, a.nBlocks, a.qtype)
 
 
 @dataclass
@@ -81,6 +111,7 @@ class Q4KWeight:
     N: int
     K: int
     rowStrideWords: int
+    qtype: int = Q4_K
 
     @property
     def nbytes(self) -> int:
@@ -89,7 +120,7 @@ class Q4KWeight:
     def rows(self, n0: int, n1: int) -> "Q4KWeight":
         """A contiguous row range [n0, n1) as a view: rows are contiguous byte ranges."""
         rb = self.rowStrideWords * 4
-        return Q4KWeight(self.buf[n0 * rb:n1 * rb], n1 - n0, self.K, self.rowStrideWords)
+        return Q4KWeight(self.buf[n0 * rb:n1 * rb], n1 - n0, self.K, self.rowStrideWords, self.qtype)
 
 
 class Q4KContext:
@@ -152,15 +183,30 @@ class Q4KContext:
         host = torch.from_numpy(packed.data.view(np.uint8))
         buf = torch.empty(max(host.numel(), 16), dtype=torch.uint8, device=f"cuda:{self.device}")
         buf[: host.numel()].copy_(host)
-        return Q4KWeight(buf, packed.N, packed.K, packed.rowStrideWords)
+        return Q4KWeight(buf, packed.N, packed.K, packed.rowStrideWords, packed.qtype)
 
     # -- operators -------------------------------------------------------
     def dequant(self, w: Q4KWeight, out=None):
         torch = self._torch
         if out is None:
             out = torch.empty((w.N, w.K), dtype=torch.float32, device=w.buf.device)
-        self._check(self.lib.bpq4k_dequant_f32(self.h, w.buf.data_ptr(), w.N, w.K, w.rowStrideWords,
-                                               out.data_ptr(), self._stream()))
+        if w.qtype == Q4_K:
+            self._check(self.lib.bpq4k_dequant_f32(self.h, w.buf.data_ptr(), w.N, w.K, w.rowStrideWords,
+                                                   out.data_ptr(), self._stream()))
+        else:
+            self._check(self.lib.bpq4k_kq_dequant_f32(self.h, w.qtype, w.buf.data_ptr(), w.N, w.K, w.rowStrideWords,
+                                                      out.data_ptr(), self._stream()))
+        return out
+
+    def gather(self, w: Q4KWeight, tokens, out=None):
+        """Embedding lookup (q6k_gather / q6k_gather_batched): out[t] = deq(W)[tokens[t]]; tokens int32/uint32 on the device."""
+        torch = self._torch
+        assert tokens.is_cuda and tokens.dtype in (torch.int32, torch.uint32) and tokens.is_contiguous()
+        T = tokens.numel()
+        if out is None:
+            out = torch.empty((T, w.K), dtype=torch.float32, device=w.buf.device)
+        self._check(self.lib.bpq4k_kq_gather_f32(self.h, w.qtype, w.buf.data_ptr(), w.N, w.K, w.rowStrideWords,
+                                                 tokens.data_ptr(), T, out.data_ptr(), self._stream()))
         return out
 
     def matmul(self, x, w: Q4KWeight, bias=None, out=None, y_offset: int = 0):
@@ -173,9 +219,14 @@ class Q4KContext:
         M = x.numel() // K if K else 0
         if out is None:
             out = torch.empty(tuple(x.shape[:-1]) + (w.N,), dtype=torch.float32, device=x.device)
-        self._check(self.lib.bpq4k_matmul_f32(
-            self.h, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
-            out.data_ptr(), M, w.N, K, w.rowStrideWords, y_offset, self._stream()))
+        if w.qtype == Q4_K:
+            self._check(self.lib.bpq4k_matmul_f32(
+                self.h, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
+                out.data_ptr(), M, w.N, K, w.rowStrideWords, y_offset, self._stream()))
+        else:
+            self._check(self.lib.bpq4k_kq_matmul_f32(
+                self.h, w.qtype, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
+                out.data_ptr(), M, w.N, K, w.rowStrideWords, y_offset, self._stream()))
         return out
 
     def matmul_moe(self, x, w: Q4KWeight, n_rows_per_expert: int, offsets, x_rows=None, bias=None, out=None):

@@ -222,6 +222,42 @@ typedef struct bpq4k_host_matmul {
 
 int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items, uint32_t count, void* stream);
 
+/* ---- the Q5_K and Q6_K siblings -------------------------------------------
+ * Real "Q4_K_M" files mix Q4_K with Q5_K / Q6_K tensors (token embedding and output
+ * head are usually Q6_K).  These entry points take the reference's GGUFType number
+ * (runtime/gguf_loader.h:27-30) and accept all three types; for Q4_K they are the
+ * entry points above.  Weights are the reference's packed words: raw GGUF blocks
+ * (176 B for Q5_K, 210 B for Q6_K), rows rowStrideWords words apart, Q6_K rows
+ * padded with zeros to a whole word (pack_q5k / pack_q6k, runtime/gguf_loader.cpp:381-424). */
+enum bpq4k_qtype { BPQ4K_TYPE_Q4_K = 12, BPQ4K_TYPE_Q5_K = 13, BPQ4K_TYPE_Q6_K = 14 };
+
+/* Bytes per 256-weight block in the file format (144, 176, 210); 0 for an unknown type. */
+uint32_t bpq4k_kq_block_bytes(int qtype);
+/* rowStrideWords of KQuantPacked: ceil(ceil(K/256) * block bytes / 4). */
+uint32_t bpq4k_kq_row_stride_words(int qtype, uint32_t K);
+/* pack_q4k / pack_q5k / pack_q6k: N rows of raw blocks into N * rowStrideWords words (host). */
+int bpq4k_kq_pack_host(int qtype, const void* raw_host, uint32_t N, uint32_t K, uint32_t* words_host);
+
+/* dequant_kquant(raw, out, N, K, type) (runtime/gguf_loader.cpp:455-573) on the device,
+ * bit-identical to the reference's float arithmetic.  W needs 4-byte alignment for Q6_K,
+ * 16-byte for the other two. */
+int bpq4k_kq_dequant_f32(bpq4k_handle_t h, int qtype, const void* W, uint32_t N, uint32_t K,
+                         uint32_t rowStrideWords, float* out, void* stream);
+
+/* Embedding lookup: out[t*K + k] = deq(W)[tokens[t]][k].  Replaces q6k_gather.wgsl (one token)
+ * and q6k_gather_batched.wgsl; Q5_K and Q6_K tables.  `tokens` is a device array; a token id
+ * >= nRows yields a row of zeros.  The values are those of bpq4k_kq_dequant_f32. */
+int bpq4k_kq_gather_f32(bpq4k_handle_t h, int qtype, const void* W, uint32_t nRows, uint32_t K,
+                        uint32_t rowStrideWords, const uint32_t* tokens, uint32_t nTokens,
+                        float* out, void* stream);
+
+/* The matmul dispatch for any of the three types: q5k_matmul.wgsl, q6k_matmul.wgsl,
+ * q6k_matmul_wide.wgsl, q5k/q6k_matmul_batched4.wgsl and the kernel selection at
+ * runtime/model_runner.cpp:2032-2054, 4124-4135, 5841-5845.  Arguments as bpq4k_matmul_f32. */
+int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W, const float* bias,
+                        float* Y, uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords,
+                        uint32_t yOffset, void* stream);
+
 /* The small-M matmul for callers that must not allocate device memory.  It has no counterpart
  * in the reference.
  *

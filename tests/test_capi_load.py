@@ -70,3 +70,22 @@ def test_fuse_kq_concatenates_rows():
     assert (f.N, f.K, f.rowStrideWords, f.nBlocks) == (9, K, 72, 2)
     want = np.concatenate([orc.dequant(q, 6, K), orc.dequant(k, 3, K)])
     assert np.array_equal(orc.dequant(f.data.view(np.uint8), 9, K), want)
+
+
+def test_kq_strides_and_pack_follow_the_reference_packers():
+    """pack_q5k keeps 176-byte blocks; pack_q6k pads rows of 210-byte blocks to whole words with zeros."""
+    from backpack_b200 import pack_kq
+    from oracle import q4k_oracle as orc
+
+    lib = _lib.load()
+    assert [lib.bpq4k_kq_block_bytes(t) for t in (12, 13, 14, 8)] == [144, 176, 210, 0]
+    for qtype, K, rs in [(12, 4096, 576), (13, 4096, 704), (14, 4096, 840), (14, 768, 158), (14, 256, 53), (13, 300, 88)]:
+        assert lib.bpq4k_kq_row_stride_words(qtype, K) == rs
+    for qtype in (12, 13, 14):
+        N, K = 5, 768
+        w = synth.make_kq_weights(qtype, N, K, 4)
+        p = pack_kq(qtype, w, N, K)
+        words, rs, nb = orc.kq_pack(qtype, w, N, K)
+        assert (p.rowStrideWords, p.nBlocks, p.qtype) == (rs, nb, qtype)
+        assert np.array_equal(p.data, words)
+    assert lib.bpq4k_kq_pack_host(7, None, 0, 256, None) == 2

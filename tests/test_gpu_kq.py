@@ -1,0 +1,127 @@
+"""GPU parity of the Q5_K / Q6_K siblings through the C ABI: bit-exact dequantisation and gather,
+matmul against the oracle on the reference's fixtures, on corner blocks and on seeded shapes."""
+import numpy as np
+import pytest
+
+from backpack_b200 import pack_kq, synth
+from conftest import KQ_GOLDEN_GATHER, KQ_GOLDEN_MATMUL, assert_close_ref, rel_l2
+from oracle import q4k_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TYPES = [orc.Q5_K, orc.Q6_K]
+NAME = {orc.Q4_K: "q4k", orc.Q5_K: "q5k", orc.Q6_K: "q6k"}
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def check(y, want):
+    """The float tolerance of the path: rel-L2 <= 1e-3 and max-abs <= 2e-2 (scaled to the output's size)."""
+    assert rel_l2(y, want) <= 1e-3
+    scale = max(1.0, float(np.abs(want).max()) / 100.0)
+    assert float(np.abs(y - want).max()) <= 2e-2 * scale
+
+
+@pytest.mark.parametrize("case", KQ_GOLDEN_MATMUL + KQ_GOLDEN_GATHER)
+def test_dequant_bit_exact_on_golden(ctx, kq_golden, case):
+    qtype = int(kq_golden[f"{case}.type"][0])
+    _, N, K = (int(v) for v in kq_golden[f"{case}.shape"])
+    w = ctx.upload(pack_kq(qtype, kq_golden[f"{case}.raw"], N, K))
+    got = ctx.dequant(w).cpu().numpy()
+    assert np.array_equal(bits(got), bits(kq_golden[f"{case}.deq"]))
+
+
+@pytest.mark.parametrize("case", KQ_GOLDEN_GATHER)
+def test_gather_matches_reference_fixture(ctx, kq_golden, case):
+    """q6k_gather_reference / q6k_gather_batched_reference: rows of the dequantised table, bit-exact."""
+    import torch
+
+    qtype = int(kq_golden[f"{case}.type"][0])
+    _, N, K = (int(v) for v in kq_golden[f"{case}.shape"])
+    tokens = kq_golden[f"{case}.tokens"].astype(np.int32)
+    w = ctx.upload(pack_kq(qtype, kq_golden[f"{case}.raw"], N, K))
+    got = ctx.gather(w, dev(torch, tokens)).cpu().numpy()
+    assert np.array_equal(bits(got), bits(kq_golden[f"{case}.deq"][tokens]))
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+def test_gather_out_of_range_token_gives_zeros(ctx, qtype):
+    import torch
+
+    N, K = 6, 512
+    raw = synth.make_kq_weights(qtype, N, K, 31)
+    w = ctx.upload(pack_kq(qtype, raw, N, K))
+    tokens = np.array([5, 6, 0, 4000000000 & 0x7FFFFFFF], np.int32)
+    got = ctx.gather(w, dev(torch, tokens)).cpu().numpy()
+    deq = orc.kq_dequant(qtype, raw, N, K)
+    assert np.array_equal(bits(got[0]), bits(deq[5])) and np.array_equal(bits(got[2]), bits(deq[0]))
+    assert not got[1].any() and not got[3].any()
+
+
+@pytest.mark.parametrize("case", KQ_GOLDEN_MATMUL)
+def test_matmul_on_golden(ctx, kq_golden, case):
+    import torch
+
+    qtype = int(kq_golden[f"{case}.type"][0])
+    M, N, K = (int(v) for v in kq_golden[f"{case}.shape"])
+    w = ctx.upload(pack_kq(qtype, kq_golden[f"{case}.raw"], N, K))
+    y = ctx.matmul(dev(torch, kq_golden[f"{case}.x"]), w, bias=dev(torch, kq_golden[f"{case}.bias"])).cpu().numpy()
+    want = kq_golden[f"{case}.y"]
+    if case.startswith("synthetic"):
+        check(y, want)
+    else:  # the reference's own assertClose(atol = rtol = 2e-4) on its fixtures and on the corner blocks
+        assert_close_ref(y, want)
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 64, 256), (1, 333, 1024), (1, 2048, 4096), (2, 100, 768), (3, 17, 512),
+                                   (4, 256, 2048), (5, 9, 768), (8, 512, 4096), (13, 40, 1280), (40, 64, 512)])
+def test_matmul_seeded_shapes(ctx, qtype, M, N, K):
+    import torch
+
+    raw = synth.make_kq_weights(qtype, N, K, 100 + N)
+    x = synth.make_activations(M, K, 200 + M)
+    bias = np.linspace(-2, 2, N).astype(np.float32)
+    w = ctx.upload(pack_kq(qtype, raw, N, K))
+    y = ctx.matmul(dev(torch, x), w, bias=dev(torch, bias)).cpu().numpy()
+    check(y, orc.kq_matmul(qtype, x, raw, bias, N, K, threads=4))
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+def test_y_offset_and_no_bias(ctx, qtype):
+    import torch
+
+    N, K = 48, 512
+    raw = synth.make_kq_weights(qtype, N, K, 7)
+    x = synth.make_activations(1, K, 8)
+    w = ctx.upload(pack_kq(qtype, raw, N, K))
+    out = torch.full((3 * N,), -7.0, device="cuda")
+    ctx.matmul(dev(torch, x), w, out=out, y_offset=N)
+    got = out.cpu().numpy()
+    check(got[N:2 * N], orc.kq_matmul(qtype, x, raw, None, N, K)[0])
+    assert (got[:N] == -7.0).all() and (got[2 * N:] == -7.0).all()
+
+
+def test_kq_errors_are_statuses(ctx):
+    import torch
+
+    from backpack_b200 import Q4KError
+
+    lib = ctx.lib
+    x = torch.zeros(256, device="cuda")
+    wbuf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    y = torch.zeros(8, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    assert lib.bpq4k_kq_matmul_f32(ctx.h, 7, x.data_ptr(), wbuf.data_ptr(), None, y.data_ptr(), 1, 8, 256, 53, 0, s) == 2
+    assert lib.bpq4k_kq_matmul_f32(ctx.h, 14, x.data_ptr(), wbuf.data_ptr(), None, y.data_ptr(), 1, 8, 300, 53, 0, s) == 2
+    assert lib.bpq4k_kq_matmul_f32(ctx.h, 14, x.data_ptr(), wbuf.data_ptr(), None, y.data_ptr(), 1, 8, 256, 52, 0, s) == 1
+    assert lib.bpq4k_kq_matmul_f32(ctx.h, 13, x.data_ptr(), wbuf.data_ptr() + 4, None, y.data_ptr(), 1, 8, 256, 44, 0, s) == 3
+    assert lib.bpq4k_kq_gather_f32(ctx.h, 12, wbuf.data_ptr(), 8, 256, 36, x.data_ptr(), 1, y.data_ptr(), s) == 2
+    assert lib.bpq4k_kq_dequant_f32(ctx.h, 14, None, 8, 256, 53, y.data_ptr(), s) == 1
+    assert isinstance(Q4KError(2, "x"), RuntimeError)
