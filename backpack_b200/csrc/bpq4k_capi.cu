@@ -387,7 +387,8 @@ int bpq4k_matmul_f32(bpq4k_handle_t h, const float* X, const void* W, const floa
 // ---- Q5_K / Q6_K siblings ----------------------------------------------------
 
 uint32_t bpq4k_kq_block_bytes(int qtype) {
-    return qtype == BPQ4K_TYPE_Q4_K ? 144u : qtype == BPQ4K_TYPE_Q5_K ? 176u : qtype == BPQ4K_TYPE_Q6_K ? 210u : 0u;
+    return qtype == BPQ4K_TYPE_Q4_K ? 144u : qtype == BPQ4K_TYPE_Q5_K ? 176u : qtype == BPQ4K_TYPE_Q6_K ? 210u
+         : qtype == BPQ4K_TYPE_Q6_K_PADDED ? 224u : 0u;
 }
 
 uint32_t bpq4k_kq_row_stride_words(int qtype, uint32_t K) {
@@ -398,9 +399,19 @@ int bpq4k_kq_pack_host(int qtype, const void* raw_host, uint32_t N, uint32_t K, 
     const uint32_t bb = bpq4k_kq_block_bytes(qtype);
     if (!bb) return BPQ4K_ERR_UNSUPPORTED;
     if ((!raw_host || !words_host) && N != 0 && K != 0) return BPQ4K_ERR_INVALID_ARG;
-    const uint64_t row_bytes = (uint64_t)bpq4k_n_blocks(K) * bb;
+    const uint32_t nb = bpq4k_n_blocks(K);
     const uint64_t stride = bpq4k_kq_row_stride_words(qtype, K);
     const uint8_t* src = static_cast<const uint8_t*>(raw_host);
+    if (qtype == BPQ4K_TYPE_Q6_K_PADDED) {  // file-format blocks in, one padded block out for each
+        for (uint64_t r = 0; r < N; r++)
+            for (uint32_t b = 0; b < nb; b++) {
+                uint8_t* dst = reinterpret_cast<uint8_t*>(words_host + r * stride) + (uint64_t)b * 224u;
+                std::memcpy(dst, src + (r * nb + b) * 210u, 210u);
+                std::memset(dst + 210, 0, 14);
+            }
+        return BPQ4K_OK;
+    }
+    const uint64_t row_bytes = (uint64_t)nb * bb;
     for (uint32_t r = 0; r < N; r++) {
         uint8_t* dst = reinterpret_cast<uint8_t*>(words_host + r * stride);
         std::memcpy(dst, src + r * row_bytes, row_bytes);
@@ -412,7 +423,7 @@ int bpq4k_kq_pack_host(int qtype, const void* raw_host, uint32_t N, uint32_t K, 
 namespace {
 int check_kq_weights(bpq4k_context* h, int qtype, const void* W, uint32_t K, uint32_t rowStrideWords) {
     const uint32_t bb = bpq4k_kq_block_bytes(qtype);
-    if (!bb) return fail(h, BPQ4K_ERR_UNSUPPORTED, "quantisation type %d is not Q4_K (12), Q5_K (13) or Q6_K (14)", qtype);
+    if (!bb) return fail(h, BPQ4K_ERR_UNSUPPORTED, "quantisation type %d is not Q4_K (12), Q5_K (13), Q6_K (14) or padded Q6_K (270)", qtype);
     if (K == 0 || K % BPQ4K_QK_K != 0)
         return fail(h, BPQ4K_ERR_UNSUPPORTED, "K=%u is not a positive multiple of 256", K);
     if (!W) return fail(h, BPQ4K_ERR_INVALID_ARG, "W is null");
@@ -482,7 +493,21 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
     a.K = K;
     a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
     int launches = 0;
-    const cudaError_t e = launch_kq_gemv_fp32(qtype, a, static_cast<cudaStream_t>(stream), &launches);
+    cudaError_t e = cudaErrorInvalidValue;
+    // padded Q6_K, few rows: the streaming kernel, one activation row per launch
+    if (qtype == BPQ4K_TYPE_Q6_K_PADDED && M <= 4 && h->gemv_variant != BPQ4K_GEMV_FP32 && aligned16(X) && K % 4u == 0) {
+        MatmulArgs c = a;
+        c.M = 1;
+        e = cudaSuccess;
+        for (uint32_t m = 0; m < M && e == cudaSuccess; m++) {
+            c.X = a.X + (uint64_t)m * K;
+            c.Y = a.Y + (uint64_t)m * N;
+            e = launch_q6k_stream(c, h->tune, h->dev_status, h->sm_count, &h->tmaps, static_cast<cudaStream_t>(stream), &launches);
+            if (e == cudaErrorInvalidValue && m == 0) break;  // shape outside the kernel: plain kernel below
+        }
+        if (e == cudaErrorInvalidValue) launches = 0;
+    }
+    if (e == cudaErrorInvalidValue) e = launch_kq_gemv_fp32(qtype, a, static_cast<cudaStream_t>(stream), &launches);
     h->launches += (uint64_t)launches;
     if (e != cudaSuccess) {
         cudaGetLastError();

@@ -87,4 +87,13 @@ cudaError_t launch_kq_dequant_f32(int qtype, const uint8_t* W, const uint32_t* r
                                   uint32_t K, uint64_t w_row_bytes, float* out, cudaStream_t stream);
 cudaError_t launch_kq_gemv_fp32(int qtype, const MatmulArgs& a, cudaStream_t stream, int* launches);
 
+// Q6_K with every block padded to 224 bytes (type number of the C ABI's BPQ4K_TYPE_Q6_K_PADDED).
+constexpr int kQ6PaddedType = 0x10E;
+constexpr uint32_t kQ6PaddedBytes = 224;
+
+// Streaming tensor-core matmul for ONE activation row of Q6_K weights in the padded layout.
+// cudaErrorInvalidValue: the shape does not fit this kernel (use launch_kq_gemv_fp32).
+cudaError_t launch_q6k_stream(const MatmulArgs& a, const StreamTuning& tune, int* status_dev, int sm_count, TmapCache* tmaps,
+                              cudaStream_t stream, int* launches);
+
 }  // namespace bpq4k

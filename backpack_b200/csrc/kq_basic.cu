@@ -10,6 +10,7 @@
 // Q6_K super-block, 210 bytes: 128 nibble bytes, 64 bytes of bit pairs, 16 signed byte scales
 //   (one per 16 weights), half d at byte 208.  w = (d*sc)*(code - 32).  210 is not a multiple of
 //   4, so blocks are only 2-byte aligned and these kernels read them with byte and 16-bit loads.
+//   The padded layout (every block followed by 14 zero bytes: 224 bytes) is read the same way.
 #include "kernels.h"
 #include "q4k_common.cuh"
 
@@ -76,7 +77,7 @@ __device__ __forceinline__ Q6Lane q6k_lane(const uint8_t* __restrict__ p, uint32
 template <int QTYPE>
 __global__ void __launch_bounds__(256) kq_dequant_kernel(const uint8_t* __restrict__ W, const uint32_t* __restrict__ rows,
                                                           uint32_t n_src_rows, uint32_t N, uint32_t nb, uint64_t w_row_bytes,
-                                                          float* __restrict__ out) {
+                                                          uint32_t q6_block_bytes, float* __restrict__ out) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint64_t warps = (uint64_t)gridDim.x * (blockDim.x >> 5);
     const uint64_t total = (uint64_t)N * nb;
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(256) kq_dequant_kernel(const uint8_t* __restri
             __stcs(reinterpret_cast<float4*>(oo), lo);
             __stcs(reinterpret_cast<float4*>(oo + 32), hi);
         } else {
-            const Q6Lane q = q6k_lane(W + (uint64_t)src * w_row_bytes + (uint64_t)b * kQ6Bytes, lane);
+            const Q6Lane q = q6k_lane(W + (uint64_t)src * w_row_bytes + (uint64_t)b * q6_block_bytes, lane);
 #pragma unroll
             for (int half = 0; half < 2; half++)
 #pragma unroll
@@ -118,7 +119,7 @@ __global__ void __launch_bounds__(256) kq_dequant_kernel(const uint8_t* __restri
 // Float-FMA matmul: one warp per output row, MB activation rows per pass; w as the dequantiser
 // computes it, acc += x*w, warp reduction by shuffles.  The always-available variant.
 template <int QTYPE, int MB>
-__global__ void __launch_bounds__(256) kq_gemv_fp32_kernel(MatmulArgs a) {
+__global__ void __launch_bounds__(256) kq_gemv_fp32_kernel(MatmulArgs a, uint32_t q6_block_bytes) {
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t n = blockIdx.x * 8u + warp;
     if (n >= a.N) return;
@@ -143,7 +144,7 @@ __global__ void __launch_bounds__(256) kq_gemv_fp32_kernel(MatmulArgs a) {
                 koff[4 + i] = base + 32u + i;
             }
         } else {
-            const Q6Lane q = q6k_lane(wp + (uint64_t)b * kQ6Bytes, lane);
+            const Q6Lane q = q6k_lane(wp + (uint64_t)b * q6_block_bytes, lane);
 #pragma unroll
             for (int half = 0; half < 2; half++)
 #pragma unroll
@@ -174,7 +175,7 @@ __global__ void __launch_bounds__(256) kq_gemv_fp32_kernel(MatmulArgs a) {
 }
 
 template <int QTYPE>
-cudaError_t gemv_fp32_typed(const MatmulArgs& a, cudaStream_t stream, int* launches) {
+cudaError_t gemv_fp32_typed(const MatmulArgs& a, uint32_t q6bb, cudaStream_t stream, int* launches) {
     const uint32_t gx = (a.N + 7) / 8;
     MatmulArgs c = a;
     const uint32_t MB = a.M >= 8 ? 8 : a.M >= 4 ? 4 : a.M >= 2 ? 2 : 1;
@@ -185,10 +186,10 @@ cudaError_t gemv_fp32_typed(const MatmulArgs& a, cudaStream_t stream, int* launc
         c.Y = a.Y + (uint64_t)m0 * a.N;
         const dim3 grid(gx, (c.M + MB - 1) / MB);
         switch (MB) {
-            case 8: kq_gemv_fp32_kernel<QTYPE, 8><<<grid, 256, 0, stream>>>(c); break;
-            case 4: kq_gemv_fp32_kernel<QTYPE, 4><<<grid, 256, 0, stream>>>(c); break;
-            case 2: kq_gemv_fp32_kernel<QTYPE, 2><<<grid, 256, 0, stream>>>(c); break;
-            default: kq_gemv_fp32_kernel<QTYPE, 1><<<grid, 256, 0, stream>>>(c); break;
+            case 8: kq_gemv_fp32_kernel<QTYPE, 8><<<grid, 256, 0, stream>>>(c, q6bb); break;
+            case 4: kq_gemv_fp32_kernel<QTYPE, 4><<<grid, 256, 0, stream>>>(c, q6bb); break;
+            case 2: kq_gemv_fp32_kernel<QTYPE, 2><<<grid, 256, 0, stream>>>(c, q6bb); break;
+            default: kq_gemv_fp32_kernel<QTYPE, 1><<<grid, 256, 0, stream>>>(c, q6bb); break;
         }
         if (launches) ++*launches;
     }
@@ -208,16 +209,18 @@ cudaError_t launch_kq_dequant_f32(int qtype, const uint8_t* W, const uint32_t* r
     uint64_t ctas = (total + 7) / 8;
     const uint64_t cap = (uint64_t)sms * 8 * 4;
     if (ctas > cap) ctas = cap;
-    if (qtype == 13) kq_dequant_kernel<13><<<(unsigned)ctas, 256, 0, stream>>>(W, rows, n_src_rows, N, nb, w_row_bytes, out);
-    else if (qtype == 14) kq_dequant_kernel<14><<<(unsigned)ctas, 256, 0, stream>>>(W, rows, n_src_rows, N, nb, w_row_bytes, out);
+    if (qtype == 13) kq_dequant_kernel<13><<<(unsigned)ctas, 256, 0, stream>>>(W, rows, n_src_rows, N, nb, w_row_bytes, 0u, out);
+    else if (qtype == 14) kq_dequant_kernel<14><<<(unsigned)ctas, 256, 0, stream>>>(W, rows, n_src_rows, N, nb, w_row_bytes, kQ6Bytes, out);
+    else if (qtype == kQ6PaddedType) kq_dequant_kernel<14><<<(unsigned)ctas, 256, 0, stream>>>(W, rows, n_src_rows, N, nb, w_row_bytes, kQ6PaddedBytes, out);
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
 }
 
 cudaError_t launch_kq_gemv_fp32(int qtype, const MatmulArgs& a, cudaStream_t stream, int* launches) {
     if (a.N == 0 || a.M == 0) return cudaSuccess;
-    if (qtype == 13) return gemv_fp32_typed<13>(a, stream, launches);
-    if (qtype == 14) return gemv_fp32_typed<14>(a, stream, launches);
+    if (qtype == 13) return gemv_fp32_typed<13>(a, 0u, stream, launches);
+    if (qtype == 14) return gemv_fp32_typed<14>(a, kQ6Bytes, stream, launches);
+    if (qtype == kQ6PaddedType) return gemv_fp32_typed<14>(a, kQ6PaddedBytes, stream, launches);
     return cudaErrorInvalidValue;
 }
 

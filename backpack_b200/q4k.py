@@ -25,6 +25,8 @@ BLOCK_BYTES = 144
 BLOCK_WORDS = 36
 # the reference's GGUFType numbers (runtime/gguf_loader.h:27-30)
 Q4_K, Q5_K, Q6_K = 12, 13, 14
+# Q6_K with every block padded to 224 bytes: the layout of the fast single-row Q6_K kernel (no reference counterpart)
+Q6_K_PADDED = 0x10E
 
 OPT_GEMV_VARIANT = 1
 OPT_PREFILL_MODE = 2
@@ -63,8 +65,9 @@ def pack_kq(qtype: int, raw, N: int, K: int) -> KQuantPacked:
     raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
     nb = lib.bpq4k_n_blocks(K)
     rs = lib.bpq4k_kq_row_stride_words(qtype, K)
-    if raw.size < N * nb * bb:
-        raise ValueError(f"raw has {raw.size} bytes, need {N * nb * bb}")
+    file_bb = 210 if qtype == Q6_K_PADDED else bb   # the input is always the file format
+    if raw.size < N * nb * file_bb:
+        raise ValueError(f"raw has {raw.size} bytes, need {N * nb * file_bb}")
     words = np.zeros(N * rs, np.uint32)
     st = lib.bpq4k_kq_pack_host(qtype, raw.ctypes.data, N, K, words.ctypes.data)
     if st:

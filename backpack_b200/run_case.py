@@ -1,7 +1,8 @@
 """Run one Q4_K matmul shape on cuda:0 a few times and report its time.
 
     python -m backpack_b200.run_case N K M [--reps R] [--variant auto|fp32|stream]
-                                           [--prefill-mode f16x3|f16|bf16] [--opt ID=VALUE ...]
+                                           [--prefill-mode f16x3|f16|bf16] [--qtype q4k|q5k|q6k|q6kp]
+                                           [--opt ID=VALUE ...]
 
 A small driver for profilers and quick checks: seeded synthetic weights and
 activations (backpack_b200.synth), `reps` back-to-back calls through the C ABI,
@@ -23,6 +24,8 @@ def main() -> None:
     ap.add_argument("--variant", default="auto", choices=["auto", "fp32", "stream"])
     ap.add_argument("--prefill-mode", default="f16x3", choices=["f16x3", "f16", "bf16"],
                     help="precision mode of the tensor-core kernel (large M)")
+    ap.add_argument("--qtype", default="q4k", choices=["q4k", "q5k", "q6k", "q6kp"],
+                    help="weight format (q6kp: Q6_K in the padded device layout of the streaming kernel)")
     ap.add_argument("--opt", action="append", default=[], metavar="ID=VALUE",
                     help="set a numbered library option (see include/bpq4k.h), e.g. --opt 10=8 for 8 warps")
     args = ap.parse_args()
@@ -38,7 +41,9 @@ def main() -> None:
     for kv in args.opt:
         k, v = kv.split("=")
         ctx.set_option(int(k), int(v))
-    w = ctx.upload(bp.pack_q4k(synth.make_q4k_weights(args.N, args.K, 0), args.N, args.K))
+    qtype = {"q4k": q4k.Q4_K, "q5k": q4k.Q5_K, "q6k": q4k.Q6_K, "q6kp": q4k.Q6_K_PADDED}[args.qtype]
+    ftype = q4k.Q6_K if qtype == q4k.Q6_K_PADDED else qtype   # the file format behind the device layout
+    w = ctx.upload(bp.pack_kq(qtype, synth.make_kq_weights(ftype, args.N, args.K, 0), args.N, args.K))
     x = torch.from_numpy(synth.make_activations(args.M, args.K, 1)).cuda()
     y = torch.zeros(args.M, args.N, device="cuda")
     ctx.matmul(x, w, out=y)
@@ -50,7 +55,7 @@ def main() -> None:
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / max(args.reps - 1, 1)
-    nbytes = synth.algorithmic_bytes(args.M, args.N, args.K)
+    nbytes = synth.kq_algorithmic_bytes(ftype, args.M, args.N, args.K)
     print(f"N={args.N} K={args.K} M={args.M}: {us:.2f} us/call, {nbytes / us / 1e3:.1f} GB/s algorithmic "
           f"(back-to-back calls on one weight: L2-warm if it fits), checksum {float(y.double().abs().sum()):.6e}")
 

@@ -229,13 +229,23 @@ int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items
  * entry points above.  Weights are the reference's packed words: raw GGUF blocks
  * (176 B for Q5_K, 210 B for Q6_K), rows rowStrideWords words apart, Q6_K rows
  * padded with zeros to a whole word (pack_q5k / pack_q6k, runtime/gguf_loader.cpp:381-424). */
-enum bpq4k_qtype { BPQ4K_TYPE_Q4_K = 12, BPQ4K_TYPE_Q5_K = 13, BPQ4K_TYPE_Q6_K = 14 };
+enum bpq4k_qtype {
+    BPQ4K_TYPE_Q4_K = 12,
+    BPQ4K_TYPE_Q5_K = 13,
+    BPQ4K_TYPE_Q6_K = 14,
+    /* Q6_K with every 210-byte block followed by 14 zero bytes (224 bytes, rows 16-byte
+     * aligned).  Not a file format: bpq4k_kq_pack_host writes it from raw GGUF blocks, and it
+     * is the layout the fast single-row Q6_K kernel (bulk copies, tensor cores) reads; the
+     * unpadded type always runs the plain kernel.  It has no counterpart in the reference. */
+    BPQ4K_TYPE_Q6_K_PADDED = 0x10E
+};
 
-/* Bytes per 256-weight block in the file format (144, 176, 210); 0 for an unknown type. */
+/* Bytes per 256-weight block as stored (144, 176, 210; 224 for the padded type); 0 for an unknown type. */
 uint32_t bpq4k_kq_block_bytes(int qtype);
 /* rowStrideWords of KQuantPacked: ceil(ceil(K/256) * block bytes / 4). */
 uint32_t bpq4k_kq_row_stride_words(int qtype, uint32_t K);
-/* pack_q4k / pack_q5k / pack_q6k: N rows of raw blocks into N * rowStrideWords words (host). */
+/* pack_q4k / pack_q5k / pack_q6k: N rows of raw GGUF blocks (always the file format: 210-byte
+ * blocks for both Q6_K types) into N * rowStrideWords words (host). */
 int bpq4k_kq_pack_host(int qtype, const void* raw_host, uint32_t N, uint32_t K, uint32_t* words_host);
 
 /* dequant_kquant(raw, out, N, K, type) (runtime/gguf_loader.cpp:455-573) on the device,

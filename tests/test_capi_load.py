@@ -89,3 +89,10 @@ def test_kq_strides_and_pack_follow_the_reference_packers():
         assert (p.rowStrideWords, p.nBlocks, p.qtype) == (rs, nb, qtype)
         assert np.array_equal(p.data, words)
     assert lib.bpq4k_kq_pack_host(7, None, 0, 256, None) == 2
+    # padded Q6_K: the same 210 bytes per block, then 14 zero bytes
+    N, K = 3, 512
+    w = synth.make_kq_weights(14, N, K, 5)
+    p = pack_kq(0x10E, w, N, K)
+    assert (p.rowStrideWords, lib.bpq4k_kq_block_bytes(0x10E)) == (112, 224)
+    blocks = p.data.view(np.uint8).reshape(N * 2, 224)
+    assert np.array_equal(blocks[:, :210], w.reshape(N * 2, 210)) and not blocks[:, 210:].any()

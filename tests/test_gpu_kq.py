@@ -9,8 +9,17 @@ from oracle import q4k_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
-TYPES = [orc.Q5_K, orc.Q6_K]
-NAME = {orc.Q4_K: "q4k", orc.Q5_K: "q5k", orc.Q6_K: "q6k"}
+Q6_K_PADDED = 0x10E     # device layout of the fast single-row Q6_K kernel; same weights as Q6_K
+TYPES = [orc.Q5_K, orc.Q6_K, Q6_K_PADDED]
+
+
+def file_type(qtype):
+    """The file format (what the oracle decodes) behind a device layout."""
+    return orc.Q6_K if qtype == Q6_K_PADDED else qtype
+
+
+def layouts(qtype):
+    return [orc.Q6_K, Q6_K_PADDED] if qtype == orc.Q6_K else [qtype]
 
 
 def bits(a):
@@ -32,9 +41,10 @@ def check(y, want):
 def test_dequant_bit_exact_on_golden(ctx, kq_golden, case):
     qtype = int(kq_golden[f"{case}.type"][0])
     _, N, K = (int(v) for v in kq_golden[f"{case}.shape"])
-    w = ctx.upload(pack_kq(qtype, kq_golden[f"{case}.raw"], N, K))
-    got = ctx.dequant(w).cpu().numpy()
-    assert np.array_equal(bits(got), bits(kq_golden[f"{case}.deq"]))
+    for lay in layouts(qtype):
+        w = ctx.upload(pack_kq(lay, kq_golden[f"{case}.raw"], N, K))
+        got = ctx.dequant(w).cpu().numpy()
+        assert np.array_equal(bits(got), bits(kq_golden[f"{case}.deq"]))
 
 
 @pytest.mark.parametrize("case", KQ_GOLDEN_GATHER)
@@ -45,9 +55,10 @@ def test_gather_matches_reference_fixture(ctx, kq_golden, case):
     qtype = int(kq_golden[f"{case}.type"][0])
     _, N, K = (int(v) for v in kq_golden[f"{case}.shape"])
     tokens = kq_golden[f"{case}.tokens"].astype(np.int32)
-    w = ctx.upload(pack_kq(qtype, kq_golden[f"{case}.raw"], N, K))
-    got = ctx.gather(w, dev(torch, tokens)).cpu().numpy()
-    assert np.array_equal(bits(got), bits(kq_golden[f"{case}.deq"][tokens]))
+    for lay in layouts(qtype):
+        w = ctx.upload(pack_kq(lay, kq_golden[f"{case}.raw"], N, K))
+        got = ctx.gather(w, dev(torch, tokens)).cpu().numpy()
+        assert np.array_equal(bits(got), bits(kq_golden[f"{case}.deq"][tokens]))
 
 
 @pytest.mark.parametrize("qtype", TYPES)
@@ -55,11 +66,11 @@ def test_gather_out_of_range_token_gives_zeros(ctx, qtype):
     import torch
 
     N, K = 6, 512
-    raw = synth.make_kq_weights(qtype, N, K, 31)
+    raw = synth.make_kq_weights(file_type(qtype), N, K, 31)
     w = ctx.upload(pack_kq(qtype, raw, N, K))
     tokens = np.array([5, 6, 0, 4000000000 & 0x7FFFFFFF], np.int32)
     got = ctx.gather(w, dev(torch, tokens)).cpu().numpy()
-    deq = orc.kq_dequant(qtype, raw, N, K)
+    deq = orc.kq_dequant(file_type(qtype), raw, N, K)
     assert np.array_equal(bits(got[0]), bits(deq[5])) and np.array_equal(bits(got[2]), bits(deq[0]))
     assert not got[1].any() and not got[3].any()
 
@@ -70,27 +81,53 @@ def test_matmul_on_golden(ctx, kq_golden, case):
 
     qtype = int(kq_golden[f"{case}.type"][0])
     M, N, K = (int(v) for v in kq_golden[f"{case}.shape"])
-    w = ctx.upload(pack_kq(qtype, kq_golden[f"{case}.raw"], N, K))
-    y = ctx.matmul(dev(torch, kq_golden[f"{case}.x"]), w, bias=dev(torch, kq_golden[f"{case}.bias"])).cpu().numpy()
     want = kq_golden[f"{case}.y"]
-    if case.startswith("synthetic"):
-        check(y, want)
-    else:  # the reference's own assertClose(atol = rtol = 2e-4) on its fixtures and on the corner blocks
-        assert_close_ref(y, want)
+    for lay in layouts(qtype):
+        w = ctx.upload(pack_kq(lay, kq_golden[f"{case}.raw"], N, K))
+        y = ctx.matmul(dev(torch, kq_golden[f"{case}.x"]), w, bias=dev(torch, kq_golden[f"{case}.bias"])).cpu().numpy()
+        if case.startswith("synthetic"):
+            check(y, want)
+        else:  # the reference's own assertClose(atol = rtol = 2e-4) on its fixtures and on the corner blocks
+            assert_close_ref(y, want)
 
 
 @pytest.mark.parametrize("qtype", TYPES)
 @pytest.mark.parametrize("M,N,K", [(1, 64, 256), (1, 333, 1024), (1, 2048, 4096), (2, 100, 768), (3, 17, 512),
-                                   (4, 256, 2048), (5, 9, 768), (8, 512, 4096), (13, 40, 1280), (40, 64, 512)])
+                                   (4, 256, 2048), (5, 9, 768), (8, 512, 4096), (13, 40, 1280), (40, 64, 512),
+                                   (1, 4096, 14336), (1, 9000, 2048), (1, 1030, 28672), (3, 700, 8192)])
 def test_matmul_seeded_shapes(ctx, qtype, M, N, K):
     import torch
 
-    raw = synth.make_kq_weights(qtype, N, K, 100 + N)
+    raw = synth.make_kq_weights(file_type(qtype), N, K, 100 + N)
     x = synth.make_activations(M, K, 200 + M)
     bias = np.linspace(-2, 2, N).astype(np.float32)
     w = ctx.upload(pack_kq(qtype, raw, N, K))
     y = ctx.matmul(dev(torch, x), w, bias=dev(torch, bias)).cpu().numpy()
-    check(y, orc.kq_matmul(qtype, x, raw, bias, N, K, threads=4))
+    check(y, orc.kq_matmul(file_type(qtype), x, raw, bias, N, K, threads=4))
+
+
+def test_q6k_streaming_kernel_is_the_one_that_runs(ctx):
+    """Padded Q6_K with one activation row takes the tensor-core streaming kernel (one launch), the
+    file-format layout the plain kernel; both agree with the oracle; extreme activations keep their
+    precision because every 16-value group has its own scale."""
+    import torch
+
+    N, K = 1000, 4096
+    raw = synth.make_kq_weights(orc.Q6_K, N, K, 17)
+    x = synth.make_activations(1, K, 18)
+    x[0, 5] = 3.0e4
+    x[0, 1000:1016] = 1.0e-6
+    x[0, 2048:2064] = 0.0
+    want = orc.kq_matmul(orc.Q6_K, x, raw, None, N, K, threads=4)
+    ys = []
+    for lay in (Q6_K_PADDED, orc.Q6_K):
+        w = ctx.upload(pack_kq(lay, raw, N, K))
+        ctx.launch_count(reset=True)
+        ys.append(ctx.matmul(dev(torch, x), w).cpu().numpy())
+        assert ctx.launch_count() == 1
+        check(ys[-1], want)
+    assert ctx.device_status() == 0
+    assert rel_l2(ys[0], ys[1]) < 1e-5
 
 
 @pytest.mark.parametrize("qtype", TYPES)
@@ -98,13 +135,13 @@ def test_y_offset_and_no_bias(ctx, qtype):
     import torch
 
     N, K = 48, 512
-    raw = synth.make_kq_weights(qtype, N, K, 7)
+    raw = synth.make_kq_weights(file_type(qtype), N, K, 7)
     x = synth.make_activations(1, K, 8)
     w = ctx.upload(pack_kq(qtype, raw, N, K))
     out = torch.full((3 * N,), -7.0, device="cuda")
     ctx.matmul(dev(torch, x), w, out=out, y_offset=N)
     got = out.cpu().numpy()
-    check(got[N:2 * N], orc.kq_matmul(qtype, x, raw, None, N, K)[0])
+    check(got[N:2 * N], orc.kq_matmul(file_type(qtype), x, raw, None, N, K)[0])
     assert (got[:N] == -7.0).all() and (got[2 * N:] == -7.0).all()
 
 
