@@ -507,6 +507,22 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
         }
         if (e == cudaErrorInvalidValue) launches = 0;
     }
+    // Q5_K: the streaming kernel in slabs of 8 rows (each slab re-reads the weights)
+    if (qtype == BPQ4K_TYPE_Q5_K && h->gemv_variant != BPQ4K_GEMV_FP32 && aligned16(X)) {
+        const size_t need = gemv_stream_scratch_bytes(M < kStreamMaxM ? M : kStreamMaxM, K);
+        if (need > h->scratch_bytes) {
+            if (int s = ensure_bytes(h, &h->scratch, &h->scratch_bytes, need)) return s;
+        }
+        MatmulArgs c = a;
+        e = cudaSuccess;
+        for (uint32_t m0 = 0; m0 < M && e == cudaSuccess; m0 += kStreamMaxM) {
+            c.M = M - m0 < kStreamMaxM ? M - m0 : kStreamMaxM;
+            c.X = a.X + (uint64_t)m0 * K;
+            c.Y = a.Y + (uint64_t)m0 * N;
+            e = launch_gemv_stream(c, h->tune, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count, &h->tmaps,
+                                   static_cast<cudaStream_t>(stream), &launches, 13);
+        }
+    }
     if (e == cudaErrorInvalidValue) e = launch_kq_gemv_fp32(qtype, a, static_cast<cudaStream_t>(stream), &launches);
     h->launches += (uint64_t)launches;
     if (e != cudaSuccess) {

@@ -62,9 +62,10 @@ struct TmapCache {
 size_t gemv_stream_scratch_bytes(uint32_t M, uint32_t K);
 
 // Streaming tensor-core matmul for M <= 8 (or the indirect form).  `scratch` may be null
-// when the activations fit in shared memory.
+// when the activations fit in shared memory.  qtype 12: Q4_K (144-byte blocks), 13: Q5_K (176-byte).
 cudaError_t launch_gemv_stream(const MatmulArgs& a, const StreamTuning& tune, void* scratch, size_t scratch_bytes,
-                               int* status_dev, int sm_count, TmapCache* tmaps, cudaStream_t stream, int* launches);
+                               int* status_dev, int sm_count, TmapCache* tmaps, cudaStream_t stream, int* launches,
+                               int qtype = 12);
 
 // Tensor-core prefill matmul (tcgen05 + TMEM).  mode follows bpq4k_prefill_mode: 0 three-pass half
 // split, 1 one pass half, 2 one pass bfloat16.  `scratch` holds the 16-bit activations.

@@ -151,12 +151,28 @@ __device__ __forceinline__ void quantize_item(const float* __restrict__ X, uint3
     quantize_loaded(v0, v1, K, tok, c8, valid, frag, SI);
 }
 
+// Q5_K: code bytes of sub-blocks 2g (low nibbles) and 2g+1 (high nibbles) of one code word, each
+// with its fifth bit (bits 2g and 2g+1 of the matching byte of `qh`) merged in at bit 4.
+template <int g>
+__device__ __forceinline__ void merge_fifth_bit(uint32_t codes, uint32_t qh, uint32_t& even, uint32_t& odd) {
+    constexpr uint32_t kLo = 0x0F0F0F0Fu, kBit = 0x10101010u;
+    const uint32_t be = g == 0 ? (qh << 4) : g == 1 ? (qh << 2) : g == 2 ? qh : (qh >> 2);
+    const uint32_t bo = g == 0 ? (qh << 3) : g == 1 ? (qh << 1) : g == 2 ? (qh >> 1) : (qh >> 3);
+    even = (codes & kLo) | (be & kBit);
+    odd = ((codes >> 4) & kLo) | (bo & kBit);
+}
+
 // PROBE (development builds only, -DBPQ4K_ENABLE_PROBES): 0 = the kernel; 1 = copies and waits
 // only; 2 = math on whatever the ring holds, no copies; 3 = as 2 without the mmas; 4 = as 2
 // without the nibble decode; 5 = as 2 without the scale decode.  Used to attribute time.
-template <int NT, bool M1, bool XG, int PROBE = 0>
+// Q5: the weights are Q5_K super-blocks (176 bytes: the Q4_K header, 32 bytes of fifth bits, 128
+// nibble bytes); the fifth bit is merged into each code byte, so odd sub-blocks reach the mma as
+// q (not 16*q) and carry no 1/16 in their scale.
+template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false>
 __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr uint32_t BB = Q5 ? 176u : kBlockBytes, BW = BB / 4u;  // bytes and words per super-block
+    constexpr uint32_t QS = Q5 ? 48u : 16u;                          // offset of the nibble bytes
     constexpr int TOK = M1 ? 1 : NT * 4;  // activation-row slots (four per 8-column mma tile)
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -201,8 +217,8 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
         if (lane == 0) {
             const uint32_t bar = bar0 + iss_st * 8u;
             const bool full = iss_c < nfull;
-            mbar_expect_tx(bar, 16u * kBlockBytes * (full ? a.cb : a.rem));
-            tma_load_2d(ring + iss_st * a.stage_bytes, full ? &a.tmap : &a.tmap_rem, (b0 + iss_c * a.cb) * kBlockWords,
+            mbar_expect_tx(bar, 16u * BB * (full ? a.cb : a.rem));
+            tma_load_2d(ring + iss_st * a.stage_bytes, full ? &a.tmap : &a.tmap_rem, (b0 + iss_c * a.cb) * BW,
                         (uint32_t)wrow0 + iss_tile * 16u, bar);
         }
         if (++iss_st == a.stages) iss_st = 0;
@@ -272,7 +288,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
     // ldmatrix row addresses: lanes 0-7 rows 0-7 bytes [0,16), 8-15 rows 8-15 bytes [0,16),
     // 16-23 rows 0-7 bytes [16,32), 24-31 rows 8-15 bytes [16,32)
     // (row pitch = bytes of the stage's box row: cb or rem blocks)
-    const uint32_t lm_row = (lane & 7u) + ((lane >> 3) & 1u) * 8u, lm_col = 16u + (lane >> 4) * 16u;
+    const uint32_t lm_row = (lane & 7u) + ((lane >> 3) & 1u) * 8u, lm_col = QS + (lane >> 4) * 16u;
     // B operand: column n = lane/4 -> pair n/2 (parity n/2%2), part n%2; t = lane%4
     const uint32_t bn = lane >> 2, bt = lane & 3u;
     const uint32_t b_par = (bn >> 1) & 1u;
@@ -281,7 +297,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
     const uint32_t c_par = lane & 1u;
     const uint32_t row_a = M1 ? (lane >> 2) + ((bt >> 1) << 3) : (lane >> 2);
     const uint32_t sel0 = 0x7440u + c_par, sel1 = 0x7442u + c_par;
-    const float par_scale = c_par ? 0.0625f : 1.f;  // odd sub-blocks arrive as 16*q
+    const float par_scale = (c_par && !Q5) ? 0.0625f : 1.f;  // Q4_K: odd sub-blocks arrive as 16*q
 
     // This lane's B data lives at  xbase + ((tok*NG + G)*2 + parity)*128 + c*64 + t*16  (c = n%2).
     // In the mmas of the other parity the lane feeds zeros: it reads the zero block with
@@ -327,7 +343,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
         for (uint32_t c = 0; c < nchunks; c++) {
             const uint32_t bs = b0 + c * a.cb;
             const uint32_t nblk = c < nfull ? a.cb : a.rem;
-            const uint32_t pitch = nblk * kBlockBytes;
+            const uint32_t pitch = nblk * BB;
             const uint32_t lm_off = lm_row * pitch + lm_col, hdr_off = row_a * pitch;
             const uint32_t bar = bar0 + st * 8u;
             if (PROBE < 2 && !failed) {
@@ -341,7 +357,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                 }
             }
             uint32_t boff = ring + st * a.stage_bytes;
-            for (uint32_t blk = bs; PROBE != 1 && blk < bs + nblk; blk++, boff += kBlockBytes) {
+            for (uint32_t blk = bs; PROBE != 1 && blk < bs + nblk; blk++, boff += BB) {
                 if constexpr (M1) {
                 // scales of this thread's rows, its parity's four sub-blocks; the odd sub-block's
                 // weights reach the mma as 16*q, so its scale carries the 1/16
@@ -380,14 +396,20 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                 // 1 KiB zero region, so the per-group offset g*256 is an immediate for both
                 const AddrT pa = pa0 + blk * 4u * stride_a, pb = pb0 + blk * 4u * stride_b;
                 const uint32_t lm_addr = boff + lm_off;
+                uint32_t qh[4] = {0u, 0u, 0u, 0u};  // Q5_K: fifth bits of this thread's weights, all eight sub-blocks
+                if constexpr (Q5) ldmatrix_x4<-32>(lm_addr, qh[0], qh[1], qh[2], qh[3]);
                 auto do_group = [&](auto gc) {
                     constexpr int g = decltype(gc)::value;
                     uint32_t r0, r1, r2, r3;
                     ldmatrix_x4<g * 32>(lm_addr, r0, r1, r2, r3);
-                    constexpr uint32_t kLo = 0x0F0F0F0Fu, kHi = 0xF0F0F0F0u;
+                    [[maybe_unused]] constexpr uint32_t kLo = 0x0F0F0F0Fu, kHi = 0xF0F0F0F0u;
                     uint32_t e[4], o[4];
                     if constexpr (PROBE == 4) {
                         e[0] = o[0] = r0; e[1] = o[1] = r1; e[2] = o[2] = r2; e[3] = o[3] = r3;
+                    } else if constexpr (Q5) {
+                        const uint32_t rr[4] = {r0, r1, r2, r3};
+#pragma unroll
+                        for (int i = 0; i < 4; i++) merge_fifth_bit<g>(rr[i], qh[i], e[i], o[i]);
                     } else {
                         e[0] = r0 & kLo; e[1] = r1 & kLo; e[2] = r2 & kLo; e[3] = r3 & kLo;  // q   (even sub-block)
                         o[0] = r0 & kHi; o[1] = r1 & kHi; o[2] = r2 & kHi; o[3] = r3 & kHi;  // 16q (odd sub-block)
@@ -435,7 +457,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                     const float d = half_bits_to_float(h.w0), dmin = half_bits_to_float(h.w0 >> 16);
                     uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
                     unpack_scales_packed(h, sc_lo, sc_hi, mn_lo, mn_hi);
-                    const float d16 = d * 0.0625f;
+                    const float d16 = Q5 ? d : d * 0.0625f;
                     const float nd = -d * 8388608.f, nd16 = -d16 * 8388608.f, ndm = -dmin * 8388608.f;
 #pragma unroll
                     for (int sb = 0; sb < 8; sb++) {
@@ -456,14 +478,23 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                     SIv[nt][3] = load16(sa, std::integral_constant<int, 48>{});
                 }
                 const uint32_t lm_addr = boff + lm_off;
+                uint32_t qh[4] = {0u, 0u, 0u, 0u};  // Q5_K: fifth bits of this thread's weights, all eight sub-blocks
+                if constexpr (Q5) ldmatrix_x4<-32>(lm_addr, qh[0], qh[1], qh[2], qh[3]);
                 const AddrT gx_blk = gx_addr + (AddrT)blk * 1024u;
                 auto do_group = [&](auto gc) {
                     constexpr int g = decltype(gc)::value;
                     uint32_t r0, r1, r2, r3;
                     ldmatrix_x4<g * 32>(lm_addr, r0, r1, r2, r3);
-                    constexpr uint32_t kLo = 0x0F0F0F0Fu, kHi = 0xF0F0F0F0u;
-                    const uint32_t e[4] = {r0 & kLo, r1 & kLo, r2 & kLo, r3 & kLo};  // q   (even sub-block)
-                    const uint32_t o[4] = {r0 & kHi, r1 & kHi, r2 & kHi, r3 & kHi};  // 16q (odd sub-block)
+                    [[maybe_unused]] constexpr uint32_t kLo = 0x0F0F0F0Fu, kHi = 0xF0F0F0F0u;
+                    uint32_t e[4], o[4];
+                    if constexpr (Q5) {
+                        const uint32_t rr[4] = {r0, r1, r2, r3};
+#pragma unroll
+                        for (int i = 0; i < 4; i++) merge_fifth_bit<g>(rr[i], qh[i], e[i], o[i]);
+                    } else {
+                        e[0] = r0 & kLo; e[1] = r1 & kLo; e[2] = r2 & kLo; e[3] = r3 & kLo;  // q   (even sub-block)
+                        o[0] = r0 & kHi; o[1] = r1 & kHi; o[2] = r2 & kHi; o[3] = r3 & kHi;  // 16q (odd sub-block)
+                    }
 #pragma unroll
                     for (int nt = 0; nt < NT; nt++) {
                         const AddrT xa = gx_blk + (AddrT)(nt * 4u * NG) * 256u;
@@ -566,7 +597,7 @@ __global__ void __launch_bounds__(256) quantize_activations_kernel(const float* 
 
 // Launch one instantiation.  The grid is persistent: at most as many CTAs as can be
 // resident at once (occupancy query, cached), never more than there are tile groups.
-template <int NT, bool M1, bool XG, int PROBE = 0>
+template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false>
 cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, uint32_t threads, size_t smem,
                        int sm_count, uint32_t ctas_per_sm_override, bool pdl, cudaStream_t stream) {
     struct Cache { int dev = -1; size_t smem_cfg = 0; uint32_t threads = 0; size_t smem = 0; int occ = 0; };
@@ -576,7 +607,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     if (cache.dev != dev) cache = Cache{};
     cache.dev = dev;
     if (smem > cache.smem_cfg) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT, M1, XG, PROBE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT, M1, XG, PROBE, Q5>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return e;
         cache.smem_cfg = smem;
@@ -584,7 +615,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     }
     if (cache.threads != threads || cache.smem != smem) {
         int occ = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_stream_kernel<NT, M1, XG, PROBE>, (int)threads, smem);
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_stream_kernel<NT, M1, XG, PROBE, Q5>, (int)threads, smem);
         if (e != cudaSuccess) return e;
         cache.threads = threads;
         cache.smem = smem;
@@ -615,7 +646,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, PROBE>, sa);
+    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, PROBE, Q5>, sa);
 }
 
 static_assert(sizeof(CUtensorMap) == 128, "TmapCache::Entry::map must hold a CUtensorMap");
@@ -628,8 +659,12 @@ size_t gemv_stream_scratch_bytes(uint32_t M, uint32_t K) {
 }
 
 cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, void* scratch, size_t scratch_bytes,
-                               int* status_dev, int sm_count, TmapCache* tmaps, cudaStream_t stream, int* launches) {
+                               int* status_dev, int sm_count, TmapCache* tmaps, cudaStream_t stream, int* launches,
+                               int qtype) {
     if (m.N == 0) return cudaSuccess;
+    if (qtype != 12 && qtype != 13) return cudaErrorInvalidValue;
+    const bool q5 = qtype == 13;
+    const uint32_t block_bytes = q5 ? 176u : kBlockBytes, block_words = block_bytes / 4u;
     const bool indirect = m.n_slots != 0;
     const uint32_t M = indirect ? 1 : m.M;
     if (M == 0) return cudaSuccess;
@@ -675,8 +710,8 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     // Stage = dense TMA box of 16 rows x cb blocks, then one box of rem blocks for the tail of
     // the warp's K range.  An odd cb keeps the 16-byte units of the eight rows an ldmatrix
     // touches in distinct bank groups (row pitch = cb*9 units).
-    uint32_t cb = tune.cb ? tune.cb : m1 ? (small ? (bpw <= 2 ? bpw : 1) : 5) : 3;
-    if (cb > 7) cb = 7;  // box width <= 256 words
+    uint32_t cb = tune.cb ? tune.cb : m1 ? (small ? (bpw <= 2 ? bpw : 1) : (q5 ? 3 : 5)) : 3;  // Q5_K: 5 wide blocks leave no room for the ring
+    if (cb > 256u / block_words) cb = 256u / block_words;  // box width <= 256 words
     if (cb > bpw) cb = bpw;
     const uint32_t x_bytes = tokens * m.K * 4u, S_bytes = tokens * (m.K / 32u) * 8u;
     uint32_t stage_bytes = 0;
@@ -702,7 +737,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         const uint32_t cb_min = (m1 || tune.cb || cb < 2) ? cb : 2;
         bool fits = false;
         for (uint32_t cb_try = cb; cb_try >= cb_min && !fits; cb_try--) {
-            stage_bytes = 16 * cb_try * kBlockBytes;
+            stage_bytes = 16 * cb_try * block_bytes;
             uint32_t s_try = stages;
             while (s_try >= 2 && layout(false, s_try, sa) > kSmemMax) s_try--;
             if (s_try >= 2) {
@@ -714,7 +749,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         if (!fits) xg = true;
     }
     const uint32_t rem = bpw % cb;
-    stage_bytes = 16 * cb * kBlockBytes;
+    stage_bytes = 16 * cb * block_bytes;
     if (xg) {
         while (stages > 1 && layout(true, stages, sa) > kSmemMax) stages--;
         if (indirect) return cudaErrorInvalidValue;  // per-slot activations are staged in shared memory only
@@ -726,10 +761,11 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     sa.ntiles = ntiles; sa.tokens = tokens; sa.status = status_dev;
     {
         const uint64_t rows_total = indirect ? m.w_total_rows : m.N;
+        const uint32_t key_nb = q5 ? (nb | 0x50000000u) : nb;  // keeps Q5_K maps apart from Q4_K maps of the same buffer
         auto get_map = [&](uint32_t width_blocks, CUtensorMap* out) -> cudaError_t {
             if (tmaps) {
                 for (const auto& en : tmaps->entries)
-                    if (en.W == m.W && en.rows == rows_total && en.row_bytes == m.w_row_bytes && en.nb == nb &&
+                    if (en.W == m.W && en.rows == rows_total && en.row_bytes == m.w_row_bytes && en.nb == key_nb &&
                         en.cb == width_blocks) {
                         std::memcpy(out, en.map, sizeof(CUtensorMap));
                         return cudaSuccess;
@@ -737,9 +773,9 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
             }
             EncodeTiledFn enc = encode_tiled_fn();
             if (!enc) return cudaErrorNotSupported;
-            const cuuint64_t gdim[2] = {(cuuint64_t)nb * kBlockWords, (cuuint64_t)rows_total};
+            const cuuint64_t gdim[2] = {(cuuint64_t)nb * block_words, (cuuint64_t)rows_total};
             const cuuint64_t gstride[1] = {(cuuint64_t)m.w_row_bytes};
-            const cuuint32_t box[2] = {width_blocks * kBlockWords, 16u};
+            const cuuint32_t box[2] = {width_blocks * block_words, 16u};
             const cuuint32_t estr[2] = {1u, 1u};
             const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(m.W), gdim, gstride, box, estr,
                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -747,7 +783,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
             if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
             if (tmaps) {
                 auto& en = tmaps->entries[tmaps->next++ % TmapCache::kEntries];
-                en.W = m.W; en.rows = rows_total; en.row_bytes = m.w_row_bytes; en.nb = nb; en.cb = width_blocks;
+                en.W = m.W; en.rows = rows_total; en.row_bytes = m.w_row_bytes; en.nb = key_nb; en.cb = width_blocks;
                 std::memcpy(en.map, out, sizeof(CUtensorMap));
             }
             return cudaSuccess;
@@ -785,11 +821,12 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
             sa.m.Y = base.Y + (uint64_t)s0 * m.N;
         }
         const uint32_t threads = warps * 32;
-#define BPQ4K_LAUNCH(NT_, M1_, XG_) \
-    launch_one<NT_, M1_, XG_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream)
+#define BPQ4K_LAUNCH(NT_, M1_, XG_)                                                                                          \
+    (q5 ? launch_one<NT_, M1_, XG_, 0, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream) \
+        : launch_one<NT_, M1_, XG_, 0, false>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream))
 #ifdef BPQ4K_ENABLE_PROBES
 #define BPQ4K_PROBE(P_) launch_one<1, true, false, P_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream)
-        if (m1 && !xg && tune.probe) {
+        if (m1 && !xg && !q5 && tune.probe) {
             switch (tune.probe) {
                 case 1: e = BPQ4K_PROBE(1); break;
                 case 2: e = BPQ4K_PROBE(2); break;
