@@ -494,8 +494,9 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
     a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
     int launches = 0;
     cudaError_t e = cudaErrorInvalidValue;
-    // padded Q6_K, few rows: the streaming kernel, one activation row per launch
-    if (qtype == BPQ4K_TYPE_Q6_K_PADDED && M <= 4 && h->gemv_variant != BPQ4K_GEMV_FP32 && aligned16(X) && K % 4u == 0) {
+    // padded Q6_K: the streaming kernel, one activation row per launch (per row it still beats the
+    // plain kernel's eight rows per pass)
+    if (qtype == BPQ4K_TYPE_Q6_K_PADDED && h->gemv_variant != BPQ4K_GEMV_FP32 && aligned16(X) && K % 4u == 0) {
         MatmulArgs c = a;
         c.M = 1;
         e = cudaSuccess;

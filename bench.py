@@ -412,6 +412,9 @@ def run_gpu_arm(args, rank, world, local_rank):
     prefill = None
     if world == 1 and not args.no_prefill:
         prefill = measure_prefill(ctx, torch, shapes, W, dev)
+    siblings = None
+    if world == 1 and not args.no_siblings:
+        siblings = measure_siblings(ctx, torch, dev)
 
     times = torch.tensor([ms, kernel_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
     if dist:
@@ -457,11 +460,51 @@ def run_gpu_arm(args, rank, world, local_rank):
             line["prefill"] = prefill
         if fused is not None:
             line["fused_projections"] = fused
+        if siblings is not None:
+            line["kquant_siblings"] = siblings
         print(json.dumps(line), flush=True)
     if dist:
         dist.barrier()
         dist.destroy_process_group()
     _ = launches_eager
+
+
+def measure_siblings(ctx, torch, dev, reps=8):
+    """The Q5_K and Q6_K versions of the output-head projection (128256 x 4096, M = 1): real
+    "Q4_K_M" files keep that tensor in Q6_K.  Algorithmic GB/s counts the file format's bytes per
+    block (176 and 210); each weight is larger than L2, so back-to-back launches stream from HBM."""
+    import backpack_b200 as bp
+    from backpack_b200 import q4k, synth
+
+    peak, peak_src = load_peaks()
+    N, K = 128256, 4096
+    x = torch.randn(1, K, device=dev, generator=torch.Generator(device=dev).manual_seed(11))
+    y = torch.empty(1, N, device=dev)
+    out = {"workload": "output head 128256 x 4096, M=1", "peak_gbs": peak, "peak_source": peak_src, "types": {}}
+    for name, layout, ftype in (("q5_k", q4k.Q5_K, q4k.Q5_K), ("q6_k", q4k.Q6_K_PADDED, q4k.Q6_K)):
+        w = ctx.upload(bp.pack_kq(layout, synth.make_kq_weights(ftype, N, K, 21), N, K))
+        for _ in range(3):
+            ctx.matmul(x, w, out=y)
+        torch.cuda.synchronize()
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for _ in range(reps):
+                    ctx.matmul(x, w, out=y)
+            g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            g.replay()
+            e1.record(stream)
+            stream.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        gbs = synth.kq_algorithmic_bytes(ftype, 1, N, K) / us / 1e3
+        out["types"][name] = {"us_per_launch": us, "value": gbs, "unit": UNIT, "frac_of_hbm_peak": gbs / peak,
+                              "device_layout": "file format" if layout == ftype else "blocks padded to 224 bytes"}
+        del w
+        torch.cuda.empty_cache()
+    return out
 
 
 def measure_prefill(ctx, torch, shapes, W, dev, M=512, reps=5):
@@ -516,6 +559,7 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
     ap.add_argument("--ref-budget", type=float, default=120.0, help="seconds the --impl reference run may take")
     ap.add_argument("--no-prefill", action="store_true", help="skip the M=512 (config 2) measurement")
+    ap.add_argument("--no-siblings", action="store_true", help="skip the Q5_K / Q6_K output-head measurement")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                     help="several ranks: fused peer-store all-gather (default) or one NCCL all-gather per projection")
     ap.add_argument("--graph-multi", action="store_true", help="with several ranks, replay the step from a CUDA graph too")
