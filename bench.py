@@ -23,9 +23,17 @@ launch streams its weights from HBM.
 ``cpu_baseline`` the reference's own CPU code for the path (dequant_kquant +
               float dot) timed on this machine's host cores on a bounded sample.
 
+``prefill``   (1 GPU) the same projections at M = 512 through the tensor-core
+              kernel, useful TFLOP/s per precision mode.
+``fused_projections`` (1 GPU) the step with Q+K+V and gate+up fused by rows.
+``kquant_siblings``   (1 GPU) the output head in Q5_K and Q6_K, M = 1.
+
 With N > 1 ranks every rank holds its own row shard of each projection (the
 shard has the single-GPU shape, i.e. the global matrix has N times the rows:
-weak scaling) and the output slices are all-gathered over NCCL.
+weak scaling).  ``--gather peer`` (default): the matmul epilogue stores each
+output slice straight into every rank's gather buffer over peer memory and one
+bounded flag barrier closes the step, all inside one CUDA graph.
+``--gather nccl``: one NCCL all-gather per projection, launched eagerly.
 
 ``--impl reference`` times the reference's CPU implementation only (rank 0).
 """
