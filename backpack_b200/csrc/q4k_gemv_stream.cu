@@ -246,40 +246,37 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
         const uint32_t per_row = K / 8u;
         uint8_t* frag = smem + a.off_x;
         float* SI = reinterpret_cast<float*>(smem + a.off_S);
-        if constexpr (M1) {
-            for (uint32_t base = 0; base < per_row; base += blockDim.x) {
-                const uint32_t it = base + tid;
-                const bool valid = it < per_row;
-                quantize_item(X, M, K, 0u, valid ? it : 0u, valid, frag, SI);
-            }
-        } else {
-            // rows past M carry zeros: clear their digits and scales instead of quantising zeros
-            const uint32_t mrows = min(M, (uint32_t)TOK);
+        // rows past M carry zeros: clear their digits and scales instead of quantising zeros
+        const uint32_t mrows = M1 ? 1u : min(M, (uint32_t)TOK);
+        if constexpr (!M1) {
             for (uint32_t i = mrows * K + tid; i < (uint32_t)TOK * K; i += blockDim.x) reinterpret_cast<uint32_t*>(frag)[i] = 0u;
             for (uint32_t i = mrows * nb * 16u + tid; i < (uint32_t)TOK * nb * 16u; i += blockDim.x) SI[i] = 0.f;
-            // four items per thread and round, all loads issued before the first use
-            constexpr int U = 4;
-            const uint32_t items = mrows * per_row;
-            for (uint32_t base = 0; base < items; base += blockDim.x * U) {
-                float4 v[U][2];
-                uint32_t tok[U], c8[U];
-                bool valid[U];
+        }
+        // up to four items per thread and round, all loads issued before the first use (a round
+        // trip to L2 or HBM per item would otherwise be paid one after the other)
+        constexpr int U = 4;
+        const uint32_t items = mrows * per_row;
+        for (uint32_t base = 0; base < items; base += blockDim.x * U) {
+            const uint32_t nj = min((uint32_t)U, (items - base + blockDim.x - 1) / blockDim.x);  // uniform over the CTA
+            float4 v[U][2];
+            uint32_t tok[U], c8[U];
+            bool valid[U];
 #pragma unroll
-                for (int j = 0; j < U; j++) {
-                    const uint32_t it = base + j * blockDim.x + tid;
-                    valid[j] = it < items;
-                    tok[j] = valid[j] ? it / per_row : 0u;
-                    c8[j] = valid[j] ? it - tok[j] * per_row : 0u;
-                    v[j][0] = v[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (valid[j]) {
-                        const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok[j] * K + (uint64_t)c8[j] * 8u);
-                        v[j][0] = __ldg(xp);
-                        v[j][1] = __ldg(xp + 1);
-                    }
+            for (int j = 0; j < U; j++) {
+                const uint32_t it = base + j * blockDim.x + tid;
+                valid[j] = (uint32_t)j < nj && it < items;
+                tok[j] = valid[j] ? it / per_row : 0u;
+                c8[j] = valid[j] ? it - tok[j] * per_row : 0u;
+                v[j][0] = v[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (valid[j]) {
+                    const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok[j] * K + (uint64_t)c8[j] * 8u);
+                    v[j][0] = __ldg(xp);
+                    v[j][1] = __ldg(xp + 1);
                 }
-#pragma unroll
-                for (int j = 0; j < U; j++) quantize_loaded(v[j][0], v[j][1], K, tok[j], c8[j], valid[j], frag, SI);
             }
+#pragma unroll
+            for (int j = 0; j < U; j++)
+                if ((uint32_t)j < nj) quantize_loaded(v[j][0], v[j][1], K, tok[j], c8[j], valid[j], frag, SI);
         }
         __syncthreads();
     }

@@ -50,17 +50,11 @@ struct Q6Args {
     int* status;
 };
 
-// Quantise 8 consecutive activations (item c8 of the row).  The two items of a 16-value group sit in
+// Quantise 8 consecutive activations v0, v1 (item c8 of the row; zeros for an idle lane).  The two items of a 16-value group sit in
 // adjacent lanes.  Digits go to  frag + (k/32)*128 + digit*32 + k%32  (plane 3 of each 128 bytes is
 // zero), the group's inv = max|x|/kXiMax6 and sum(xi)*inv to
 //   SI[blk*32 + hh*8 + j] and SI[blk*32 + 16 + hh*8 + j],  group g16 = blk*16 + 2*j + hh.
-__device__ __forceinline__ void q6_quantize_item(const float* __restrict__ X, uint32_t c8, bool valid, uint8_t* frag, float* SI) {
-    float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
-    if (valid) {
-        const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)c8 * 8u);
-        v0 = __ldg(xp);
-        v1 = __ldg(xp + 1);
-    }
+__device__ __forceinline__ void q6_quantize_item(float4 v0, float4 v1, uint32_t c8, bool valid, uint8_t* frag, float* SI) {
     float amax = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
                        fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
@@ -153,11 +147,29 @@ __global__ void __launch_bounds__(512, 1) q6k_stream_kernel(const __grid_constan
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     {
+        // up to four 8-value items per thread and round, all loads issued before the first use
+        constexpr int U = 4;
         const uint32_t per_row = K / 8u;
-        for (uint32_t base = 0; base < per_row; base += blockDim.x) {
-            const uint32_t it = base + tid;
-            const bool valid = it < per_row;
-            q6_quantize_item(X, valid ? it : 0u, valid, smem + a.off_x, reinterpret_cast<float*>(smem + a.off_S));
+        for (uint32_t base = 0; base < per_row; base += blockDim.x * U) {
+            const uint32_t nj = min((uint32_t)U, (per_row - base + blockDim.x - 1) / blockDim.x);  // uniform over the CTA
+            float4 v[U][2];
+#pragma unroll
+            for (int j = 0; j < U; j++) {
+                const uint32_t it = base + j * blockDim.x + tid;
+                v[j][0] = v[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if ((uint32_t)j < nj && it < per_row) {
+                    const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)it * 8u);
+                    v[j][0] = __ldg(xp);
+                    v[j][1] = __ldg(xp + 1);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < U; j++) {
+                const uint32_t it = base + j * blockDim.x + tid;
+                if ((uint32_t)j < nj)
+                    q6_quantize_item(v[j][0], v[j][1], it < per_row ? it : 0u, it < per_row, smem + a.off_x,
+                                     reinterpret_cast<float*>(smem + a.off_S));
+            }
         }
         __syncthreads();
     }
