@@ -57,6 +57,7 @@ SIGNATURES["bpq4k_kq_pack_host"] = (C.c_int, [C.c_int, vp, u32, u32, vp])
 SIGNATURES["bpq4k_kq_dequant_f32"] = (C.c_int, [vp, C.c_int, vp, u32, u32, u32, vp, vp])
 SIGNATURES["bpq4k_kq_gather_f32"] = (C.c_int, [vp, C.c_int, vp, u32, u32, u32, vp, u32, vp, vp])
 SIGNATURES["bpq4k_kq_matmul_f32"] = (C.c_int, [vp, C.c_int, vp, vp, vp, vp, u32, u32, u32, u32, u32, vp])
+SIGNATURES["bpq4k_matmul_fused_f32"] = (C.c_int, [vp, C.c_int, C.c_int, vp, vp, C.c_float, vp, vp, vp, vp, u32, u32, u32, u32, vp])
 
 _lib = None
 

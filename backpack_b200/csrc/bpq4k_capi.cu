@@ -533,6 +533,49 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
     return BPQ4K_OK;
 }
 
+int bpq4k_matmul_fused_f32(bpq4k_handle_t h, int qtype, int prologue, const float* X, const float* aux, float eps,
+                           const void* W, const float* bias, const float* residual, float* Y, uint32_t N, uint32_t K,
+                           uint32_t rowStrideWords, uint32_t yOffset, void* stream) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (N == 0) return BPQ4K_OK;
+    if (qtype != BPQ4K_TYPE_Q4_K && qtype != BPQ4K_TYPE_Q5_K)
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "the fused forms cover Q4_K (12) and Q5_K (13), not type %d", qtype);
+    if (prologue < BPQ4K_PROLOGUE_NONE || prologue > BPQ4K_PROLOGUE_SILU_MUL)
+        return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown prologue %d", prologue);
+    if (int s = check_kq_weights(h, qtype, W, K, rowStrideWords)) return s;
+    if (!X || !Y) return fail(h, BPQ4K_ERR_INVALID_ARG, "X or Y is null");
+    if (prologue != BPQ4K_PROLOGUE_NONE && !aux) return fail(h, BPQ4K_ERR_INVALID_ARG, "aux is null");
+    if (!aligned16(X) || (aux && !aligned16(aux))) return fail(h, BPQ4K_ERR_MISALIGNED, "X or aux is not 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(Y) & 3u) return fail(h, BPQ4K_ERR_MISALIGNED, "Y is not 4-byte aligned");
+    DeviceGuard g(h->device);
+    MatmulArgs a{};
+    a.X = X;
+    a.W = static_cast<const uint8_t*>(W);
+    a.bias = bias;
+    a.Y = Y + yOffset;
+    a.M = 1;
+    a.N = N;
+    a.K = K;
+    a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
+    a.prologue = (uint32_t)prologue;
+    a.aux = aux;
+    a.eps = eps;
+    a.residual = residual;
+    int launches = 0;
+    const cudaError_t e = launch_gemv_stream(a, h->tune, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count, &h->tmaps,
+                                             static_cast<cudaStream_t>(stream), &launches, qtype);
+    h->launches += (uint64_t)launches;
+    if (e == cudaErrorInvalidValue) {
+        cudaGetLastError();
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "K=%u is too long for the fused single-row kernel", K);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return cuda_fail(h, e, "matmul launch");
+    }
+    return BPQ4K_OK;
+}
+
 int bpq4k_matmul_moe_f32(bpq4k_handle_t h, const float* X, const void* W, const float* bias, float* Y,
                          const uint32_t* offsets, const uint32_t* x_rows, uint32_t nSlots, uint32_t N, uint32_t K,
                          uint32_t rowStrideWords, uint32_t wRows, void* stream) {

@@ -24,6 +24,13 @@ struct MatmulArgs {
     // fused all-gather: every output is also stored to these buffers (other GPUs' memory, plain stores)
     float* peer_Y[8];
     uint32_t n_peers;
+    // fused prologue on the activation row (single row only) and residual epilogue:
+    //   1: x = X * rsqrt(mean(X^2) + eps) * aux      (aux = RMSNorm weight[K])
+    //   2: x = gelu_tanh(X) * aux,  3: x = silu(X) * aux   (aux = the "up" vector[K])
+    uint32_t prologue;
+    const float* aux;
+    float eps;
+    const float* residual;  // null or float[N]: added to every output
 };
 
 cudaError_t launch_dequant_f32(const uint8_t* W, uint32_t N, uint32_t K, uint64_t w_row_bytes, float* out,

@@ -252,10 +252,67 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
             for (uint32_t i = mrows * K + tid; i < (uint32_t)TOK * K; i += blockDim.x) reinterpret_cast<uint32_t*>(frag)[i] = 0u;
             for (uint32_t i = mrows * nb * 16u + tid; i < (uint32_t)TOK * nb * 16u; i += blockDim.x) SI[i] = 0.f;
         }
+        const uint32_t items = mrows * per_row;
+        if (M1 && a.m.prologue) {
+            // Fused prologue on the single activation row (the reference's q4k_matmul_norm.wgsl:47-92
+            // and q4k_down_gelu.wgsl:47-62, plus the silu form of silu_mul_fused): transform while staging.
+            float rstd = 1.f;
+            if (a.m.prologue == 1u) {
+                float ss = 0.f;
+                for (uint32_t i = tid; i < K / 4u; i += blockDim.x) {
+                    const float4 v = __ldg(reinterpret_cast<const float4*>(X) + i);
+                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+                float* red = reinterpret_cast<float*>(smem + a.off_part);
+                if (lane == 0) red[warp] = ss;
+                __syncthreads();
+                float tot = 0.f;
+                for (uint32_t w2 = 0; w2 < nwarps; w2++) tot += red[w2];
+                rstd = 1.f / sqrtf(tot / (float)K + a.m.eps);
+                __syncthreads();  // red is the partial-sum buffer of the main loop
+            }
+            constexpr int UP = 4;  // items per thread and round, loads of x and aux issued together
+            for (uint32_t base = 0; base < items; base += blockDim.x * UP) {
+                const uint32_t nj = min((uint32_t)UP, (items - base + blockDim.x - 1) / blockDim.x);  // uniform over the CTA
+                float4 v[UP][2], w[UP][2];
+#pragma unroll
+                for (int j = 0; j < UP; j++) {
+                    const uint32_t it = base + j * blockDim.x + tid;
+                    v[j][0] = v[j][1] = w[j][0] = w[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if ((uint32_t)j < nj && it < items) {
+                        v[j][0] = __ldg(reinterpret_cast<const float4*>(X) + 2u * it);
+                        v[j][1] = __ldg(reinterpret_cast<const float4*>(X) + 2u * it + 1u);
+                        w[j][0] = __ldg(reinterpret_cast<const float4*>(a.m.aux) + 2u * it);
+                        w[j][1] = __ldg(reinterpret_cast<const float4*>(a.m.aux) + 2u * it + 1u);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < UP; j++) {
+                    if ((uint32_t)j >= nj) continue;
+                    const uint32_t it = base + j * blockDim.x + tid;
+                    float* vf = reinterpret_cast<float*>(v[j]);
+                    const float* wf = reinterpret_cast<const float*>(w[j]);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const float g = vf[i];
+                        if (a.m.prologue == 1u) {
+                            vf[i] = g * rstd * wf[i];
+                        } else if (a.m.prologue == 2u) {
+                            const float inner = 0.7978845608f * (g + 0.044715f * g * g * g);
+                            vf[i] = 0.5f * g * (1.f + tanhf(inner)) * wf[i];
+                        } else {
+                            vf[i] = __fdividef(g, 1.f + __expf(-g)) * wf[i];  // relative error ~1e-6: far inside the digits' 2^-22
+                        }
+                    }
+                    quantize_loaded(v[j][0], v[j][1], K, 0u, it < items ? it : 0u, it < items, frag, SI);
+                }
+            }
+        } else {
         // up to four items per thread and round, all loads issued before the first use (a round
         // trip to L2 or HBM per item would otherwise be paid one after the other)
         constexpr int U = 4;
-        const uint32_t items = mrows * per_row;
         for (uint32_t base = 0; base < items; base += blockDim.x * U) {
             const uint32_t nj = min((uint32_t)U, (items - base + blockDim.x - 1) / blockDim.x);  // uniform over the CTA
             float4 v[U][2];
@@ -277,6 +334,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
 #pragma unroll
             for (int j = 0; j < U; j++)
                 if ((uint32_t)j < nj) quantize_loaded(v[j][0], v[j][1], K, tok[j], c8[j], valid[j], frag, SI);
+        }
         }
         __syncthreads();
     }
@@ -333,6 +391,9 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
 
     for (uint32_t ti = 0; ti < my_tiles; ti++) {
         const uint32_t tile = tile0 + ti * tstride;
+        // single-row calls: fetch this lane's residual value now, it is added when the tile is stored
+        float res_pre = 0.f;
+        if (M1 && a.m.residual && wk == 0 && lane < 16u && tile * 16u + lane < N) res_pre = __ldg(a.m.residual + tile * 16u + lane);
         float acc[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = 0.f;
@@ -562,7 +623,8 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                 if (tok < M && row < N) {
                     float s = 0.f;
                     for (uint32_t k2 = 0; k2 < a.wk; k2++) s += gbuf[(uint64_t)k2 * (TOK * 16u) + idx];
-                    const float yv = s + (a.m.bias ? a.m.bias[row] : 0.f);
+                    float yv = s + (a.m.bias ? a.m.bias[row] : 0.f);
+                    if (M1) yv += res_pre;
                     Y[(uint64_t)tok * N + row] = yv;
                     // fused all-gather: the same value goes straight into every peer's gather buffer
                     for (uint32_t p = 0; p < a.m.n_peers; p++) a.m.peer_Y[p][(uint64_t)tok * N + row] = yv;
@@ -729,7 +791,9 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     bool xg = false;
     uint32_t stages = tune.stages ? tune.stages : (small ? 2 : 4);
     if (stages > kMaxStages) stages = kMaxStages;
-    if (tune.force_scratch) xg = true;
+    const bool fused = m.prologue != 0 || m.residual != nullptr;
+    if (fused && (!m1 || indirect)) return cudaErrorInvalidValue;  // the fused forms are single-row, direct
+    if (tune.force_scratch && !fused) xg = true;
     if (!xg) {
         const uint32_t cb_min = (m1 || tune.cb || cb < 2) ? cb : 2;
         bool fits = false;
@@ -749,7 +813,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     stage_bytes = 16 * cb * block_bytes;
     if (xg) {
         while (stages > 1 && layout(true, stages, sa) > kSmemMax) stages--;
-        if (indirect) return cudaErrorInvalidValue;  // per-slot activations are staged in shared memory only
+        if (indirect || fused) return cudaErrorInvalidValue;  // these stage their activations in shared memory only
         if (!scratch || scratch_bytes < gemv_stream_scratch_bytes(M, m.K)) return cudaErrorInvalidValue;
     }
     const uint32_t smem = layout(xg, stages, sa);

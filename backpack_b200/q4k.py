@@ -35,6 +35,7 @@ OPT_STREAM_WARPS, OPT_STREAM_KSPLIT, OPT_STREAM_STAGE_BLOCKS = 10, 11, 12
 OPT_STREAM_STAGES, OPT_STREAM_CTAS_PER_SM, OPT_STREAM_FORCE_SCRATCH = 13, 14, 15
 OPT_STREAM_NO_PDL = 16
 GEMV_AUTO, GEMV_FP32, GEMV_STREAM = 0, 1, 2
+PROLOGUE_NONE, PROLOGUE_RMSNORM, PROLOGUE_GELU_MUL, PROLOGUE_SILU_MUL = 0, 1, 2, 3
 PREFILL_F16X3, PREFILL_F16, PREFILL_BF16 = 0, 1, 2
 
 
@@ -230,6 +231,21 @@ class Q4KContext:
             self._check(self.lib.bpq4k_kq_matmul_f32(
                 self.h, w.qtype, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
                 out.data_ptr(), M, w.N, K, w.rowStrideWords, y_offset, self._stream()))
+        return out
+
+    def matmul_fused(self, x, w: Q4KWeight, prologue: int = PROLOGUE_NONE, aux=None, eps: float = 0.0, bias=None,
+                     residual=None, out=None, y_offset: int = 0):
+        """Single-row matmul with a fused prologue on x (RMSNorm with weight `aux`, or gelu/silu(x) * aux)
+        and an optional residual added to the output (bpq4k_matmul_fused_f32)."""
+        torch = self._torch
+        assert x.dtype == torch.float32 and x.is_cuda and x.is_contiguous() and x.numel() == w.K
+        if out is None:
+            out = torch.empty((1, w.N), dtype=torch.float32, device=x.device)
+        self._check(self.lib.bpq4k_matmul_fused_f32(
+            self.h, w.qtype, prologue, x.data_ptr(), aux.data_ptr() if aux is not None else None, float(eps),
+            w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
+            residual.data_ptr() if residual is not None else None, out.data_ptr(), w.N, w.K, w.rowStrideWords,
+            y_offset, self._stream()))
         return out
 
     def matmul_moe(self, x, w: Q4KWeight, n_rows_per_expert: int, offsets, x_rows=None, bias=None, out=None):

@@ -27,6 +27,8 @@ launch streams its weights from HBM.
               kernel, useful TFLOP/s per precision mode.
 ``fused_projections`` (1 GPU) the step with Q+K+V and gate+up fused by rows.
 ``kquant_siblings``   (1 GPU) the output head in Q5_K and Q6_K, M = 1.
+``fused_prologues``   (1 GPU) launch time with and without a fused RMSNorm /
+              silu*up prologue and residual epilogue.
 
 With N > 1 ranks every rank holds its own row shard of each projection (the
 shard has the single-GPU shape, i.e. the global matrix has N times the rows:
@@ -420,9 +422,10 @@ def run_gpu_arm(args, rank, world, local_rank):
     prefill = None
     if world == 1 and not args.no_prefill:
         prefill = measure_prefill(ctx, torch, shapes, W, dev)
-    siblings = None
+    siblings = fusions = None
     if world == 1 and not args.no_siblings:
         siblings = measure_siblings(ctx, torch, dev)
+        fusions = measure_fusions(ctx, torch, dev)
 
     times = torch.tensor([ms, kernel_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
     if dist:
@@ -470,11 +473,57 @@ def run_gpu_arm(args, rank, world, local_rank):
             line["fused_projections"] = fused
         if siblings is not None:
             line["kquant_siblings"] = siblings
+        if fusions is not None:
+            line["fused_prologues"] = fusions
         print(json.dumps(line), flush=True)
     if dist:
         dist.barrier()
         dist.destroy_process_group()
     _ = launches_eager
+
+
+def measure_fusions(ctx, torch, dev):
+    """What the fused prologues cost on top of the plain single-row matmul (graph replay over enough
+    weight copies to stay out of L2): Q+K+V with the RMSNorm prologue, the down projection with the
+    silu*up prologue and the residual epilogue.  The reference runs each of these steps as its own
+    dispatch; here each is folded into the matmul launch."""
+    import backpack_b200 as bp
+    from backpack_b200 import q4k, synth
+
+    out = {"unit": "us per launch", "cases": {}}
+    for name, N, K, kind, with_res in (("qkv_rmsnorm", 6144, 4096, q4k.PROLOGUE_RMSNORM, False),
+                                       ("down_silu_mul_residual", 4096, 14336, q4k.PROLOGUE_SILU_MUL, True)):
+        ncopies = int(400e6 // synth.weight_bytes(N, K)) + 1
+        packed = bp.pack_q4k(synth.make_q4k_weights(N, K, 31), N, K)
+        Ws = [ctx.upload(packed) for _ in range(ncopies)]
+        g0 = torch.Generator(device=dev).manual_seed(5)
+        x = torch.randn(1, K, device=dev, generator=g0)
+        aux = torch.randn(K, device=dev, generator=g0)
+        res = torch.randn(N, device=dev, generator=g0) if with_res else None
+        y = torch.empty(1, N, device=dev)
+        row = {}
+        for label, fn in (("plain", lambda w: ctx.matmul(x, w, out=y)),
+                          ("fused", lambda w: ctx.matmul_fused(x, w, kind, aux=aux, eps=1e-5, residual=res, out=y))):
+            for w in Ws[:2]:
+                fn(w)
+            torch.cuda.synchronize()
+            stream = torch.cuda.Stream(device=dev)
+            with torch.cuda.stream(stream):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    for i in range(2 * ncopies):
+                        fn(Ws[i % ncopies])
+                g.replay()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                g.replay()
+                e1.record(stream)
+                stream.synchronize()
+            row[label] = e0.elapsed_time(e1) * 1e3 / (2 * ncopies)
+        out["cases"][name] = row
+        del Ws
+        torch.cuda.empty_cache()
+    return out
 
 
 def measure_siblings(ctx, torch, dev, reps=8):

@@ -268,6 +268,30 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
                         float* Y, uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords,
                         uint32_t yOffset, void* stream);
 
+/* ---- decode matmul with a fused prologue / epilogue -------------------------
+ * The single-row (M = 1) matmul with the element-wise step that precedes it computed
+ * while the activation row is staged, and an optional residual added to the output:
+ *   BPQ4K_PROLOGUE_RMSNORM   x = X * (1/sqrt(mean(X^2) + eps)) * aux,  aux = norm weight[K]
+ *                            (q4k_matmul_norm.wgsl:47-92, q5k_matmul_norm.wgsl)
+ *   BPQ4K_PROLOGUE_GELU_MUL  x = 0.5*g*(1 + tanh(0.7978845608*(g + 0.044715*g^3))) * aux,
+ *                            g = X, aux = the "up" vector[K]  (q4k_down_gelu.wgsl:47-62; the
+ *                            reference passes gate and up as one buffer: aux = X + K)
+ *   BPQ4K_PROLOGUE_SILU_MUL  x = g/(1 + exp(-g)) * aux   (silu_mul_fused followed by the down
+ *                            projection, runtime/model_runner.cpp:3755-3766)
+ *   Y[yOffset + n] = sum_k x[k]*deq(W)[n][k] + bias[n] + residual[n]   (bias, residual may be NULL;
+ *   the residual add is the dispatch at runtime/model_runner.cpp:3774)
+ * Q4_K and Q5_K weights.  Each removes one small launch and one round trip of the activation
+ * row through memory per projection.  X and aux must be 16-byte aligned. */
+enum bpq4k_prologue {
+    BPQ4K_PROLOGUE_NONE = 0,
+    BPQ4K_PROLOGUE_RMSNORM = 1,
+    BPQ4K_PROLOGUE_GELU_MUL = 2,
+    BPQ4K_PROLOGUE_SILU_MUL = 3
+};
+int bpq4k_matmul_fused_f32(bpq4k_handle_t h, int qtype, int prologue, const float* X, const float* aux,
+                           float eps, const void* W, const float* bias, const float* residual, float* Y,
+                           uint32_t N, uint32_t K, uint32_t rowStrideWords, uint32_t yOffset, void* stream);
+
 /* The small-M matmul for callers that must not allocate device memory.  It has no counterpart
  * in the reference.
  *

@@ -17,9 +17,14 @@
  * whose expected values were generated with that compiled reference and are
  * stored under tests/golden/.
  *
+ * One function at the end, oracle_prologue (the element-wise step of the reference's
+ * fused decode shaders), is UNPINNED: the reference has neither a test nor a caller for
+ * those shaders, so there is nothing of the reference's to check it against.
+ *
  * Type numbers are the reference's GGUFType values (runtime/gguf_loader.h:27-30):
  * Q4_K = 12, Q5_K = 13, Q6_K = 14.
  */
+#include <math.h>
 #include <pthread.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -198,4 +203,35 @@ void oracle_kq_matmul(uint32_t type, const float *X, const void *raw, const floa
     for (uint32_t t = 0; t < threads; t++) pthread_join(tid[t], NULL);
     free(jobs);
     free(tid);
+}
+
+/* The element-wise step the reference's fused decode shaders apply to the activation row before
+ * the matmul, in binary32:
+ *   kind 1  out = x * rstd * aux,  rstd = 1/sqrt(sum(x^2)/K + eps)
+ *           (runtime/kernels/quant_kq/q4k_matmul_norm.wgsl:47-92; the shader adds the squares in
+ *           256 strided partial sums and a tree, this restatement adds them in index order --
+ *           the two differ by float rounding of the sum only)
+ *   kind 2  out = 0.5*g*(1 + tanh(0.7978845608*(g + 0.044715*g*g*g))) * aux
+ *           (runtime/kernels/quant_kq/q4k_down_gelu.wgsl:54-59)
+ *   kind 3  out = g/(1 + exp(-g)) * aux   (silu_mul_fused ahead of the down projection,
+ *           runtime/model_runner.cpp:3755-3766)
+ * Parity of this function is UNPINNED: the reference has no test or caller for these shaders. */
+void oracle_prologue(uint32_t kind, const float *x, const float *aux, float eps, uint32_t K, float *out)
+{
+    if (kind == 1u) {
+        float ss = 0.0f;
+        for (uint32_t k = 0; k < K; k++) ss += x[k] * x[k];
+        const float rstd = 1.0f / sqrtf(ss / (float)K + eps);
+        for (uint32_t k = 0; k < K; k++) out[k] = x[k] * rstd * aux[k];
+    } else if (kind == 2u) {
+        for (uint32_t k = 0; k < K; k++) {
+            const float g = x[k];
+            const float inner = 0.7978845608f * (g + 0.044715f * g * g * g);
+            out[k] = 0.5f * g * (1.0f + tanhf(inner)) * aux[k];
+        }
+    } else if (kind == 3u) {
+        for (uint32_t k = 0; k < K; k++) out[k] = x[k] / (1.0f + expf(-x[k])) * aux[k];
+    } else {
+        memcpy(out, x, (size_t)K * sizeof(float));
+    }
 }

@@ -62,6 +62,7 @@ def lib() -> C.CDLL:
         L.oracle_kq_dequant.argtypes = [_u32, C.c_void_p, _fp, _u32, _u32]
         L.oracle_kq_pack.argtypes = [_u32, C.c_void_p, _u32, _u32, C.c_void_p, C.POINTER(_u32), C.POINTER(_u32)]
         L.oracle_kq_matmul.argtypes = [_u32, _fp, C.c_void_p, _fp, _fp, _u32, _u32, _u32, _u32]
+        L.oracle_prologue.argtypes = [_u32, _fp, _fp, C.c_float, _u32, _fp]
         _lib = L
     return _lib
 
@@ -220,6 +221,15 @@ def kq_pack(qtype: int, raw: np.ndarray, N: int, K: int, use_ref: bool = False):
     if words.size:
         fn(qtype, raw.ctypes.data, N, K, words.ctypes.data, C.byref(rs), C.byref(nb))
     return words, rs.value, nb.value
+
+
+def prologue(kind: int, x: np.ndarray, aux: np.ndarray | None, eps: float = 0.0) -> np.ndarray:
+    """The fused decode shaders' element-wise step on one activation row (1 RMSNorm, 2 gelu*up, 3 silu*up)."""
+    x = np.ascontiguousarray(x, np.float32).reshape(-1)
+    a = np.ascontiguousarray(aux if aux is not None else np.zeros_like(x), np.float32).reshape(-1)
+    out = np.zeros_like(x)
+    lib().oracle_prologue(kind, _f(x), _f(a), float(eps), x.size, _f(out))
+    return out
 
 
 def kq_dequant_numpy(qtype: int, raw: np.ndarray, N: int, K: int) -> np.ndarray:
