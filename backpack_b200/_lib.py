@@ -58,6 +58,28 @@ SIGNATURES["bpq4k_kq_dequant_f32"] = (C.c_int, [vp, C.c_int, vp, u32, u32, u32, 
 SIGNATURES["bpq4k_kq_gather_f32"] = (C.c_int, [vp, C.c_int, vp, u32, u32, u32, vp, u32, vp, vp])
 SIGNATURES["bpq4k_kq_matmul_f32"] = (C.c_int, [vp, C.c_int, vp, vp, vp, vp, u32, u32, u32, u32, u32, vp])
 SIGNATURES["bpq4k_matmul_fused_f32"] = (C.c_int, [vp, C.c_int, C.c_int, vp, vp, C.c_float, vp, vp, vp, vp, u32, u32, u32, u32, vp])
+i64 = C.c_int64
+cp = C.c_char_p
+SIGNATURES["bpq4k_device_index"] = (C.c_int, [vp])
+SIGNATURES["bpq4k_gguf_open"] = (C.c_int, [cp, C.POINTER(vp)])
+SIGNATURES["bpq4k_gguf_close"] = (C.c_int, [vp])
+SIGNATURES["bpq4k_gguf_last_error"] = (cp, [vp])
+SIGNATURES["bpq4k_gguf_version"] = (u32, [vp])
+SIGNATURES["bpq4k_gguf_n_tensors"] = (u64, [vp])
+SIGNATURES["bpq4k_gguf_data_offset"] = (u64, [vp])
+SIGNATURES["bpq4k_gguf_has_key"] = (C.c_int, [vp, cp])
+SIGNATURES["bpq4k_gguf_get_u32"] = (u32, [vp, cp, u32])
+SIGNATURES["bpq4k_gguf_get_f32"] = (C.c_float, [vp, cp, C.c_float])
+SIGNATURES["bpq4k_gguf_get_bool"] = (C.c_int, [vp, cp, C.c_int])
+SIGNATURES["bpq4k_gguf_get_string"] = (i64, [vp, cp, i64, vp, u64])
+SIGNATURES["bpq4k_gguf_array_length"] = (i64, [vp, cp])
+SIGNATURES["bpq4k_gguf_get_i32_array"] = (C.c_int, [vp, cp, u64, u64, vp])
+SIGNATURES["bpq4k_gguf_find_tensor"] = (C.c_int, [vp, cp, C.POINTER(u64)])
+SIGNATURES["bpq4k_gguf_tensor_info"] = (C.c_int, [vp, u64, C.POINTER(cp), C.POINTER(u32), C.POINTER(u64 * 4), C.POINTER(u32),
+                                                  C.POINTER(u64), C.POINTER(u64)])
+SIGNATURES["bpq4k_gguf_read_tensor"] = (C.c_int, [vp, u64, u64, u64, vp])
+SIGNATURES["bpq4k_gguf_upload_tensor"] = (C.c_int, [vp, vp, u64, C.c_int, C.POINTER(vp), C.POINTER(C.c_int), C.POINTER(u32),
+                                                    C.POINTER(u32), C.POINTER(u32)])
 
 _lib = None
 

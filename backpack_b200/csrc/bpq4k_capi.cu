@@ -213,6 +213,8 @@ int bpq4k_destroy(bpq4k_handle_t h) {
 
 const char* bpq4k_last_error_string(bpq4k_handle_t h) { return h ? h->err : "null handle"; }
 
+int bpq4k_device_index(bpq4k_handle_t h) { return h ? h->device : -1; }
+
 int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
     if (!h) return BPQ4K_ERR_INVALID_ARG;
     switch (option) {

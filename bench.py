@@ -29,6 +29,7 @@ launch streams its weights from HBM.
 ``kquant_siblings``   (1 GPU) the output head in Q5_K and Q6_K, M = 1.
 ``fused_prologues``   (1 GPU) launch time with and without a fused RMSNorm /
               silu*up prologue and residual epilogue.
+``gguf_upload``       (1 GPU) file -> HBM rate of the GGUF tensor loader.
 
 With N > 1 ranks every rank holds its own row shard of each projection (the
 shard has the single-GPU shape, i.e. the global matrix has N times the rows:
@@ -422,10 +423,11 @@ def run_gpu_arm(args, rank, world, local_rank):
     prefill = None
     if world == 1 and not args.no_prefill:
         prefill = measure_prefill(ctx, torch, shapes, W, dev)
-    siblings = fusions = None
+    siblings = fusions = gguf_up = None
     if world == 1 and not args.no_siblings:
         siblings = measure_siblings(ctx, torch, dev)
         fusions = measure_fusions(ctx, torch, dev)
+        gguf_up = measure_gguf_upload(ctx)
 
     times = torch.tensor([ms, kernel_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
     if dist:
@@ -475,11 +477,56 @@ def run_gpu_arm(args, rank, world, local_rank):
             line["kquant_siblings"] = siblings
         if fusions is not None:
             line["fused_prologues"] = fusions
+        if gguf_up is not None:
+            line["gguf_upload"] = gguf_up
         print(json.dumps(line), flush=True)
     if dist:
         dist.barrier()
         dist.destroy_process_group()
     _ = launches_eager
+
+
+def measure_gguf_upload(ctx):
+    """File -> HBM rate of the GGUF tensor loader on the output head (128256 x 4096, Q4_K, 295 MB) and on
+    its Q6_K form re-spaced into the padded layout on the device.  The file is written to the temp
+    directory just before, so it is read from the page cache: the figure is the pinned double-buffer
+    copy path, not a disk."""
+    import struct
+    import tempfile
+
+    from backpack_b200 import q4k, synth
+    from backpack_b200.gguf import GGUFFile
+
+    def s(b):
+        return struct.pack("<Q", len(b)) + b
+
+    N, K = 128256, 4096
+    out = {"unit": "GB/s of file bytes", "tensors": {}}
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "head.gguf")
+        q4 = synth.make_q4k_weights(N, K, 41)
+        q6 = synth.make_kq_weights(q4k.Q6_K, N, K, 42)
+        hdr = struct.pack("<IIQQ", 0x46554747, 3, 2, 0)
+        hdr += s(b"output.q4k") + struct.pack("<IQQIQ", 2, K, N, 12, 0)
+        off6 = (q4.nbytes + 31) // 32 * 32
+        hdr += s(b"output.q6k") + struct.pack("<IQQIQ", 2, K, N, 14, off6)
+        hdr += b"\0" * ((-len(hdr)) % 32)
+        with open(path, "wb") as f:
+            f.write(hdr)
+            f.write(q4.tobytes())
+            f.write(b"\0" * (off6 - q4.nbytes))
+            f.write(q6.tobytes())
+        g = GGUFFile(path)
+        for name, layout, nbytes in (("output.q4k", 0, q4.nbytes), ("output.q6k", q4k.Q6_K_PADDED, q6.nbytes)):
+            best = 1e9
+            for _ in range(3):
+                t0 = time.perf_counter()
+                t = g.upload(ctx, name, layout)
+                best = min(best, time.perf_counter() - t0)
+                t.free()
+            out["tensors"][name] = {"file_bytes": int(nbytes), "seconds": best, "value": nbytes / best / 1e9}
+        g.close()
+    return out
 
 
 def measure_fusions(ctx, torch, dev):

@@ -107,6 +107,9 @@ int bpq4k_destroy(bpq4k_handle_t h);
  * stderr reporting of Dawn's error callbacks (runtime/gpu_context.cpp:212-237). */
 const char* bpq4k_last_error_string(bpq4k_handle_t h);
 
+/* CUDA device the handle was created on (-1 for a null handle). */
+int bpq4k_device_index(bpq4k_handle_t h);
+
 int bpq4k_set_option(bpq4k_handle_t h, int option, int value);
 int bpq4k_get_option(bpq4k_handle_t h, int option, int* value);
 
@@ -291,6 +294,46 @@ enum bpq4k_prologue {
 int bpq4k_matmul_fused_f32(bpq4k_handle_t h, int qtype, int prologue, const float* X, const float* aux,
                            float eps, const void* W, const float* bias, const float* residual, float* Y,
                            uint32_t N, uint32_t K, uint32_t rowStrideWords, uint32_t yOffset, void* stream);
+
+/* ---- GGUF files ------------------------------------------------------------
+ * Reader for the file format the weights come in, and the tensor -> device step.  Stands in for
+ * GGUFFile::open and its accessors (runtime/gguf_loader.h:46-91, runtime/gguf_loader.cpp:14-182)
+ * and for pack_q*k + uploadKQWeight (runtime/model_runner.cpp:958-963, 1054-1061).  The parser
+ * needs no GPU.  Differences from the reference's reader: every length is checked against the
+ * file size (a corrupt file is an error, not an allocation), general.alignment is honoured when
+ * present (the reference always aligns the tensor data to 32 bytes), and arrays of every scalar
+ * type are kept. */
+typedef struct bpq4k_gguf* bpq4k_gguf_t;
+int bpq4k_gguf_open(const char* path, bpq4k_gguf_t* out); /* UNSUPPORTED: not a GGUF v2+ file or corrupt */
+int bpq4k_gguf_close(bpq4k_gguf_t g);
+const char* bpq4k_gguf_last_error(bpq4k_gguf_t g);
+uint32_t bpq4k_gguf_version(bpq4k_gguf_t g);
+uint64_t bpq4k_gguf_n_tensors(bpq4k_gguf_t g);
+uint64_t bpq4k_gguf_data_offset(bpq4k_gguf_t g);
+/* hasKey / getU32 / getFloat / getBool / getString of the reference, same coercions
+ * (getU32: any integer scalar, or the maximum of an int32 array). */
+int bpq4k_gguf_has_key(bpq4k_gguf_t g, const char* key);
+uint32_t bpq4k_gguf_get_u32(bpq4k_gguf_t g, const char* key, uint32_t def);
+float bpq4k_gguf_get_f32(bpq4k_gguf_t g, const char* key, float def);
+int bpq4k_gguf_get_bool(bpq4k_gguf_t g, const char* key, int def);
+/* String value (index < 0) or element `index` of a string array, copied NUL-terminated into buf
+ * (cap bytes; may be NULL to query).  Returns the string's length, -1 if absent or not a string. */
+int64_t bpq4k_gguf_get_string(bpq4k_gguf_t g, const char* key, int64_t index, char* buf, uint64_t cap);
+int64_t bpq4k_gguf_array_length(bpq4k_gguf_t g, const char* key); /* -1: absent or not an array */
+int bpq4k_gguf_get_i32_array(bpq4k_gguf_t g, const char* key, uint64_t first, uint64_t n, int32_t* out);
+int bpq4k_gguf_find_tensor(bpq4k_gguf_t g, const char* name, uint64_t* index);
+/* name, dims (shape[0] is the contiguous one, K of a weight matrix), GGML type, offset from the
+ * start of the tensor data, size in bytes (0 for a type this reader cannot size).  Any output
+ * pointer may be NULL. */
+int bpq4k_gguf_tensor_info(bpq4k_gguf_t g, uint64_t index, const char** name, uint32_t* n_dims, uint64_t shape[4],
+                           uint32_t* type, uint64_t* offset, uint64_t* n_bytes);
+int bpq4k_gguf_read_tensor(bpq4k_gguf_t g, uint64_t index, uint64_t first, uint64_t n, void* dst_host);
+/* A Q4_K / Q5_K / Q6_K tensor from the file into device memory on the handle's device, in the layout
+ * the matmul entry points take (layout_qtype 0: the packed layout of the tensor's type;
+ * BPQ4K_TYPE_Q6_K_PADDED for a Q6_K tensor: the padded one).  N = product of the dims after the
+ * first.  Free *w_dev with bpq4k_free_device.  Synchronous. */
+int bpq4k_gguf_upload_tensor(bpq4k_handle_t h, bpq4k_gguf_t g, uint64_t index, int layout_qtype, void** w_dev,
+                             int* qtype_out, uint32_t* N_out, uint32_t* K_out, uint32_t* rowStrideWords_out);
 
 /* The small-M matmul for callers that must not allocate device memory.  It has no counterpart
  * in the reference.

@@ -9,6 +9,7 @@
 #include "gguf_loader.h"   // -I <reference>/runtime
 
 #include <cstdint>
+#include <cstdio>
 #include <cstring>
 #include <thread>
 #include <vector>
@@ -122,6 +123,58 @@ void ref_kq_matmul(uint32_t type, const float* X, const void* raw, const float* 
         pool.emplace_back([=]() { kq_rows(type, X, src, bias, Y, M, N, K, n0, n1); });
     }
     for (auto& th : pool) th.join();
+}
+
+// ---- the reference's GGUF reader (GGUFFile::open and accessors, runtime/gguf_loader.cpp:14-182) ----
+
+void* ref_gguf_open(const char* path) {
+    GGUFFile* f = new GGUFFile();
+    if (!f->open(path)) {
+        delete f;
+        return nullptr;
+    }
+    return f;
+}
+void ref_gguf_close(void* p) { delete static_cast<GGUFFile*>(p); }
+uint32_t ref_gguf_version(void* p) { return static_cast<GGUFFile*>(p)->version; }
+uint64_t ref_gguf_n_tensors(void* p) { return static_cast<GGUFFile*>(p)->n_tensors; }
+uint64_t ref_gguf_data_offset(void* p) { return static_cast<GGUFFile*>(p)->data_offset; }
+int ref_gguf_tensor(void* p, uint64_t i, char* name, uint64_t cap, uint32_t* n_dims, uint64_t* shape4, uint32_t* type,
+                    uint64_t* offset) {
+    GGUFFile* f = static_cast<GGUFFile*>(p);
+    if (i >= f->tensors.size()) return -1;
+    const GGUFTensorInfo& t = f->tensors[i];
+    std::snprintf(name, cap, "%s", t.name.c_str());
+    *n_dims = (uint32_t)t.shape.size();
+    for (size_t d = 0; d < 4; d++) shape4[d] = d < t.shape.size() ? t.shape[d] : 1;
+    *type = (uint32_t)t.type;
+    *offset = t.offset;
+    return 0;
+}
+int ref_gguf_has_key(void* p, const char* key) { return static_cast<GGUFFile*>(p)->hasKey(key) ? 1 : 0; }
+uint32_t ref_gguf_get_u32(void* p, const char* key, uint32_t def) { return static_cast<GGUFFile*>(p)->getU32(key, def); }
+float ref_gguf_get_f32(void* p, const char* key, float def) { return static_cast<GGUFFile*>(p)->getFloat(key, def); }
+int ref_gguf_get_bool(void* p, const char* key, int def) { return static_cast<GGUFFile*>(p)->getBool(key, def != 0) ? 1 : 0; }
+int64_t ref_gguf_get_string(void* p, const char* key, int64_t index, char* buf, uint64_t cap) {
+    GGUFFile* f = static_cast<GGUFFile*>(p);
+    std::string s;
+    if (index < 0) {
+        if (!f->hasKey(key)) return -1;
+        s = f->getString(key, "\x01absent");
+        if (s == "\x01absent") return -1;
+    } else {
+        const std::vector<std::string>* a = f->getStringArray(key);
+        if (!a || (uint64_t)index >= a->size()) return -1;
+        s = (*a)[index];
+    }
+    std::snprintf(buf, cap, "%s", s.c_str());
+    return (int64_t)s.size();
+}
+int64_t ref_gguf_i32_array(void* p, const char* key, int32_t* out, uint64_t cap) {
+    const std::vector<int32_t>* a = static_cast<GGUFFile*>(p)->getI32Array(key);
+    if (!a) return -1;
+    for (uint64_t i = 0; i < a->size() && i < cap; i++) out[i] = (*a)[i];
+    return (int64_t)a->size();
 }
 
 }  // extern "C"
