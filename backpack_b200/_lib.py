@@ -80,6 +80,7 @@ SIGNATURES["bpq4k_gguf_tensor_info"] = (C.c_int, [vp, u64, C.POINTER(cp), C.POIN
 SIGNATURES["bpq4k_gguf_read_tensor"] = (C.c_int, [vp, u64, u64, u64, vp])
 SIGNATURES["bpq4k_gguf_upload_tensor"] = (C.c_int, [vp, vp, u64, C.c_int, C.POINTER(vp), C.POINTER(C.c_int), C.POINTER(u32),
                                                     C.POINTER(u32), C.POINTER(u32)])
+SIGNATURES["bpq4k_argmax_f32"] = (C.c_int, [vp, vp, u32, vp, vp])
 
 _lib = None
 

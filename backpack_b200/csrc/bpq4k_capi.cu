@@ -578,6 +578,20 @@ int bpq4k_matmul_fused_f32(bpq4k_handle_t h, int qtype, int prologue, const floa
     return BPQ4K_OK;
 }
 
+int bpq4k_argmax_f32(bpq4k_handle_t h, const float* logits, uint32_t n, int32_t* result, void* stream) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (!logits || !result || n == 0) return fail(h, BPQ4K_ERR_INVALID_ARG, "logits or result is null, or n is 0");
+    if (reinterpret_cast<uintptr_t>(logits) & 3u || reinterpret_cast<uintptr_t>(result) & 3u)
+        return fail(h, BPQ4K_ERR_MISALIGNED, "logits or result is not 4-byte aligned");
+    DeviceGuard g(h->device);
+    // bytes 64..79 of the status allocation are this kernel's two scratch words (zeroed at creation)
+    const cudaError_t e = launch_argmax(logits, n, result, reinterpret_cast<char*>(h->dev_status) + 64, h->sm_count,
+                                        static_cast<cudaStream_t>(stream));
+    h->launches += 1;
+    if (e != cudaSuccess) return cuda_fail(h, e, "argmax launch");
+    return BPQ4K_OK;
+}
+
 int bpq4k_matmul_moe_f32(bpq4k_handle_t h, const float* X, const void* W, const float* bias, float* Y,
                          const uint32_t* offsets, const uint32_t* x_rows, uint32_t nSlots, uint32_t N, uint32_t K,
                          uint32_t rowStrideWords, uint32_t wRows, void* stream) {

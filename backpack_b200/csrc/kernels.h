@@ -86,6 +86,10 @@ cudaError_t launch_prefill_tc(const MatmulArgs& a, int mode, void* scratch, size
 cudaError_t launch_peer_barrier(uint32_t* const* flag_ptrs_host, uint32_t n_peers, uint32_t rank, uint32_t epoch,
                                 uint64_t timeout_cycles, int* status_dev, cudaStream_t stream);
 
+// Index of the largest of n floats (lowest index on ties; 0 when nothing exceeds -1e30) into *result.
+// `scratch`: 16 zeroed, 8-byte aligned device bytes that the kernel leaves zeroed.
+cudaError_t launch_argmax(const float* logits, uint32_t n, int32_t* result, void* scratch, int sm_count, cudaStream_t stream);
+
 // One warp per output row, float FMAs in the reference shader's arithmetic.
 cudaError_t launch_gemv_fp32(const MatmulArgs& a, cudaStream_t stream, int* launches);
 

@@ -248,6 +248,15 @@ class Q4KContext:
             y_offset, self._stream()))
         return out
 
+    def argmax(self, logits, out=None):
+        """Index of the largest logit (int32 device tensor of one element); see bpq4k_argmax_f32."""
+        torch = self._torch
+        assert logits.dtype == torch.float32 and logits.is_cuda and logits.is_contiguous()
+        if out is None:
+            out = torch.empty(1, dtype=torch.int32, device=logits.device)
+        self._check(self.lib.bpq4k_argmax_f32(self.h, logits.data_ptr(), logits.numel(), out.data_ptr(), self._stream()))
+        return out
+
     def matmul_moe(self, x, w: Q4KWeight, n_rows_per_expert: int, offsets, x_rows=None, bias=None, out=None):
         """Indirect form: slot s uses weight rows offsets[s] .. offsets[s]+N of the expert stack."""
         torch = self._torch

@@ -295,6 +295,15 @@ int bpq4k_matmul_fused_f32(bpq4k_handle_t h, int qtype, int prologue, const floa
                            float eps, const void* W, const float* bias, const float* residual, float* Y,
                            uint32_t N, uint32_t K, uint32_t rowStrideWords, uint32_t yOffset, void* stream);
 
+/* ---- greedy sampling step ----------------------------------------------------
+ * *result = index of the largest of the n logits, in one launch.  Replaces the reference's
+ * argmax + argmax_reduce dispatches after the output head (runtime/kernels/shape/argmax.wgsl,
+ * argmax_reduce.wgsl; runtime/model_runner.cpp:2246, 2441-2452): same strict comparison against a
+ * start value of -1e30 (NaNs and values <= -1e30 never win; 0 when nothing does); on ties, where the
+ * reference's answer depends on its scan order, the lowest index.  `logits` and `result` are device
+ * pointers.  Calls on one handle that may overlap on the GPU must be serialised by the caller. */
+int bpq4k_argmax_f32(bpq4k_handle_t h, const float* logits, uint32_t n, int32_t* result, void* stream);
+
 /* ---- GGUF files ------------------------------------------------------------
  * Reader for the file format the weights come in, and the tensor -> device step.  Stands in for
  * GGUFFile::open and its accessors (runtime/gguf_loader.h:46-91, runtime/gguf_loader.cpp:14-182)

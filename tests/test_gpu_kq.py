@@ -162,3 +162,34 @@ def test_kq_errors_are_statuses(ctx):
     assert lib.bpq4k_kq_gather_f32(ctx.h, 12, wbuf.data_ptr(), 8, 256, 36, x.data_ptr(), 1, y.data_ptr(), s) == 2
     assert lib.bpq4k_kq_dequant_f32(ctx.h, 14, None, 8, 256, 53, y.data_ptr(), s) == 1
     assert isinstance(Q4KError(2, "x"), RuntimeError)
+
+
+def argmax_oracle(v):
+    """The reference's argmax.wgsl / argmax_reduce.wgsl where the maximum is unique: strict > against a
+    start of -1e30, index 0 when nothing wins; lowest index on ties."""
+    v = np.asarray(v, np.float32)
+    ok = v > np.float32(-1e30)          # False for NaN too
+    if not ok.any():
+        return 0
+    m = v[ok].max()
+    return int(np.flatnonzero(ok & (v == m))[0])
+
+
+@pytest.mark.parametrize("n", [1, 7, 256, 1000, 32000, 128256, 400000])
+def test_argmax_matches_reference_rule(ctx, n):
+    import torch
+
+    rng = np.random.default_rng(n)
+    cases = [rng.standard_normal(n).astype(np.float32) * 10]
+    t = cases[0].copy(); t[n // 2] = t.max() + 1; t[n - 1] = t[n // 2]; cases.append(t)       # a tie: lowest index wins
+    t = cases[0].copy(); t[: max(1, n // 3)] = np.nan; cases.append(t)                           # NaNs never win
+    cases.append(np.full(n, -2e30, np.float32))                                                   # nothing above the start value
+    t = np.full(n, -np.inf, np.float32); t[n - 1] = -5.0; cases.append(t)                         # maximum at the very end
+    cases.append(-np.abs(cases[0]) - 1)                                                           # all negative
+    for v in cases:
+        got = int(ctx.argmax(dev(torch, v)).cpu()[0])
+        assert got == argmax_oracle(v)
+    # back to back on one stream: the scratch words are left clean
+    a = dev(torch, cases[0]); b = dev(torch, cases[5])
+    r1, r2 = ctx.argmax(a), ctx.argmax(b)
+    assert (int(r1.cpu()[0]), int(r2.cpu()[0])) == (argmax_oracle(cases[0]), argmax_oracle(cases[5]))
