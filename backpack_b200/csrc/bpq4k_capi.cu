@@ -496,19 +496,26 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
     a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
     int launches = 0;
     cudaError_t e = cudaErrorInvalidValue;
-    // padded Q6_K: the streaming kernel, one activation row per launch (per row it still beats the
-    // plain kernel's eight rows per pass)
+    // padded Q6_K: the streaming kernel in slabs of up to 8 rows; a slab whose rows do not fit in shared
+    // memory together (long K) is halved (8 -> 4 -> 2 -> 1 rows), which still beats the plain kernel
     if (qtype == BPQ4K_TYPE_Q6_K_PADDED && h->gemv_variant != BPQ4K_GEMV_FP32 && aligned16(X) && K % 4u == 0) {
+        const cudaStream_t st = static_cast<cudaStream_t>(stream);
         MatmulArgs c = a;
-        c.M = 1;
         e = cudaSuccess;
-        for (uint32_t m = 0; m < M && e == cudaSuccess; m++) {
-            c.X = a.X + (uint64_t)m * K;
-            c.Y = a.Y + (uint64_t)m * N;
-            e = launch_q6k_stream(c, h->tune, h->dev_status, h->sm_count, &h->tmaps, static_cast<cudaStream_t>(stream), &launches);
-            if (e == cudaErrorInvalidValue && m == 0) break;  // shape outside the kernel: plain kernel below
+        uint32_t slab = kStreamMaxM;
+        for (uint32_t m0 = 0; m0 < M && e == cudaSuccess;) {
+            c.M = M - m0 < slab ? M - m0 : slab;
+            c.X = a.X + (uint64_t)m0 * K;
+            c.Y = a.Y + (uint64_t)m0 * N;
+            e = launch_q6k_stream(c, h->tune, h->dev_status, h->sm_count, &h->tmaps, st, &launches);
+            if (e == cudaErrorInvalidValue && c.M > 1) {  // does not fit: smaller slabs from here on
+                slab = c.M > 4 ? 4 : c.M > 2 ? 2 : 1;
+                e = cudaSuccess;
+                continue;
+            }
+            m0 += c.M;
         }
-        if (e == cudaErrorInvalidValue) launches = 0;
+        if (e == cudaErrorInvalidValue) launches = 0;  // not even one row fits: the plain kernel below
     }
     // Q5_K: the streaming kernel in slabs of 8 rows (each slab re-reads the weights)
     if (qtype == BPQ4K_TYPE_Q5_K && h->gemv_variant != BPQ4K_GEMV_FP32 && aligned16(X)) {

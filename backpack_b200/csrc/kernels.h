@@ -103,8 +103,8 @@ cudaError_t launch_kq_gemv_fp32(int qtype, const MatmulArgs& a, cudaStream_t str
 constexpr int kQ6PaddedType = 0x10E;
 constexpr uint32_t kQ6PaddedBytes = 224;
 
-// Streaming tensor-core matmul for ONE activation row of Q6_K weights in the padded layout.
-// cudaErrorInvalidValue: the shape does not fit this kernel (use launch_kq_gemv_fp32).
+// Streaming tensor-core matmul for M <= 8 activation rows of Q6_K weights in the padded layout.
+// cudaErrorInvalidValue: the shape does not fit the kernel (several rows of a long K; go row by row).
 cudaError_t launch_q6k_stream(const MatmulArgs& a, const StreamTuning& tune, int* status_dev, int sm_count, TmapCache* tmaps,
                               cudaStream_t stream, int* launches);
 

@@ -48,6 +48,7 @@ struct Q6Args {
     uint32_t wk, wt, cb, rem, bpw, stages, stage_bytes, ntiles;
     uint32_t off_S, off_x, off_part, off_ring;
     int* status;
+    uint32_t tokens;  // activation-row slots of the several-row kernel (4 or 8)
 };
 
 // Quantise 8 consecutive activations v0, v1 (item c8 of the row; zeros for an idle lane).  The two items of a 16-value group sit in
@@ -319,14 +320,291 @@ __global__ void __launch_bounds__(512, 1) q6k_stream_kernel(const __grid_constan
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Several activation rows (M = 2..8): the eight mma columns are four activation rows x the two
+// 16-weight scale groups of a 32-weight group, one mma per digit.  Thread t of a quad then holds,
+// for rows r and r+8 of the tile, both scale groups of activation row t.
+//
+// Layouts in shared memory (TOK = 4 or 8 row slots, rows past M are zero):
+//   digits  frag + ((G*TOK + tok)*128) + w*16 + d*4 : the four k-bytes of word w (k = 4w..4w+3 of
+//           32-weight group G) of digit d (d = 3: zero) -- one 16-byte load gives a thread the three
+//           digit words of its B fragment, and the four rows of a tile are 128 bytes apart
+//   scales  SI[((blk*8 + c)*TOK + tok)*4 + f%4],  c = f/4,  f = g16 (inv, 0..15) or 16 + g16 (sum*inv)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void q6_quantize_item_rows(float4 v0, float4 v1, uint32_t tok, uint32_t TOK, uint32_t c8, bool valid,
+                                                      uint8_t* frag, float* SI) {
+    float amax = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
+                       fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    float scale = 1.f, inv = 1.f;
+    if (amax > 1e-30f && amax < 3e38f) {
+        scale = kXiMax6 / amax;
+        inv = amax / kXiMax6;
+    }
+    const float xs[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    uint32_t w0[2] = {0, 0}, w1[2] = {0, 0}, w2[2] = {0, 0};
+    int sum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float vc = fminf(fmaxf(xs[i] * scale, -kXiMax6), kXiMax6);
+        const int xi = __float2int_rn(vc);
+        const int d2 = ((xi + 64) & 127) - 64;
+        const int r1 = (xi - d2) >> 7;
+        const int d1 = ((r1 + 64) & 127) - 64;
+        const int d0 = (r1 - d1) >> 7;
+        sum += xi;
+        w0[i >> 2] |= (uint32_t)(d0 & 255) << (8 * (i & 3));
+        w1[i >> 2] |= (uint32_t)(d1 & 255) << (8 * (i & 3));
+        w2[i >> 2] |= (uint32_t)(d2 & 255) << (8 * (i & 3));
+    }
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    if (!valid) return;
+    const uint32_t k0 = c8 * 8u, G = k0 >> 5, w = (k0 & 31u) >> 2;
+    uint4* dst = reinterpret_cast<uint4*>(frag + ((uint64_t)G * TOK + tok) * 128u + w * 16u);
+    dst[0] = make_uint4(w0[0], w1[0], w2[0], 0u);
+    dst[1] = make_uint4(w0[1], w1[1], w2[1], 0u);
+    if ((c8 & 1u) == 0) {
+        const uint32_t g16 = k0 >> 4, blk = g16 >> 4, f = g16 & 15u;
+        SI[((blk * 8u + (f >> 2)) * TOK + tok) * 4u + (f & 3u)] = inv;
+        SI[((blk * 8u + 4u + (f >> 2)) * TOK + tok) * 4u + (f & 3u)] = (float)sum * inv;
+    }
+}
+
+template <int NT>
+__global__ void __launch_bounds__(256, 1) q6k_stream_rows_kernel(const __grid_constant__ Q6Args a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr uint32_t TOK = NT * 4;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t nwarps = blockDim.x >> 5;
+    const uint32_t wk = warp % a.wk, wt = warp / a.wk;
+    const uint32_t K = a.m.K, N = a.m.N, M = a.m.M;
+    const uint32_t b0 = wk * a.bpw;
+    const uint32_t nfull = a.bpw / a.cb;
+    const uint32_t nchunks = nfull + (a.rem ? 1u : 0u);
+    const float* X = a.m.X;
+    float* Y = a.m.Y;
+
+    const uint32_t tstride = gridDim.x * a.wt;
+    const uint32_t tile0 = blockIdx.x * a.wt + wt;
+    const uint32_t my_tiles = tile0 < a.ntiles ? (a.ntiles - tile0 + tstride - 1) / tstride : 0;
+    const uint32_t total_units = my_tiles * nchunks;
+
+    const uint32_t bar0 = smem_u32(smem) + warp * kMaxStages6 * 8u;
+    const uint32_t ring = smem_u32(smem + a.off_ring) + warp * a.stages * a.stage_bytes;
+    if (lane == 0) {
+        for (uint32_t s = 0; s < a.stages; s++) mbar_init(bar0 + s * 8u, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    fence_proxy_async();
+    __syncwarp();
+
+    uint32_t iss_tile = tile0, iss_c = 0, iss_st = 0;
+    auto issue_next = [&]() {
+        if (lane == 0) {
+            const uint32_t bar = bar0 + iss_st * 8u;
+            const bool full = iss_c < nfull;
+            mbar_expect_tx(bar, 16u * kQ6Pad * (full ? a.cb : a.rem));
+            tma_load_2d(ring + iss_st * a.stage_bytes, full ? &a.tmap : &a.tmap_rem, (b0 + iss_c * a.cb) * kQ6PadWords,
+                        iss_tile * 16u, bar);
+        }
+        if (++iss_st == a.stages) iss_st = 0;
+        if (++iss_c == nchunks) {
+            iss_c = 0;
+            iss_tile += tstride;
+        }
+    };
+    {
+        const uint32_t pre = min(a.stages, total_units);
+        for (uint32_t i = 0; i < pre; i++) issue_next();
+    }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    {
+        uint8_t* frag = smem + a.off_x;
+        float* SI = reinterpret_cast<float*>(smem + a.off_S);
+        const uint32_t nb = K / kQK, mrows = min(M, TOK);
+        // rows past M: zero digits and scales (every slot of the layouts interleaves the rows)
+        if (mrows < TOK) {
+            for (uint32_t i = tid; i < TOK * K; i += blockDim.x) {  // word i of the digit area: row = (i / 32) % TOK
+                if ((i >> 5) % TOK >= mrows) reinterpret_cast<uint32_t*>(frag)[i] = 0u;
+            }
+            for (uint32_t i = tid; i < nb * 8u * TOK * 4u; i += blockDim.x) {
+                if ((i >> 2) % TOK >= mrows) SI[i] = 0.f;
+            }
+        }
+        constexpr int U = 4;
+        const uint32_t per_row = K / 8u, items = mrows * per_row;
+        for (uint32_t base = 0; base < items; base += blockDim.x * U) {
+            const uint32_t nj = min((uint32_t)U, (items - base + blockDim.x - 1) / blockDim.x);
+            float4 v[U][2];
+            uint32_t tok[U], c8[U];
+#pragma unroll
+            for (int j = 0; j < U; j++) {
+                const uint32_t it = base + j * blockDim.x + tid;
+                const bool ok = (uint32_t)j < nj && it < items;
+                tok[j] = ok ? it / per_row : 0u;
+                c8[j] = ok ? it - tok[j] * per_row : 0u;
+                v[j][0] = v[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (ok) {
+                    const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok[j] * K + (uint64_t)c8[j] * 8u);
+                    v[j][0] = __ldg(xp);
+                    v[j][1] = __ldg(xp + 1);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < U; j++) {
+                const uint32_t it = base + j * blockDim.x + tid;
+                if ((uint32_t)j < nj) q6_quantize_item_rows(v[j][0], v[j][1], tok[j], TOK, c8[j], it < items, frag, SI);
+            }
+        }
+        __syncthreads();
+    }
+
+    const uint32_t r = lane >> 2, t = lane & 3u;
+    const uint32_t lm_row = (lane & 7u) + ((lane >> 3) & 1u) * 8u, lm_col = (lane >> 4) * 16u;
+    // B operand: column n = lane/4 -> activation row n/2 of the mma tile, scale group (half) n%2
+    const uint32_t bn = lane >> 2, bhalf = bn & 1u;
+    const uint32_t x_lane = smem_u32(smem + a.off_x) + (bn >> 1) * 128u + (bhalf * 4u + t) * 16u;  // + (G*TOK + nt*4)*128
+    const uint32_t mask0 = bhalf ? 0u : 0xFFFFFFFFu, mask1 = ~mask0;
+    const uint32_t s_lane = smem_u32(smem + a.off_S) + t * 16u;  // + ((blk*8 + c)*TOK + nt*4)*16
+
+    float* part = reinterpret_cast<float*>(smem + a.off_part);
+    uint32_t st = 0, ph = 0, u = 0, failed = 0;
+
+    for (uint32_t ti = 0; ti < my_tiles; ti++) {
+        const uint32_t tile = tile0 + ti * tstride;
+        float acc[NT][2], acc_s[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc_s[nt][0] = acc_s[nt][1] = 0.f;
+        for (uint32_t c = 0; c < nchunks; c++) {
+            const uint32_t bs = b0 + c * a.cb;
+            const uint32_t nblk = c < nfull ? a.cb : a.rem;
+            const uint32_t pitch = nblk * kQ6Pad;
+            const uint32_t bar = bar0 + st * 8u;
+            if (!failed) {
+                uint32_t polls = 0;
+                while (!mbar_try_wait(bar, ph)) {
+                    if (++polls > kWaitPolls6) {
+                        failed = 1;
+                        if (lane == 0 && a.status) atomicExch(a.status, kDeviceTimeout);
+                        break;
+                    }
+                }
+            }
+            uint32_t boff = ring + st * a.stage_bytes;
+            for (uint32_t blk = bs; blk < bs + nblk; blk++, boff += kQ6Pad) {
+                const uint32_t lm_addr = boff + lm_row * pitch + lm_col;
+                auto do_half = [&](auto hc) {
+                    constexpr int h = decltype(hc)::value;
+                    // d*scale of rows r, r+8 for the eight scale groups of this half (index 2*gg + column half)
+                    float ds[2][8];
+#pragma unroll
+                    for (int rr = 0; rr < 2; rr++) {
+                        const uint32_t hdr = boff + (r + rr * 8u) * pitch + 192u;
+                        const uint4 sv = lds128<0>(hdr);
+                        const uint4 dv = lds128<16>(hdr);
+                        const float d = half_bits_to_float(dv.x);
+                        const uint32_t swa = h ? sv.z : sv.x, swb = h ? sv.w : sv.y;
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            int sc;  // sign-extending pick of byte j%4
+                            asm("prmt.b32 %0, %1, 0, %2;" : "=r"(sc) : "r"(j < 4 ? swa : swb), "r"(0x8880 + (j & 3) * 0x1111));
+                            ds[rr][j] = d * (float)sc;
+                        }
+                    }
+                    uint32_t la[4], lb[4], lh[4];
+                    ldmatrix_x4<h * 64>(lm_addr, la[0], la[1], la[2], la[3]);
+                    ldmatrix_x4<h * 64 + 32>(lm_addr, lb[0], lb[1], lb[2], lb[3]);
+                    ldmatrix_x4<128 + h * 32>(lm_addr, lh[0], lh[1], lh[2], lh[3]);
+                    uint32_t q[4][4];
+#pragma unroll
+                    for (int gg = 0; gg < 4; gg++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const uint32_t lo = (gg & 1) ? lb[i] : la[i];
+                            const uint32_t nib = (gg & 2) ? (lo >> 4) : lo;
+                            const uint32_t hi = gg == 0 ? (lh[i] << 4) : gg == 1 ? (lh[i] << 2) : gg == 2 ? lh[i] : (lh[i] >> 2);
+                            q[gg][i] = (nib & 0x0F0F0F0Fu) | (hi & 0x30303030u);
+                        }
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        // this thread's activation row (t of tile nt): inv and sum*inv of the half's eight scale groups
+                        const uint32_t sa = s_lane + ((blk * 8u + 2u * h) * TOK + nt * 4u) * 16u;
+                        const uint4 i0 = lds128<0>(sa), i1 = lds128<0>(sa + TOK * 16u);
+                        const uint4 s0 = lds128<0>(sa + 4u * TOK * 16u), s1 = lds128<0>(sa + 5u * TOK * 16u);
+                        const float inv[8] = {__uint_as_float(i0.x), __uint_as_float(i0.y), __uint_as_float(i0.z), __uint_as_float(i0.w),
+                                              __uint_as_float(i1.x), __uint_as_float(i1.y), __uint_as_float(i1.z), __uint_as_float(i1.w)};
+                        const float sm[8] = {__uint_as_float(s0.x), __uint_as_float(s0.y), __uint_as_float(s0.z), __uint_as_float(s0.w),
+                                             __uint_as_float(s1.x), __uint_as_float(s1.y), __uint_as_float(s1.z), __uint_as_float(s1.w)};
+                        const uint32_t xb = x_lane + (((blk * 8u + h * 4u) * TOK) + nt * 4u) * 128u;
+#pragma unroll
+                        for (int gg = 0; gg < 4; gg++) {
+                            const uint4 dw = lds128<0>(xb + gg * TOK * 128u);  // digit words d0, d1, d2 of this column
+                            int c0[4], c1[4], c2[4];
+                            imma16832_first(c0, q[gg][0], q[gg][1], q[gg][2], q[gg][3], dw.x & mask0, dw.x & mask1);
+                            imma16832_first(c1, q[gg][0], q[gg][1], q[gg][2], q[gg][3], dw.y & mask0, dw.y & mask1);
+                            imma16832_first(c2, q[gg][0], q[gg][1], q[gg][2], q[gg][3], dw.z & mask0, dw.z & mask1);
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {  // e: row r (0, 1) or r+8 (2, 3); column half e%2
+                                const int rr = e >> 1, j = 2 * gg + (e & 1);
+                                const float T = fmaf((float)c0[e], 16384.f, (float)(c1[e] * 128 + c2[e]));
+                                acc[nt][rr] = fmaf(T, ds[rr][j] * inv[j], acc[nt][rr]);
+                                acc_s[nt][rr] = fmaf(ds[rr][j], sm[j], acc_s[nt][rr]);
+                            }
+                        }
+                    }
+                };
+                do_half(std::integral_constant<int, 0>{});
+                do_half(std::integral_constant<int, 1>{});
+            }
+            __syncwarp();
+            fence_proxy_async();
+            if (u + a.stages < total_units) issue_next();
+            u++;
+            if (++st == a.stages) {
+                st = 0;
+                ph ^= 1u;
+            }
+        }
+
+        // ---- tile epilogue: K slices -> bias -> Y ----
+        float* pbuf = part + ((uint64_t)((ti & 1u) * nwarps + warp)) * (TOK * 16u);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            pbuf[(nt * 4u + t) * 16u + r] = fmaf(-32.f, acc_s[nt][0], acc[nt][0]);
+            pbuf[(nt * 4u + t) * 16u + r + 8u] = fmaf(-32.f, acc_s[nt][1], acc[nt][1]);
+        }
+        if (a.wk > 1) {
+            asm volatile("bar.sync %0, %1;" ::"r"(wt + 1u), "r"(a.wk * 32u) : "memory");
+        } else {
+            __syncwarp();
+        }
+        if (wk == 0) {
+            for (uint32_t idx = lane; idx < TOK * 16u; idx += 32u) {
+                const uint32_t tok = idx >> 4, row = tile * 16u + (idx & 15u);
+                if (tok < M && row < N) {
+                    float s = 0.f;
+                    for (uint32_t k2 = 0; k2 < a.wk; k2++) s += pbuf[(uint64_t)k2 * (TOK * 16u) + idx];
+                    Y[(uint64_t)tok * N + row] = s + (a.m.bias ? a.m.bias[row] : 0.f);
+                }
+            }
+        }
+    }
+}
+
 }  // namespace
 
-// One activation row, Q6_K weights in the padded layout.  Returns cudaErrorInvalidValue when the
-// shape does not fit this kernel (the caller then uses the plain kernel).
+// Up to 8 activation rows, Q6_K weights in the padded layout.  Returns cudaErrorInvalidValue when the
+// shape does not fit the kernel (several rows of a long K need more shared memory than there is;
+// the caller then goes row by row, or uses the plain kernel).
 cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int* status_dev, int sm_count, TmapCache* tmaps,
                               cudaStream_t stream, int* launches) {
     if (m.N == 0) return cudaSuccess;
-    if (m.M != 1 || m.n_slots) return cudaErrorInvalidValue;
+    if (m.M == 0 || m.M > 8 || m.n_slots) return cudaErrorInvalidValue;
+    const bool rows = m.M > 1;                           // the several-row kernel
+    const uint32_t tokens = rows ? (m.M + 3) / 4 * 4 : 1;
     const uint32_t nb = m.K / kQK;
     const uint32_t ntiles = (m.N + 15) / 16;
     constexpr uint32_t kSmemMax = 227 * 1024;
@@ -338,6 +616,7 @@ cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int
     uint32_t warps = 0, wk = 0, wt = 0, bpw = 0, cb = 0, rem = 0, stage_bytes = 0, stages = 0, smem = 0;
     auto plan = [&](uint32_t warps_want, uint32_t cb_want, uint32_t stages_want) -> bool {
         warps = warps_want > kMaxWarps6 ? kMaxWarps6 : warps_want;
+        if (rows && warps > 8) warps = 8;  // the several-row kernel is built for 256 threads
         wk = tune.wk;
         if (!wk) {
             if (small) {
@@ -361,9 +640,9 @@ cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int
         stages = stages_want > kMaxStages6 ? kMaxStages6 : stages_want;
         auto layout = [&](uint32_t st) -> uint32_t {
             uint32_t off = kBarBytes6;
-            qa.off_S = off; off += nb * 128u;
-            qa.off_x = align_up(off, 128); off = qa.off_x + m.K * 4u;
-            qa.off_part = align_up(off, 16); off = qa.off_part + 2u * warps * 16u * 4u;
+            qa.off_S = off; off += tokens * nb * 128u;
+            qa.off_x = align_up(off, 128); off = qa.off_x + tokens * m.K * 4u;
+            qa.off_part = align_up(off, 16); off = qa.off_part + 2u * warps * tokens * 16u * 4u;
             qa.off_ring = align_up(off, 128); off = qa.off_ring + warps * st * stage_bytes;
             return off;
         };
@@ -374,8 +653,10 @@ cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int
     // the tuned plan first; with a long K the digits leave less room: narrower stages, then fewer warps
     const uint32_t warps0 = tune.warps ? tune.warps : (small ? 16 : 8);
     const uint32_t stages0 = tune.stages ? tune.stages : (small ? 2 : 4);
-    if (!plan(warps0, tune.cb, stages0) && !plan(warps0, 1, 2) && !plan(8, 1, 2) && !plan(4, 1, 2)) return cudaErrorInvalidValue;
+    if (!plan(warps0, tune.cb, stages0) && !(rows && plan(warps0, 2, 2)) && !plan(warps0, 1, 2) && !plan(8, 1, 2) && !plan(4, 1, 2))
+        return cudaErrorInvalidValue;
     qa.m = m;
+    qa.tokens = tokens;
     qa.wk = wk; qa.wt = wt; qa.cb = cb; qa.rem = rem; qa.bpw = bpw; qa.stages = stages; qa.stage_bytes = stage_bytes;
     qa.ntiles = ntiles; qa.status = status_dev;
 
@@ -412,15 +693,18 @@ cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int
         qa.tmap_rem = qa.tmap;
     }
 
-    static size_t smem_cfg = 0;
+    static size_t smem_cfg[3] = {0, 0, 0};
     static int cfg_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
-    if (cfg_dev != dev) smem_cfg = 0, cfg_dev = dev;
-    if (smem > smem_cfg) {
-        cudaError_t e = cudaFuncSetAttribute(q6k_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (cfg_dev != dev) smem_cfg[0] = smem_cfg[1] = smem_cfg[2] = 0, cfg_dev = dev;
+    const int variant = !rows ? 0 : tokens == 4 ? 1 : 2;
+    if (smem > smem_cfg[variant]) {
+        const cudaError_t e = variant == 0 ? cudaFuncSetAttribute(q6k_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                            : variant == 1 ? cudaFuncSetAttribute(q6k_stream_rows_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                           : cudaFuncSetAttribute(q6k_stream_rows_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        smem_cfg = smem;
+        smem_cfg[variant] = smem;
     }
     // persistent grid, one CTA per SM, balanced: the smallest grid that needs no more rounds than
     // the whole machine would
@@ -440,7 +724,9 @@ cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = tune.no_pdl ? 0 : 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, q6k_stream_kernel, qa);
+    const cudaError_t e = variant == 0 ? cudaLaunchKernelEx(&cfg, q6k_stream_kernel, qa)
+                        : variant == 1 ? cudaLaunchKernelEx(&cfg, q6k_stream_rows_kernel<1>, qa)
+                                       : cudaLaunchKernelEx(&cfg, q6k_stream_rows_kernel<2>, qa);
     if (launches) ++*launches;
     return e;
 }
