@@ -58,7 +58,8 @@ namespace {
 
 constexpr uint32_t kMaxWarps = 16;
 constexpr uint32_t kMaxStages = 8;
-constexpr uint32_t kBarBytes = kMaxWarps * kMaxStages * 8;  // 1 KiB of mbarriers
+constexpr uint32_t kRingBarBytes = kMaxWarps * kMaxStages * 8;  // 1 KiB of ring mbarriers
+constexpr uint32_t kBarBytes = kRingBarBytes + 64;              // + the barrier of the activation copy (XC)
 constexpr uint32_t kWaitPolls = 1u << 22;                    // bounded mbarrier wait
 
 constexpr uint32_t kZeroBytes = 1024;  // zero region the "other parity" lanes read their B operand from
@@ -168,8 +169,12 @@ __device__ __forceinline__ void merge_fifth_bit(uint32_t codes, uint32_t qh, uin
 // Q5: the weights are Q5_K super-blocks (176 bytes: the Q4_K header, 32 bytes of fifth bits, 128
 // nibble bytes); the fifth bit is merged into each code byte, so odd sub-blocks reach the mma as
 // q (not 16*q) and carry no 1/16 in their scale.
-template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false>
+// XC (with XG false): the digits live in shared memory as usual, but they were quantised once per call by
+// quantize_activations_kernel and every CTA only copies them in (bulk copies from the scratch) instead of
+// quantising all rows itself -- with eight rows that is ~1 us instead of ~8 us per CTA.
+template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false, bool XC = false>
 __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
+    static_assert(!(XG && XC), "digits are read from the scratch directly (XG) or copied into shared memory (XC)");
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr uint32_t BB = Q5 ? 176u : kBlockBytes, BW = BB / 4u;  // bytes and words per super-block
     constexpr uint32_t QS = Q5 ? 48u : 16u;                          // offset of the nibble bytes
@@ -204,8 +209,10 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
     const uint32_t bar0 = smem_u32(smem) + warp * kMaxStages * 8u;
     const uint32_t ring = smem_u32(smem + a.off_ring) + warp * a.stages * a.stage_bytes;
 
+    const uint32_t xbar = smem_u32(smem) + kRingBarBytes;  // XC: completion of the activation copy
     if (lane == 0) {
         for (uint32_t s = 0; s < a.stages; s++) mbar_init(bar0 + s * 8u, 1);
+        if (XC && warp == 0) mbar_init(xbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     fence_proxy_async();
@@ -240,7 +247,34 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
 
     // ---- activations: quantise to base-128 digits, once per CTA ---------------------
     const uint32_t NG = K / 64u;
-    if constexpr (!XG) {
+    if constexpr (XC) {
+        // digits and scales of all rows, quantised by the kernel that precedes this one in the stream:
+        // warp 0 copies them in (one bulk copy per row for each), everybody waits for the bytes
+        for (uint32_t i = tid; i < kZeroBytes / 4u; i += blockDim.x) reinterpret_cast<uint32_t*>(smem + a.off_zero)[i] = 0u;
+        if (warp == 0) {
+            const uint32_t seg = K * 4u, sseg = nb * 64u;
+            if (lane == 0) mbar_expect_tx(xbar, (uint32_t)TOK * (seg + sseg));
+            __syncwarp();
+            for (uint32_t tok = lane; tok < (uint32_t)TOK; tok += 32u) {
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 smem_u32(smem + a.off_x) + tok * seg),
+                             "l"(a.xfrag_g + kZeroBytes + (uint64_t)tok * seg), "r"(seg), "r"(xbar)
+                             : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 smem_u32(smem + a.off_S) + tok * sseg),
+                             "l"(reinterpret_cast<const uint8_t*>(a.S_g) + (uint64_t)tok * sseg), "r"(sseg), "r"(xbar)
+                             : "memory");
+            }
+        }
+        uint32_t polls = 0;
+        while (!mbar_try_wait(xbar, 0)) {
+            if (++polls > kWaitPolls) {  // give up: flag it and carry on with whatever is there
+                if (tid == 0 && a.status) atomicExch(a.status, kDeviceTimeout);
+                break;
+            }
+        }
+        __syncthreads();  // zero region written
+    } else if constexpr (!XG) {
         // one pass: every thread quantises 8-float items straight from global memory
         for (uint32_t i = tid; i < kZeroBytes / 4u; i += blockDim.x) reinterpret_cast<uint32_t*>(smem + a.off_zero)[i] = 0u;
         const uint32_t per_row = K / 8u;
@@ -641,6 +675,9 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) quantize_activations_kernel(const float* __restrict__ X, uint32_t M, uint32_t K,
                                                                    uint32_t tokens, uint8_t* __restrict__ scratch) {
+    // the matmul kernel that follows may start its weight prefetch now; it waits for this grid to
+    // complete before it reads the scratch
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint8_t* frag = scratch + kZeroBytes;
     float* SI = reinterpret_cast<float*>(frag + (uint64_t)tokens * K * 4u);
     const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x;
@@ -656,7 +693,7 @@ __global__ void __launch_bounds__(256) quantize_activations_kernel(const float* 
 
 // Launch one instantiation.  The grid is persistent: at most as many CTAs as can be
 // resident at once (occupancy query, cached), never more than there are tile groups.
-template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false>
+template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false, bool XC = false>
 cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, uint32_t threads, size_t smem,
                        int sm_count, uint32_t ctas_per_sm_override, bool pdl, cudaStream_t stream) {
     struct Cache { int dev = -1; size_t smem_cfg = 0; uint32_t threads = 0; size_t smem = 0; int occ = 0; };
@@ -666,7 +703,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     if (cache.dev != dev) cache = Cache{};
     cache.dev = dev;
     if (smem > cache.smem_cfg) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT, M1, XG, PROBE, Q5>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return e;
         cache.smem_cfg = smem;
@@ -674,7 +711,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     }
     if (cache.threads != threads || cache.smem != smem) {
         int occ = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_stream_kernel<NT, M1, XG, PROBE, Q5>, (int)threads, smem);
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC>, (int)threads, smem);
         if (e != cudaSuccess) return e;
         cache.threads = threads;
         cache.smem = smem;
@@ -705,7 +742,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, PROBE, Q5>, sa);
+    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC>, sa);
 }
 
 static_assert(sizeof(CUtensorMap) == 128, "TmapCache::Entry::map must hold a CUtensorMap");
@@ -809,6 +846,8 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         }
         if (!fits) xg = true;
     }
+    // eight rows that fit in shared memory: quantise them once per call (scratch), copy them in per CTA
+    const bool xc = !xg && !m1 && NT > 1 && !indirect && scratch && scratch_bytes >= gemv_stream_scratch_bytes(M, m.K);
     const uint32_t rem = bpw % cb;
     stage_bytes = 16 * cb * block_bytes;
     if (xg) {
@@ -860,7 +899,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     const uint32_t groups = (ntiles + wt - 1) / wt;  // CTAs needed to give every tile a slot once
     const uint32_t slots_total = indirect ? m.n_slots : 1;
 
-    if (xg) {
+    if (xg || xc) {
         uint8_t* sc = static_cast<uint8_t*>(scratch);
         const uint32_t items = tokens * (m.K / 8u);
         uint32_t qgrid = (items + 255) / 256;
@@ -900,6 +939,9 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
 #endif
         if (m1) e = xg ? BPQ4K_LAUNCH(1, true, true) : BPQ4K_LAUNCH(1, true, false);
         else if (NT == 1) e = xg ? BPQ4K_LAUNCH(1, false, true) : BPQ4K_LAUNCH(1, false, false);
+        else if (xc)
+            e = q5 ? launch_one<2, false, false, 0, true, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream)
+                   : launch_one<2, false, false, 0, false, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream);
         else e = xg ? BPQ4K_LAUNCH(2, false, true) : BPQ4K_LAUNCH(2, false, false);
 #undef BPQ4K_LAUNCH
         if (launches) ++*launches;

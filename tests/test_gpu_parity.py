@@ -249,7 +249,8 @@ def test_prefill_threshold_option(ctx):
     ctx.set_option(q4k.OPT_PREFILL_MIN_M, 64)
     y_tc = ctx.matmul(dev(torch, x), w).cpu().numpy()
     n_tc = ctx.launch_count()
-    assert n_stream == 8 and n_tc in (2, 3)     # eight slabs of 8 rows vs. cast + tensor-core launch (+ reduction)
+    # eight slabs of 8 rows (each: quantise the activations once, then the matmul) vs. cast + tensor-core launch (+ reduction)
+    assert n_stream == 16 and n_tc in (2, 3)
     check(y_stream, want)
     check(y_tc, want)
 
@@ -396,3 +397,16 @@ def test_llama70b_shard_shapes(ctx, M, N, K):
     x = synth.make_activations(M, K, 81)
     y = run_matmul(ctx, x, raw, None, N, K)
     check(y, orc.matmul(x, raw, None, N, K, threads=8))
+
+
+@pytest.mark.parametrize("M", [2, 3, 4, 5, 7, 8])
+@pytest.mark.parametrize("N,K", [(600, 14336), (300, 28672), (1000, 8192), (33, 14336), (2500, 8192)])
+def test_several_rows_with_long_k_walk_k_in_phases(ctx, M, N, K):
+    """Rows whose digits do not fit in shared memory together: the kernel copies them in K range by K
+    range (tile counts that are odd, below a group, and spread unevenly over the warps of a CTA)."""
+    raw = synth.make_q4k_weights(N, K, 90 + M)
+    x = synth.make_activations(M, K, 91)
+    bias = np.linspace(-3, 3, N).astype(np.float32)
+    y = run_matmul(ctx, x, raw, bias, N, K)
+    check(y, orc.matmul(x, raw, bias, N, K, threads=8))
+    assert ctx.device_status() == 0
