@@ -846,8 +846,10 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         }
         if (!fits) xg = true;
     }
-    // eight rows that fit in shared memory: quantise them once per call (scratch), copy them in per CTA
-    const bool xc = !xg && !m1 && NT > 1 && !indirect && scratch && scratch_bytes >= gemv_stream_scratch_bytes(M, m.K);
+    // several rows that fit in shared memory, 32K values or more: quantise them once per call (scratch) and
+    // copy them in per CTA (measured: faster from there on; below, the extra launch costs more than it saves)
+    const bool xc = !xg && !m1 && !indirect && (uint64_t)tokens * m.K >= 32768u && scratch &&
+                    scratch_bytes >= gemv_stream_scratch_bytes(M, m.K);
     const uint32_t rem = bpw % cb;
     stage_bytes = 16 * cb * block_bytes;
     if (xg) {
@@ -939,6 +941,9 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
 #endif
         if (m1) e = xg ? BPQ4K_LAUNCH(1, true, true) : BPQ4K_LAUNCH(1, true, false);
         else if (NT == 1) e = xg ? BPQ4K_LAUNCH(1, false, true) : BPQ4K_LAUNCH(1, false, false);
+        else if (xc && NT == 1)
+            e = q5 ? launch_one<1, false, false, 0, true, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream)
+                   : launch_one<1, false, false, 0, false, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream);
         else if (xc)
             e = q5 ? launch_one<2, false, false, 0, true, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream)
                    : launch_one<2, false, false, 0, false, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream);
