@@ -90,6 +90,17 @@ cudaError_t launch_peer_barrier(uint32_t* const* flag_ptrs_host, uint32_t n_peer
 // `scratch`: 16 zeroed, 8-byte aligned device bytes that the kernel leaves zeroed.
 cudaError_t launch_argmax(const float* logits, uint32_t n, int32_t* result, void* scratch, int sm_count, cudaStream_t stream);
 
+// Up to kMax segment copies in one launch; every pointer must be addressable by the GPU and 16-byte
+// aligned, every size a multiple of 4 bytes.
+struct CopySegments {
+    static constexpr uint32_t kMax = 32;
+    const void* src[kMax];
+    void* dst[kMax];
+    uint32_t bytes[kMax];
+    uint32_t count;
+};
+cudaError_t launch_copy_segments(const CopySegments& segs, cudaStream_t stream);
+
 // One warp per output row, float FMAs in the reference shader's arithmetic.
 cudaError_t launch_gemv_fp32(const MatmulArgs& a, cudaStream_t stream, int* launches);
 

@@ -15,9 +15,12 @@ launch streams its weights from HBM.
               once) with everything resident in HBM, the step replayed from a
               CUDA graph, timed with CUDA events; max over ranks.
 ``e2e``       the same metric through the host-buffer C-ABI call
-              (bpq4k_matmul_host_batch_f32, one call per step): every step copies
-              the activations from pinned host memory, runs the kernels on the
-              resident weights, reads the outputs back and waits.
+              (bpq4k_matmul_host_batch_f32, one call per step): every step moves
+              the activations from pinned host memory to the device (one gather
+              kernel), runs the kernels on the resident weights, writes the
+              outputs to pinned host memory (one scatter kernel) and waits; the
+              library replays that list from a CUDA graph once it has seen it
+              twice.
 ``roofline``  the dominant kernel (the streaming matmul kernel) against the
               measured HBM copy bandwidth.
 ``cpu_baseline`` the reference's own CPU code for the path (dequant_kquant +

@@ -317,6 +317,41 @@ def test_matmul_host_batch(ctx):
                 check(y, want)
 
 
+def test_matmul_host_batch_pinned_buffers_replay(ctx):
+    """Pinned host buffers: inputs and outputs move with one kernel each, and from the third call on the
+    same dispatch list is replayed from a CUDA graph.  New input values in the same buffers give new
+    results; a different list falls back to recording again."""
+    import torch
+
+    shapes = [(1, 300, 1024), (1, 1024, 4096), (3, 64, 512), (1, 2000, 2048)]
+    items, raws = [], []
+    for i, (M, N, K) in enumerate(shapes):
+        raw = synth.make_q4k_weights(N, K, 140 + i)
+        x = torch.zeros((M, K), dtype=torch.float32).pin_memory()
+        y = torch.full((M, N), float("nan"), dtype=torch.float32).pin_memory()
+        items.append((x.numpy(), ctx.upload(pack_q4k(raw, N, K)), y.numpy(), None))
+        raws.append((raw, x, y))
+    batch = ctx.make_host_batch(items)
+    for rep in range(5):
+        for i, (M, N, K) in enumerate(shapes):
+            items[i][0][...] = synth.make_activations(M, K, 150 + 10 * rep + i)
+            items[i][2][...] = np.nan
+        ctx.launch_count(reset=True)
+        ctx.matmul_host_batch(batch)
+        assert ctx.launch_count() == len(shapes) + 2          # gather, the matmuls, scatter -- also when replayed
+        for (xh, w, yh, _), (raw, _, _), (M, N, K) in zip(items, raws, shapes):
+            check(yh, orc.matmul(xh, raw, None, N, K))
+    # another list (the first two items only) after the graph exists
+    batch2 = ctx.make_host_batch(items[:2])
+    for rep in range(3):
+        for i in range(2):
+            items[i][0][...] = synth.make_activations(shapes[i][0], shapes[i][2], 300 + rep + i)
+        ctx.matmul_host_batch(batch2)
+        for (xh, w, yh, _), (raw, _, _), (M, N, K) in zip(items[:2], raws[:2], shapes[:2]):
+            check(yh, orc.matmul(xh, raw, None, N, K))
+    assert ctx.device_status() == 0
+
+
 # ---------------------------------------------------------------- error behaviour
 
 def test_errors_are_statuses_not_faults(ctx):
