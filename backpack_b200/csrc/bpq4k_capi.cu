@@ -528,6 +528,15 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
         }
         if (e == cudaErrorInvalidValue) launches = 0;  // not even one row fits: the plain kernel below
     }
+    // Q5_K, many rows: the tensor-core kernel, as for Q4_K
+    if (qtype == BPQ4K_TYPE_Q5_K && h->gemv_variant == BPQ4K_GEMV_AUTO && aligned16(X) && M >= (uint32_t)h->prefill_min_m) {
+        const size_t need = prefill_scratch_bytes(M, N, K, h->prefill_mode, h->sm_count);
+        if (need > h->scratch_bytes) {
+            if (int s = ensure_bytes(h, &h->scratch, &h->scratch_bytes, need)) return s;
+        }
+        e = launch_prefill_tc(a, h->prefill_mode, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count,
+                              static_cast<cudaStream_t>(stream), &launches, 13);
+    } else
     // Q5_K: the streaming kernel in slabs of 8 rows (each slab re-reads the weights)
     if (qtype == BPQ4K_TYPE_Q5_K && h->gemv_variant != BPQ4K_GEMV_FP32 && aligned16(X)) {
         const size_t need = gemv_stream_scratch_bytes(M < kStreamMaxM ? M : kStreamMaxM, K);

@@ -204,8 +204,13 @@ struct Plan {
     static constexpr uint32_t SMEM_BYTES = 1024 /*align slack*/ + STAGES * STAGE_BYTES + 256 /*barriers*/;
 };
 
-template <int ROWS, int PASSES, bool BF16>
+// Q5: Q5_K weights (176-byte blocks: the Q4_K header, 32 bytes of fifth bits, 128 nibble bytes); the
+// fifth bit is merged into the code before the float dequantisation (the packed 16-bit shortcut of the
+// single-pass modes is Q4_K only).
+template <int ROWS, int PASSES, bool BF16, bool Q5 = false>
 __global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_kernel(const __grid_constant__ PrefillArgs a) {
+    constexpr int BU = Q5 ? 11 : 9;   // 16-byte units per super-block
+    constexpr int CU = Q5 ? 3 : 1;    // first unit of the nibble bytes
     using P = Plan<ROWS, PASSES>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -304,21 +309,23 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_ker
         const bool row_ok = n < a.N;
         const uint4* wrow = reinterpret_cast<const uint4*>(a.W + (uint64_t)(row_ok ? n : 0) * a.w_row_bytes);
         const uint32_t nblocks = blk1 - blk0;
-        wrow += (uint64_t)blk0 * 9u;
-        uint4 raw[9], nxt[9];
+        wrow += (uint64_t)blk0 * BU;
+        uint4 raw[BU], nxt[BU];
 #pragma unroll
-        for (int i = 0; i < 9; i++) nxt[i] = (row_ok && nblocks) ? __ldg(wrow + i) : make_uint4(0, 0, 0, 0);
+        for (int i = 0; i < BU; i++) nxt[i] = (row_ok && nblocks) ? __ldg(wrow + i) : make_uint4(0, 0, 0, 0);
         bool ok = true;
         // swizzled address of 16-byte chunk c of row r: 8-row group base + row*128 + ((c ^ (r&7)) * 16)
         const uint32_t row_off = (r >> 3) * 1024u + (r & 7u) * 128u;
         const uint32_t sw = r & 7u;
         for (uint32_t b = 0; b < nblocks && ok; b++) {
 #pragma unroll
-            for (int i = 0; i < 9; i++) raw[i] = nxt[i];
+            for (int i = 0; i < BU; i++) raw[i] = nxt[i];
             if (b + 1 < nblocks && row_ok) {
 #pragma unroll
-                for (int i = 0; i < 9; i++) nxt[i] = __ldg(wrow + (uint64_t)(b + 1) * 9u + i);
+                for (int i = 0; i < BU; i++) nxt[i] = __ldg(wrow + (uint64_t)(b + 1) * BU + i);
             }
+            // Q5_K: the eight words of fifth bits (word w: weights 4w..4w+3 of every sub-block)
+            [[maybe_unused]] const uint32_t qhw[8] = {raw[1].x, raw[1].y, raw[1].z, raw[1].w, raw[2].x, raw[2].y, raw[2].z, raw[2].w};
             const BlockHeader h{raw[0].x, raw[0].y, raw[0].z, raw[0].w};
             const float d = half_bits_to_float(h.w0), dmin = half_bits_to_float(h.w0 >> 16);
             uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
@@ -334,13 +341,13 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_ker
                 // w = (d*sc)*q - dmin*mn in float, rounded to 16 bits afterwards
                 const float dsc_e = d * (float)byte_of(sc_lo, sc_hi, 2 * g), dmn_e = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g);
                 const float dsc_o = d * (float)byte_of(sc_lo, sc_hi, 2 * g + 1), dmn_o = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g + 1);
-                const uint4 c0 = raw[1 + 2 * g], c1 = raw[2 + 2 * g];  // the group's 32 code bytes
+                const uint4 c0 = raw[CU + 2 * g], c1 = raw[CU + 1 + 2 * g];  // the group's 32 code bytes
                 const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
                 const uint32_t ta = a_tile(s, 0) + row_off;
 #pragma unroll
                 for (uint32_t c = 0; c < 4; c++) {  // chunk c: weights 8c..8c+7 of the even sub-block, chunk c+4: of the odd one
                     uint32_t lo_bits[4], hi_bits[4], lo_l[4], hi_l[4];
-                    if constexpr (PASSES == 1) {
+                    if constexpr (PASSES == 1 && !Q5) {
                         const uint32_t dsc_e2 = pack2<BF16>(dsc_e, dsc_e), ndmn_e2 = pack2<BF16>(-dmn_e, -dmn_e);
                         const uint32_t dsc_o2 = pack2<BF16>(dsc_o, dsc_o), ndmn_o2 = pack2<BF16>(-dmn_o, -dmn_o);
 #pragma unroll
@@ -362,8 +369,14 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_ker
                             // 0x4B000000 | q is the float 2^23 + q: one subtraction gives q without the
                             // (slow) integer-to-float unit; w = dsc*q - dmn as one fma (the rounding to
                             // 16 bits that follows is 2^13 times coarser than the fma/mul+sub difference)
-                            const float qe = __uint_as_float(((w >> (8 * q)) & 15u) | 0x4B000000u) - 8388608.f;
-                            const float qo = __uint_as_float(((w >> (8 * q + 4)) & 15u) | 0x4B000000u) - 8388608.f;
+                            uint32_t ce = (w >> (8 * q)) & 15u, co = (w >> (8 * q + 4)) & 15u;
+                            if constexpr (Q5) {
+                                const uint32_t hq = qhw[2 * c + j] >> (8 * q + 2 * g);  // bits 2g, 2g+1 of the weight's byte
+                                ce |= (hq & 1u) << 4;
+                                co |= (hq & 2u) << 3;
+                            }
+                            const float qe = __uint_as_float(ce | 0x4B000000u) - 8388608.f;
+                            const float qo = __uint_as_float(co | 0x4B000000u) - 8388608.f;
                             e[q] = fmaf(dsc_e, qe, -dmn_e);
                             o[q] = fmaf(dsc_o, qo, -dmn_o);
                         }
@@ -485,18 +498,18 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int ROWS, int PASSES, bool BF16>
+template <int ROWS, int PASSES, bool BF16, bool Q5 = false>
 cudaError_t launch_tc(const PrefillArgs& pa, cudaStream_t stream) {
     using P = Plan<ROWS, PASSES>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<ROWS, PASSES, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<ROWS, PASSES, BF16, Q5>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)P::SMEM_BYTES);
         if (e != cudaSuccess) return e;
         configured = true;
     }
     const dim3 grid((pa.N + ROWS - 1) / ROWS, (pa.M + kTokTile - 1) / kTokTile, pa.ksplit);
-    prefill_tc_kernel<ROWS, PASSES, BF16><<<grid, P::THREADS, P::SMEM_BYTES, stream>>>(pa);
+    prefill_tc_kernel<ROWS, PASSES, BF16, Q5><<<grid, P::THREADS, P::SMEM_BYTES, stream>>>(pa);
     return cudaGetLastError();
 }
 
@@ -527,8 +540,10 @@ size_t prefill_scratch_bytes(uint32_t M, uint32_t N, uint32_t K, int mode, int s
 
 // mode: 0 = three-pass half split, 1 = one pass half, 2 = one pass bfloat16 (the values of bpq4k_prefill_mode)
 cudaError_t launch_prefill_tc(const MatmulArgs& m, int mode, void* scratch, size_t scratch_bytes, int* status_dev,
-                              int sm_count, cudaStream_t stream, int* launches) {
+                              int sm_count, cudaStream_t stream, int* launches, int qtype) {
     if (m.M == 0 || m.N == 0) return cudaSuccess;
+    if (qtype != 12 && qtype != 13) return cudaErrorInvalidValue;
+    const bool q5 = qtype == 13;
     if (m.n_slots) return cudaErrorInvalidValue;
     if (!scratch || scratch_bytes < prefill_scratch_bytes(m.M, m.N, m.K, mode, sm_count)) return cudaErrorInvalidValue;
     EncodeTiledFn enc = encode_fn();
@@ -570,9 +585,9 @@ cudaError_t launch_prefill_tc(const MatmulArgs& m, int mode, void* scratch, size
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
     if (mode != 0) pa.tmap_x[1] = pa.tmap_x[0];
-    if (mode == 0) e = launch_tc<128, 3, false>(pa, stream);
-    else if (mode == 1) e = launch_tc<256, 1, false>(pa, stream);
-    else e = launch_tc<256, 1, true>(pa, stream);
+    if (mode == 0) e = q5 ? launch_tc<128, 3, false, true>(pa, stream) : launch_tc<128, 3, false>(pa, stream);
+    else if (mode == 1) e = q5 ? launch_tc<256, 1, false, true>(pa, stream) : launch_tc<256, 1, false>(pa, stream);
+    else e = q5 ? launch_tc<256, 1, true, true>(pa, stream) : launch_tc<256, 1, true>(pa, stream);
     if (launches) ++*launches;
     if (e != cudaSuccess) return e;
     if (pa.ksplit > 1) {
