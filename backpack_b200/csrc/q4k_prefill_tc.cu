@@ -501,12 +501,14 @@ EncodeTiledFn encode_fn() {
 template <int ROWS, int PASSES, bool BF16, bool Q5 = false>
 cudaError_t launch_tc(const PrefillArgs& pa, cudaStream_t stream) {
     using P = Plan<ROWS, PASSES>;
-    static bool configured = false;
-    if (!configured) {
+    static int configured_dev = -1;  // the attribute is per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
         cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<ROWS, PASSES, BF16, Q5>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)P::SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured_dev = dev;
     }
     const dim3 grid((pa.N + ROWS - 1) / ROWS, (pa.M + kTokTile - 1) / kTokTile, pa.ksplit);
     prefill_tc_kernel<ROWS, PASSES, BF16, Q5><<<grid, P::THREADS, P::SMEM_BYTES, stream>>>(pa);
