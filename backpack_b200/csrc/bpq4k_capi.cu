@@ -716,6 +716,59 @@ int bpq4k_matmul_allgather_f32(bpq4k_handle_t h, const float* X, const void* W, 
     return BPQ4K_OK;
 }
 
+int bpq4k_kq_matmul_allgather_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W, const float* bias,
+                                  float* const* slot_ptrs, uint32_t nPeers, uint32_t M, uint32_t N, uint32_t K,
+                                  uint32_t rowStrideWords, void* stream) {
+    if (qtype == BPQ4K_TYPE_Q4_K) return bpq4k_matmul_allgather_f32(h, X, W, bias, slot_ptrs, nPeers, M, N, K, rowStrideWords, stream);
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return BPQ4K_OK;
+    if (qtype != BPQ4K_TYPE_Q5_K && qtype != BPQ4K_TYPE_Q6_K_PADDED)
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "the fused gather covers Q4_K, Q5_K and padded Q6_K, not type %d", qtype);
+    if (int s = check_kq_weights(h, qtype, W, K, rowStrideWords)) return s;
+    if (!X || !slot_ptrs) return fail(h, BPQ4K_ERR_INVALID_ARG, "X or slot_ptrs is null");
+    if (nPeers == 0 || nPeers > 8) return fail(h, BPQ4K_ERR_UNSUPPORTED, "nPeers=%u: 1..8 GPUs are supported", nPeers);
+    const uint32_t max_m = qtype == BPQ4K_TYPE_Q6_K_PADDED ? 1u : kStreamMaxM;
+    if (M > max_m) return fail(h, BPQ4K_ERR_UNSUPPORTED, "the fused gather covers M <= %u for this type (M=%u)", max_m, M);
+    if (!aligned16(X)) return fail(h, BPQ4K_ERR_MISALIGNED, "X is not 16-byte aligned");
+    for (uint32_t p = 0; p < nPeers; p++)
+        if (!slot_ptrs[p] || (reinterpret_cast<uintptr_t>(slot_ptrs[p]) & 3u))
+            return fail(h, BPQ4K_ERR_INVALID_ARG, "slot_ptrs[%u] is null or misaligned", p);
+    DeviceGuard g(h->device);
+    MatmulArgs a{};
+    a.X = X;
+    a.W = static_cast<const uint8_t*>(W);
+    a.bias = bias;
+    a.Y = slot_ptrs[0];
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
+    a.n_peers = nPeers - 1;
+    for (uint32_t p = 1; p < nPeers; p++) a.peer_Y[p - 1] = slot_ptrs[p];
+    int launches = 0;
+    cudaError_t e;
+    if (qtype == BPQ4K_TYPE_Q5_K) {
+        const size_t need = gemv_stream_scratch_bytes(M, K);
+        if (need > h->scratch_bytes) {
+            if (int s = ensure_bytes(h, &h->scratch, &h->scratch_bytes, need)) return s;
+        }
+        e = launch_gemv_stream(a, h->tune, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count, &h->tmaps,
+                               static_cast<cudaStream_t>(stream), &launches, 13);
+    } else {
+        e = launch_q6k_stream(a, h->tune, h->dev_status, h->sm_count, &h->tmaps, static_cast<cudaStream_t>(stream), &launches);
+    }
+    h->launches += (uint64_t)launches;
+    if (e == cudaErrorInvalidValue) {
+        cudaGetLastError();
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "K=%u is too long for the fused single-row kernel", K);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return cuda_fail(h, e, "matmul launch");
+    }
+    return BPQ4K_OK;
+}
+
 int bpq4k_peer_barrier(bpq4k_handle_t h, uint32_t* const* flag_ptrs, uint32_t nPeers, uint32_t rank, uint32_t epoch,
                        uint32_t timeout_ms, void* stream) {
     if (!h) return BPQ4K_ERR_INVALID_ARG;

@@ -302,9 +302,14 @@ class Q4KContext:
         slot_ptrs: ctypes array of device addresses, own slot first (see bpq4k_matmul_allgather_f32)."""
         K = x.shape[-1]
         M = x.numel() // K
-        self._check(self.lib.bpq4k_matmul_allgather_f32(
-            self.h, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
-            slot_ptrs, len(slot_ptrs), M, w.N, K, w.rowStrideWords, self._stream()))
+        if w.qtype == Q4_K:
+            self._check(self.lib.bpq4k_matmul_allgather_f32(
+                self.h, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
+                slot_ptrs, len(slot_ptrs), M, w.N, K, w.rowStrideWords, self._stream()))
+        else:
+            self._check(self.lib.bpq4k_kq_matmul_allgather_f32(
+                self.h, w.qtype, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
+                slot_ptrs, len(slot_ptrs), M, w.N, K, w.rowStrideWords, self._stream()))
 
     def peer_barrier(self, flag_ptrs, rank: int, epoch: int, timeout_ms: int = 1000) -> None:
         """Bounded cross-GPU barrier on this stream (bpq4k_peer_barrier)."""

@@ -36,9 +36,10 @@ def shard_range(N: int, world: int, rank: int) -> tuple[int, int]:
     return min(rank * ns, N), min((rank + 1) * ns, N)
 
 
-def shard_raw(raw: np.ndarray, N: int, K: int, world: int, rank: int) -> np.ndarray:
-    """This rank's rows of a raw [N, K/256*144] weight, zero-padded to shard_rows(N, world) rows."""
-    rb = (K // QK_K) * BLOCK_BYTES
+def shard_raw(raw: np.ndarray, N: int, K: int, world: int, rank: int, block_bytes: int = BLOCK_BYTES) -> np.ndarray:
+    """This rank's rows of a raw [N, K/256*block_bytes] weight (144-byte Q4_K blocks unless told otherwise),
+    zero-padded to shard_rows(N, world) rows."""
+    rb = (K // QK_K) * block_bytes
     raw = np.ascontiguousarray(raw).view(np.uint8).reshape(N, rb)
     n0, n1 = shard_range(N, world, rank)
     ns = shard_rows(N, world)

@@ -275,6 +275,11 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
                         float* Y, uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords,
                         uint32_t yOffset, void* stream);
 
+/* bpq4k_matmul_allgather_f32 for the sibling types: Q5_K (M <= 8) and padded Q6_K (M = 1). */
+int bpq4k_kq_matmul_allgather_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W, const float* bias,
+                                  float* const* slot_ptrs, uint32_t nPeers, uint32_t M, uint32_t N, uint32_t K,
+                                  uint32_t rowStrideWords, void* stream);
+
 /* ---- decode matmul with a fused prologue / epilogue -------------------------
  * The single-row (M = 1) matmul with the element-wise step that precedes it computed
  * while the activation row is staged, and an optional residual added to the output:
