@@ -82,6 +82,7 @@ SIGNATURES["bpq4k_gguf_upload_tensor"] = (C.c_int, [vp, vp, u64, C.c_int, C.POIN
                                                     C.POINTER(u32), C.POINTER(u32)])
 SIGNATURES["bpq4k_argmax_f32"] = (C.c_int, [vp, vp, u32, vp, vp])
 SIGNATURES["bpq4k_kq_matmul_allgather_f32"] = (C.c_int, [vp, C.c_int, vp, vp, vp, C.POINTER(vp), u32, u32, u32, u32, u32, vp])
+SIGNATURES["bpq4k_kq_matmul_moe_f32"] = (C.c_int, [vp, C.c_int, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, vp])
 
 _lib = None
 

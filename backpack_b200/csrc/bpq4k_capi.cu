@@ -646,6 +646,47 @@ int bpq4k_matmul_moe_f32(bpq4k_handle_t h, const float* X, const void* W, const 
     return run_matmul(h, a, static_cast<cudaStream_t>(stream));
 }
 
+int bpq4k_kq_matmul_moe_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W, const float* bias, float* Y,
+                            const uint32_t* offsets, const uint32_t* x_rows, uint32_t nSlots, uint32_t N, uint32_t K,
+                            uint32_t rowStrideWords, uint32_t wRows, void* stream) {
+    if (qtype == BPQ4K_TYPE_Q4_K) return bpq4k_matmul_moe_f32(h, X, W, bias, Y, offsets, x_rows, nSlots, N, K, rowStrideWords, wRows, stream);
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (nSlots == 0 || N == 0) return BPQ4K_OK;
+    if (qtype != BPQ4K_TYPE_Q5_K) return fail(h, BPQ4K_ERR_UNSUPPORTED, "the expert-indexed form covers Q4_K and Q5_K, not type %d", qtype);
+    if (int s = check_kq_weights(h, qtype, W, K, rowStrideWords)) return s;
+    if (!X || !Y || !offsets) return fail(h, BPQ4K_ERR_INVALID_ARG, "X, Y or offsets is null");
+    if (wRows < N) return fail(h, BPQ4K_ERR_INVALID_ARG, "wRows=%u is smaller than N=%u", wRows, N);
+    if (!aligned16(X)) return fail(h, BPQ4K_ERR_MISALIGNED, "X is not 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(Y) & 3u) return fail(h, BPQ4K_ERR_MISALIGNED, "Y is not 4-byte aligned");
+    DeviceGuard g(h->device);
+    MatmulArgs a{};
+    a.X = X;
+    a.W = static_cast<const uint8_t*>(W);
+    a.bias = bias;
+    a.Y = Y;
+    a.M = 1;
+    a.N = N;
+    a.K = K;
+    a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
+    a.offsets = offsets;
+    a.x_rows = x_rows;
+    a.n_slots = nSlots;
+    a.w_total_rows = wRows;
+    int launches = 0;
+    const cudaError_t e = launch_gemv_stream(a, h->tune, nullptr, 0, h->dev_status, h->sm_count, &h->tmaps,
+                                             static_cast<cudaStream_t>(stream), &launches, 13);
+    h->launches += (uint64_t)launches;
+    if (e == cudaErrorInvalidValue) {
+        cudaGetLastError();
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "K=%u is too long for the expert-indexed kernel", K);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return cuda_fail(h, e, "matmul launch");
+    }
+    return BPQ4K_OK;
+}
+
 int bpq4k_matmul_host_f32(bpq4k_handle_t h, const float* X_host, const void* W_dev, const float* bias_dev,
                           float* Y_host, uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords,
                           void* stream) {

@@ -266,8 +266,8 @@ class Q4KContext:
         N = n_rows_per_expert
         if out is None:
             out = torch.empty((S, N), dtype=torch.float32, device=x.device)
-        self._check(self.lib.bpq4k_matmul_moe_f32(
-            self.h, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
+        self._check(self.lib.bpq4k_kq_matmul_moe_f32(
+            self.h, w.qtype, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
             out.data_ptr(), offsets.data_ptr(), x_rows.data_ptr() if x_rows is not None else None,
             S, N, w.K, w.rowStrideWords, w.N, self._stream()))
         return out

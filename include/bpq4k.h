@@ -275,6 +275,11 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
                         float* Y, uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords,
                         uint32_t yOffset, void* stream);
 
+/* bpq4k_matmul_moe_f32 with the weight type given: Q4_K or Q5_K expert stacks. */
+int bpq4k_kq_matmul_moe_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W, const float* bias, float* Y,
+                            const uint32_t* offsets, const uint32_t* x_rows, uint32_t nSlots, uint32_t N, uint32_t K,
+                            uint32_t rowStrideWords, uint32_t wRows, void* stream);
+
 /* bpq4k_matmul_allgather_f32 for the sibling types: Q5_K (M <= 8) and padded Q6_K (M = 1). */
 int bpq4k_kq_matmul_allgather_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W, const float* bias,
                                   float* const* slot_ptrs, uint32_t nPeers, uint32_t M, uint32_t N, uint32_t K,

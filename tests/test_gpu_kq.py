@@ -221,3 +221,26 @@ def test_q5k_many_rows_run_the_tensor_core_kernel(ctx, M, N, K, mode, tol):
     else:
         assert rel_l2(y, want) <= tol
     assert ctx.device_status() == 0
+
+
+def test_q5k_expert_indexed_form(ctx):
+    """The indirect (expert-stacked) form on Q5_K weights: every slot multiplies its own activation row with
+    the rows of its expert, one launch for all slots."""
+    import torch
+
+    E, N, K, S = 6, 48, 1024, 9
+    raw = synth.make_kq_weights(orc.Q5_K, E * N, K, 61)
+    x = synth.make_activations(4, K, 62)
+    rng = np.random.default_rng(63)
+    experts = rng.integers(0, E, S).astype(np.uint32)
+    x_rows = rng.integers(0, 4, S).astype(np.uint32)
+    bias = np.linspace(-1, 1, N).astype(np.float32)
+    w = ctx.upload(pack_kq(orc.Q5_K, raw, E * N, K))
+    ctx.launch_count(reset=True)
+    y = ctx.matmul_moe(dev(torch, x), w, N, dev(torch, (experts * N).astype(np.int32)), x_rows=dev(torch, x_rows.astype(np.int32)),
+                       bias=dev(torch, bias)).cpu().numpy()
+    assert ctx.launch_count() == 1
+    rawr = raw.reshape(E, N, -1)
+    for s in range(S):
+        want = orc.kq_matmul(orc.Q5_K, x[x_rows[s]:x_rows[s] + 1], rawr[experts[s]], bias, N, K)[0]
+        check(y[s], want)
