@@ -507,9 +507,12 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
     a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
     int launches = 0;
     cudaError_t e = cudaErrorInvalidValue;
+    // many rows of Q5_K or padded Q6_K: the tensor-core kernel, as for Q4_K
+    const bool tensor_cores = (qtype == BPQ4K_TYPE_Q5_K || qtype == BPQ4K_TYPE_Q6_K_PADDED) && h->gemv_variant == BPQ4K_GEMV_AUTO &&
+                              aligned16(X) && M >= (uint32_t)h->prefill_min_m;
     // padded Q6_K: the streaming kernel in slabs of up to 8 rows; a slab whose rows do not fit in shared
     // memory together (long K) is halved (8 -> 4 -> 2 -> 1 rows), which still beats the plain kernel
-    if (qtype == BPQ4K_TYPE_Q6_K_PADDED && h->gemv_variant != BPQ4K_GEMV_FP32 && aligned16(X) && K % 4u == 0) {
+    if (!tensor_cores && qtype == BPQ4K_TYPE_Q6_K_PADDED && h->gemv_variant != BPQ4K_GEMV_FP32 && aligned16(X) && K % 4u == 0) {
         const cudaStream_t st = static_cast<cudaStream_t>(stream);
         MatmulArgs c = a;
         e = cudaSuccess;
@@ -528,14 +531,13 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
         }
         if (e == cudaErrorInvalidValue) launches = 0;  // not even one row fits: the plain kernel below
     }
-    // Q5_K, many rows: the tensor-core kernel, as for Q4_K
-    if (qtype == BPQ4K_TYPE_Q5_K && h->gemv_variant == BPQ4K_GEMV_AUTO && aligned16(X) && M >= (uint32_t)h->prefill_min_m) {
+    if (tensor_cores) {
         const size_t need = prefill_scratch_bytes(M, N, K, h->prefill_mode, h->sm_count);
         if (need > h->scratch_bytes) {
             if (int s = ensure_bytes(h, &h->scratch, &h->scratch_bytes, need)) return s;
         }
         e = launch_prefill_tc(a, h->prefill_mode, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count,
-                              static_cast<cudaStream_t>(stream), &launches, 13);
+                              static_cast<cudaStream_t>(stream), &launches, qtype);
     } else
     // Q5_K: the streaming kernel in slabs of 8 rows (each slab re-reads the weights)
     if (qtype == BPQ4K_TYPE_Q5_K && h->gemv_variant != BPQ4K_GEMV_FP32 && aligned16(X)) {

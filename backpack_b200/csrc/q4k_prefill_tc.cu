@@ -207,10 +207,13 @@ struct Plan {
 // Q5: Q5_K weights (176-byte blocks: the Q4_K header, 32 bytes of fifth bits, 128 nibble bytes); the
 // fifth bit is merged into the code before the float dequantisation (the packed 16-bit shortcut of the
 // single-pass modes is Q4_K only).
-template <int ROWS, int PASSES, bool BF16, bool Q5 = false>
+// QT = 2: Q6_K weights in the padded layout (224-byte blocks: 128 nibble bytes, 64 bit-pair bytes, 16 signed
+// scales, half d, padding); w = d*sc*(code - 32) with one scale per 16 weights.
+template <int ROWS, int PASSES, bool BF16, int QT = 0>
 __global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_kernel(const __grid_constant__ PrefillArgs a) {
-    constexpr int BU = Q5 ? 11 : 9;   // 16-byte units per super-block
-    constexpr int CU = Q5 ? 3 : 1;    // first unit of the nibble bytes
+    constexpr bool Q5 = QT == 1, Q6 = QT == 2;
+    constexpr int BU = Q6 ? 14 : Q5 ? 11 : 9;   // 16-byte units per super-block
+    constexpr int CU = Q5 ? 3 : 1;              // first unit of the nibble bytes (Q4_K, Q5_K)
     using P = Plan<ROWS, PASSES>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -310,13 +313,122 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_ker
         const uint4* wrow = reinterpret_cast<const uint4*>(a.W + (uint64_t)(row_ok ? n : 0) * a.w_row_bytes);
         const uint32_t nblocks = blk1 - blk0;
         wrow += (uint64_t)blk0 * BU;
-        uint4 raw[BU], nxt[BU];
-#pragma unroll
-        for (int i = 0; i < BU; i++) nxt[i] = (row_ok && nblocks) ? __ldg(wrow + i) : make_uint4(0, 0, 0, 0);
         bool ok = true;
         // swizzled address of 16-byte chunk c of row r: 8-row group base + row*128 + ((c ^ (r&7)) * 16)
         const uint32_t row_off = (r >> 3) * 1024u + (r & 7u) * 128u;
         const uint32_t sw = r & 7u;
+        if constexpr (Q6) {
+            // Per half of 128 weights six units (64 nibble bytes, 32 bit-pair bytes) serve two k-steps of 64:
+            // the low nibbles first, then the high ones.  The next half is fetched while this one is used.
+            const uint4 zero4 = make_uint4(0, 0, 0, 0);
+            uint4 cur[6], nx[6], scu = zero4, dun = zero4, scn = zero4, dnn = zero4;
+            auto load_half = [&](uint32_t b, uint32_t h, uint4 (&dst)[6]) {
+                const uint4* p = wrow + (uint64_t)b * 14u;
+#pragma unroll
+                for (int i = 0; i < 4; i++) dst[i] = __ldg(p + h * 4u + i);
+                dst[4] = __ldg(p + 8u + h * 2u);
+                dst[5] = __ldg(p + 9u + h * 2u);
+            };
+#pragma unroll
+            for (int i = 0; i < 6; i++) nx[i] = zero4;
+            if (row_ok && nblocks) {
+                load_half(0, 0, nx);
+                scn = __ldg(wrow + 12);
+                dnn = __ldg(wrow + 13);
+            }
+            for (uint32_t b = 0; b < nblocks && ok; b++) {
+                scu = scn;
+                dun = dnn;
+                const float d = half_bits_to_float(dun.x);
+#pragma unroll
+                for (uint32_t h = 0; h < 2; h++) {
+#pragma unroll
+                    for (int i = 0; i < 6; i++) cur[i] = nx[i];
+                    if (row_ok) {
+                        if (h == 0) {
+                            load_half(b, 1, nx);
+                        } else if (b + 1 < nblocks) {
+                            load_half(b + 1, 0, nx);
+                            scn = __ldg(wrow + (uint64_t)(b + 1) * 14u + 12);
+                            dnn = __ldg(wrow + (uint64_t)(b + 1) * 14u + 13);
+                        }
+                    }
+                    const uint32_t wa[8] = {cur[0].x, cur[0].y, cur[0].z, cur[0].w, cur[1].x, cur[1].y, cur[1].z, cur[1].w};
+                    const uint32_t wb[8] = {cur[2].x, cur[2].y, cur[2].z, cur[2].w, cur[3].x, cur[3].y, cur[3].z, cur[3].w};
+                    const uint32_t wq[8] = {cur[4].x, cur[4].y, cur[4].z, cur[4].w, cur[5].x, cur[5].y, cur[5].z, cur[5].w};
+#pragma unroll
+                    for (uint32_t gl = 0; gl < 2 && ok; gl++) {
+                        const uint32_t g = 2u * h + gl, kb = b * 4u + g;
+                        const uint32_t s = kb % P::STAGES, it = kb / P::STAGES;
+                        if (it > 0 && !wait_bar(empty_bar(s), (it - 1) & 1u, abort_flag, a.status)) {
+                            ok = false;
+                            break;
+                        }
+                        // the k-step's four scales: first group of 32 (weights < 16, >= 16), second group (same)
+                        const uint32_t scw = h ? (gl ? scu.w : scu.z) : (gl ? scu.y : scu.x);
+                        float ds[4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) ds[i] = d * (float)(int)(int8_t)((scw >> (8 * i)) & 0xFFu);
+                        const uint32_t ta = a_tile(s, 0) + row_off;
+#pragma unroll
+                        for (uint32_t c = 0; c < 4; c++) {
+                            uint32_t lo_bits[4], hi_bits[4], lo_l[4], hi_l[4];
+                            const float dsa = ds[c >> 1], dsb = ds[2 + (c >> 1)];
+#pragma unroll
+                            for (uint32_t j = 0; j < 2; j++) {
+                                const uint32_t va = wa[2 * c + j] >> (4 * gl), vb = wb[2 * c + j] >> (4 * gl), vq = wq[2 * c + j] >> (4 * gl);
+                                float e[4], o[4];
+#pragma unroll
+                                for (uint32_t q = 0; q < 4; q++) {
+                                    const uint32_t ca = ((va >> (8 * q)) & 15u) | (((vq >> (8 * q)) & 3u) << 4);
+                                    const uint32_t cb2 = ((vb >> (8 * q)) & 15u) | (((vq >> (8 * q + 2)) & 3u) << 4);
+                                    const float qa = __uint_as_float(ca | 0x4B000000u) - 8388640.f;   // code - 32
+                                    const float qb = __uint_as_float(cb2 | 0x4B000000u) - 8388640.f;
+                                    e[q] = dsa * qa;
+                                    o[q] = dsb * qb;
+                                }
+                                lo_bits[2 * j] = pack2<BF16>(e[0], e[1]);
+                                lo_bits[2 * j + 1] = pack2<BF16>(e[2], e[3]);
+                                hi_bits[2 * j] = pack2<BF16>(o[0], o[1]);
+                                hi_bits[2 * j + 1] = pack2<BF16>(o[2], o[3]);
+                                if constexpr (PASSES == 3) {
+                                    lo_l[2 * j] = pack2_lo(e[0], e[1], lo_bits[2 * j]);
+                                    lo_l[2 * j + 1] = pack2_lo(e[2], e[3], lo_bits[2 * j + 1]);
+                                    hi_l[2 * j] = pack2_lo(o[0], o[1], hi_bits[2 * j]);
+                                    hi_l[2 * j + 1] = pack2_lo(o[2], o[3], hi_bits[2 * j + 1]);
+                                }
+                            }
+                            if (!row_ok) {
+#pragma unroll
+                                for (int q = 0; q < 4; q++) lo_bits[q] = hi_bits[q] = lo_l[q] = hi_l[q] = 0u;
+                            }
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + ((c ^ sw) << 4)), "r"(lo_bits[0]),
+                                         "r"(lo_bits[1]), "r"(lo_bits[2]), "r"(lo_bits[3])
+                                         : "memory");
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + (((c + 4u) ^ sw) << 4)), "r"(hi_bits[0]),
+                                         "r"(hi_bits[1]), "r"(hi_bits[2]), "r"(hi_bits[3])
+                                         : "memory");
+                            if constexpr (PASSES == 3) {
+                                const uint32_t tl = a_tile(s, 1) + row_off;
+                                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tl + ((c ^ sw) << 4)), "r"(lo_l[0]),
+                                             "r"(lo_l[1]), "r"(lo_l[2]), "r"(lo_l[3])
+                                             : "memory");
+                                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tl + (((c + 4u) ^ sw) << 4)), "r"(hi_l[0]),
+                                             "r"(hi_l[1]), "r"(hi_l[2]), "r"(hi_l[3])
+                                             : "memory");
+                            }
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(full_bar(s));
+                    }
+                    if (!ok) break;
+                }
+            }
+        } else {
+        uint4 raw[BU], nxt[BU];
+#pragma unroll
+        for (int i = 0; i < BU; i++) nxt[i] = (row_ok && nblocks) ? __ldg(wrow + i) : make_uint4(0, 0, 0, 0);
         for (uint32_t b = 0; b < nblocks && ok; b++) {
 #pragma unroll
             for (int i = 0; i < BU; i++) raw[i] = nxt[i];
@@ -418,6 +530,7 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_ker
                 if (lane == 0) mbar_arrive(full_bar(s));
             }
         }
+        }
         // ---------------- epilogue: TMEM -> registers -> Y ----------------
         if (ok && wait_bar(acc_bar, 0, abort_flag, a.status)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -498,20 +611,20 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int ROWS, int PASSES, bool BF16, bool Q5 = false>
+template <int ROWS, int PASSES, bool BF16, int QT = 0>
 cudaError_t launch_tc(const PrefillArgs& pa, cudaStream_t stream) {
     using P = Plan<ROWS, PASSES>;
     static int configured_dev = -1;  // the attribute is per device
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<ROWS, PASSES, BF16, Q5>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<ROWS, PASSES, BF16, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)P::SMEM_BYTES);
         if (e != cudaSuccess) return e;
         configured_dev = dev;
     }
     const dim3 grid((pa.N + ROWS - 1) / ROWS, (pa.M + kTokTile - 1) / kTokTile, pa.ksplit);
-    prefill_tc_kernel<ROWS, PASSES, BF16, Q5><<<grid, P::THREADS, P::SMEM_BYTES, stream>>>(pa);
+    prefill_tc_kernel<ROWS, PASSES, BF16, QT><<<grid, P::THREADS, P::SMEM_BYTES, stream>>>(pa);
     return cudaGetLastError();
 }
 
@@ -544,8 +657,8 @@ size_t prefill_scratch_bytes(uint32_t M, uint32_t N, uint32_t K, int mode, int s
 cudaError_t launch_prefill_tc(const MatmulArgs& m, int mode, void* scratch, size_t scratch_bytes, int* status_dev,
                               int sm_count, cudaStream_t stream, int* launches, int qtype) {
     if (m.M == 0 || m.N == 0) return cudaSuccess;
-    if (qtype != 12 && qtype != 13) return cudaErrorInvalidValue;
-    const bool q5 = qtype == 13;
+    if (qtype != 12 && qtype != 13 && qtype != kQ6PaddedType) return cudaErrorInvalidValue;
+    const bool q5 = qtype == 13, q6 = qtype == kQ6PaddedType;
     if (m.n_slots) return cudaErrorInvalidValue;
     if (!scratch || scratch_bytes < prefill_scratch_bytes(m.M, m.N, m.K, mode, sm_count)) return cudaErrorInvalidValue;
     EncodeTiledFn enc = encode_fn();
@@ -587,9 +700,9 @@ cudaError_t launch_prefill_tc(const MatmulArgs& m, int mode, void* scratch, size
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
     if (mode != 0) pa.tmap_x[1] = pa.tmap_x[0];
-    if (mode == 0) e = q5 ? launch_tc<128, 3, false, true>(pa, stream) : launch_tc<128, 3, false>(pa, stream);
-    else if (mode == 1) e = q5 ? launch_tc<256, 1, false, true>(pa, stream) : launch_tc<256, 1, false>(pa, stream);
-    else e = q5 ? launch_tc<256, 1, true, true>(pa, stream) : launch_tc<256, 1, true>(pa, stream);
+    if (mode == 0) e = q6 ? launch_tc<128, 3, false, 2>(pa, stream) : q5 ? launch_tc<128, 3, false, 1>(pa, stream) : launch_tc<128, 3, false>(pa, stream);
+    else if (mode == 1) e = q6 ? launch_tc<256, 1, false, 2>(pa, stream) : q5 ? launch_tc<256, 1, false, 1>(pa, stream) : launch_tc<256, 1, false>(pa, stream);
+    else e = q6 ? launch_tc<256, 1, true, 2>(pa, stream) : q5 ? launch_tc<256, 1, true, 1>(pa, stream) : launch_tc<256, 1, true>(pa, stream);
     if (launches) ++*launches;
     if (e != cudaSuccess) return e;
     if (pa.ksplit > 1) {

@@ -195,20 +195,21 @@ def test_argmax_matches_reference_rule(ctx, n):
     assert (int(r1.cpu()[0]), int(r2.cpu()[0])) == (argmax_oracle(cases[0]), argmax_oracle(cases[5]))
 
 
+@pytest.mark.parametrize("layout,ftype", [(orc.Q5_K, orc.Q5_K), (Q6_K_PADDED, orc.Q6_K)], ids=["q5k", "q6k_padded"])
 @pytest.mark.parametrize("mode,tol", [(0, 1e-3), (1, 1e-3), (2, 8e-3)], ids=["f16x3", "f16", "bf16"])
 @pytest.mark.parametrize("M,N,K", [(25, 130, 512), (64, 256, 256), (100, 300, 1024), (512, 1024, 4096), (300, 1000, 14336)])
-def test_q5k_many_rows_run_the_tensor_core_kernel(ctx, M, N, K, mode, tol):
-    """Q5_K from M = 25 on: tcgen05 kernel with the fifth bit merged in before dequantisation.  The
-    three-pass mode keeps the float tolerance; the single-pass modes are held to their rounding."""
+def test_siblings_many_rows_run_the_tensor_core_kernel(ctx, M, N, K, mode, tol, layout, ftype):
+    """Q5_K and padded Q6_K from M = 25 on: tcgen05 kernel with the codes assembled before dequantisation.
+    The three-pass mode keeps the float tolerance; the single-pass modes are held to their rounding."""
     import torch
 
     from backpack_b200 import q4k
 
-    raw = synth.make_kq_weights(orc.Q5_K, N, K, 500 + N)
+    raw = synth.make_kq_weights(ftype, N, K, 500 + N)
     x = synth.make_activations(M, K, 501)
     bias = np.linspace(-2, 2, N).astype(np.float32)
-    w = ctx.upload(pack_kq(orc.Q5_K, raw, N, K))
-    want = orc.kq_matmul(orc.Q5_K, x, raw, bias, N, K, threads=8)
+    w = ctx.upload(pack_kq(layout, raw, N, K))
+    want = orc.kq_matmul(ftype, x, raw, bias, N, K, threads=8)
     ctx.set_option(q4k.OPT_PREFILL_MODE, mode)
     try:
         ctx.launch_count(reset=True)
