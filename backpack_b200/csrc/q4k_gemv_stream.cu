@@ -172,8 +172,11 @@ __device__ __forceinline__ void merge_fifth_bit(uint32_t codes, uint32_t qh, uin
 // XC (with XG false): the digits live in shared memory as usual, but they were quantised once per call by
 // quantize_activations_kernel and every CTA only copies them in (bulk copies from the scratch) instead of
 // quantising all rows itself -- with eight rows that is ~1 us instead of ~8 us per CTA.
-template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false, bool XC = false>
+// FP (single row only): the call has a fused prologue and/or a residual; kept out of the plain kernel, whose
+// code it would otherwise slow down by ~1 %.
+template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false, bool XC = false, bool FP = false>
 __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
+    static_assert(!FP || (M1 && !XG && !XC), "the fused forms are single-row and stage the row themselves");
     static_assert(!(XG && XC), "digits are read from the scratch directly (XG) or copied into shared memory (XC)");
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr uint32_t BB = Q5 ? 176u : kBlockBytes, BW = BB / 4u;  // bytes and words per super-block
@@ -287,7 +290,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
             for (uint32_t i = mrows * nb * 16u + tid; i < (uint32_t)TOK * nb * 16u; i += blockDim.x) SI[i] = 0.f;
         }
         const uint32_t items = mrows * per_row;
-        if (M1 && a.m.prologue) {
+        if (FP && a.m.prologue) {
             // Fused prologue on the single activation row (the reference's q4k_matmul_norm.wgsl:47-92
             // and q4k_down_gelu.wgsl:47-62, plus the silu form of silu_mul_fused): transform while staging.
             float rstd = 1.f;
@@ -427,7 +430,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
         const uint32_t tile = tile0 + ti * tstride;
         // single-row calls: fetch this lane's residual value now, it is added when the tile is stored
         float res_pre = 0.f;
-        if (M1 && a.m.residual && wk == 0 && lane < 16u && tile * 16u + lane < N) res_pre = __ldg(a.m.residual + tile * 16u + lane);
+        if (FP && a.m.residual && wk == 0 && lane < 16u && tile * 16u + lane < N) res_pre = __ldg(a.m.residual + tile * 16u + lane);
         float acc[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = 0.f;
@@ -658,7 +661,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                     float s = 0.f;
                     for (uint32_t k2 = 0; k2 < a.wk; k2++) s += gbuf[(uint64_t)k2 * (TOK * 16u) + idx];
                     float yv = s + (a.m.bias ? a.m.bias[row] : 0.f);
-                    if (M1) yv += res_pre;
+                    if (FP) yv += res_pre;
                     Y[(uint64_t)tok * N + row] = yv;
                     // fused all-gather: the same value goes straight into every peer's gather buffer
                     for (uint32_t p = 0; p < a.m.n_peers; p++) a.m.peer_Y[p][(uint64_t)tok * N + row] = yv;
@@ -693,7 +696,7 @@ __global__ void __launch_bounds__(256) quantize_activations_kernel(const float* 
 
 // Launch one instantiation.  The grid is persistent: at most as many CTAs as can be
 // resident at once (occupancy query, cached), never more than there are tile groups.
-template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false, bool XC = false>
+template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false, bool XC = false, bool FP = false>
 cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, uint32_t threads, size_t smem,
                        int sm_count, uint32_t ctas_per_sm_override, bool pdl, cudaStream_t stream) {
     struct Cache { int dev = -1; size_t smem_cfg = 0; uint32_t threads = 0; size_t smem = 0; int occ = 0; };
@@ -703,7 +706,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     if (cache.dev != dev) cache = Cache{};
     cache.dev = dev;
     if (smem > cache.smem_cfg) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC, FP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return e;
         cache.smem_cfg = smem;
@@ -711,7 +714,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     }
     if (cache.threads != threads || cache.smem != smem) {
         int occ = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC>, (int)threads, smem);
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC, FP>, (int)threads, smem);
         if (e != cudaSuccess) return e;
         cache.threads = threads;
         cache.smem = smem;
@@ -742,7 +745,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC>, sa);
+    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC, FP>, sa);
 }
 
 static_assert(sizeof(CUtensorMap) == 128, "TmapCache::Entry::map must hold a CUtensorMap");
@@ -939,7 +942,10 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         } else
 #undef BPQ4K_PROBE
 #endif
-        if (m1) e = xg ? BPQ4K_LAUNCH(1, true, true) : BPQ4K_LAUNCH(1, true, false);
+        if (m1 && fused)
+            e = q5 ? launch_one<1, true, false, 0, true, false, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream)
+                   : launch_one<1, true, false, 0, false, false, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream);
+        else if (m1) e = xg ? BPQ4K_LAUNCH(1, true, true) : BPQ4K_LAUNCH(1, true, false);
         else if (NT == 1) e = xg ? BPQ4K_LAUNCH(1, false, true) : BPQ4K_LAUNCH(1, false, false);
         else if (xc && NT == 1)
             e = q5 ? launch_one<1, false, false, 0, true, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream)
