@@ -380,6 +380,33 @@ int bpq4k_gguf_read_tensor(bpq4k_gguf_t g, uint64_t index, uint64_t first, uint6
     return c.read(dst_host, n) ? BPQ4K_OK : gfail(g, BPQ4K_ERR_INVALID_ARG, "short read");
 }
 
+// File-format Q6_K blocks already on the device (N rows of K/256 blocks of 210 bytes, no padding) ->
+// the layout `layout_qtype` asks for (BPQ4K_TYPE_Q6_K: pack_q6k's word-padded rows; BPQ4K_TYPE_Q6_K_PADDED:
+// 224-byte blocks).  `out_dev` holds N * bpq4k_kq_row_stride_words(layout_qtype, K) words.
+int bpq4k_kq_respace_device(bpq4k_handle_t h, int layout_qtype, const void* raw_dev, uint32_t N, uint32_t K, void* out_dev,
+                            void* stream) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (layout_qtype != BPQ4K_TYPE_Q6_K && layout_qtype != BPQ4K_TYPE_Q6_K_PADDED) return BPQ4K_ERR_UNSUPPORTED;
+    if (K == 0 || K % 256 != 0) return BPQ4K_ERR_UNSUPPORTED;
+    if (N == 0) return BPQ4K_OK;
+    if (!raw_dev || !out_dev || (reinterpret_cast<uintptr_t>(raw_dev) & 1u) || (reinterpret_cast<uintptr_t>(out_dev) & 3u))
+        return BPQ4K_ERR_INVALID_ARG;
+    const uint32_t nb = K / 256;
+    const uint64_t nblocks = (uint64_t)N * nb;
+    uint64_t ctas = (nblocks + 7) / 8;
+    if (ctas > 148ull * 32) ctas = 148ull * 32;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    const int dev = bpq4k_device_index(h);
+    if (dev != prev) cudaSetDevice(dev);
+    q6k_respace_kernel<<<(unsigned)ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(raw_dev), nblocks, nb, static_cast<uint8_t*>(out_dev),
+        (uint64_t)bpq4k_kq_row_stride_words(layout_qtype, K) * 4u, bpq4k_kq_block_bytes(layout_qtype));
+    const cudaError_t e = cudaGetLastError();
+    if (dev != prev && prev >= 0) cudaSetDevice(prev);
+    return e == cudaSuccess ? BPQ4K_OK : BPQ4K_ERR_CUDA;
+}
+
 // Load a Q4_K / Q5_K / Q6_K tensor into device memory in the layout the matmul entry points take.
 // layout_qtype: 0 = the reference's packed layout of the tensor's own type; BPQ4K_TYPE_Q6_K_PADDED for
 // a Q6_K tensor selects the padded layout.  Rows = product of all dims but the first (expert stacks

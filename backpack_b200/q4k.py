@@ -189,6 +189,16 @@ class Q4KContext:
         buf[: host.numel()].copy_(host)
         return Q4KWeight(buf, packed.N, packed.K, packed.rowStrideWords, packed.qtype)
 
+    def respace_q6k(self, raw_dev, N: int, K: int, layout: int = Q6_K_PADDED) -> Q4KWeight:
+        """File-format Q6_K blocks already on the device (uint8, N*K/256*210 bytes) -> a weight in `layout`."""
+        torch = self._torch
+        if raw_dev.dtype != torch.uint8 or not raw_dev.is_contiguous() or raw_dev.numel() < N * (K // 256) * 210:
+            raise ValueError("raw_dev: contiguous uint8 tensor of N*K/256*210 bytes")
+        rs = self.lib.bpq4k_kq_row_stride_words(layout, K)
+        buf = torch.empty(max(N * rs * 4, 16), dtype=torch.uint8, device=raw_dev.device)
+        self._check(self.lib.bpq4k_kq_respace_device(self.h, layout, raw_dev.data_ptr(), N, K, buf.data_ptr(), self._stream()))
+        return Q4KWeight(buf, N, K, rs, layout)
+
     # -- operators -------------------------------------------------------
     def dequant(self, w: Q4KWeight, out=None):
         torch = self._torch

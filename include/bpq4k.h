@@ -255,6 +255,13 @@ uint32_t bpq4k_kq_row_stride_words(int qtype, uint32_t K);
  * blocks for both Q6_K types) into N * rowStrideWords words (host). */
 int bpq4k_kq_pack_host(int qtype, const void* raw_host, uint32_t N, uint32_t K, uint32_t* words_host);
 
+/* Q6_K blocks in the file format that are already on the device (N rows of K/256 blocks of 210
+ * bytes, no padding) into the layout of `layout_qtype` (BPQ4K_TYPE_Q6_K: the word-padded rows of
+ * pack_q6k; BPQ4K_TYPE_Q6_K_PADDED: 224-byte blocks).  out_dev: N * row stride words of that layout.
+ * The device-side twin of bpq4k_kq_pack_host for callers that hold raw tensor bytes on the GPU. */
+int bpq4k_kq_respace_device(bpq4k_handle_t h, int layout_qtype, const void* raw_dev, uint32_t N, uint32_t K,
+                            void* out_dev, void* stream);
+
 /* dequant_kquant(raw, out, N, K, type) (runtime/gguf_loader.cpp:455-573) on the device,
  * bit-identical to the reference's float arithmetic.  W needs 4-byte alignment for Q6_K,
  * 16-byte for the other two. */

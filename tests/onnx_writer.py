@@ -67,16 +67,18 @@ def model(nodes, inputs, outputs, initializers=()) -> bytes:
     return field_varint(1, 8) + field_bytes(7, g) + field_bytes(8, opset)
 
 
-def matmul_q4k_model(N: int, K: int, x_shape, weights: np.ndarray | None, with_bias: bool) -> bytes:
-    """One MatMulQ4K node.  `weights` given: W is an initializer; else W is a runtime input."""
+def matmul_q4k_model(N: int, K: int, x_shape, weights: np.ndarray | None, with_bias: bool, op: str = "MatMulQ4K",
+                     block_bytes: int = 144) -> bytes:
+    """One MatMulQ4K (or MatMulQ5K / MatMulQ6K: `op`, `block_bytes` 176 / 210) node.  `weights` given: W is an
+    initializer; else W is a runtime input."""
     ins = ["X", "W"] + (["Bias"] if with_bias else [])
-    n = node("MatMulQ4K", ins, ["Y"], attrs=[attribute_int("K", K), attribute_int("N", N)], domain="ai.backpack")
+    n = node(op, ins, ["Y"], attrs=[attribute_int("K", K), attribute_int("N", N)], domain="ai.backpack")
     graph_inputs = [value_info("X", "float32", x_shape)]
     inits = []
     if weights is not None:
         inits.append(tensor("W", weights))
     else:
-        graph_inputs.append(value_info("W", "uint8", (N, K // 256 * 144)))
+        graph_inputs.append(value_info("W", "uint8", (N, K // 256 * block_bytes)))
     if with_bias:
         graph_inputs.append(value_info("Bias", "float32", (N,)))
     return model([n], graph_inputs, [value_info("Y", "float32", tuple(x_shape[:-1]) + (N,))], inits)

@@ -245,3 +245,19 @@ def test_q5k_expert_indexed_form(ctx):
     for s in range(S):
         want = orc.kq_matmul(orc.Q5_K, x[x_rows[s]:x_rows[s] + 1], rawr[experts[s]], bias, N, K)[0]
         check(y[s], want)
+
+
+@pytest.mark.parametrize("layout", [orc.Q6_K, Q6_K_PADDED])
+@pytest.mark.parametrize("N,K", [(1, 256), (37, 768), (512, 4096)])
+def test_respace_on_device_equals_host_pack(ctx, layout, N, K):
+    """bpq4k_kq_respace_device writes the same bytes as bpq4k_kq_pack_host, gaps zeroed."""
+    import torch
+    from backpack_b200 import Q4KError
+    raw = synth.make_kq_weights(orc.Q6_K, N, K, 5)
+    want = pack_kq(layout, raw, N, K)
+    w = ctx.respace_q6k(dev(torch, raw.reshape(-1)), N, K, layout)
+    assert w.rowStrideWords == want.rowStrideWords and w.qtype == layout
+    got = w.buf[: want.data.size * 4].cpu().numpy()
+    assert np.array_equal(got, want.data.view(np.uint8))
+    with pytest.raises(Q4KError):    # only Q6_K needs re-spacing
+        ctx._check(ctx.lib.bpq4k_kq_respace_device(ctx.h, orc.Q5_K, w.buf.data_ptr(), N, K, w.buf.data_ptr(), 0))

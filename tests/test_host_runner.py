@@ -19,11 +19,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 RUNNER = os.path.join(ROOT, "backpack_b200", "bin", "bpq4k_op_test_runner")
 
 
-def write_case(tmp, N, K, x, raw, bias, w_as_initializer):
+def write_case(tmp, N, K, x, raw, bias, w_as_initializer, op="MatMulQ4K", block_bytes=144):
     tmp.mkdir(parents=True, exist_ok=True)
     indir, outdir = tmp / "in", tmp / "out"
     indir.mkdir()
-    model = ow.matmul_q4k_model(N, K, x.shape, raw if w_as_initializer else None, bias is not None)
+    model = ow.matmul_q4k_model(N, K, x.shape, raw if w_as_initializer else None, bias is not None, op, block_bytes)
     (tmp / "m.onnx").write_bytes(model)
     inputs = [{"name": "X", "dtype": "float32", "shape": list(x.shape)}]
     x.tofile(indir / "X.bin")
@@ -62,6 +62,18 @@ def test_parse_only_reads_model_and_manifest(tmp_path):
     assert out.strip().endswith("OK")
 
 
+def test_parse_only_knows_the_sibling_ops(tmp_path):
+    for op, qtype in (("MatMulQ5K", orc.Q5_K), ("MatMulQ6K", orc.Q6_K)):
+        N, K = 6, 512
+        raw = synth.make_kq_weights(qtype, N, K, 1).reshape(N, -1)
+        x = synth.make_activations(2, K, 2)
+        model, indir, outdir = write_case(tmp_path / op, N, K, x, raw, None, True, op, synth.KQ_BLOCK_BYTES[qtype])
+        r = subprocess.run([RUNNER, "--parse-only", model, indir, outdir], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+        assert f"op={op} registered=1 inputs=2 outputs=1" in r.stdout
+        assert f"initializer W dtype=uint8 bytes={raw.size}" in r.stdout
+
+
 def test_parse_only_rejects_garbage(tmp_path):
     (tmp_path / "in").mkdir()
     (tmp_path / "in" / "manifest.json").write_text('{"inputs": []}')
@@ -95,6 +107,28 @@ def test_runner_end_to_end(tmp_path, M, N, K, with_bias, w_as_initializer):
     assert man == {"outputs": [{"name": "Y", "dtype": "float32", "shape": [M, N]}]}
     y = np.fromfile(os.path.join(outdir, "Y.bin"), np.float32).reshape(M, N)
     want = orc.matmul(x, raw, bias, N, K, threads=4)
+    assert np.linalg.norm(y - want) / np.linalg.norm(want) <= 1e-3
+    assert np.abs(y - want).max() <= 2e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("op,qtype", [("MatMulQ5K", orc.Q5_K), ("MatMulQ6K", orc.Q6_K)])
+@pytest.mark.parametrize("M,N,K,with_bias,w_as_initializer",
+                         [(1, 40, 1024, False, True), (5, 9, 512, True, False), (3, 1024, 4096, False, True),
+                          (40, 256, 2048, True, True)])
+def test_runner_sibling_ops_end_to_end(tmp_path, op, qtype, M, N, K, with_bias, w_as_initializer):
+    """MatMulQ5K / MatMulQ6K take W in the file format of their type (Q6_K: 210-byte blocks, re-spaced on the device)."""
+    raw = synth.make_kq_weights(qtype, N, K, 17).reshape(N, -1)
+    x = synth.make_activations(M, K, 18)
+    bias = (np.arange(N) * 0.01).astype(np.float32) if with_bias else None
+    model, indir, outdir = write_case(tmp_path / "c", N, K, x, raw, bias, w_as_initializer, op, synth.KQ_BLOCK_BYTES[qtype])
+    r = subprocess.run([RUNNER, model, indir, outdir], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.strip() == "OK"
+    man = json.loads(open(os.path.join(outdir, "manifest.json")).read())
+    assert man == {"outputs": [{"name": "Y", "dtype": "float32", "shape": [M, N]}]}
+    y = np.fromfile(os.path.join(outdir, "Y.bin"), np.float32).reshape(M, N)
+    want = orc.kq_matmul(qtype, x, raw.reshape(-1), bias, N, K, threads=4)
     assert np.linalg.norm(y - want) / np.linalg.norm(want) <= 1e-3
     assert np.abs(y - want).max() <= 2e-2
 
