@@ -83,6 +83,8 @@ SIGNATURES["bpq4k_gguf_upload_tensor"] = (C.c_int, [vp, vp, u64, C.c_int, C.POIN
 SIGNATURES["bpq4k_argmax_f32"] = (C.c_int, [vp, vp, u32, vp, vp])
 SIGNATURES["bpq4k_kq_matmul_allgather_f32"] = (C.c_int, [vp, C.c_int, vp, vp, vp, C.POINTER(vp), u32, u32, u32, u32, u32, vp])
 SIGNATURES["bpq4k_kq_matmul_moe_f32"] = (C.c_int, [vp, C.c_int, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, vp])
+SIGNATURES["bpq4k_moe_ffn_work_floats"] = (C.c_uint64, [u32, u32, u32, u32])
+SIGNATURES["bpq4k_moe_ffn_f32"] = (C.c_int, [vp, C.c_int, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, vp, C.c_uint64, vp])
 SIGNATURES["bpq4k_kq_respace_device"] = (C.c_int, [vp, C.c_int, vp, u32, u32, vp, vp])
 
 _lib = None

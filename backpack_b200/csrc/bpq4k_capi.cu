@@ -689,6 +689,80 @@ int bpq4k_kq_matmul_moe_f32(bpq4k_handle_t h, int qtype, const float* X, const v
     return BPQ4K_OK;
 }
 
+uint64_t bpq4k_moe_ffn_work_floats(uint32_t T, uint32_t topk, uint32_t H, uint32_t F) {
+    return (uint64_t)T * topk * (2ull * F + H);
+}
+
+int bpq4k_moe_ffn_f32(bpq4k_handle_t h, int qtype, const float* X, const void* Wgate, const void* Wup, const void* Wdown,
+                      const uint32_t* expert_ids, const float* route_w, float* Y, uint32_t T, uint32_t topk,
+                      uint32_t nExperts, uint32_t H, uint32_t F, float* work, uint64_t work_floats, void* stream) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (T == 0 || topk == 0) return BPQ4K_OK;
+    if (qtype != BPQ4K_TYPE_Q4_K && qtype != BPQ4K_TYPE_Q5_K)
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "the routed-expert layer covers Q4_K (12) and Q5_K (13), not type %d", qtype);
+    if (nExperts == 0 || H == 0 || F == 0) return fail(h, BPQ4K_ERR_INVALID_ARG, "nExperts, H or F is 0");
+    if (H % 256u || F % 256u) return fail(h, BPQ4K_ERR_UNSUPPORTED, "H=%u and F=%u must be multiples of 256", H, F);
+    const uint64_t pairs = (uint64_t)T * topk;
+    if (pairs > 0x7FFFFFFFull || (uint64_t)nExperts * F > 0xFFFFFFFFull || (uint64_t)nExperts * H > 0xFFFFFFFFull)
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "the expert stacks have more than 2^32 rows");
+    const uint32_t rs_h = bpq4k_kq_row_stride_words(qtype, H), rs_f = bpq4k_kq_row_stride_words(qtype, F);
+    if (int s = check_kq_weights(h, qtype, Wgate, H, rs_h)) return s;
+    if (int s = check_kq_weights(h, qtype, Wup, H, rs_h)) return s;
+    if (int s = check_kq_weights(h, qtype, Wdown, F, rs_f)) return s;
+    if (!X || !Y || !expert_ids || !route_w || !work) return fail(h, BPQ4K_ERR_INVALID_ARG, "a pointer argument is null");
+    if (work_floats < bpq4k_moe_ffn_work_floats(T, topk, H, F))
+        return fail(h, BPQ4K_ERR_INVALID_ARG, "work holds %llu floats, the call needs %llu", (unsigned long long)work_floats,
+                    (unsigned long long)bpq4k_moe_ffn_work_floats(T, topk, H, F));
+    if (!aligned16(X) || !aligned16(Y) || !aligned16(work)) return fail(h, BPQ4K_ERR_MISALIGNED, "X, Y or work is not 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(expert_ids) | reinterpret_cast<uintptr_t>(route_w)) & 3u)
+        return fail(h, BPQ4K_ERR_MISALIGNED, "expert_ids or route_w is not 4-byte aligned");
+    DeviceGuard g(h->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float* gate_out = work;
+    float* up_out = work + pairs * F;
+    float* down_out = work + 2 * pairs * F;
+    int launches = 0;
+    cudaError_t e = cudaSuccess;
+    auto expert_matmul = [&](const float* x, const void* W, float* y, uint32_t N, uint32_t K, uint32_t rs, uint32_t x_div,
+                             const float* aux) {
+        MatmulArgs a{};
+        a.X = x;
+        a.W = static_cast<const uint8_t*>(W);
+        a.Y = y;
+        a.M = 1;
+        a.N = N;
+        a.K = K;
+        a.w_row_bytes = (uint64_t)rs * 4u;
+        a.offsets = expert_ids;
+        a.offset_mul = N;  // expert e starts at row e*N of its stack
+        a.x_row_div = x_div;
+        a.n_slots = (uint32_t)pairs;
+        a.w_total_rows = (uint64_t)nExperts * N;
+        if (aux) {
+            a.prologue = BPQ4K_PROLOGUE_SILU_MUL;
+            a.aux = aux;
+        }
+        return launch_gemv_stream(a, h->tune, nullptr, 0, h->dev_status, h->sm_count, &h->tmaps, st, &launches, qtype);
+    };
+    e = expert_matmul(X, Wgate, gate_out, F, H, rs_h, topk, nullptr);
+    if (e == cudaSuccess) e = expert_matmul(X, Wup, up_out, F, H, rs_h, topk, nullptr);
+    if (e == cudaSuccess) e = expert_matmul(gate_out, Wdown, down_out, H, F, rs_f, 0, up_out);
+    if (e == cudaSuccess) {
+        e = launch_moe_accumulate(Y, down_out, route_w, T, topk, H, h->sm_count, st);
+        launches++;
+    }
+    h->launches += (uint64_t)launches;
+    if (e == cudaErrorInvalidValue) {
+        cudaGetLastError();
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "H=%u or F=%u is too long for the expert-indexed kernel", H, F);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return cuda_fail(h, e, "routed-expert layer launch");
+    }
+    return BPQ4K_OK;
+}
+
 int bpq4k_matmul_host_f32(bpq4k_handle_t h, const float* X_host, const void* W_dev, const float* bias_dev,
                           float* Y_host, uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords,
                           void* stream) {

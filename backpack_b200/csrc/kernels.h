@@ -21,12 +21,15 @@ struct MatmulArgs {
     const uint32_t* x_rows;   // null: slot s reads row s
     uint32_t n_slots;         // 0 for the direct form
     uint64_t w_total_rows;    // indirect form: rows of the whole expert stack (bounds the copies)
+    uint32_t offset_mul;      // 0: offsets[s] is a weight row; else offsets[s] is an expert id and the row is offsets[s]*offset_mul
+    uint32_t x_row_div;       // x_rows null and this non-zero: slot s reads activation row s / x_row_div
     // fused all-gather: every output is also stored to these buffers (other GPUs' memory, plain stores)
     float* peer_Y[8];
     uint32_t n_peers;
     // fused prologue on the activation row (single row only) and residual epilogue:
     //   1: x = X * rsqrt(mean(X^2) + eps) * aux      (aux = RMSNorm weight[K])
     //   2: x = gelu_tanh(X) * aux,  3: x = silu(X) * aux   (aux = the "up" vector[K])
+    // indirect form: slot s transforms its own row with row s of aux ([n_slots][K]); no residual there
     uint32_t prologue;
     const float* aux;
     float eps;
@@ -100,6 +103,10 @@ struct CopySegments {
     uint32_t count;
 };
 cudaError_t launch_copy_segments(const CopySegments& segs, cudaStream_t stream);
+
+// Y[t][n] += sum over k ascending of route_w[t*topk + k] * O[(t*topk + k)*N + n]; N a multiple of 4, rows 16-byte aligned.
+cudaError_t launch_moe_accumulate(float* Y, const float* O, const float* route_w, uint32_t T, uint32_t topk, uint32_t N,
+                                  int sm_count, cudaStream_t stream);
 
 // One warp per output row, float FMAs in the reference shader's arithmetic.
 cudaError_t launch_gemv_fp32(const MatmulArgs& a, cudaStream_t stream, int* launches);

@@ -197,11 +197,14 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
     float* Y = a.m.Y;
     uint32_t wrow0 = 0;
     uint32_t M = a.m.M;
+    const float* AUX = FP ? a.m.aux : nullptr;
     if (a.m.n_slots) {
         const uint32_t s = blockIdx.y;
         wrow0 = a.m.offsets[s];
-        X += (uint64_t)(a.m.x_rows ? a.m.x_rows[s] : s) * K;
+        if (a.m.offset_mul) wrow0 *= a.m.offset_mul;
+        X += (uint64_t)(a.m.x_rows ? a.m.x_rows[s] : a.m.x_row_div ? s / a.m.x_row_div : s) * K;
         Y += (uint64_t)s * N;
+        if (FP && AUX) AUX += (uint64_t)s * K;
         M = 1;
     }
     const uint32_t tstride = gridDim.x * a.wt;
@@ -321,8 +324,8 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                     if ((uint32_t)j < nj && it < items) {
                         v[j][0] = __ldg(reinterpret_cast<const float4*>(X) + 2u * it);
                         v[j][1] = __ldg(reinterpret_cast<const float4*>(X) + 2u * it + 1u);
-                        w[j][0] = __ldg(reinterpret_cast<const float4*>(a.m.aux) + 2u * it);
-                        w[j][1] = __ldg(reinterpret_cast<const float4*>(a.m.aux) + 2u * it + 1u);
+                        w[j][0] = __ldg(reinterpret_cast<const float4*>(AUX) + 2u * it);
+                        w[j][1] = __ldg(reinterpret_cast<const float4*>(AUX) + 2u * it + 1u);
                     }
                 }
 #pragma unroll
@@ -832,7 +835,8 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     uint32_t stages = tune.stages ? tune.stages : (small ? 2 : 4);
     if (stages > kMaxStages) stages = kMaxStages;
     const bool fused = m.prologue != 0 || m.residual != nullptr;
-    if (fused && (!m1 || indirect)) return cudaErrorInvalidValue;  // the fused forms are single-row, direct
+    if (fused && !m1) return cudaErrorInvalidValue;                   // the fused forms are single-row
+    if (indirect && m.residual) return cudaErrorInvalidValue;         // slots share no output row
     if (tune.force_scratch && !fused) xg = true;
     if (!xg) {
         const uint32_t cb_min = (m1 || tune.cb || cb < 2) ? cb : 2;

@@ -282,6 +282,28 @@ class Q4KContext:
             S, N, w.K, w.rowStrideWords, w.N, self._stream()))
         return out
 
+    def moe_ffn(self, x, w_gate: Q4KWeight, w_up: Q4KWeight, w_down: Q4KWeight, expert_ids, route_w, y, n_experts: int,
+                work=None):
+        """One routed-expert feed-forward step: y[t] += sum_k route_w[t,k] * down_e(silu(gate_e(x[t])) * up_e(x[t])),
+        e = expert_ids[t,k]; the stacks hold n_experts matrices ([F,H] gate/up, [H,F] down).  y is updated in place."""
+        torch = self._torch
+        T, H = x.shape
+        topk = expert_ids.numel() // T
+        F = w_gate.N // n_experts
+        assert x.dtype == torch.float32 and x.is_contiguous() and y.dtype == torch.float32 and y.is_contiguous()
+        assert y.shape == x.shape and route_w.dtype == torch.float32 and route_w.numel() == T * topk
+        assert expert_ids.dtype in (torch.int32, torch.uint32) and expert_ids.is_contiguous() and route_w.is_contiguous()
+        assert w_gate.qtype == w_up.qtype == w_down.qtype and w_gate.K == w_up.K == H and w_down.K == F
+        assert w_up.N == n_experts * F and w_down.N == n_experts * H
+        need = self.lib.bpq4k_moe_ffn_work_floats(T, topk, H, F)
+        if work is None:
+            work = torch.empty(max(need, 4), dtype=torch.float32, device=x.device)
+        self._check(self.lib.bpq4k_moe_ffn_f32(
+            self.h, w_gate.qtype, x.data_ptr(), w_gate.buf.data_ptr(), w_up.buf.data_ptr(), w_down.buf.data_ptr(),
+            expert_ids.data_ptr(), route_w.data_ptr(), y.data_ptr(), T, topk, n_experts, H, F, work.data_ptr(),
+            work.numel(), self._stream()))
+        return y
+
     def matmul_host(self, x_host: np.ndarray, w: Q4KWeight, y_host: np.ndarray, bias=None) -> np.ndarray:
         """Host activations in, host outputs out; copies and the wait are inside the call."""
         assert x_host.dtype == np.float32 and y_host.dtype == np.float32

@@ -282,6 +282,24 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
                         float* Y, uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords,
                         uint32_t yOffset, void* stream);
 
+/* The routed-expert feed-forward step of one layer, for T tokens, in four launches.  The reference
+ * issues six dispatches per routed slot -- gate, up, silu, mul, down, weighted accumulate
+ * (runtime/model_runner.cpp:3584-3651; offsets from compute_offsets.wgsl:26-36; the accumulate step
+ * is runtime/kernels/moe/weighted_accumulate_decode.wgsl).  For pair p = t*topk + k with expert
+ * e = expert_ids[p]:
+ *     g = X[t] . Wgate[e]^T,  u = X[t] . Wup[e]^T          two expert-indexed matmuls, F values each
+ *     o = (silu(g) * u) . Wdown[e]^T                        silu*up staged by the down matmul itself
+ *     Y[t] = Y[t] + route_w[p] * o                          k ascending, as the reference accumulates
+ * X and Y are [T][H] (Y is read and written: the caller leaves the residual stream or zeros there),
+ * Wgate / Wup stack the experts' [F][H] matrices row-wise, Wdown the [H][F] matrices, all of type
+ * `qtype` (Q4_K or Q5_K) with the packed row stride of their K.  expert_ids and route_w are device
+ * arrays of T*topk entries; an id >= nExperts reads zeros.  `work` is caller-owned device scratch of
+ * at least bpq4k_moe_ffn_work_floats() floats (the call allocates nothing). */
+uint64_t bpq4k_moe_ffn_work_floats(uint32_t T, uint32_t topk, uint32_t H, uint32_t F);
+int bpq4k_moe_ffn_f32(bpq4k_handle_t h, int qtype, const float* X, const void* Wgate, const void* Wup, const void* Wdown,
+                      const uint32_t* expert_ids, const float* route_w, float* Y, uint32_t T, uint32_t topk,
+                      uint32_t nExperts, uint32_t H, uint32_t F, float* work, uint64_t work_floats, void* stream);
+
 /* bpq4k_matmul_moe_f32 with the weight type given: Q4_K or Q5_K expert stacks. */
 int bpq4k_kq_matmul_moe_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W, const float* bias, float* Y,
                             const uint32_t* offsets, const uint32_t* x_rows, uint32_t nSlots, uint32_t N, uint32_t K,

@@ -232,6 +232,29 @@ def prologue(kind: int, x: np.ndarray, aux: np.ndarray | None, eps: float = 0.0)
     return out
 
 
+def moe_ffn(qtype: int, x: np.ndarray, raw_gate: np.ndarray, raw_up: np.ndarray, raw_down: np.ndarray,
+            expert_ids: np.ndarray, route_w: np.ndarray, y0: np.ndarray, F: int, H: int) -> np.ndarray:
+    """The reference's routed-expert loop for T tokens (runtime/model_runner.cpp:3584-3651): per token and slot
+    k ascending -- gate and up projections of expert e, silu(gate)*up, down projection, then
+    y[t] = y[t] + w[t,k] * out in float32 (runtime/kernels/moe/weighted_accumulate_decode.wgsl)."""
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, H)
+    T = x.shape[0]
+    ids = np.ascontiguousarray(expert_ids).reshape(T, -1)
+    w = np.ascontiguousarray(route_w, np.float32).reshape(T, -1)
+    y = np.array(y0, np.float32).reshape(T, H).copy()
+    bg, bd = KQ_BLOCK_BYTES[qtype] * (H // QK_K), KQ_BLOCK_BYTES[qtype] * (F // QK_K)   # bytes per weight row
+    rg, ru, rd = _raw(raw_gate), _raw(raw_up), _raw(raw_down)
+    for t in range(T):
+        for k in range(ids.shape[1]):
+            e = int(ids[t, k])
+            g = kq_matmul(qtype, x[t], rg[e * F * bg:(e + 1) * F * bg], None, F, H).reshape(-1)
+            u = kq_matmul(qtype, x[t], ru[e * F * bg:(e + 1) * F * bg], None, F, H).reshape(-1)
+            act = prologue(3, g, u)
+            o = kq_matmul(qtype, act, rd[e * H * bd:(e + 1) * H * bd], None, H, F).reshape(-1)
+            y[t] = y[t] + w[t, k] * o
+    return y
+
+
 def kq_dequant_numpy(qtype: int, raw: np.ndarray, N: int, K: int) -> np.ndarray:
     """Independent vectorised restatement of the Q5_K / Q6_K branches of dequant_kquant
     (runtime/gguf_loader.cpp:497-573); Q4_K goes to dequant_numpy."""

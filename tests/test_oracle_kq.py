@@ -71,3 +71,30 @@ def test_against_compiled_reference(qtype):
     assert np.array_equal(bits(orc.kq_matmul(qtype, x, w, None, N, K)), bits(orc.kq_matmul(qtype, x, w, None, N, K, use_ref=True)))
     a, b = orc.kq_pack(qtype, w, N, K), orc.kq_pack(qtype, w, N, K, use_ref=True)
     assert np.array_equal(a[0], b[0]) and a[1:] == b[1:]
+
+
+def test_moe_ffn_loop_equals_its_parts():
+    """The routed-expert restatement is the composition of the pinned pieces: matmuls on expert slices,
+    the silu*up step, and a float32 accumulate in slot order."""
+    E, H, F, T, topk = 3, 512, 256, 2, 2
+    for qtype in (orc.Q4_K, orc.Q5_K):
+        bb = orc.KQ_BLOCK_BYTES[qtype]
+        rg, ru = synth.make_kq_weights(qtype, E * F, H, 1), synth.make_kq_weights(qtype, E * F, H, 2)
+        rd = synth.make_kq_weights(qtype, E * H, F, 3)
+        x = (synth.make_activations(T, H, 4) * 0.05).astype(np.float32)
+        ids = np.array([[2, 0], [1, 2]])
+        w = np.array([[0.25, 0.75], [0.6, 0.4]], np.float32)
+        y0 = synth.make_activations(T, H, 5)
+        got = orc.moe_ffn(qtype, x, rg, ru, rd, ids, w, y0, F, H)
+        want = y0.copy()
+        deq = [orc.kq_dequant(qtype, r, n, k) for r, n, k in ((rg, E * F, H), (ru, E * F, H), (rd, E * H, F))]
+        for t in range(T):
+            for k in range(topk):
+                e = ids[t, k]
+                g = deq[0][e * F:(e + 1) * F].astype(np.float64) @ x[t]
+                u = deq[1][e * F:(e + 1) * F].astype(np.float64) @ x[t]
+                act = g / (1 + np.exp(-g)) * u
+                want[t] = want[t] + w[t, k] * (deq[2][e * H:(e + 1) * H].astype(np.float64) @ act).astype(np.float32)
+        assert np.linalg.norm(got - want) / np.linalg.norm(want) < 1e-5
+        assert np.linalg.norm((got - y0) - (want - y0)) / np.linalg.norm(want - y0) < 1e-5
+        assert bb in (144, 176)
