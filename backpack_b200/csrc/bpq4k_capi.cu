@@ -269,6 +269,9 @@ int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
         case BPQ4K_OPT_STREAM_NO_PDL:
             h->tune.no_pdl = value ? 1u : 0u;
             return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_NO_UNIT_LIST:
+            h->tune.no_unit_list = value ? 1u : 0u;
+            return BPQ4K_OK;
 #ifdef BPQ4K_ENABLE_PROBES
         case 99:
             h->tune.probe = (uint32_t)value;
@@ -291,6 +294,7 @@ int bpq4k_get_option(bpq4k_handle_t h, int option, int* value) {
         case BPQ4K_OPT_STREAM_CTAS_PER_SM: *value = (int)h->tune.ctas_per_sm; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_FORCE_SCRATCH: *value = (int)h->tune.force_scratch; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_NO_PDL: *value = (int)h->tune.no_pdl; return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_NO_UNIT_LIST: *value = (int)h->tune.no_unit_list; return BPQ4K_OK;
         default: return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown option %d", option);
     }
 }
@@ -654,7 +658,8 @@ int bpq4k_kq_matmul_moe_f32(bpq4k_handle_t h, int qtype, const float* X, const v
     if (qtype == BPQ4K_TYPE_Q4_K) return bpq4k_matmul_moe_f32(h, X, W, bias, Y, offsets, x_rows, nSlots, N, K, rowStrideWords, wRows, stream);
     if (!h) return BPQ4K_ERR_INVALID_ARG;
     if (nSlots == 0 || N == 0) return BPQ4K_OK;
-    if (qtype != BPQ4K_TYPE_Q5_K) return fail(h, BPQ4K_ERR_UNSUPPORTED, "the expert-indexed form covers Q4_K and Q5_K, not type %d", qtype);
+    if (qtype != BPQ4K_TYPE_Q5_K && qtype != BPQ4K_TYPE_Q6_K_PADDED)
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "the expert-indexed form covers Q4_K, Q5_K and padded Q6_K, not type %d", qtype);
     if (int s = check_kq_weights(h, qtype, W, K, rowStrideWords)) return s;
     if (!X || !Y || !offsets) return fail(h, BPQ4K_ERR_INVALID_ARG, "X, Y or offsets is null");
     if (wRows < N) return fail(h, BPQ4K_ERR_INVALID_ARG, "wRows=%u is smaller than N=%u", wRows, N);
@@ -675,12 +680,14 @@ int bpq4k_kq_matmul_moe_f32(bpq4k_handle_t h, int qtype, const float* X, const v
     a.n_slots = nSlots;
     a.w_total_rows = wRows;
     int launches = 0;
-    const cudaError_t e = launch_gemv_stream(a, h->tune, nullptr, 0, h->dev_status, h->sm_count, &h->tmaps,
-                                             static_cast<cudaStream_t>(stream), &launches, 13);
+    const cudaError_t e = qtype == BPQ4K_TYPE_Q6_K_PADDED
+                              ? launch_q6k_stream(a, h->tune, h->dev_status, h->sm_count, &h->tmaps, static_cast<cudaStream_t>(stream), &launches)
+                              : launch_gemv_stream(a, h->tune, nullptr, 0, h->dev_status, h->sm_count, &h->tmaps,
+                                                   static_cast<cudaStream_t>(stream), &launches, 13);
     h->launches += (uint64_t)launches;
     if (e == cudaErrorInvalidValue) {
         cudaGetLastError();
-        return fail(h, BPQ4K_ERR_UNSUPPORTED, "K=%u is too long for the expert-indexed kernel", K);
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "K=%u is too long (or there are too many slots) for the expert-indexed kernel", K);
     }
     if (e != cudaSuccess) {
         cudaGetLastError();
@@ -724,7 +731,7 @@ int bpq4k_moe_ffn_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W
     int launches = 0;
     cudaError_t e = cudaSuccess;
     auto expert_matmul = [&](const float* x, const void* W, float* y, uint32_t N, uint32_t K, uint32_t rs, uint32_t x_div,
-                             const float* aux) {
+                             const float* aux, const void* W2, float* y2) {
         MatmulArgs a{};
         a.X = x;
         a.W = static_cast<const uint8_t*>(W);
@@ -738,15 +745,22 @@ int bpq4k_moe_ffn_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W
         a.x_row_div = x_div;
         a.n_slots = (uint32_t)pairs;
         a.w_total_rows = (uint64_t)nExperts * N;
+        a.W2 = static_cast<const uint8_t*>(W2);
+        a.Y2 = y2;
         if (aux) {
             a.prologue = BPQ4K_PROLOGUE_SILU_MUL;
             a.aux = aux;
         }
         return launch_gemv_stream(a, h->tune, nullptr, 0, h->dev_status, h->sm_count, &h->tmaps, st, &launches, qtype);
     };
-    e = expert_matmul(X, Wgate, gate_out, F, H, rs_h, topk, nullptr);
-    if (e == cudaSuccess) e = expert_matmul(X, Wup, up_out, F, H, rs_h, topk, nullptr);
-    if (e == cudaSuccess) e = expert_matmul(gate_out, Wdown, down_out, H, F, rs_f, 0, up_out);
+    // gate and up in one launch (same activations and experts) when the unit list allows it
+    e = expert_matmul(X, Wgate, gate_out, F, H, rs_h, topk, nullptr, Wup, up_out);
+    if (e == cudaErrorInvalidValue) {
+        cudaGetLastError();
+        e = expert_matmul(X, Wgate, gate_out, F, H, rs_h, topk, nullptr, nullptr, nullptr);
+        if (e == cudaSuccess) e = expert_matmul(X, Wup, up_out, F, H, rs_h, topk, nullptr, nullptr, nullptr);
+    }
+    if (e == cudaSuccess) e = expert_matmul(gate_out, Wdown, down_out, H, F, rs_f, 0, up_out, nullptr, nullptr);
     if (e == cudaSuccess) {
         e = launch_moe_accumulate(Y, down_out, route_w, T, topk, H, h->sm_count, st);
         launches++;

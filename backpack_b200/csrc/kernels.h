@@ -23,6 +23,10 @@ struct MatmulArgs {
     uint64_t w_total_rows;    // indirect form: rows of the whole expert stack (bounds the copies)
     uint32_t offset_mul;      // 0: offsets[s] is a weight row; else offsets[s] is an expert id and the row is offsets[s]*offset_mul
     uint32_t x_row_div;       // x_rows null and this non-zero: slot s reads activation row s / x_row_div
+    // indirect form, optional second stack of the same shape served by the same launch with the same
+    // activations and offsets (an expert layer's gate and up stacks): results to Y2[s*N + n]
+    const uint8_t* W2;
+    float* Y2;
     // fused all-gather: every output is also stored to these buffers (other GPUs' memory, plain stores)
     float* peer_Y[8];
     uint32_t n_peers;
@@ -51,6 +55,7 @@ struct StreamTuning {
     uint32_t ctas_per_sm = 0;  // cap on resident CTAs per SM
     uint32_t force_scratch = 0;  // 1: always split activations into global scratch first
     uint32_t no_pdl = 0;       // 1: launch without programmatic dependent launch
+    uint32_t no_unit_list = 0; // 1: indirect form always as one grid row per slot
     uint32_t probe = 0;        // development builds only: time-attribution variants of the kernel
 };
 

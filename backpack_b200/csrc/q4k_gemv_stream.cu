@@ -67,6 +67,7 @@ constexpr uint32_t kZeroBytes = 1024;  // zero region the "other parity" lanes r
 struct StreamArgs {
     CUtensorMap tmap;      // W as a 2-D tensor [rows][row words], box = 16 rows x cb blocks
     CUtensorMap tmap_rem;  // same tensor, box = 16 rows x rem blocks (tail of a warp's K range)
+    CUtensorMap tmap_b, tmap_b_rem;  // IND with two matrices: the same two boxes over m.W2
     MatmulArgs m;
     uint32_t wk, wt, cb, rem, bpw, stages, stage_bytes, ntiles, tokens;  // bpw: blocks per warp per tile
     uint32_t off_zero, off_S, off_x, off_part, off_ring;
@@ -74,6 +75,8 @@ struct StreamArgs {
     // activations prepared by quantize_activations_kernel (XG mode)
     const uint8_t* xfrag_g;
     const float* S_g;
+    uint32_t nvslots;  // IND: slots times matrices (virtual slot vs: matrix vs / n_slots, slot vs % n_slots)
+    uint32_t u_base, u_extra;  // IND: CTA c takes u_base units (+1 for c < u_extra) of the unit list, in order
 };
 
 // Largest |xi|: its top base-128 digit still fits a signed byte.
@@ -174,9 +177,17 @@ __device__ __forceinline__ void merge_fifth_bit(uint32_t codes, uint32_t qh, uin
 // quantising all rows itself -- with eight rows that is ~1 us instead of ~8 us per CTA.
 // FP (single row only): the call has a fused prologue and/or a residual; kept out of the plain kernel, whose
 // code it would otherwise slow down by ~1 %.
-template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false, bool XC = false, bool FP = false>
+// IND (single row only): the indirect form as ONE list of (slot, tile) units over a 1-D grid.  CTA c takes the
+// units [U*c/G, U*(c+1)/G), which lie in at most kMaxLocalSlots consecutive slots; it stages those slots'
+// activation rows side by side and every tile picks its slot's row.  All SMs carry the same load whatever the
+// number of slots (with blockIdx.y = slot, 64 slots occupy 128 of 148 SMs).  With a second matrix (m.W2, same
+// shape, activations and offsets: the gate and up stacks of an expert layer) the list simply continues
+// over it, results to m.Y2.
+constexpr uint32_t kMaxLocalSlots = 4;
+template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false>
 __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
     static_assert(!FP || (M1 && !XG && !XC), "the fused forms are single-row and stage the row themselves");
+    static_assert(!IND || (M1 && !XG && !XC && PROBE == 0), "the unit-list form is single-row and stages its rows itself");
     static_assert(!(XG && XC), "digits are read from the scratch directly (XG) or copied into shared memory (XC)");
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr uint32_t BB = Q5 ? 176u : kBlockBytes, BW = BB / 4u;  // bytes and words per super-block
@@ -198,18 +209,45 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
     uint32_t wrow0 = 0;
     uint32_t M = a.m.M;
     const float* AUX = FP ? a.m.aux : nullptr;
-    if (a.m.n_slots) {
+    uint32_t tstride = gridDim.x * a.wt;
+    uint32_t tile0 = blockIdx.x * a.wt + wt;   // IND: a unit index, not a tile
+    uint32_t my_tiles = tile0 < a.ntiles ? (a.ntiles - tile0 + tstride - 1) / tstride : 0;
+    // IND: this CTA's first virtual slot, how many it touches, and their first weight rows
+    [[maybe_unused]] uint32_t s_first = 0, nloc = 1;
+    [[maybe_unused]] uint32_t offs[kMaxLocalSlots] = {0u, 0u, 0u, 0u};
+    [[maybe_unused]] const float* xrow[kMaxLocalSlots] = {a.m.X, a.m.X, a.m.X, a.m.X};
+    [[maybe_unused]] const float* arow[kMaxLocalSlots] = {a.m.aux, a.m.aux, a.m.aux, a.m.aux};
+    auto slot_of = [&](uint32_t vs) { return vs >= a.m.n_slots ? vs - a.m.n_slots : vs; };
+    auto x_row_of = [&](uint32_t s) { return a.m.x_rows ? a.m.x_rows[s] : a.m.x_row_div ? s / a.m.x_row_div : s; };
+    if constexpr (IND) {
+        const uint32_t u_begin = blockIdx.x * a.u_base + min(blockIdx.x, a.u_extra);
+        const uint32_t u_end = u_begin + a.u_base + (blockIdx.x < a.u_extra ? 1u : 0u);
+        s_first = u_begin / a.ntiles;  // the only division; everything else advances by subtraction
+        tstride = a.wt;
+        tile0 = u_begin + wt;
+        my_tiles = tile0 < u_end ? (u_end - tile0 + tstride - 1u) / tstride : 0u;  // tstride is a small power of two or close: cheap
+        nloc = u_end > u_begin ? 1u : 0u;
+        for (uint32_t r = u_end - 1u - s_first * a.ntiles; nloc && r >= a.ntiles && nloc <= kMaxLocalSlots; r -= a.ntiles) nloc++;
+        if (nloc > kMaxLocalSlots) nloc = 0, my_tiles = 0;  // the host sizes the grid so that this never happens
+#pragma unroll
+        for (uint32_t l = 0; l < kMaxLocalSlots; l++)
+            if (l < nloc) {
+                const uint32_t s = slot_of(s_first + l);
+                const uint32_t o = a.m.offsets[s];
+                offs[l] = a.m.offset_mul ? o * a.m.offset_mul : o;
+                xrow[l] = a.m.X + (uint64_t)x_row_of(s) * K;  // addresses only; the rows are read after the dependency wait
+                if (FP && a.m.aux) arow[l] = a.m.aux + (uint64_t)s * K;
+            }
+        M = 1;
+    } else if (a.m.n_slots) {
         const uint32_t s = blockIdx.y;
         wrow0 = a.m.offsets[s];
         if (a.m.offset_mul) wrow0 *= a.m.offset_mul;
-        X += (uint64_t)(a.m.x_rows ? a.m.x_rows[s] : a.m.x_row_div ? s / a.m.x_row_div : s) * K;
+        X += (uint64_t)x_row_of(s) * K;
         Y += (uint64_t)s * N;
         if (FP && AUX) AUX += (uint64_t)s * K;
         M = 1;
     }
-    const uint32_t tstride = gridDim.x * a.wt;
-    const uint32_t tile0 = blockIdx.x * a.wt + wt;
-    const uint32_t my_tiles = tile0 < a.ntiles ? (a.ntiles - tile0 + tstride - 1) / tstride : 0;
     const uint32_t total_units = my_tiles * nchunks;
 
     const uint32_t bar0 = smem_u32(smem) + warp * kMaxStages * 8u;
@@ -226,18 +264,35 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
 
     // ---- producer side: lane 0 issues one tensor copy per unit ------------------
     uint32_t iss_tile = tile0, iss_c = 0, iss_st = 0;
+    // IND: the unit as (local slot, tile of that slot), advanced without divisions
+    [[maybe_unused]] uint32_t iss_l = 0, iss_tl = 0;
+    if constexpr (IND) {
+        iss_tl = tile0 - s_first * a.ntiles;
+        while (iss_tl >= a.ntiles) iss_tl -= a.ntiles, iss_l++;
+    }
     auto issue_next = [&]() {
         if (lane == 0) {
             const uint32_t bar = bar0 + iss_st * 8u;
             const bool full = iss_c < nfull;
             mbar_expect_tx(bar, 16u * BB * (full ? a.cb : a.rem));
+            if constexpr (IND) {
+                const uint32_t l = iss_l;
+                const uint32_t row = (l == 0 ? offs[0] : l == 1 ? offs[1] : l == 2 ? offs[2] : offs[3]) + iss_tl * 16u;
+                const CUtensorMap* map = s_first + l >= a.m.n_slots ? (full ? &a.tmap_b : &a.tmap_b_rem) : (full ? &a.tmap : &a.tmap_rem);
+                tma_load_2d(ring + iss_st * a.stage_bytes, map, (b0 + iss_c * a.cb) * BW, row, bar);
+            } else {
             tma_load_2d(ring + iss_st * a.stage_bytes, full ? &a.tmap : &a.tmap_rem, (b0 + iss_c * a.cb) * BW,
                         (uint32_t)wrow0 + iss_tile * 16u, bar);
+            }
         }
         if (++iss_st == a.stages) iss_st = 0;
         if (++iss_c == nchunks) {
             iss_c = 0;
             iss_tile += tstride;
+            if constexpr (IND) {
+                iss_tl += tstride;
+                while (iss_tl >= a.ntiles) iss_tl -= a.ntiles, iss_l++;  // at most tstride (<= 16) rounds
+            }
         }
     };
     if constexpr (PROBE < 2) {
@@ -292,7 +347,11 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
             for (uint32_t i = mrows * K + tid; i < (uint32_t)TOK * K; i += blockDim.x) reinterpret_cast<uint32_t*>(frag)[i] = 0u;
             for (uint32_t i = mrows * nb * 16u + tid; i < (uint32_t)TOK * nb * 16u; i += blockDim.x) SI[i] = 0.f;
         }
-        const uint32_t items = mrows * per_row;
+        // IND: the rows of all local slots in one pass, slot l staged as "row l" of the shared-memory layout
+        const uint32_t items = (IND ? nloc : mrows) * per_row;
+        [[maybe_unused]] auto pick = [&](const float* const* rows, uint32_t l) {
+            return l == 0 ? rows[0] : l == 1 ? rows[1] : l == 2 ? rows[2] : rows[3];
+        };
         if (FP && a.m.prologue) {
             // Fused prologue on the single activation row (the reference's q4k_matmul_norm.wgsl:47-92
             // and q4k_down_gelu.wgsl:47-62, plus the silu form of silu_mul_fused): transform while staging.
@@ -322,10 +381,13 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                     const uint32_t it = base + j * blockDim.x + tid;
                     v[j][0] = v[j][1] = w[j][0] = w[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
                     if ((uint32_t)j < nj && it < items) {
-                        v[j][0] = __ldg(reinterpret_cast<const float4*>(X) + 2u * it);
-                        v[j][1] = __ldg(reinterpret_cast<const float4*>(X) + 2u * it + 1u);
-                        w[j][0] = __ldg(reinterpret_cast<const float4*>(AUX) + 2u * it);
-                        w[j][1] = __ldg(reinterpret_cast<const float4*>(AUX) + 2u * it + 1u);
+                        const uint32_t l = IND ? it / per_row : 0u, c = it - l * per_row;
+                        const float4* xp = reinterpret_cast<const float4*>(IND ? pick(xrow, l) : X) + 2u * c;
+                        const float4* ap = reinterpret_cast<const float4*>(IND ? pick(arow, l) : AUX) + 2u * c;
+                        v[j][0] = __ldg(xp);
+                        v[j][1] = __ldg(xp + 1);
+                        w[j][0] = __ldg(ap);
+                        w[j][1] = __ldg(ap + 1);
                     }
                 }
 #pragma unroll
@@ -346,7 +408,8 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                             vf[i] = __fdividef(g, 1.f + __expf(-g)) * wf[i];  // relative error ~1e-6: far inside the digits' 2^-22
                         }
                     }
-                    quantize_loaded(v[j][0], v[j][1], K, 0u, it < items ? it : 0u, it < items, frag, SI);
+                    const uint32_t l = (IND && it < items) ? it / per_row : 0u;
+                    quantize_loaded(v[j][0], v[j][1], K, l, it < items ? it - l * per_row : 0u, it < items, frag, SI);
                 }
             }
         } else {
@@ -366,7 +429,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                 c8[j] = valid[j] ? it - tok[j] * per_row : 0u;
                 v[j][0] = v[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (valid[j]) {
-                    const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok[j] * K + (uint64_t)c8[j] * 8u);
+                    const float4* xp = reinterpret_cast<const float4*>((IND ? pick(xrow, tok[j]) : X + (uint64_t)tok[j] * K) + (uint64_t)c8[j] * 8u);
                     v[j][0] = __ldg(xp);
                     v[j][1] = __ldg(xp + 1);
                 }
@@ -428,9 +491,27 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
 
     float* part = reinterpret_cast<float*>(smem + a.off_part);
     uint32_t st = 0, ph = 0, u = 0, failed = 0;
+    [[maybe_unused]] uint32_t cur_l = 0, cur_tl = 0;
+    if constexpr (IND) {
+        cur_tl = tile0 - s_first * a.ntiles;
+        while (cur_tl >= a.ntiles) cur_tl -= a.ntiles, cur_l++;
+    }
 
     for (uint32_t ti = 0; ti < my_tiles; ti++) {
-        const uint32_t tile = tile0 + ti * tstride;
+        uint32_t tile = tile0 + ti * tstride;
+        // IND: the unit's slot selects the staged row (data lanes only; zero lanes stay in the zero region),
+        // its scales and the output row
+        [[maybe_unused]] AddrT pa_t = pa0, pb_t = pb0, s_t = s0_addr;
+        if constexpr (IND) {
+            const uint32_t l = cur_l, vs = s_first + l;
+            tile = cur_tl;
+            cur_tl += tstride;
+            while (cur_tl >= a.ntiles) cur_tl -= a.ntiles, cur_l++;
+            pa_t += b_par == 0 ? l * K * 4u : 0u;
+            pb_t += b_par == 1 ? l * K * 4u : 0u;
+            s_t += l * nb * 64u;
+            Y = vs >= a.m.n_slots ? a.m.Y2 + (uint64_t)(vs - a.m.n_slots) * N : a.m.Y + (uint64_t)vs * N;
+        }
         // single-row calls: fetch this lane's residual value now, it is added when the tile is stored
         float res_pre = 0.f;
         if (FP && a.m.residual && wk == 0 && lane < 16u && tile * 16u + lane < N) res_pre = __ldg(a.m.residual + tile * 16u + lane);
@@ -487,12 +568,12 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                 uint4 Sv[NT], Iv[NT];  // per group: sum(xi)*inv and inv of this parity's sub-block
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
-                    Sv[nt] = load16(s0_addr + (AddrT)blk * 64u, std::integral_constant<int, 0>{});
-                    Iv[nt] = load16(s0_addr + (AddrT)blk * 64u, std::integral_constant<int, 16>{});
+                    Sv[nt] = load16((IND ? s_t : s0_addr) + (AddrT)blk * 64u, std::integral_constant<int, 0>{});
+                    Iv[nt] = load16((IND ? s_t : s0_addr) + (AddrT)blk * 64u, std::integral_constant<int, 16>{});
                 }
                 // data lanes advance 1 KiB per block (4 groups x 256 B); zero lanes stay inside the
                 // 1 KiB zero region, so the per-group offset g*256 is an immediate for both
-                const AddrT pa = pa0 + blk * 4u * stride_a, pb = pb0 + blk * 4u * stride_b;
+                const AddrT pa = (IND ? pa_t : pa0) + blk * 4u * stride_a, pb = (IND ? pb_t : pb0) + blk * 4u * stride_b;
                 const uint32_t lm_addr = boff + lm_off;
                 uint32_t qh[4] = {0u, 0u, 0u, 0u};  // Q5_K: fifth bits of this thread's weights, all eight sub-blocks
                 if constexpr (Q5) ldmatrix_x4<-32>(lm_addr, qh[0], qh[1], qh[2], qh[3]);
@@ -699,9 +780,9 @@ __global__ void __launch_bounds__(256) quantize_activations_kernel(const float* 
 
 // Launch one instantiation.  The grid is persistent: at most as many CTAs as can be
 // resident at once (occupancy query, cached), never more than there are tile groups.
-template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false, bool XC = false, bool FP = false>
+template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false>
 cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, uint32_t threads, size_t smem,
-                       int sm_count, uint32_t ctas_per_sm_override, bool pdl, cudaStream_t stream) {
+                       int sm_count, uint32_t ctas_per_sm_override, bool pdl, cudaStream_t stream, uint32_t flat_grid = 0) {
     struct Cache { int dev = -1; size_t smem_cfg = 0; uint32_t threads = 0; size_t smem = 0; int occ = 0; };
     static Cache cache;
     int dev = 0;
@@ -709,7 +790,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     if (cache.dev != dev) cache = Cache{};
     cache.dev = dev;
     if (smem > cache.smem_cfg) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC, FP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC, FP, IND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return e;
         cache.smem_cfg = smem;
@@ -717,7 +798,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     }
     if (cache.threads != threads || cache.smem != smem) {
         int occ = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC, FP>, (int)threads, smem);
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC, FP, IND>, (int)threads, smem);
         if (e != cudaSuccess) return e;
         cache.threads = threads;
         cache.smem = smem;
@@ -738,6 +819,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
         gx = (groups + rounds - 1) / rounds;
     }
     if (gx == 0) gx = 1;
+    if (flat_grid) gx = flat_grid, slots_y = 1;  // IND: the planner fixed the grid (one CTA per SM at most)
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(gx, slots_y);
     cfg.blockDim = dim3(threads);
@@ -748,7 +830,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC, FP>, sa);
+    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC, FP, IND>, sa);
 }
 
 static_assert(sizeof(CUtensorMap) == 128, "TmapCache::Entry::map must hold a CUtensorMap");
@@ -815,7 +897,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     uint32_t cb = tune.cb ? tune.cb : m1 ? (small ? (bpw <= 2 ? bpw : 1) : (q5 ? 3 : 5)) : 3;  // Q5_K: 5 wide blocks leave no room for the ring
     if (cb > 256u / block_words) cb = 256u / block_words;  // box width <= 256 words
     if (cb > bpw) cb = bpw;
-    const uint32_t x_bytes = tokens * m.K * 4u, S_bytes = tokens * (m.K / 32u) * 8u;
+    uint32_t x_bytes = tokens * m.K * 4u, S_bytes = tokens * (m.K / 32u) * 8u;  // IND: times the local slots (set below)
     uint32_t stage_bytes = 0;
     auto layout = [&](bool xg, uint32_t stages, StreamArgs& sa) -> uint32_t {
         uint32_t off = kBarBytes;
@@ -826,9 +908,37 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         sa.off_ring = align_up(off, 128); off = sa.off_ring + warps * stages * stage_bytes;
         return off;
     };
+    // Indirect form as one unit list (IND) when every CTA's share of it spans few enough slots for their
+    // activation rows to sit side by side in shared memory; otherwise one grid row per slot.
+    const uint32_t n_mats = indirect && m.W2 ? 2u : 1u;
+    if (m.W2 && !indirect) return cudaErrorInvalidValue;
+    uint32_t flat_grid = 0, nloc_max = 1, u_base = 0, u_extra = 0;
+    if (indirect && !tune.force_scratch && !tune.no_unit_list) {
+        const uint64_t U = (uint64_t)m.n_slots * n_mats * ntiles;
+        if (U <= 0x7FFFFFFFull) {
+            const uint64_t groups_flat = (U + wt - 1) / wt;
+            const uint32_t G = (uint32_t)(groups_flat < (uint64_t)sm_count ? groups_flat : (uint64_t)sm_count);
+            const uint32_t chunk = (uint32_t)((U + G - 1) / G);
+            uint32_t nl = (chunk + ntiles - 2) / ntiles + 1;
+            if (nl > m.n_slots * n_mats) nl = m.n_slots * n_mats;
+            // One grid row per slot keeps every CTA on one slot (one staged row, less bookkeeping per tile) and is
+            // 5-10 % faster while all slots' CTAs are resident at once (measured: 8 to 64 slots of 768x2048 and
+            // 2048x768 experts).  With more slots than SMs it needs several waves, each paying the prologue again,
+            // and the unit list wins (256 slots: 39.8 against 41.9 us).  Two stacks always share one unit list.
+            const bool several_waves = m.n_slots > (uint32_t)sm_count;
+            if (nl <= kMaxLocalSlots && (m.W2 || several_waves)) {
+                flat_grid = G, nloc_max = nl;
+                u_base = (uint32_t)(U / G), u_extra = (uint32_t)(U % G);
+            }
+        }
+    }
+    if (m.W2 && !flat_grid) return cudaErrorInvalidValue;  // two stacks only as a unit list
     StreamArgs sa{};
     sa.m = m;
     sa.m.M = M;
+    sa.nvslots = m.n_slots * n_mats;
+    sa.u_base = u_base;
+    sa.u_extra = u_extra;
     // activations in shared memory if they leave room for at least 2 stages per warp; with several
     // activation rows a narrower stage (down to 2 blocks) is tried before giving up on that
     bool xg = false;
@@ -840,17 +950,30 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     if (tune.force_scratch && !fused) xg = true;
     if (!xg) {
         const uint32_t cb_min = (m1 || tune.cb || cb < 2) ? cb : 2;
+        auto fit = [&]() {
+            for (uint32_t cb_try = cb; cb_try >= cb_min; cb_try--) {
+                stage_bytes = 16 * cb_try * block_bytes;
+                uint32_t s_try = stages;
+                while (s_try >= 2 && layout(false, s_try, sa) > kSmemMax) s_try--;
+                if (s_try >= 2) {
+                    stages = s_try;
+                    cb = cb_try;
+                    return true;
+                }
+            }
+            return false;
+        };
         bool fits = false;
-        for (uint32_t cb_try = cb; cb_try >= cb_min && !fits; cb_try--) {
-            stage_bytes = 16 * cb_try * block_bytes;
-            uint32_t s_try = stages;
-            while (s_try >= 2 && layout(false, s_try, sa) > kSmemMax) s_try--;
-            if (s_try >= 2) {
-                stages = s_try;
-                cb = cb_try;
-                fits = true;
+        if (flat_grid) {
+            x_bytes *= nloc_max, S_bytes *= nloc_max;
+            fits = fit();
+            if (!fits) {  // the rows of several slots leave no room for the rings: one grid row per slot instead
+                x_bytes /= nloc_max, S_bytes /= nloc_max;
+                flat_grid = 0;
+                if (m.W2) return cudaErrorInvalidValue;
             }
         }
+        if (!fits) fits = fit();
         if (!fits) xg = true;
     }
     // several rows that fit in shared memory, 32K values or more: quantise them once per call (scratch) and
@@ -871,10 +994,10 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     {
         const uint64_t rows_total = indirect ? m.w_total_rows : m.N;
         const uint32_t key_nb = q5 ? (nb | 0x50000000u) : nb;  // keeps Q5_K maps apart from Q4_K maps of the same buffer
-        auto get_map = [&](uint32_t width_blocks, CUtensorMap* out) -> cudaError_t {
+        auto get_map = [&](uint32_t width_blocks, CUtensorMap* out, const uint8_t* Wp) -> cudaError_t {
             if (tmaps) {
                 for (const auto& en : tmaps->entries)
-                    if (en.W == m.W && en.rows == rows_total && en.row_bytes == m.w_row_bytes && en.nb == key_nb &&
+                    if (en.W == Wp && en.rows == rows_total && en.row_bytes == m.w_row_bytes && en.nb == key_nb &&
                         en.cb == width_blocks) {
                         std::memcpy(out, en.map, sizeof(CUtensorMap));
                         return cudaSuccess;
@@ -886,22 +1009,33 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
             const cuuint64_t gstride[1] = {(cuuint64_t)m.w_row_bytes};
             const cuuint32_t box[2] = {width_blocks * block_words, 16u};
             const cuuint32_t estr[2] = {1u, 1u};
-            const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(m.W), gdim, gstride, box, estr,
+            const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(Wp), gdim, gstride, box, estr,
                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
             if (tmaps) {
                 auto& en = tmaps->entries[tmaps->next++ % TmapCache::kEntries];
-                en.W = m.W; en.rows = rows_total; en.row_bytes = m.w_row_bytes; en.nb = key_nb; en.cb = width_blocks;
+                en.W = Wp; en.rows = rows_total; en.row_bytes = m.w_row_bytes; en.nb = key_nb; en.cb = width_blocks;
                 std::memcpy(en.map, out, sizeof(CUtensorMap));
             }
             return cudaSuccess;
         };
-        if (cudaError_t e = get_map(cb, &sa.tmap)) return e;
+        if (cudaError_t e = get_map(cb, &sa.tmap, m.W)) return e;
         if (rem) {
-            if (cudaError_t e = get_map(rem, &sa.tmap_rem)) return e;
+            if (cudaError_t e = get_map(rem, &sa.tmap_rem, m.W)) return e;
         } else {
             sa.tmap_rem = sa.tmap;
+        }
+        if (m.W2) {
+            if (cudaError_t e = get_map(cb, &sa.tmap_b, m.W2)) return e;
+            if (rem) {
+                if (cudaError_t e = get_map(rem, &sa.tmap_b_rem, m.W2)) return e;
+            } else {
+                sa.tmap_b_rem = sa.tmap_b;
+            }
+        } else {
+            sa.tmap_b = sa.tmap;
+            sa.tmap_b_rem = sa.tmap_rem;
         }
     }
 
@@ -920,6 +1054,19 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     }
 
     cudaError_t e = cudaSuccess;
+    if (flat_grid) {
+        if (xg || !m1) return cudaErrorInvalidValue;
+        const uint32_t threads = warps * 32;
+        const bool pdl = !tune.no_pdl;
+        if (fused)
+            e = q5 ? launch_one<1, true, false, 0, true, false, true, true>(sa, groups, 1, threads, smem, sm_count, 1, pdl, stream, flat_grid)
+                   : launch_one<1, true, false, 0, false, false, true, true>(sa, groups, 1, threads, smem, sm_count, 1, pdl, stream, flat_grid);
+        else
+            e = q5 ? launch_one<1, true, false, 0, true, false, false, true>(sa, groups, 1, threads, smem, sm_count, 1, pdl, stream, flat_grid)
+                   : launch_one<1, true, false, 0, false, false, false, true>(sa, groups, 1, threads, smem, sm_count, 1, pdl, stream, flat_grid);
+        if (launches) ++*launches;
+        return e;
+    }
     MatmulArgs base = sa.m;
     for (uint32_t s0 = 0; s0 < slots_total; s0 += 65535u) {
         const uint32_t cnt = indirect ? min(65535u, m.n_slots - s0) : 1;

@@ -107,6 +107,15 @@ __global__ void __launch_bounds__(512, 1) q6k_stream_kernel(const __grid_constan
     const uint32_t nchunks = nfull + (a.rem ? 1u : 0u);
     const float* X = a.m.X;
     float* Y = a.m.Y;
+    // indirect (expert-stacked) form: blockIdx.y is the slot -- its expert's first row, activation row and output row
+    uint32_t wrow0 = 0;
+    if (a.m.n_slots) {
+        const uint32_t s = blockIdx.y;
+        wrow0 = a.m.offsets[s];
+        if (a.m.offset_mul) wrow0 *= a.m.offset_mul;
+        X += (uint64_t)(a.m.x_rows ? a.m.x_rows[s] : a.m.x_row_div ? s / a.m.x_row_div : s) * K;
+        Y += (uint64_t)s * N;
+    }
 
     const uint32_t tstride = gridDim.x * a.wt;
     const uint32_t tile0 = blockIdx.x * a.wt + wt;
@@ -130,7 +139,7 @@ __global__ void __launch_bounds__(512, 1) q6k_stream_kernel(const __grid_constan
             const bool full = iss_c < nfull;
             mbar_expect_tx(bar, 16u * kQ6Pad * (full ? a.cb : a.rem));
             tma_load_2d(ring + iss_st * a.stage_bytes, full ? &a.tmap : &a.tmap_rem, (b0 + iss_c * a.cb) * kQ6PadWords,
-                        iss_tile * 16u, bar);
+                        wrow0 + iss_tile * 16u, bar);
         }
         if (++iss_st == a.stages) iss_st = 0;
         if (++iss_c == nchunks) {
@@ -602,7 +611,9 @@ __global__ void __launch_bounds__(256, 1) q6k_stream_rows_kernel(const __grid_co
 cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int* status_dev, int sm_count, TmapCache* tmaps,
                               cudaStream_t stream, int* launches) {
     if (m.N == 0) return cudaSuccess;
-    if (m.M == 0 || m.M > 8 || m.n_slots) return cudaErrorInvalidValue;
+    if (m.M == 0 || m.M > 8) return cudaErrorInvalidValue;
+    const bool indirect = m.n_slots != 0;                // slots of one row each, blockIdx.y = slot
+    if (indirect && (m.M != 1 || m.n_peers || m.W2)) return cudaErrorInvalidValue;
     const bool rows = m.M > 1;                           // the several-row kernel
     const uint32_t tokens = rows ? (m.M + 3) / 4 * 4 : 1;
     const uint32_t nb = m.K / kQK;
@@ -611,7 +622,9 @@ cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int
 
     // plan: as the Q4_K kernel's single-row plan (small: everything in one round with K split over
     // the warps of a CTA; large: 8 warps, deeper rings)
-    const bool small = ntiles <= 640;
+    const uint64_t tiles_total = (uint64_t)ntiles * (indirect ? m.n_slots : 1);
+    const bool small = tiles_total <= 640;
+    const uint64_t rows_total = indirect ? m.w_total_rows : m.N;  // rows the tensor map may touch
     Q6Args qa{};
     uint32_t warps = 0, wk = 0, wt = 0, bpw = 0, cb = 0, rem = 0, stage_bytes = 0, stages = 0, smem = 0;
     auto plan = [&](uint32_t warps_want, uint32_t cb_want, uint32_t stages_want) -> bool {
@@ -621,7 +634,7 @@ cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int
         if (!wk) {
             if (small) {
                 wk = 1;
-                while (wk * 2 <= warps && nb % (wk * 2) == 0 && (uint64_t)ntiles * (wk * 2) <= (uint64_t)sm_count * warps) wk *= 2;
+                while (wk * 2 <= warps && nb % (wk * 2) == 0 && tiles_total * (wk * 2) <= (uint64_t)sm_count * warps) wk *= 2;
             } else {
                 wk = nb >= 64 ? 8 : nb >= 32 ? 4 : nb >= 16 ? 2 : 1;
             }
@@ -664,14 +677,14 @@ cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int
         const uint32_t key_nb = nb | 0x60000000u;  // keeps these entries apart from the Q4_K maps of the cache
         if (tmaps) {
             for (const auto& en : tmaps->entries)
-                if (en.W == m.W && en.rows == m.N && en.row_bytes == m.w_row_bytes && en.nb == key_nb && en.cb == width_blocks) {
+                if (en.W == m.W && en.rows == rows_total && en.row_bytes == m.w_row_bytes && en.nb == key_nb && en.cb == width_blocks) {
                     std::memcpy(out, en.map, sizeof(CUtensorMap));
                     return cudaSuccess;
                 }
         }
         EncodeTiledFn enc = encode_tiled_fn();
         if (!enc) return cudaErrorNotSupported;
-        const cuuint64_t gdim[2] = {(cuuint64_t)nb * kQ6PadWords, (cuuint64_t)m.N};
+        const cuuint64_t gdim[2] = {(cuuint64_t)nb * kQ6PadWords, (cuuint64_t)rows_total};
         const cuuint64_t gstride[1] = {(cuuint64_t)m.w_row_bytes};
         const cuuint32_t box[2] = {width_blocks * kQ6PadWords, 16u};
         const cuuint32_t estr[2] = {1u, 1u};
@@ -681,7 +694,7 @@ cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int
         if (res != CUDA_SUCCESS) return cudaErrorInvalidValue;
         if (tmaps) {
             auto& en = tmaps->entries[tmaps->next++ % TmapCache::kEntries];
-            en.W = m.W; en.rows = m.N; en.row_bytes = m.w_row_bytes; en.nb = key_nb; en.cb = width_blocks;
+            en.W = m.W; en.rows = rows_total; en.row_bytes = m.w_row_bytes; en.nb = key_nb; en.cb = width_blocks;
             std::memcpy(en.map, out, sizeof(CUtensorMap));
         }
         return cudaSuccess;
@@ -710,12 +723,19 @@ cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int
     // the whole machine would
     const uint32_t groups = (ntiles + wt - 1) / wt;
     uint32_t gx = groups;
-    if (gx > (uint32_t)sm_count) {
-        const uint32_t rounds = (groups + sm_count - 1) / sm_count;
-        gx = (groups + rounds - 1) / rounds;
+    const uint32_t slots_y = indirect ? m.n_slots : 1;
+    if (slots_y > 65535u) return cudaErrorInvalidValue;
+    {
+        // all slots' CTAs resident at once (never a partial second wave), each slot's tiles in balanced rounds
+        uint32_t cap_x = (uint32_t)sm_count / slots_y;
+        if (cap_x == 0) cap_x = 1;
+        if (gx > cap_x) {
+            const uint32_t rounds = (groups + cap_x - 1) / cap_x;
+            gx = (groups + rounds - 1) / rounds;
+        }
     }
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(gx);
+    cfg.gridDim = dim3(gx, slots_y);
     cfg.blockDim = dim3(warps * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;

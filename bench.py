@@ -32,6 +32,8 @@ launch streams its weights from HBM.
 ``kquant_siblings``   (1 GPU) the output head in Q5_K and Q6_K, M = 1.
 ``fused_prologues``   (1 GPU) launch time with and without a fused RMSNorm /
               silu*up prologue and residual epilogue.
+``routed_experts``    (1 GPU) configuration 3: one routed-expert layer (128 experts,
+              8 tokens x 8 experts), the matmuls alone and the whole step.
 ``gguf_upload``       (1 GPU) file -> HBM rate of the GGUF tensor loader.
 
 With N > 1 ranks every rank holds its own row shard of each projection (the
@@ -426,10 +428,11 @@ def run_gpu_arm(args, rank, world, local_rank):
     prefill = None
     if world == 1 and not args.no_prefill:
         prefill = measure_prefill(ctx, torch, shapes, W, dev)
-    siblings = fusions = gguf_up = None
+    siblings = fusions = gguf_up = experts = None
     if world == 1 and not args.no_siblings:
         siblings = measure_siblings(ctx, torch, dev)
         fusions = measure_fusions(ctx, torch, dev)
+        experts = measure_routed_experts(ctx, torch, dev)
         gguf_up = measure_gguf_upload(ctx)
 
     times = torch.tensor([ms, kernel_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
@@ -480,6 +483,8 @@ def run_gpu_arm(args, rank, world, local_rank):
             line["kquant_siblings"] = siblings
         if fusions is not None:
             line["fused_prologues"] = fusions
+        if experts is not None:
+            line["routed_experts"] = experts
         if gguf_up is not None:
             line["gguf_upload"] = gguf_up
         print(json.dumps(line), flush=True)
@@ -573,6 +578,79 @@ def measure_fusions(ctx, torch, dev):
         out["cases"][name] = row
         del Ws
         torch.cuda.empty_cache()
+    return out
+
+
+def measure_routed_experts(ctx, torch, dev):
+    """Configuration 3: 128 experts with gate/up [768, 2048] and down [2048, 768] stacks (113 MB each), 8 tokens
+    routed to 8 distinct experts each.  Times (a) the three expert-indexed matmuls alone and (b) the whole
+    routed-expert step (gate+up in one launch, down with the silu*up prologue, weighted accumulate) -- the
+    reference issues 6 dispatches per slot, 384 for this step.  Graph replay over three copies of the stacks and
+    six routings, so that a replayed step finds none of its experts in L2.  Algorithmic bytes count each distinct
+    expert touched once per matrix."""
+    import backpack_b200 as bp
+    from backpack_b200 import synth
+
+    peak, peak_src = load_peaks()
+    E, F, H, T, topk, ncopies = 128, 768, 2048, 8, 8, 3
+    stacks = []
+    for N, K, seed in ((E * F, H, 41), (E * F, H, 42), (E * H, F, 43)):
+        packed = bp.pack_q4k(synth.make_q4k_weights(N, K, seed), N, K)
+        stacks.append([ctx.upload(packed) for _ in range(ncopies)])
+    n = 2 * ncopies
+    routes = [synth.make_moe_routing(T, E, topk, 100 + i).reshape(-1) for i in range(n)]
+    ids = [torch.from_numpy(r.astype(np.int32)).to(dev) for r in routes]
+    offg = [torch.from_numpy((r * F).astype(np.int32)).to(dev) for r in routes]
+    offd = [torch.from_numpy((r * H).astype(np.int32)).to(dev) for r in routes]
+    gen = torch.Generator(device=dev).manual_seed(9)
+    x = torch.randn(T, H, device=dev, generator=gen) * 0.05
+    act = torch.randn(T * topk, F, device=dev, generator=gen)
+    rw = torch.softmax(torch.randn(T, topk, device=dev, generator=gen), dim=1).reshape(-1).contiguous()
+    x_rows = torch.arange(T, device=dev, dtype=torch.int32).repeat_interleave(topk)
+    yg, yu = torch.empty(T * topk, F, device=dev), torch.empty(T * topk, F, device=dev)
+    yd, y = torch.empty(T * topk, H, device=dev), torch.zeros(T, H, device=dev)
+    work = torch.empty(T * topk * (2 * F + H), device=dev)
+
+    def three_matmuls(i):
+        c, r = i % ncopies, i % n
+        ctx.matmul_moe(x, stacks[0][c], F, offg[r], x_rows=x_rows, out=yg)
+        ctx.matmul_moe(x, stacks[1][c], F, offg[r], x_rows=x_rows, out=yu)
+        ctx.matmul_moe(act, stacks[2][c], H, offd[r], out=yd)
+
+    def whole_step(i):
+        c = i % ncopies
+        ctx.moe_ffn(x, stacks[0][c], stacks[1][c], stacks[2][c], ids[i % n], rw, y, E, work=work)
+
+    distinct = float(np.mean([len(np.unique(r)) for r in routes]))
+    weight_bytes = distinct * 3 * synth.weight_bytes(F, H)
+    out = {"workload": "128 experts, gate/up 768 x 2048 and down 2048 x 768 (Q4_K), 8 tokens x 8 experts",
+           "distinct_experts_per_step": distinct, "weight_bytes_per_step": weight_bytes, "peak_gbs": peak,
+           "peak_source": peak_src, "reference_dispatches_per_step": 6 * T * topk}
+    for name, fn in (("three_matmuls", three_matmuls), ("whole_step", whole_step)):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        ctx.launch_count(reset=True)
+        fn(0)
+        launches = ctx.launch_count()
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(n):
+                    fn(i)
+            g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(5):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (5 * n)
+        gbs = weight_bytes / us / 1e3
+        out[name] = {"us_per_step": us, "launches_per_step": launches, "value": gbs, "unit": UNIT, "frac_of_hbm_peak": gbs / peak}
+    del stacks
+    torch.cuda.empty_cache()
     return out
 
 

@@ -75,9 +75,14 @@ typedef enum bpq4k_option {
     BPQ4K_OPT_STREAM_FORCE_SCRATCH = 15, /* 1: split activations into global scratch even if they fit on chip */
     /* The streaming kernel is launched with programmatic dependent launch: it prefetches
      * WEIGHTS while the preceding kernel of the stream drains, and reads X / writes Y only
-     * after that kernel has completed.  Set to 1 if a preceding kernel in the same stream
-     * writes the weight buffer itself. */
-    BPQ4K_OPT_STREAM_NO_PDL = 16
+     * after that kernel has completed.  The expert-indexed forms also read their slot tables
+     * (offsets / expert ids, x_rows) in that early phase.  A kernel that does not itself trigger
+     * dependent launches early is always complete before this one starts; set to 1 if a
+     * preceding kernel that does trigger early writes the weights or the slot tables. */
+    BPQ4K_OPT_STREAM_NO_PDL = 16,
+    /* 1: the expert-indexed form always runs one grid row per slot (default 0: one list of
+     * (slot, tile) units over a persistent 1-D grid whenever each CTA's share spans at most four slots). */
+    BPQ4K_OPT_STREAM_NO_UNIT_LIST = 17
 } bpq4k_option;
 
 typedef enum bpq4k_gemv_variant {
@@ -282,12 +287,13 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
                         float* Y, uint32_t M, uint32_t N, uint32_t K, uint32_t rowStrideWords,
                         uint32_t yOffset, void* stream);
 
-/* The routed-expert feed-forward step of one layer, for T tokens, in four launches.  The reference
+/* The routed-expert feed-forward step of one layer, for T tokens, in three launches (four when the
+ * shapes do not allow gate and up to share one).  The reference
  * issues six dispatches per routed slot -- gate, up, silu, mul, down, weighted accumulate
  * (runtime/model_runner.cpp:3584-3651; offsets from compute_offsets.wgsl:26-36; the accumulate step
  * is runtime/kernels/moe/weighted_accumulate_decode.wgsl).  For pair p = t*topk + k with expert
  * e = expert_ids[p]:
- *     g = X[t] . Wgate[e]^T,  u = X[t] . Wup[e]^T          two expert-indexed matmuls, F values each
+ *     g = X[t] . Wgate[e]^T,  u = X[t] . Wup[e]^T          expert-indexed matmuls, F values each
  *     o = (silu(g) * u) . Wdown[e]^T                        silu*up staged by the down matmul itself
  *     Y[t] = Y[t] + route_w[p] * o                          k ascending, as the reference accumulates
  * X and Y are [T][H] (Y is read and written: the caller leaves the residual stream or zeros there),
@@ -300,7 +306,8 @@ int bpq4k_moe_ffn_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W
                       const uint32_t* expert_ids, const float* route_w, float* Y, uint32_t T, uint32_t topk,
                       uint32_t nExperts, uint32_t H, uint32_t F, float* work, uint64_t work_floats, void* stream);
 
-/* bpq4k_matmul_moe_f32 with the weight type given: Q4_K or Q5_K expert stacks. */
+/* bpq4k_matmul_moe_f32 with the weight type given: Q4_K, Q5_K or padded Q6_K (BPQ4K_TYPE_Q6_K_PADDED,
+ * at most 65535 slots) expert stacks. */
 int bpq4k_kq_matmul_moe_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W, const float* bias, float* Y,
                             const uint32_t* offsets, const uint32_t* x_rows, uint32_t nSlots, uint32_t N, uint32_t K,
                             uint32_t rowStrideWords, uint32_t wRows, void* stream);

@@ -224,27 +224,40 @@ def test_siblings_many_rows_run_the_tensor_core_kernel(ctx, M, N, K, mode, tol, 
     assert ctx.device_status() == 0
 
 
-def test_q5k_expert_indexed_form(ctx):
-    """The indirect (expert-stacked) form on Q5_K weights: every slot multiplies its own activation row with
-    the rows of its expert, one launch for all slots."""
+@pytest.mark.parametrize("qtype", [orc.Q5_K, Q6_K_PADDED])
+@pytest.mark.parametrize("E,N,K,S", [(6, 48, 1024, 9), (3, 40, 256, 1), (16, 768, 2048, 64), (12, 16, 512, 200)])
+def test_expert_indexed_form_of_the_siblings(ctx, qtype, E, N, K, S):
+    """The indirect (expert-stacked) form on Q5_K and padded Q6_K weights: every slot multiplies its own activation
+    row with the rows of its expert, one launch for all slots."""
     import torch
 
-    E, N, K, S = 6, 48, 1024, 9
-    raw = synth.make_kq_weights(orc.Q5_K, E * N, K, 61)
+    ftype = file_type(qtype)
+    raw = synth.make_kq_weights(ftype, E * N, K, 61)
     x = synth.make_activations(4, K, 62)
     rng = np.random.default_rng(63)
     experts = rng.integers(0, E, S).astype(np.uint32)
     x_rows = rng.integers(0, 4, S).astype(np.uint32)
     bias = np.linspace(-1, 1, N).astype(np.float32)
-    w = ctx.upload(pack_kq(orc.Q5_K, raw, E * N, K))
+    w = ctx.upload(pack_kq(qtype, raw, E * N, K))
     ctx.launch_count(reset=True)
     y = ctx.matmul_moe(dev(torch, x), w, N, dev(torch, (experts * N).astype(np.int32)), x_rows=dev(torch, x_rows.astype(np.int32)),
                        bias=dev(torch, bias)).cpu().numpy()
     assert ctx.launch_count() == 1
     rawr = raw.reshape(E, N, -1)
-    for s in range(S):
-        want = orc.kq_matmul(orc.Q5_K, x[x_rows[s]:x_rows[s] + 1], rawr[experts[s]], bias, N, K)[0]
+    for s in range(min(S, 48)):
+        want = orc.kq_matmul(ftype, x[x_rows[s]:x_rows[s] + 1], rawr[experts[s]], bias, N, K)[0]
         check(y[s], want)
+    assert ctx.device_status() == 0
+
+
+def test_expert_indexed_form_rejects_unpadded_q6k(ctx):
+    import torch
+    from backpack_b200 import Q4KError
+
+    raw = synth.make_kq_weights(orc.Q6_K, 32, 256, 1)
+    w = ctx.upload(pack_kq(orc.Q6_K, raw, 32, 256))
+    with pytest.raises(Q4KError):
+        ctx.matmul_moe(dev(torch, synth.make_activations(1, 256, 2)), w, 16, dev(torch, np.zeros(1, np.int32)))
 
 
 @pytest.mark.parametrize("layout", [orc.Q6_K, Q6_K_PADDED])

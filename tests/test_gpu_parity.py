@@ -242,6 +242,7 @@ def test_prefill_threshold_option(ctx):
     x = synth.make_activations(M, K, 63)
     w = ctx.upload(pack_q4k(raw, N, K))
     want = orc.matmul(x, raw, None, N, K)
+    default_min_m = ctx.get_option(q4k.OPT_PREFILL_MIN_M)
     ctx.set_option(q4k.OPT_PREFILL_MIN_M, 65)
     ctx.launch_count(reset=True)
     y_stream = ctx.matmul(dev(torch, x), w).cpu().numpy()
@@ -249,6 +250,7 @@ def test_prefill_threshold_option(ctx):
     ctx.set_option(q4k.OPT_PREFILL_MIN_M, 64)
     y_tc = ctx.matmul(dev(torch, x), w).cpu().numpy()
     n_tc = ctx.launch_count()
+    ctx.set_option(q4k.OPT_PREFILL_MIN_M, default_min_m)
     # eight slabs of 8 rows (one launch each; two where the activations are quantised by a kernel of their own)
     # vs. cast + tensor-core launch (+ reduction)
     assert n_stream in (8, 16) and n_tc in (2, 3)
@@ -279,6 +281,41 @@ def test_moe_indirect(ctx, variant):
     check(y.cpu().numpy(), want.reshape(T * topk, N))
     want2 = orc.matmul_moe(xs, raw, None, N, K, offsets.astype(np.uint32))
     check(y2.cpu().numpy(), want2.reshape(T * topk, N))
+
+
+@pytest.mark.parametrize("E,N,K,slots", [(32, 16, 256, 700),      # one tile per expert, many slots: one grid row per slot
+                                         (5, 40, 768, 9),         # ragged last tile of every slot
+                                         (3, 16, 256, 1), (7, 48, 512, 2),
+                                         (16, 768, 2048, 64),     # the gate/up shape of benchmark configuration 3
+                                         (16, 2048, 768, 64),     # its down shape
+                                         (4, 4096, 1024, 5), (9, 272, 4096, 37), (64, 32, 512, 300),
+                                         (16, 768, 2048, 256),    # more slots than SMs: served as one unit list
+                                         (8, 512, 256, 200)])
+def test_moe_unit_list_shapes(ctx, E, N, K, slots):
+    """Slots are served as one list of (slot, tile) units when each CTA's share spans few slots, else as one grid row
+    per slot: both against the per-slot oracle, with repeated experts and a shuffled activation-row map."""
+    import torch
+
+    rng = np.random.default_rng(E * 1000 + slots)
+    raw = synth.make_q4k_weights(E * N, K, 31)
+    w = ctx.upload(pack_q4k(raw, E * N, K))
+    ids = rng.integers(0, E, slots)
+    offsets = (ids * N).astype(np.int32)
+    n_x = max(1, slots // 3)
+    x = synth.make_activations(n_x, K, 32)
+    x_rows = rng.integers(0, n_x, slots).astype(np.int32)
+    y = ctx.matmul_moe(dev(torch, x), w, N, dev(torch, offsets), dev(torch, x_rows)).cpu().numpy()
+    sample = np.arange(slots) if slots <= 64 else rng.choice(slots, 64, replace=False)
+    want = orc.matmul_moe(x[x_rows[sample]], raw, None, N, K, offsets[sample].astype(np.uint32)).reshape(len(sample), N)
+    check(y[sample], want)
+    assert ctx.device_status() == 0
+    # the other form of the launch walks the same tiles with the same arithmetic: identical bits
+    ctx.set_option(q4k.OPT_STREAM_NO_UNIT_LIST, 1)
+    try:
+        y_rows = ctx.matmul_moe(dev(torch, x), w, N, dev(torch, offsets), dev(torch, x_rows)).cpu().numpy()
+    finally:
+        ctx.set_option(q4k.OPT_STREAM_NO_UNIT_LIST, 0)
+    assert np.array_equal(y.view(np.uint32), y_rows.view(np.uint32))
 
 
 # ---------------------------------------------------------------- host entry point
