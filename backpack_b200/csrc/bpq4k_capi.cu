@@ -270,7 +270,7 @@ int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
             h->tune.no_pdl = value ? 1u : 0u;
             return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_NO_UNIT_LIST:
-            h->tune.no_unit_list = value ? 1u : 0u;
+            h->tune.no_unit_list = value == 2 ? 2u : value ? 1u : 0u;
             return BPQ4K_OK;
 #ifdef BPQ4K_ENABLE_PROBES
         case 99:

@@ -875,7 +875,8 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     // (single row, rows of at most four super-blocks: a tile is over so quickly that 16 warps are needed to keep
     //  copies in flight -- 2048x768 expert matrices, 64 slots: 13.1 us against 14.8 us with 8 warps)
     uint32_t warps_m1 = small ? 16 : 8;
-    if (!small && nb <= 4) {  // only where 16 two-stage rings of whole rows fit next to the staged row
+    // (not with more slots than SMs: those run as a unit list, whose CTAs stage several rows and need the room)
+    if (!small && nb <= 4 && !(indirect && m.n_slots > (uint32_t)sm_count)) {  // only where 16 two-stage rings of whole rows fit next to the staged row
         const uint32_t cbw = nb < (q5 ? 3u : 5u) ? nb : (q5 ? 3u : 5u);
         if (16u * 2u * 16u * cbw * block_bytes + m.K * 4u + 8192u <= kSmemMax) warps_m1 = 16;
     }
@@ -920,7 +921,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     const uint32_t n_mats = indirect && m.W2 ? 2u : 1u;
     if (m.W2 && !indirect) return cudaErrorInvalidValue;
     uint32_t flat_grid = 0, nloc_max = 1, u_base = 0, u_extra = 0;
-    if (indirect && !tune.force_scratch && !tune.no_unit_list) {
+    if (indirect && !tune.force_scratch && tune.no_unit_list != 1) {
         const uint64_t U = (uint64_t)m.n_slots * n_mats * ntiles;
         if (U <= 0x7FFFFFFFull) {
             const uint64_t groups_flat = (U + wt - 1) / wt;
@@ -933,7 +934,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
             // 2048x768 experts).  With more slots than SMs it needs several waves, each paying the prologue again,
             // and the unit list wins (256 slots: 39.8 against 41.9 us).  Two stacks always share one unit list.
             const bool several_waves = m.n_slots > (uint32_t)sm_count;
-            if (nl <= kMaxLocalSlots && (m.W2 || several_waves)) {
+            if (nl <= kMaxLocalSlots && (m.W2 || several_waves || tune.no_unit_list == 2)) {
                 flat_grid = G, nloc_max = nl;
                 u_base = (uint32_t)(U / G), u_extra = (uint32_t)(U % G);
             }

@@ -81,7 +81,8 @@ typedef enum bpq4k_option {
      * preceding kernel that does trigger early writes the weights or the slot tables. */
     BPQ4K_OPT_STREAM_NO_PDL = 16,
     /* 1: the expert-indexed form always runs one grid row per slot (default 0: one list of
-     * (slot, tile) units over a persistent 1-D grid whenever each CTA's share spans at most four slots). */
+     * (slot, tile) units over a persistent 1-D grid when there are more slots than SMs or two stacks share
+     * the launch, and each CTA's share spans at most four slots); 2: the unit list whenever it is possible. */
     BPQ4K_OPT_STREAM_NO_UNIT_LIST = 17
 } bpq4k_option;
 
