@@ -960,8 +960,15 @@ int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items
 
     // Host buffers the GPU can address (pinned memory) are gathered and scattered by one kernel each
     // instead of one asynchronous copy per vector; other host memory takes the copy path.
+    // Outputs of items the streaming kernel serves (every value stored exactly once, by the tile's
+    // epilogue) go straight to the pinned host buffer: the stores cross PCIe while the kernel still
+    // streams weights, and only the tensor-core items (split-K partial sums) are staged and scattered.
     CopySegments gin{}, gout{};
     bool direct = live <= CopySegments::kMax;
+    float* y_direct[CopySegments::kMax] = {};
+    auto stores_once = [&](const bpq4k_host_matmul& it) {
+        return !(h->gemv_variant == BPQ4K_GEMV_AUTO && it.M >= (uint32_t)h->prefill_min_m);
+    };
     {
         size_t xo = 0, yo = 0;
         for (uint32_t i = 0; i < count && direct; i++) {
@@ -974,12 +981,16 @@ int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items
                 direct = false;
                 break;
             }
+            if (stores_once(it)) {
+                y_direct[gin.count] = static_cast<float*>(ya);
+            } else {
+                gout.src[gout.count] = reinterpret_cast<uint8_t*>(h->stage_y) + yo;
+                gout.dst[gout.count] = ya;
+                gout.bytes[gout.count++] = (uint32_t)ybytes;
+            }
             gin.src[gin.count] = xa;
             gin.dst[gin.count] = reinterpret_cast<uint8_t*>(h->stage_x) + xo;
             gin.bytes[gin.count++] = (uint32_t)xbytes;
-            gout.src[gout.count] = reinterpret_cast<uint8_t*>(h->stage_y) + yo;
-            gout.dst[gout.count] = ya;
-            gout.bytes[gout.count++] = (uint32_t)ybytes;
             xo += (xbytes + 255u) & ~(size_t)255u;
             yo += (ybytes + 255u) & ~(size_t)255u;
         }
@@ -1003,6 +1014,7 @@ int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items
         }
         if (e != cudaSuccess) return cuda_fail(h, e, "activation upload");
         size_t xo = 0, yo = 0;
+        uint32_t li = 0;  // index among the live items
         for (uint32_t i = 0; i < count; i++) {
             const bpq4k_host_matmul& it = items[i];
             if (it.M == 0 || it.N == 0) continue;
@@ -1011,6 +1023,8 @@ int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items
             a.W = static_cast<const uint8_t*>(it.W_dev);
             a.bias = it.bias_dev;
             a.Y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(h->stage_y) + yo);
+            if (direct && y_direct[li]) a.Y = y_direct[li];
+            li++;
             a.M = it.M;
             a.N = it.N;
             a.K = it.K;
@@ -1020,8 +1034,10 @@ int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items
             yo += ((size_t)it.M * it.N * 4u + 255u) & ~(size_t)255u;
         }
         if (direct) {
-            e = launch_copy_segments(gout, s_);
-            h->launches += 1;
+            if (gout.count) {
+                e = launch_copy_segments(gout, s_);
+                h->launches += 1;
+            }
         } else {
             yo = 0;
             for (uint32_t i = 0; i < count && e == cudaSuccess; i++) {

@@ -9,6 +9,9 @@ namespace bpq4k {
 namespace {
 
 __global__ void __launch_bounds__(256) copy_segments_kernel(const __grid_constant__ CopySegments segs) {
+    // a streaming matmul launched behind this kernel may start prefetching its weights now; it reads
+    // the gathered activations only after this grid has completed
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t s = blockIdx.y;
     if (s >= segs.count) return;
     const uint4* __restrict__ src = static_cast<const uint4*>(segs.src[s]);

@@ -221,8 +221,10 @@ int bpq4k_peer_barrier(bpq4k_handle_t h, uint32_t* const* flag_ptrs, uint32_t nP
  * pre-recorded list of Dispatch structs replayed by one queue submit, one small write before
  * and one read-back after (runtime/gpu_context.h:36-44, runtime/model_runner.cpp:4839,
  * 5725-5764).  Entries are independent of each other (no entry reads another's output).
- * With pinned (GPU-addressable) host buffers one kernel gathers all inputs and one scatters all
- * outputs, and a list seen twice (same buffers, shapes and options) is replayed from a CUDA graph
+ * With pinned (GPU-addressable) host buffers one kernel gathers all inputs, the streaming kernel
+ * stores its outputs straight into the host buffers (they cross the bus while the kernel still
+ * streams weights; entries served by the tensor-core kernel are staged and scattered by one kernel),
+ * and a list seen twice (same buffers, shapes and options) is replayed from a CUDA graph
  * on a stream of the handle's, ordered after the work already queued on `stream`; other host
  * memory takes one copy per vector.  The call returns when the outputs are in host memory. */
 typedef struct bpq4k_host_matmul {
