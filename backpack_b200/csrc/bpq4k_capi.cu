@@ -15,6 +15,7 @@ struct bpq4k_context {
     int device = 0;
     int sm_count = 0;
     int cc_major = 0;
+    int clock_khz = 0;  // SM clock for cycle-counted time-outs; queried once (the query takes about a millisecond)
     char err[512] = "no error";
     int gemv_variant = BPQ4K_GEMV_AUTO;
     int prefill_mode = BPQ4K_PREFILL_F16X3;
@@ -907,9 +908,11 @@ int bpq4k_peer_barrier(bpq4k_handle_t h, uint32_t* const* flag_ptrs, uint32_t nP
     for (uint32_t p = 0; p < nPeers; p++)
         if (!flag_ptrs[p]) return fail(h, BPQ4K_ERR_INVALID_ARG, "flag_ptrs[%u] is null", p);
     DeviceGuard g(h->device);
-    int khz = 0;
-    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, h->device);
-    if (khz <= 0) khz = 1900000;
+    if (h->clock_khz <= 0) {
+        cudaDeviceGetAttribute(&h->clock_khz, cudaDevAttrClockRate, h->device);
+        if (h->clock_khz <= 0) h->clock_khz = 1900000;
+    }
+    const int khz = h->clock_khz;
     const uint64_t cycles = (uint64_t)(timeout_ms ? timeout_ms : 1000u) * (uint64_t)khz;
     const cudaError_t e = launch_peer_barrier(flag_ptrs, nPeers, rank, epoch, cycles, h->dev_status, static_cast<cudaStream_t>(stream));
     h->launches += 1;

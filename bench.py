@@ -251,9 +251,17 @@ def run_gpu_arm(args, rank, world, local_rank):
     if world > 1 and args.gather == "peer":
         # fused all-gather: the matmul epilogue stores every slice into all ranks' gather buffers
         pg = sharded.PeerGather(ctx, world, rank, {name: (1, N) for name, N, _ in shapes})
+    # all activation vectors in one device buffer (64-float aligned views), so that the end-to-end pass of the
+    # multi-rank run can bring them up with one copy
+    x_off, x_total = {}, 0
+    for name, _, K in shapes:
+        x_off[name] = x_total
+        x_total += (K + 63) // 64 * 64
+    X_all = torch.zeros(x_total, dtype=torch.float32, device=dev)
     for name, N, K in shapes:
         W[name] = ctx.upload(bp.pack_q4k(weights_h[name], N, K))
-        X[name] = torch.from_numpy(xs_h[name]).to(dev)
+        X[name] = X_all[x_off[name]: x_off[name] + K].view(1, K)
+        X[name].copy_(torch.from_numpy(xs_h[name]))
         if world > 1:
             # weak scaling: this rank's shard has the single-GPU shape, the global matrix has world*N rows
             Yall[name] = torch.zeros((world, 1, N), dtype=torch.float32, device=dev)
@@ -354,21 +362,29 @@ def run_gpu_arm(args, rank, world, local_rank):
 
             def e2e_pass():
                 ctx.matmul_host_batch(batch)
+        elif pg is not None and graph is not None:
+            # one copy up (all activation vectors), the recorded step (matmuls storing into every rank's gather
+            # buffer + flag barrier), one copy down (the whole gather buffer), then a second barrier: no rank may
+            # start storing the next step's slices into a buffer that its owner is still reading back
+            x_all_pin = torch.zeros(x_total, dtype=torch.float32).pin_memory()
+            for name, _, K in shapes:
+                x_all_pin[x_off[name]: x_off[name] + K] = xs_pin[name].view(-1)
+            y_all_pin = torch.zeros(pg.buf.numel(), dtype=torch.float32).pin_memory()
+
+            def e2e_pass():
+                X_all.copy_(x_all_pin, non_blocking=True)
+                graph.replay()
+                y_all_pin.copy_(pg.buf, non_blocking=True)
+                pg.barrier()
+                torch.cuda.current_stream().synchronize()
         else:
             yall_pin = {n: torch.zeros(world * N, dtype=torch.float32).pin_memory() for n, N, _ in shapes}
 
             def e2e_pass():
                 for name, N, K in shapes:
                     X[name].copy_(xs_pin[name], non_blocking=True)
-                    if pg is not None:
-                        pg.matmul(name, X[name], W[name])
-                    else:
-                        lin[name].forward(X[name], Yall[name])
-                        yall_pin[name].copy_(Yall[name].view(-1), non_blocking=True)
-                if pg is not None:
-                    pg.barrier()
-                    for name, N, K in shapes:
-                        yall_pin[name].copy_(pg.gathered(name).reshape(-1), non_blocking=True)
+                    lin[name].forward(X[name], Yall[name])
+                    yall_pin[name].copy_(Yall[name].view(-1), non_blocking=True)
                 torch.cuda.current_stream().synchronize()
 
         for _ in range(3):
@@ -450,7 +466,7 @@ def run_gpu_arm(args, rank, world, local_rank):
         achieved = per_launch_bytes / per_launch_s / 1e9
         cpu, _ = cpu_baseline(args.cpu_budget, shapes, weights_h, xs_h)
         h2d = sum(K * 4 for _, _, K in shapes)
-        d2h = sum(N * 4 for _, N, _ in shapes)
+        d2h = world * sum(N * 4 for _, N, _ in shapes)     # every rank reads back the gathered outputs of all ranks
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
