@@ -41,6 +41,11 @@ struct bpq4k_context {
     cudaGraphExec_t batch_exec = nullptr;
     cudaStream_t batch_stream = nullptr;
     cudaEvent_t batch_event = nullptr;
+    uint32_t batch_records = 0;  // how many times a list was captured into a graph (BPQ4K_OPT_BATCH_RECORDS)
+    // device blocks that were outgrown; freed at destroy (see ensure_bytes)
+    static constexpr uint32_t kMaxRetired = 48;
+    void* retired[kMaxRetired] = {};
+    uint32_t n_retired = 0;
 };
 
 namespace {
@@ -88,18 +93,46 @@ int check_weights(bpq4k_context* h, const void* W, uint32_t N, uint32_t K, uint3
     return BPQ4K_OK;
 }
 
+// Forget the recorded dispatch list of the host-batch call (its graph holds raw buffer addresses).
+void drop_batch_graph(bpq4k_context* h) {
+    if (h->batch_exec) cudaGraphExecDestroy(h->batch_exec);
+    h->batch_exec = nullptr;
+    h->batch_key = 0;
+    h->batch_seen = 0;
+}
+
+// Grow one of the handle's device buffers.  The old block is NOT freed here: a CUDA graph (the
+// handle's own replay graph of the host-batch call, or one the caller captured around a matmul
+// that uses the scratch) may still hold its address, and a replay would then touch freed memory.
+// Old blocks are retired and freed at bpq4k_destroy; sizes at least double, so the retired blocks
+// together stay below the live one.  The handle's own replay graph is dropped and re-recorded.
 int ensure_bytes(bpq4k_context* h, void** p, size_t* have, size_t need) {
     if (*have >= need) return BPQ4K_OK;
-    if (*p) cudaFree(*p);
-    *p = nullptr;
-    *have = 0;
     size_t want = need < (1u << 20) ? (1u << 20) : need;
-    cudaError_t e = cudaMalloc(p, want);
+    if (want < 2 * *have) want = 2 * *have;
+    void* fresh = nullptr;
+    cudaError_t e = cudaMalloc(&fresh, want);
+    if (e != cudaSuccess && want > need) {
+        cudaGetLastError();
+        want = need;
+        e = cudaMalloc(&fresh, want);
+    }
     if (e != cudaSuccess) {
         cudaGetLastError();
         return fail(h, BPQ4K_ERR_ALLOC, "cudaMalloc(%zu) failed: %s", want, cudaGetErrorString(e));
     }
+    if (*p) {
+        if (h->n_retired < bpq4k_context::kMaxRetired) {
+            h->retired[h->n_retired++] = *p;
+        } else {
+            // cannot happen with doubling sizes (48 doublings exceed any device); wait for all work, then free
+            cudaDeviceSynchronize();
+            cudaFree(*p);
+        }
+    }
+    *p = fresh;
     *have = want;
+    drop_batch_graph(h);
     return BPQ4K_OK;
 }
 
@@ -215,6 +248,7 @@ int bpq4k_destroy(bpq4k_handle_t h) {
         if (h->stage_y) cudaFree(h->stage_y);
         if (h->scratch) cudaFree(h->scratch);
         if (h->dev_status) cudaFree(h->dev_status);
+        for (uint32_t i = 0; i < h->n_retired; i++) cudaFree(h->retired[i]);
         if (h->batch_exec) cudaGraphExecDestroy(h->batch_exec);
         if (h->batch_stream) cudaStreamDestroy(h->batch_stream);
         if (h->batch_event) cudaEventDestroy(h->batch_event);
@@ -273,11 +307,6 @@ int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
         case BPQ4K_OPT_STREAM_NO_UNIT_LIST:
             h->tune.no_unit_list = value == 2 ? 2u : value ? 1u : 0u;
             return BPQ4K_OK;
-#ifdef BPQ4K_ENABLE_PROBES
-        case 99:
-            h->tune.probe = (uint32_t)value;
-            return BPQ4K_OK;
-#endif
         default: return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown option %d", option);
     }
 }
@@ -296,6 +325,7 @@ int bpq4k_get_option(bpq4k_handle_t h, int option, int* value) {
         case BPQ4K_OPT_STREAM_FORCE_SCRATCH: *value = (int)h->tune.force_scratch; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_NO_PDL: *value = (int)h->tune.no_pdl; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_NO_UNIT_LIST: *value = (int)h->tune.no_unit_list; return BPQ4K_OK;
+        case BPQ4K_OPT_BATCH_RECORDS: *value = (int)h->batch_records; return BPQ4K_OK;
         default: return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown option %d", option);
     }
 }
@@ -1062,6 +1092,8 @@ int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items
     key = fnv1a(key, &h->tune, sizeof(h->tune));
     const int opts[3] = {h->gemv_variant, h->prefill_mode, h->prefill_min_m};
     key = fnv1a(key, opts, sizeof(opts));
+    const void* bufs[3] = {h->stage_x, h->stage_y, h->scratch};  // the graph holds these addresses
+    key = fnv1a(key, bufs, sizeof(bufs));
     if (direct && h->batch_key == key && h->batch_seen >= 1) {
         cudaError_t e = cudaSuccess;
         if (!h->batch_stream) e = cudaStreamCreateWithFlags(&h->batch_stream, cudaStreamNonBlocking);
@@ -1076,6 +1108,7 @@ int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items
                 e = s != BPQ4K_OK ? cudaErrorUnknown : e2;
             }
             if (e == cudaSuccess) e = cudaGraphInstantiate(&h->batch_exec, graph, 0);
+            if (e == cudaSuccess) h->batch_records++;
             if (graph) cudaGraphDestroy(graph);
             h->batch_launches = h->launches - before;
             h->launches = before;  // nothing ran yet

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 namespace bpq4k {
 
 // One matmul problem as the kernels see it.  Rows of W are `w_row_bytes`
@@ -56,7 +58,48 @@ struct StreamTuning {
     uint32_t force_scratch = 0;  // 1: always split activations into global scratch first
     uint32_t no_pdl = 0;       // 1: launch without programmatic dependent launch
     uint32_t no_unit_list = 0; // 1: indirect form always as one grid row per slot
-    uint32_t probe = 0;        // development builds only: time-attribution variants of the kernel
+};
+
+// Launch configuration of ONE kernel instantiation per device: the opt-in dynamic shared-memory size
+// (a per-device function attribute) and the occupancy of the last (threads, smem) pair asked for.
+// The launchers keep one of these in a function-local static per instantiation; handles on different
+// devices and threads share it, hence the mutex and the per-device slots.
+struct KernelConfig {
+    static constexpr int kMaxDevices = 64;
+    struct Entry {
+        size_t smem_cfg = 0;
+        uint32_t threads = 0;
+        size_t smem = 0;
+        int occ = 0;
+    };
+    std::mutex mu;
+    Entry per_dev[kMaxDevices];
+
+    // Make `func` launchable with `smem` bytes of dynamic shared memory on the current device and, when
+    // occ_out is given, report how many CTAs of `threads` threads fit one SM.
+    cudaError_t prepare(const void* func, uint32_t threads, size_t smem, int* occ_out) {
+        int dev = 0;
+        if (cudaError_t e = cudaGetDevice(&dev)) return e;
+        if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> lock(mu);
+        Entry& en = per_dev[dev];
+        if (smem > en.smem_cfg) {
+            if (cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) return e;
+            en.smem_cfg = smem;
+            en.threads = 0;
+        }
+        if (occ_out) {
+            if (en.threads != threads || en.smem != smem) {
+                int occ = 0;
+                if (cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, func, (int)threads, smem)) return e;
+                en.threads = threads;
+                en.smem = smem;
+                en.occ = occ > 0 ? occ : 1;
+            }
+            *occ_out = en.occ;
+        }
+        return cudaSuccess;
+    }
 };
 
 // Encoded tensor maps of recently used weight matrices (encoding one costs ~15 us of host time;

@@ -166,9 +166,6 @@ __device__ __forceinline__ void merge_fifth_bit(uint32_t codes, uint32_t qh, uin
     odd = ((codes >> 4) & kLo) | (bo & kBit);
 }
 
-// PROBE (development builds only, -DBPQ4K_ENABLE_PROBES): 0 = the kernel; 1 = copies and waits
-// only; 2 = math on whatever the ring holds, no copies; 3 = as 2 without the mmas; 4 = as 2
-// without the nibble decode; 5 = as 2 without the scale decode.  Used to attribute time.
 // Q5: the weights are Q5_K super-blocks (176 bytes: the Q4_K header, 32 bytes of fifth bits, 128
 // nibble bytes); the fifth bit is merged into each code byte, so odd sub-blocks reach the mma as
 // q (not 16*q) and carry no 1/16 in their scale.
@@ -184,10 +181,10 @@ __device__ __forceinline__ void merge_fifth_bit(uint32_t codes, uint32_t qh, uin
 // shape, activations and offsets: the gate and up stacks of an expert layer) the list simply continues
 // over it, results to m.Y2.
 constexpr uint32_t kMaxLocalSlots = 4;
-template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false>
+template <int NT, bool M1, bool XG, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false>
 __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
     static_assert(!FP || (M1 && !XG && !XC), "the fused forms are single-row and stage the row themselves");
-    static_assert(!IND || (M1 && !XG && !XC && PROBE == 0), "the unit-list form is single-row and stages its rows itself");
+    static_assert(!IND || (M1 && !XG && !XC), "the unit-list form is single-row and stages its rows itself");
     static_assert(!(XG && XC), "digits are read from the scratch directly (XG) or copied into shared memory (XC)");
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr uint32_t BB = Q5 ? 176u : kBlockBytes, BW = BB / 4u;  // bytes and words per super-block
@@ -295,7 +292,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
             }
         }
     };
-    if constexpr (PROBE < 2) {
+    {
         const uint32_t pre = min(a.stages, total_units);
         for (uint32_t i = 0; i < pre; i++) issue_next();
     }
@@ -525,7 +522,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
             const uint32_t pitch = nblk * BB;
             const uint32_t lm_off = lm_row * pitch + lm_col, hdr_off = row_a * pitch;
             const uint32_t bar = bar0 + st * 8u;
-            if (PROBE < 2 && !failed) {
+            if (!failed) {
                 uint32_t polls = 0;
                 while (!mbar_try_wait(bar, ph)) {
                     if (++polls > kWaitPolls) {  // give up: flag it, keep the barriers matched
@@ -536,18 +533,13 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                 }
             }
             uint32_t boff = ring + st * a.stage_bytes;
-            for (uint32_t blk = bs; PROBE != 1 && blk < bs + nblk; blk++, boff += BB) {
+            for (uint32_t blk = bs; blk < bs + nblk; blk++, boff += BB) {
                 if constexpr (M1) {
                 // scales of this thread's rows, its parity's four sub-blocks; the odd sub-block's
                 // weights reach the mma as 16*q, so its scale carries the 1/16
                 float dsc[1][4], dmn[1][4];
 #pragma unroll
                 for (int r = 0; r < 1; r++) {
-                    if constexpr (PROBE == 5) {
-#pragma unroll
-                        for (int g = 0; g < 4; g++) dsc[r][g] = 1.f, dmn[r][g] = 2.f;
-                        continue;
-                    }
                     const uint4 hv = lds128<0>(boff + hdr_off + r * 8u * pitch);
                     const BlockHeader h{hv.x, hv.y, hv.z, hv.w};
                     const float d = half_bits_to_float(h.w0) * par_scale, dmin = half_bits_to_float(h.w0 >> 16);
@@ -583,9 +575,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                     ldmatrix_x4<g * 32>(lm_addr, r0, r1, r2, r3);
                     [[maybe_unused]] constexpr uint32_t kLo = 0x0F0F0F0Fu, kHi = 0xF0F0F0F0u;
                     uint32_t e[4], o[4];
-                    if constexpr (PROBE == 4) {
-                        e[0] = o[0] = r0; e[1] = o[1] = r1; e[2] = o[2] = r2; e[3] = o[3] = r3;
-                    } else if constexpr (Q5) {
+                    if constexpr (Q5) {
                         const uint32_t rr[4] = {r0, r1, r2, r3};
 #pragma unroll
                         for (int i = 0; i < 4; i++) merge_fifth_bit<g>(rr[i], qh[i], e[i], o[i]);
@@ -598,16 +588,10 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                         const uint4 qa = load16(pa, std::integral_constant<int, g * 256>{});
                         const uint4 qb = load16(pb, std::integral_constant<int, g * 256>{});
                         int c01[4], c2[4];  // column pair = digits (d0, d1) resp. (d2, 0)
-                        if constexpr (PROBE == 3) {
-                            c01[0] = e[0] ^ o[1] ^ qa.x ^ qb.y; c01[1] = e[1] ^ o[2] ^ qa.y ^ qb.z;
-                            c01[2] = e[2] ^ o[3] ^ qa.z ^ qb.w; c01[3] = e[3] ^ o[0] ^ qa.w ^ qb.x;
-                            c2[0] = c01[1]; c2[2] = c01[3];
-                        } else {
-                            imma16832_first(c01, e[0], e[1], e[2], e[3], qa.x, qa.y);
-                            imma16832_first(c2, e[0], e[1], e[2], e[3], qa.z, qa.w);
-                            imma16832(c01, o[0], o[1], o[2], o[3], qb.x, qb.y);
-                            imma16832(c2, o[0], o[1], o[2], o[3], qb.z, qb.w);
-                        }
+                        imma16832_first(c01, e[0], e[1], e[2], e[3], qa.x, qa.y);
+                        imma16832_first(c2, e[0], e[1], e[2], e[3], qa.z, qa.w);
+                        imma16832(c01, o[0], o[1], o[2], o[3], qb.x, qb.y);
+                        imma16832(c2, o[0], o[1], o[2], o[3], qb.z, qb.w);
                         const uint32_t sbits = g == 0 ? Sv[nt].x : g == 1 ? Sv[nt].y : g == 2 ? Sv[nt].z : Sv[nt].w;
                         const float Sg = __uint_as_float(sbits);
                         const float Ig = __uint_as_float(g == 0 ? Iv[nt].x : g == 1 ? Iv[nt].y : g == 2 ? Iv[nt].z : Iv[nt].w);
@@ -711,7 +695,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
             // the stage is free: refill it with the unit `stages` ahead
             __syncwarp();
             fence_proxy_async();
-            if (PROBE < 2 && u + a.stages < total_units) issue_next();
+            if (u + a.stages < total_units) issue_next();
             u++;
             if (++st == a.stages) {
                 st = 0;
@@ -780,31 +764,14 @@ __global__ void __launch_bounds__(256) quantize_activations_kernel(const float* 
 
 // Launch one instantiation.  The grid is persistent: at most as many CTAs as can be
 // resident at once (occupancy query, cached), never more than there are tile groups.
-template <int NT, bool M1, bool XG, int PROBE = 0, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false>
+template <int NT, bool M1, bool XG, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false>
 cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, uint32_t threads, size_t smem,
                        int sm_count, uint32_t ctas_per_sm_override, bool pdl, cudaStream_t stream, uint32_t flat_grid = 0) {
-    struct Cache { int dev = -1; size_t smem_cfg = 0; uint32_t threads = 0; size_t smem = 0; int occ = 0; };
-    static Cache cache;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cache.dev != dev) cache = Cache{};
-    cache.dev = dev;
-    if (smem > cache.smem_cfg) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC, FP, IND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
-        if (e != cudaSuccess) return e;
-        cache.smem_cfg = smem;
-        cache.threads = 0;
-    }
-    if (cache.threads != threads || cache.smem != smem) {
-        int occ = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC, FP, IND>, (int)threads, smem);
-        if (e != cudaSuccess) return e;
-        cache.threads = threads;
-        cache.smem = smem;
-        cache.occ = occ > 0 ? occ : 1;
-    }
-    uint32_t per_sm = (uint32_t)cache.occ;
+    static KernelConfig kcfg;  // per instantiation; per-device slots and a mutex inside
+    int occ = 1;
+    if (cudaError_t e = kcfg.prepare(reinterpret_cast<const void*>(gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND>), threads, smem, &occ))
+        return e;
+    uint32_t per_sm = (uint32_t)occ;
     if (ctas_per_sm_override && ctas_per_sm_override < per_sm) per_sm = ctas_per_sm_override;
     // Every CTA walks ceil(groups/gx) tile groups.  Pick the smallest grid that needs no more
     // rounds than the full machine would, so that all CTAs carry (almost) the same load:
@@ -830,7 +797,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, PROBE, Q5, XC, FP, IND>, sa);
+    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND>, sa);
 }
 
 static_assert(sizeof(CUtensorMap) == 128, "TmapCache::Entry::map must hold a CUtensorMap");
@@ -1067,11 +1034,11 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         const uint32_t threads = warps * 32;
         const bool pdl = !tune.no_pdl;
         if (fused)
-            e = q5 ? launch_one<1, true, false, 0, true, false, true, true>(sa, groups, 1, threads, smem, sm_count, 1, pdl, stream, flat_grid)
-                   : launch_one<1, true, false, 0, false, false, true, true>(sa, groups, 1, threads, smem, sm_count, 1, pdl, stream, flat_grid);
+            e = q5 ? launch_one<1, true, false, true, false, true, true>(sa, groups, 1, threads, smem, sm_count, 1, pdl, stream, flat_grid)
+                   : launch_one<1, true, false, false, false, true, true>(sa, groups, 1, threads, smem, sm_count, 1, pdl, stream, flat_grid);
         else
-            e = q5 ? launch_one<1, true, false, 0, true, false, false, true>(sa, groups, 1, threads, smem, sm_count, 1, pdl, stream, flat_grid)
-                   : launch_one<1, true, false, 0, false, false, false, true>(sa, groups, 1, threads, smem, sm_count, 1, pdl, stream, flat_grid);
+            e = q5 ? launch_one<1, true, false, true, false, false, true>(sa, groups, 1, threads, smem, sm_count, 1, pdl, stream, flat_grid)
+                   : launch_one<1, true, false, false, false, false, true>(sa, groups, 1, threads, smem, sm_count, 1, pdl, stream, flat_grid);
         if (launches) ++*launches;
         return e;
     }
@@ -1085,34 +1052,14 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
             sa.m.Y = base.Y + (uint64_t)s0 * m.N;
         }
         const uint32_t threads = warps * 32;
-#define BPQ4K_LAUNCH(NT_, M1_, XG_)                                                                                          \
-    (q5 ? launch_one<NT_, M1_, XG_, 0, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream) \
-        : launch_one<NT_, M1_, XG_, 0, false>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream))
-#ifdef BPQ4K_ENABLE_PROBES
-#define BPQ4K_PROBE(P_) launch_one<1, true, false, P_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream)
-        if (m1 && !xg && !q5 && tune.probe) {
-            switch (tune.probe) {
-                case 1: e = BPQ4K_PROBE(1); break;
-                case 2: e = BPQ4K_PROBE(2); break;
-                case 3: e = BPQ4K_PROBE(3); break;
-                case 4: e = BPQ4K_PROBE(4); break;
-                default: e = BPQ4K_PROBE(5); break;
-            }
-        } else
-#undef BPQ4K_PROBE
-#endif
-        if (m1 && fused)
-            e = q5 ? launch_one<1, true, false, 0, true, false, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream)
-                   : launch_one<1, true, false, 0, false, false, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream);
-        else if (m1) e = xg ? BPQ4K_LAUNCH(1, true, true) : BPQ4K_LAUNCH(1, true, false);
-        else if (NT == 1) e = xg ? BPQ4K_LAUNCH(1, false, true) : BPQ4K_LAUNCH(1, false, false);
-        else if (xc && NT == 1)
-            e = q5 ? launch_one<1, false, false, 0, true, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream)
-                   : launch_one<1, false, false, 0, false, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream);
-        else if (xc)
-            e = q5 ? launch_one<2, false, false, 0, true, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream)
-                   : launch_one<2, false, false, 0, false, true>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream);
-        else e = xg ? BPQ4K_LAUNCH(2, false, true) : BPQ4K_LAUNCH(2, false, false);
+#define BPQ4K_LAUNCH(NT_, M1_, XG_, XC_, FP_)                                                                          \
+    (q5 ? launch_one<NT_, M1_, XG_, true, XC_, FP_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream) \
+        : launch_one<NT_, M1_, XG_, false, XC_, FP_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream))
+        if (m1 && fused) e = BPQ4K_LAUNCH(1, true, false, false, true);
+        else if (m1) e = xg ? BPQ4K_LAUNCH(1, true, true, false, false) : BPQ4K_LAUNCH(1, true, false, false, false);
+        else if (xc) e = NT == 1 ? BPQ4K_LAUNCH(1, false, false, true, false) : BPQ4K_LAUNCH(2, false, false, true, false);
+        else if (NT == 1) e = xg ? BPQ4K_LAUNCH(1, false, true, false, false) : BPQ4K_LAUNCH(1, false, false, false, false);
+        else e = xg ? BPQ4K_LAUNCH(2, false, true, false, false) : BPQ4K_LAUNCH(2, false, false, false, false);
 #undef BPQ4K_LAUNCH
         if (launches) ++*launches;
         if (e != cudaSuccess) return e;

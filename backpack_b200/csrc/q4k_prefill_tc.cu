@@ -614,15 +614,10 @@ EncodeTiledFn encode_fn() {
 template <int ROWS, int PASSES, bool BF16, int QT = 0>
 cudaError_t launch_tc(const PrefillArgs& pa, cudaStream_t stream) {
     using P = Plan<ROWS, PASSES>;
-    static int configured_dev = -1;  // the attribute is per device
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (configured_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<ROWS, PASSES, BF16, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)P::SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-        configured_dev = dev;
-    }
+    static KernelConfig kcfg;  // per-device slots inside
+    if (cudaError_t e = kcfg.prepare(reinterpret_cast<const void*>(prefill_tc_kernel<ROWS, PASSES, BF16, QT>), P::THREADS,
+                                     P::SMEM_BYTES, nullptr))
+        return e;
     const dim3 grid((pa.N + ROWS - 1) / ROWS, (pa.M + kTokTile - 1) / kTokTile, pa.ksplit);
     prefill_tc_kernel<ROWS, PASSES, BF16, QT><<<grid, P::THREADS, P::SMEM_BYTES, stream>>>(pa);
     return cudaGetLastError();

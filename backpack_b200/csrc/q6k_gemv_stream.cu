@@ -706,18 +706,13 @@ cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int
         qa.tmap_rem = qa.tmap;
     }
 
-    static size_t smem_cfg[3] = {0, 0, 0};
-    static int cfg_dev = -1;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cfg_dev != dev) smem_cfg[0] = smem_cfg[1] = smem_cfg[2] = 0, cfg_dev = dev;
+    static KernelConfig kcfg[3];  // one per kernel variant; per-device slots inside
     const int variant = !rows ? 0 : tokens == 4 ? 1 : 2;
-    if (smem > smem_cfg[variant]) {
-        const cudaError_t e = variant == 0 ? cudaFuncSetAttribute(q6k_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                            : variant == 1 ? cudaFuncSetAttribute(q6k_stream_rows_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                                           : cudaFuncSetAttribute(q6k_stream_rows_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        smem_cfg[variant] = smem;
+    {
+        const void* fn = variant == 0 ? reinterpret_cast<const void*>(q6k_stream_kernel)
+                       : variant == 1 ? reinterpret_cast<const void*>(q6k_stream_rows_kernel<1>)
+                                      : reinterpret_cast<const void*>(q6k_stream_rows_kernel<2>);
+        if (cudaError_t e = kcfg[variant].prepare(fn, warps * 32, smem, nullptr)) return e;
     }
     // persistent grid, one CTA per SM, balanced: the smallest grid that needs no more rounds than
     // the whole machine would

@@ -11,7 +11,10 @@
  *  - Plain C: pointers, sizes, an opaque handle.  No C++ or framework types.
  *  - Unless a name ends in `_host`, every data pointer is a DEVICE pointer on
  *    the handle's device, owned by the caller.  The library owns only the
- *    scratch memory inside the handle.
+ *    scratch memory inside the handle.  That scratch grows on demand (a call with a
+ *    larger M*K than any before); an outgrown block stays allocated until
+ *    bpq4k_destroy, so a CUDA graph the caller captured around an earlier call keeps
+ *    pointing at valid memory.
  *  - `stream` is a cudaStream_t / CUstream passed as void*; NULL is the
  *    default stream.  Calls are asynchronous with respect to the host and
  *    ordered on that stream, like dispatches on the reference's single WebGPU
@@ -83,7 +86,11 @@ typedef enum bpq4k_option {
     /* 1: the expert-indexed form always runs one grid row per slot (default 0: one list of
      * (slot, tile) units over a persistent 1-D grid when there are more slots than SMs or two stacks share
      * the launch, and each CTA's share spans at most four slots); 2: the unit list whenever it is possible. */
-    BPQ4K_OPT_STREAM_NO_UNIT_LIST = 17
+    BPQ4K_OPT_STREAM_NO_UNIT_LIST = 17,
+    /* Read-only (bpq4k_get_option): how many times bpq4k_matmul_host_batch_f32 has recorded a dispatch
+     * list into a replay graph on this handle.  A list is recorded again after any of the handle's
+     * buffers had to grow. */
+    BPQ4K_OPT_BATCH_RECORDS = 30
 } bpq4k_option;
 
 typedef enum bpq4k_gemv_variant {

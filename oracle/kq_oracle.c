@@ -18,8 +18,10 @@
  * stored under tests/golden/.
  *
  * One function at the end, oracle_prologue (the element-wise step of the reference's
- * fused decode shaders), is UNPINNED: the reference has neither a test nor a caller for
- * those shaders, so there is nothing of the reference's to check it against.
+ * fused decode shaders), is UNPINNED: it follows the reference's CPU formulas refSilu
+ * (runtime/tests/kernel_test.cpp:165-166) and refRMSNorm (runtime/tests/op_test.cpp:684-693),
+ * but those are file-static functions of test programs that cannot be built without the
+ * reference's GPU backend, and the fused shaders have neither a test nor a caller.
  *
  * Type numbers are the reference's GGUFType values (runtime/gguf_loader.h:27-30):
  * Q4_K = 12, Q5_K = 13, Q6_K = 14.
@@ -206,23 +208,31 @@ void oracle_kq_matmul(uint32_t type, const float *X, const void *raw, const floa
 }
 
 /* The element-wise step the reference's fused decode shaders apply to the activation row before
- * the matmul, in binary32:
- *   kind 1  out = x * rstd * aux,  rstd = 1/sqrt(sum(x^2)/K + eps)
- *           (runtime/kernels/quant_kq/q4k_matmul_norm.wgsl:47-92; the shader adds the squares in
- *           256 strided partial sums and a tree, this restatement adds them in index order --
- *           the two differ by float rounding of the sum only)
+ * the matmul, in binary32.  Where the reference holds a CPU formula for the step, that formula's
+ * order of operations is followed:
+ *   kind 1  rms = sqrtf(sum(x^2)/K + eps), out = x / rms * aux
+ *           -- refRMSNorm of runtime/tests/op_test.cpp:684-693 (division by rms, then the weight:
+ *           one more rounding than x * rstd * aux); the shader form is
+ *           runtime/kernels/quant_kq/q4k_matmul_norm.wgsl:47-92, which adds the squares in 256
+ *           strided partial sums and a tree where refRMSNorm (and this code) add in index order.
  *   kind 2  out = 0.5*g*(1 + tanh(0.7978845608*(g + 0.044715*g*g*g))) * aux
- *           (runtime/kernels/quant_kq/q4k_down_gelu.wgsl:54-59)
- *   kind 3  out = g/(1 + exp(-g)) * aux   (silu_mul_fused ahead of the down projection,
- *           runtime/model_runner.cpp:3755-3766)
- * Parity of this function is UNPINNED: the reference has no test or caller for these shaders. */
+ *           -- the tanh form of runtime/kernels/quant_kq/q4k_down_gelu.wgsl:54-59.  The
+ *           reference's CPU formula is the erf form (refGelu, runtime/tests/kernel_test.cpp:167),
+ *           and its own test widens the tolerance to 5e-4 because the shaders use tanh
+ *           (kernel_test.cpp:382-384); the shader's form is the one restated here.
+ *   kind 3  out = g * (1/(1 + expf(-g))) * aux
+ *           -- refSilu = x * refSigmoid(x) of runtime/tests/kernel_test.cpp:165-166, then the
+ *           multiply of silu_mul_fused ahead of the down projection (runtime/model_runner.cpp:3755-3766).
+ * Parity of this function is UNPINNED: refSilu and refRMSNorm are file-static functions of test
+ * programs that need the Dawn GPU backend to build, so they cannot be compiled and run here, and
+ * the reference has no test or caller for the fused shaders themselves. */
 void oracle_prologue(uint32_t kind, const float *x, const float *aux, float eps, uint32_t K, float *out)
 {
     if (kind == 1u) {
         float ss = 0.0f;
         for (uint32_t k = 0; k < K; k++) ss += x[k] * x[k];
-        const float rstd = 1.0f / sqrtf(ss / (float)K + eps);
-        for (uint32_t k = 0; k < K; k++) out[k] = x[k] * rstd * aux[k];
+        const float rms = sqrtf(ss / (float)K + eps);
+        for (uint32_t k = 0; k < K; k++) out[k] = x[k] / rms * aux[k];
     } else if (kind == 2u) {
         for (uint32_t k = 0; k < K; k++) {
             const float g = x[k];
@@ -230,7 +240,10 @@ void oracle_prologue(uint32_t kind, const float *x, const float *aux, float eps,
             out[k] = 0.5f * g * (1.0f + tanhf(inner)) * aux[k];
         }
     } else if (kind == 3u) {
-        for (uint32_t k = 0; k < K; k++) out[k] = x[k] / (1.0f + expf(-x[k])) * aux[k];
+        for (uint32_t k = 0; k < K; k++) {
+            const float sig = 1.0f / (1.0f + expf(-x[k]));
+            out[k] = x[k] * sig * aux[k];
+        }
     } else {
         memcpy(out, x, (size_t)K * sizeof(float));
     }

@@ -34,9 +34,10 @@ _fp = C.POINTER(C.c_float)
 
 
 def build(ref_root: str | None = None) -> None:
-    """Compile the restatement, and the reference shim when its tree is present."""
+    """Compile the restatement, and the reference shim when the reference tree can be found: `ref_root`,
+    else the BPQ4K_REFERENCE_ROOT environment variable, else a directory `reference` beside this repository."""
     subprocess.run(["make", "-s", "-C", HERE], check=True)
-    ref_root = ref_root or os.environ.get("BPQ4K_REFERENCE_ROOT", "/root/reference")
+    ref_root = ref_root or os.environ.get("BPQ4K_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
     if os.path.isfile(os.path.join(ref_root, "runtime", "gguf_loader.cpp")):
         subprocess.run(["make", "-s", "-C", HERE, "ref", f"REF={ref_root}"], check=True)
 

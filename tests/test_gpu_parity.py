@@ -392,6 +392,65 @@ def test_matmul_host_batch_pinned_buffers_replay(ctx):
     assert ctx.device_status() == 0
 
 
+def test_host_batch_replay_graph_is_rerecorded_after_a_buffer_grows():
+    """The replay graph of a dispatch list holds the addresses of the handle's staging and scratch buffers.  A larger
+    call through another entry point makes those buffers grow; the list must then be recorded again (never replayed
+    against the outgrown blocks), and results stay right throughout."""
+    import torch
+
+    import backpack_b200 as bp
+
+    c = bp.Q4KContext(0)
+    try:
+        shapes = [(1, 300, 1024), (4, 64, 8192), (1, 1024, 4096)]
+        items, raws = [], []
+        for i, (M, N, K) in enumerate(shapes):
+            raw = synth.make_q4k_weights(N, K, 240 + i)
+            x = torch.from_numpy(synth.make_activations(M, K, 250 + i)).pin_memory()
+            y = torch.full((M, N), float("nan"), dtype=torch.float32).pin_memory()
+            items.append((x.numpy(), c.upload(pack_q4k(raw, N, K)), y.numpy(), None))
+            raws.append((raw, x, y))
+        batch = c.make_host_batch(items)
+
+        def run_and_check():
+            for it in items:
+                it[2][...] = np.nan
+            c.matmul_host_batch(batch)
+            for (xh, w, yh, _), (raw, _, _), (M, N, K) in zip(items, raws, shapes):
+                check(yh, orc.matmul(xh, raw, None, N, K))
+
+        for _ in range(3):
+            run_and_check()
+        assert c.get_option(q4k.OPT_BATCH_RECORDS) == 1
+        # a call whose activations (32 MB) and outputs outgrow the staging buffers
+        N2, K2, M2 = 64, 4096, 2048
+        raw2 = synth.make_q4k_weights(N2, K2, 260)
+        x2 = synth.make_activations(M2, K2, 261)
+        y2 = np.zeros((M2, N2), np.float32)
+        c.matmul_host(x2, c.upload(pack_q4k(raw2, N2, K2)), y2)
+        check(y2, orc.matmul(x2, raw2, None, N2, K2, threads=8))
+        for _ in range(3):
+            run_and_check()
+        assert c.get_option(q4k.OPT_BATCH_RECORDS) == 2
+        assert c.device_status() == 0
+    finally:
+        c.close()
+
+
+def test_four_rows_of_long_k_quantise_once_and_copy_in(ctx):
+    """2..4 rows with 32K or more staged values: one quantising launch, then the matmul copies the digits in."""
+    import torch
+
+    N, K, M = 1000, 8192, 4
+    raw = synth.make_q4k_weights(N, K, 270)
+    x = synth.make_activations(M, K, 271)
+    w = ctx.upload(pack_q4k(raw, N, K))
+    ctx.launch_count(reset=True)
+    y = ctx.matmul(dev(torch, x), w).cpu().numpy()
+    assert ctx.launch_count() == 2
+    check(y, orc.matmul(x, raw, None, N, K, threads=4))
+
+
 # ---------------------------------------------------------------- error behaviour
 
 def test_errors_are_statuses_not_faults(ctx):

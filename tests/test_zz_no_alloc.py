@@ -5,7 +5,9 @@ process whose own pool already owns all free HBM, or a decode loop that cannot t
 device-wide stall of cudaMalloc/cudaFree.  For them the library keeps a fixed scratch array
 on the device and offers one entry point that uses it and takes no handle.  This test calls
 that entry point through the C ABI twice in a row (the second call finds the first call's
-leftovers in the shared scratch) and compares each result with the regular entry point's.
+leftovers in the shared scratch) and compares each result with the regular entry point's and
+with the CPU checker's, and checks the property the entry point exists for: the free device
+memory is the same before and after a call.
 
 The file name sorts last on purpose: if this test fails, a run that stops at the first
 failure has already run every other test.
@@ -16,6 +18,7 @@ import numpy as np
 import pytest
 
 from backpack_b200 import _lib, pack_q4k, synth
+from oracle import q4k_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
@@ -31,30 +34,66 @@ def _noalloc(lib, x, w, bias, y, M, N, K, stride, y_offset=0):
                                         torch.cuda.current_stream().cuda_stream)
 
 
-def test_noalloc_matches_regular_entry_point_twice_in_a_row():
+def _close(a, b):
+    assert np.isfinite(a).all()
+    assert np.linalg.norm(a.astype(np.float64) - b) / np.linalg.norm(b.astype(np.float64)) <= REL_L2_TOL
+    assert np.abs(a - b).max() <= MAX_ABS_TOL
+
+
+def _run_cases(device: int):
     import torch
 
     import backpack_b200 as bp
 
     lib = _lib.load()
-    ctx = bp.Q4KContext(0)          # only for the regular entry point we compare against
-    torch.cuda.set_device(0)
-    # two different problems back to back: the second must not be disturbed by what the first left behind
+    ctx = bp.Q4KContext(device)          # only for the regular entry point we compare against
+    torch.cuda.set_device(device)
+    dev = f"cuda:{device}"
+    # different problems back to back: each must not be disturbed by what the one before left behind
     for (M, N, K, seed) in [(8, 600, 4096, 1), (1, 1000, 14336, 2), (3, 130, 512, 3), (8, 600, 4096, 4)]:
         raw = synth.make_q4k_weights(N, K, seed)
-        packed = pack_q4k(raw, N, K)
-        w = ctx.upload(packed)
-        x = torch.from_numpy(synth.make_activations(M, K, seed + 10)).cuda()
-        bias = torch.linspace(-1, 1, N, device="cuda")
-        want = ctx.matmul(x, w, bias)
-        got = torch.full((M, N), float("nan"), device="cuda")
+        w = ctx.upload(pack_q4k(raw, N, K))
+        x_host = synth.make_activations(M, K, seed + 10)
+        x = torch.from_numpy(x_host).to(dev)
+        bias_host = np.linspace(-1, 1, N).astype(np.float32)
+        bias = torch.from_numpy(bias_host).to(dev)
+        want = ctx.matmul(x, w, bias).cpu().numpy()
+        want_cpu = orc.matmul(x_host, raw, bias_host, N, K)
+        got = torch.full((M, N), float("nan"), device=dev)
+        # first call of this shape: may load the kernel's module (the driver loads code lazily)
         st = _noalloc(lib, x, w.buf, bias, got, M, N, K, w.rowStrideWords)
         assert st == 0, lib.bpq4k_noalloc_last_error().decode()
         torch.cuda.synchronize()
-        a, b = got.cpu().numpy(), want.cpu().numpy()
-        assert np.isfinite(a).all()
-        assert np.linalg.norm(a - b) / np.linalg.norm(b) <= REL_L2_TOL
-        assert np.abs(a - b).max() <= MAX_ABS_TOL
+        _close(got.cpu().numpy(), want)
+        _close(got.cpu().numpy(), want_cpu)
+        # second call in a row: same result, and the device's free memory does not move across it
+        got.fill_(float("nan"))
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info(device)
+        st = _noalloc(lib, x, w.buf, bias, got, M, N, K, w.rowStrideWords)
+        assert st == 0, lib.bpq4k_noalloc_last_error().decode()
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info(device)
+        assert free_after == free_before, (free_before, free_after)
+        _close(got.cpu().numpy(), want)
+        _close(got.cpu().numpy(), want_cpu)
+    ctx.close()
+
+
+def test_noalloc_matches_regular_entry_point_twice_in_a_row():
+    _run_cases(0)
+
+
+def test_noalloc_on_a_second_device_when_there_is_one():
+    """The scratch array's address is looked up once per device, with that device current."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("one GPU visible")
+    try:
+        _run_cases(1)
+    finally:
+        torch.cuda.set_device(0)
 
 
 def test_noalloc_rejects_sizes_beyond_its_scratch_and_bad_arguments():
