@@ -48,6 +48,7 @@ class HostMatmul(C.Structure):
 SIGNATURES["bpq4k_matmul_noalloc_f32"] = (C.c_int, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp])
 SIGNATURES["bpq4k_noalloc_last_error"] = (C.c_char_p, [])
 SIGNATURES["bpq4k_matmul_allgather_f32"] = (C.c_int, [vp, vp, vp, vp, C.POINTER(vp), u32, u32, u32, u32, u32, vp])
+SIGNATURES["bpq4k_peer_double_buffer"] = (C.c_int, [vp, vp, u64])
 SIGNATURES["bpq4k_peer_barrier"] = (C.c_int, [vp, C.POINTER(vp), u32, u32, u32, u32, vp])
 SIGNATURES["bpq4k_matmul_host_batch_f32"] = (C.c_int, [vp, C.POINTER(HostMatmul), u32, vp])
 

@@ -41,6 +41,9 @@ struct bpq4k_context {
     cudaGraphExec_t batch_exec = nullptr;
     cudaStream_t batch_stream = nullptr;
     cudaEvent_t batch_event = nullptr;
+    // double-buffered gather slots of the fused all-gather (bpq4k_peer_double_buffer)
+    const uint32_t* peer_parity = nullptr;
+    uint64_t peer_parity_stride = 0;
     uint32_t batch_records = 0;  // how many times a list was captured into a graph (BPQ4K_OPT_BATCH_RECORDS)
     // device blocks that were outgrown; freed at destroy (see ensure_bytes)
     static constexpr uint32_t kMaxRetired = 48;
@@ -863,6 +866,8 @@ int bpq4k_matmul_allgather_f32(bpq4k_handle_t h, const float* X, const void* W, 
     a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
     a.n_peers = nPeers - 1;
     for (uint32_t p = 1; p < nPeers; p++) a.peer_Y[p - 1] = slot_ptrs[p];
+    a.slot_parity = h->peer_parity;
+    a.slot_parity_stride = h->peer_parity_stride;
     const size_t need = gemv_stream_scratch_bytes(M, K);
     if (need > h->scratch_bytes) {
         if (int s = ensure_bytes(h, &h->scratch, &h->scratch_bytes, need)) return s;
@@ -907,6 +912,8 @@ int bpq4k_kq_matmul_allgather_f32(bpq4k_handle_t h, int qtype, const float* X, c
     a.w_row_bytes = (uint64_t)rowStrideWords * 4u;
     a.n_peers = nPeers - 1;
     for (uint32_t p = 1; p < nPeers; p++) a.peer_Y[p - 1] = slot_ptrs[p];
+    a.slot_parity = h->peer_parity;
+    a.slot_parity_stride = h->peer_parity_stride;
     int launches = 0;
     cudaError_t e;
     if (qtype == BPQ4K_TYPE_Q5_K) {
@@ -928,6 +935,14 @@ int bpq4k_kq_matmul_allgather_f32(bpq4k_handle_t h, int qtype, const float* X, c
         cudaGetLastError();
         return cuda_fail(h, e, "matmul launch");
     }
+    return BPQ4K_OK;
+}
+
+int bpq4k_peer_double_buffer(bpq4k_handle_t h, const uint32_t* step_word, uint64_t stride_floats) {
+    if (!h) return BPQ4K_ERR_INVALID_ARG;
+    if (step_word && (reinterpret_cast<uintptr_t>(step_word) & 3u)) return fail(h, BPQ4K_ERR_MISALIGNED, "step_word is not 4-byte aligned");
+    h->peer_parity = step_word;
+    h->peer_parity_stride = step_word ? stride_floats : 0;
     return BPQ4K_OK;
 }
 

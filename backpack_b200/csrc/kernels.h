@@ -32,6 +32,11 @@ struct MatmulArgs {
     // fused all-gather: every output is also stored to these buffers (other GPUs' memory, plain stores)
     float* peer_Y[8];
     uint32_t n_peers;
+    // fused all-gather, double-buffered slots: when slot_parity is set, Y and every peer_Y are advanced by
+    // (*slot_parity & 1) * slot_parity_stride floats (read after the dependency wait; the word is the step count
+    // that the peer barrier keeps in this GPU's own flag array)
+    const uint32_t* slot_parity;
+    uint64_t slot_parity_stride;
     // fused prologue on the activation row (single row only) and residual epilogue:
     //   1: x = X * rsqrt(mean(X^2) + eps) * aux      (aux = RMSNorm weight[K])
     //   2: x = gelu_tanh(X) * aux,  3: x = silu(X) * aux   (aux = the "up" vector[K])
@@ -135,7 +140,7 @@ cudaError_t launch_prefill_tc(const MatmulArgs& a, int mode, void* scratch, size
 // `rank` of every peer's flag array, then wait -- at most timeout_cycles -- until every slot of the
 // own array has reached `epoch`.  On a time-out the kernel stores kDeviceTimeout to *status.
 cudaError_t launch_peer_barrier(uint32_t* const* flag_ptrs_host, uint32_t n_peers, uint32_t rank, uint32_t epoch,
-                                uint64_t timeout_cycles, int* status_dev, cudaStream_t stream);
+                                uint64_t timeout_cycles, int* status_dev, cudaStream_t stream, bool pdl = true);
 
 // Index of the largest of n floats (lowest index on ties; 0 when nothing exceeds -1e30) into *result.
 // `scratch`: 16 zeroed, 8-byte aligned device bytes that the kernel leaves zeroed.

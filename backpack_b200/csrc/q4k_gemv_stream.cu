@@ -487,6 +487,9 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
     };
 
     float* part = reinterpret_cast<float*>(smem + a.off_part);
+    // double-buffered gather slots: which half this step writes (the word was last written by the barrier
+    // kernel that closed the previous step, which precedes this kernel in the stream)
+    const uint64_t par_off = a.m.slot_parity ? (uint64_t)(*reinterpret_cast<const volatile uint32_t*>(a.m.slot_parity) & 1u) * a.m.slot_parity_stride : 0ull;
     uint32_t st = 0, ph = 0, u = 0, failed = 0;
     [[maybe_unused]] uint32_t cur_l = 0, cur_tl = 0;
     if constexpr (IND) {
@@ -730,9 +733,9 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                     for (uint32_t k2 = 0; k2 < a.wk; k2++) s += gbuf[(uint64_t)k2 * (TOK * 16u) + idx];
                     float yv = s + (a.m.bias ? a.m.bias[row] : 0.f);
                     if (FP) yv += res_pre;
-                    Y[(uint64_t)tok * N + row] = yv;
+                    Y[(uint64_t)tok * N + row + par_off] = yv;
                     // fused all-gather: the same value goes straight into every peer's gather buffer
-                    for (uint32_t p = 0; p < a.m.n_peers; p++) a.m.peer_Y[p][(uint64_t)tok * N + row] = yv;
+                    for (uint32_t p = 0; p < a.m.n_peers; p++) a.m.peer_Y[p][(uint64_t)tok * N + row + par_off] = yv;
                 }
             }
         }

@@ -322,8 +322,10 @@ __global__ void __launch_bounds__(512, 1) q6k_stream_kernel(const __grid_constan
                 float s = 0.f;
                 for (uint32_t k2 = 0; k2 < a.wk; k2++) s += pbuf[k2 * 16u + lane];
                 const float yv = s + (a.m.bias ? a.m.bias[row] : 0.f);
-                Y[row] = yv;
-                for (uint32_t p = 0; p < a.m.n_peers; p++) a.m.peer_Y[p][row] = yv;
+                // double-buffered gather slots: the half this step writes (see MatmulArgs::slot_parity)
+                const uint64_t par_off = a.m.slot_parity ? (uint64_t)(*reinterpret_cast<const volatile uint32_t*>(a.m.slot_parity) & 1u) * a.m.slot_parity_stride : 0ull;
+                Y[row + par_off] = yv;
+                for (uint32_t p = 0; p < a.m.n_peers; p++) a.m.peer_Y[p][row + par_off] = yv;
             }
         }
     }

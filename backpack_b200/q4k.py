@@ -345,6 +345,10 @@ class Q4KContext:
                 self.h, w.qtype, x.data_ptr(), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
                 slot_ptrs, len(slot_ptrs), M, w.N, K, w.rowStrideWords, self._stream()))
 
+    def peer_double_buffer(self, step_word_ptr: int, stride_floats: int) -> None:
+        """Fused all-gather calls that follow store to the half (step & 1) of double-buffered slots (0: off)."""
+        self._check(self.lib.bpq4k_peer_double_buffer(self.h, step_word_ptr or None, stride_floats))
+
     def peer_barrier(self, flag_ptrs, rank: int, epoch: int, timeout_ms: int = 1000) -> None:
         """Bounded cross-GPU barrier on this stream (bpq4k_peer_barrier)."""
         self._check(self.lib.bpq4k_peer_barrier(self.h, flag_ptrs, len(flag_ptrs), rank, epoch, timeout_ms,

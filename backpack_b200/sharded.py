@@ -107,13 +107,18 @@ def make_cuda_linear(ctx, raw: np.ndarray, N: int, K: int, world: int, rank: int
 class PeerGather:
     """Fused all-gather over peer-mapped memory for a set of projections.
 
-    One symmetric allocation per rank holds, for every projection, the gather buffer
-    [world][M][Ns]; the matmul kernel of rank g stores its slice into slot g of EVERY rank's
-    buffer (plain stores over NVLink), and one bounded flag barrier per step makes the slices
-    visible.  Replaces the per-projection NCCL all-gather of `ShardedQ4KLinear.forward`.
+    One symmetric allocation per rank holds, for every projection, the gather buffer [world][M][Ns] -- twice
+    (`double_buffer`, the default): the matmul kernel of rank g stores its slice into slot g of EVERY rank's
+    buffer (plain stores over NVLink), steps alternate between the two halves, and ONE bounded flag barrier per
+    step makes the slices visible.  With two halves a rank that runs ahead stores the next step's slices into the
+    half nobody reads; a rank that has passed barrier t+1 knows that every peer queued its reads of step t ahead
+    of that barrier, so step t+2 may overwrite step t's half.  With `double_buffer=False` there is one half and a
+    consumer that reads the buffer must put a second barrier after its reads.
+    Replaces the per-projection NCCL all-gather of `ShardedQ4KLinear.forward`.
     """
 
-    def __init__(self, ctx, world: int, rank: int, slots: dict, group=None, timeout_ms: int = 1000):
+    def __init__(self, ctx, world: int, rank: int, slots: dict, group=None, timeout_ms: int = 1000,
+                 double_buffer: bool = True):
         import ctypes as C
 
         import torch
@@ -128,7 +133,9 @@ class PeerGather:
             self.offsets[name] = (total, M, Ns)
             total += world * M * Ns
             total = (total + 63) // 64 * 64
-        self.buf = symm.empty(max(total, 64), dtype=torch.float32, device=dev)
+        self.half = max(total, 64)
+        self.halves = 2 if double_buffer else 1
+        self.buf = symm.empty(self.half * self.halves, dtype=torch.float32, device=dev)
         self.flags = symm.empty(64, dtype=torch.int32, device=dev)
         self.buf.zero_()
         self.flags.zero_()
@@ -143,17 +150,30 @@ class PeerGather:
             self.slot_ptrs[name] = arr
         self.flag_ptrs = (C.c_void_p * world)(*[int(hf.buffer_ptrs[p]) for p in range(world)])
         self._handles = (hb, hf)
-        self.epoch = 0
+        self.steps = 0                     # barriers enqueued so far (every rank enqueues the same ones)
+        # word 63 of the own flag array is the step counter the barrier kernel keeps
+        ctx.peer_double_buffer(int(hf.buffer_ptrs[rank]) + 63 * 4 if double_buffer else 0, self.half)
 
-    def gathered(self, name: str):
-        """[world, M, Ns] view of this rank's gather buffer for one projection."""
+    def close(self) -> None:
+        self.ctx.peer_double_buffer(0, 0)
+
+    def gathered(self, name: str, step: int | None = None):
+        """[world, M, Ns] view of this rank's gather buffer for one projection: the slices of step `step`
+        (0-based count of barriers; default: the last one enqueued)."""
         off, M, Ns = self.offsets[name]
-        return self.buf[off: off + self.world * M * Ns].view(self.world, M, Ns)
+        step = self.steps - 1 if step is None else step
+        base = (step % self.halves) * self.half if self.halves == 2 else 0
+        return self.buf[base + off: base + off + self.world * M * Ns].view(self.world, M, Ns)
 
     def matmul(self, name: str, x, shard, bias=None) -> None:
         self.ctx.matmul_allgather(x, shard, self.slot_ptrs[name], bias)
 
-    def barrier(self) -> None:
+    def barrier(self, replays: int = 1) -> None:
         """Epoch 0 = self-advancing (the count lives in the flag array), so this call can be captured
-        into a CUDA graph and replayed."""
+        into a CUDA graph and replayed.  `note_replays` keeps the host-side step count right for replays."""
         self.ctx.peer_barrier(self.flag_ptrs, self.rank, 0, self.timeout_ms)
+        self.steps += 1
+
+    def note_replays(self, n: int = 1) -> None:
+        """A CUDA graph holding one step (matmuls + barrier) was replayed n times."""
+        self.steps += n

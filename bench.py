@@ -157,7 +157,8 @@ def cpu_pass(kind_ref: bool, threads: int, shapes, weights, xs):
 
 
 def cpu_baseline(budget_s: float, shapes, weights, xs):
-    """Time the reference's CPU path on a bounded sample: whole passes over `shapes`."""
+    """Time the reference's CPU path on a bounded sample: whole passes over `shapes`, row-parallel over all
+    host cores, and one pass on a single thread (the reference itself runs this code single-threaded)."""
     from oracle import q4k_oracle as orc
 
     kind_ref = orc.ref_available()
@@ -169,9 +170,12 @@ def cpu_baseline(budget_s: float, shapes, weights, xs):
         spent += dt
         reps += 1
     nbytes = sum(synth.algorithmic_bytes(1, N, K) for _, N, K in shapes)
+    single = cpu_pass(kind_ref, 1, shapes, weights, xs)
     return {"value": nbytes / best / 1e9, "unit": UNIT, "cores": cores,
             "kind": "reference" if kind_ref else "port",
-            "sample": f"{reps} passes over {len(shapes)} projections ({nbytes / 1e6:.0f} MB each), best pass"}, best
+            "sample": f"{reps} passes over {len(shapes)} projections ({nbytes / 1e6:.0f} MB each), best pass",
+            "single_thread": {"value": nbytes / single / 1e9, "unit": UNIT, "cores": 1,
+                              "sample": "one pass over the same projections on one thread, as the reference runs it"}}
 
 
 def make_host_inputs(shapes, config_tag, rank=0):
@@ -225,6 +229,81 @@ def run_reference_arm(args, rank):
 # --------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------
+def timed_groups(torch, dist, stream, run_step, steps, groups, world, dev, after_step=None):
+    """`groups` back-to-back groups of exactly `steps` steps, each group between two CUDA events on `stream`.
+    Several ranks: a host barrier, then one untimed step (its flag barrier, or its collectives, line the
+    devices up), then the groups; every group's time is the maximum over ranks.  Returns the per-group
+    milliseconds (max over ranks)."""
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    run_step()
+    if after_step:
+        after_step(1)
+    evs = []
+    for _ in range(groups):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            run_step()
+        e1.record(stream)
+        evs.append((e0, e1))
+    stream.synchronize()
+    if after_step:
+        after_step(steps * groups)
+    ms = torch.tensor([a.elapsed_time(b) for a, b in evs], dtype=torch.float64, device=dev)
+    if dist:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.barrier()
+    torch.cuda.synchronize()
+    return [float(v) for v in ms.cpu()]
+
+
+def wall_groups(torch, dist, run_step, steps, groups, dev):
+    """Host-clock version for the end-to-end passes (each pass ends with its own wait): per-group seconds,
+    maximum over ranks."""
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    run_step()
+    out = []
+    for _ in range(groups):
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            run_step()
+        out.append(time.perf_counter() - t0)
+    t = torch.tensor(out, dtype=torch.float64, device=dev)
+    if dist:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+    return [float(v) for v in t.cpu()]
+
+
+def check_all_slots(torch, dist, rank, world, dev, names, dims, xs_h, weights_h, slices_of, M=1):
+    """Before timing: every rank computes the expected values of ITS OWN slice with the CPU checker, the
+    expectations are all-gathered, and every rank compares EVERY slot of its gather buffer (its own slice
+    and the ones that arrived from the peers) with them."""
+    from oracle import q4k_oracle as orc
+
+    worst_rel, worst_abs, n = 0.0, 0.0, 0
+    for name in names:
+        N, K = dims[name]
+        want_own = torch.from_numpy(orc.matmul(xs_h[name], weights_h[name], None, N, K, threads=4)).to(dev)
+        if world > 1:
+            want = torch.empty((world,) + tuple(want_own.shape), dtype=torch.float32, device=dev)
+            dist.all_gather_into_tensor(want.view(-1), want_own.reshape(-1))
+        else:
+            want = want_own.unsqueeze(0)
+        got = slices_of(name).reshape(want.shape)
+        for p in range(world):
+            rel = float((got[p] - want[p]).norm() / want[p].norm())
+            mx = float((got[p] - want[p]).abs().max())
+            assert rel <= 1e-3 and mx <= 2e-2, f"parity check failed before timing: {name} slot {p} on rank {rank}: rel_l2={rel} max_abs={mx}"
+            worst_rel, worst_abs, n = max(worst_rel, rel), max(worst_abs, mx), n + 1
+    return {"slots_checked_per_rank": n, "projections": list(names), "worst_rel_l2": worst_rel, "worst_max_abs": worst_abs,
+            "against": "CPU checker, every rank's slice (expected values all-gathered)"}
+
+
 def run_gpu_arm(args, rank, world, local_rank):
     import torch
 
@@ -236,16 +315,21 @@ def run_gpu_arm(args, rank, world, local_rank):
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    # the clock sampler starts NVML here, long before any timed region (its start-up takes milliseconds
+    # and differs between ranks)
+    sampler = ClockSampler(local_rank)
     ctx = bp.Q4KContext(local_rank)
     if args.no_pdl:
         from backpack_b200 import q4k as _q4k
 
         ctx.set_option(_q4k.OPT_STREAM_NO_PDL, 1)
     shapes = synth.LLAMA3_8B
+    dims = {n: (N, K) for n, N, K in shapes}
     weights_h, xs_h = make_host_inputs(shapes, "config1", rank)
     dev = f"cuda:{local_rank}"
     from backpack_b200 import sharded
 
+    steps, groups = max(args.steps, 1), max(args.groups, 1)
     W, X, Y, Yall, lin = {}, {}, {}, {}, {}
     pg = None
     if world > 1 and args.gather == "peer":
@@ -265,12 +349,10 @@ def run_gpu_arm(args, rank, world, local_rank):
         if world > 1:
             # weak scaling: this rank's shard has the single-GPU shape, the global matrix has world*N rows
             Yall[name] = torch.zeros((world, 1, N), dtype=torch.float32, device=dev)
-            Y[name] = Yall[name][rank]                          # the rank's slice, written in place
             lin[name] = sharded.ShardedQ4KLinear(
                 world * N, K, world, rank, W[name],
                 lambda x, shard, out=None: ctx.matmul(x, shard, out=out))
-        else:
-            Y[name] = torch.zeros(1, N, dtype=torch.float32, device=dev)
+        Y[name] = torch.zeros(1, N, dtype=torch.float32, device=dev)
 
     def one_pass():
         for name, N, K in shapes:
@@ -283,51 +365,45 @@ def run_gpu_arm(args, rank, world, local_rank):
         if pg is not None:
             pg.barrier()                                        # one bounded flag barrier per step
 
-    # correctness spot-check before timing (one projection against the CPU checker)
-    from oracle import q4k_oracle as orc
-
+    # correctness before timing: every slot of the gathered k and lm_head outputs (on one GPU: those two outputs)
     one_pass()
     torch.cuda.synchronize()
-    want = orc.matmul(xs_h["k"], weights_h["k"], None, 1024, 4096)
-    got = (pg.gathered("k")[rank] if pg is not None else Y["k"]).reshape(1, -1).cpu().numpy()
-    rel = float(np.linalg.norm(got - want) / np.linalg.norm(want))
-    assert rel < 1e-3, f"parity check failed before timing: rel_l2={rel}"
+    parity = check_all_slots(
+        torch, dist, rank, world, dev, ("k", "lm_head"), dims, xs_h, weights_h,
+        (lambda n: pg.gathered(n)) if pg is not None else (lambda n: Yall[n]) if world > 1 else (lambda n: Y[n]))
+    assert ctx.device_status() == 0
 
     # ---- resident (graph-replayed) timing --------------------------------
     stream = torch.cuda.Stream()
     graph = None
+    sampler.start()
     with torch.cuda.stream(stream):
         for _ in range(3):
             one_pass()
         stream.synchronize()
         if world == 1 or args.graph_multi or pg is not None:
             graph = torch.cuda.CUDAGraph()
+            steps_before = pg.steps if pg is not None else 0
             with torch.cuda.graph(graph, stream=stream):
                 one_pass()
-        # (with several ranks the step is timed as eager launches unless --graph-multi is given:
-        # capturing the NCCL all-gathers together with the dependent-launch kernels into one graph
-        # did not complete on this pool)
+            if pg is not None:
+                pg.steps = steps_before                         # capturing enqueued nothing
+        # (NCCL gather: the step is timed as eager launches unless --graph-multi is given; capturing the NCCL
+        # all-gathers together with the dependent-launch kernels into one graph did not complete on this pool)
         run_step = graph.replay if graph is not None else one_pass
+        note = pg.note_replays if (pg is not None and graph is not None) else None
         for _ in range(max(args.warmup, 3)):
             run_step()
+        if note:
+            note(max(args.warmup, 3))
         stream.synchronize()
-        if dist:
-            dist.barrier()
-        torch.cuda.synchronize()
-        sampler = ClockSampler(local_rank)
-        sampler.start()
         ctx.launch_count(reset=True)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(args.steps):
-            run_step()
-        e1.record(stream)
-        stream.synchronize()
-        if dist:
-            dist.barrier()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        launches_eager = ctx.launch_count()
+        group_ms = timed_groups(torch, dist, stream, run_step, steps, groups, world, dev, note)
+        ms = float(np.median(group_ms))
+
+        # the gathered outputs after the timed replays are still right (slot check on the last step)
+        if pg is not None:
+            check_all_slots(torch, dist, rank, world, dev, ("k",), dims, xs_h, weights_h, lambda n: pg.gathered(n))
 
         # ---- kernel-only duration of the dominant kernel (no collectives) ----
         def kernels_only():
@@ -342,19 +418,14 @@ def run_gpu_arm(args, rank, world, local_rank):
         launches_per_step = ctx.launch_count()
         for _ in range(3):
             kgraph.replay()
-        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        k0.record(stream)
-        for _ in range(args.steps):
-            kgraph.replay()
-        k1.record(stream)
-        stream.synchronize()
-        kernel_ms = k0.elapsed_time(k1)
+        kernel_ms = float(np.median(timed_groups(torch, dist, stream, kgraph.replay, steps, groups, world, dev)))
 
         # ---- end to end through the host-buffer entry point ---------------
         xs_pin = {n: torch.from_numpy(xs_h[n]).pin_memory() for n, _, _ in shapes}
         ys_pin = {n: torch.zeros(1, N, dtype=torch.float32).pin_memory() for n, N, _ in shapes}
         xs_np = {n: xs_pin[n].numpy() for n in xs_pin}
         ys_np = {n: ys_pin[n].numpy() for n in ys_pin}
+        d2h = sum(N * 4 for _, N, _ in shapes)
 
         if world == 1:
             # the user-facing call: one dispatch list on host buffers (uploads, kernels, read-backs, one wait)
@@ -362,23 +433,33 @@ def run_gpu_arm(args, rank, world, local_rank):
 
             def e2e_pass():
                 ctx.matmul_host_batch(batch)
+            e2e_note = "one bpq4k_matmul_host_batch_f32 call per step on pinned host buffers"
         elif pg is not None and graph is not None:
             # one copy up (all activation vectors), the recorded step (matmuls storing into every rank's gather
-            # buffer + flag barrier), one copy down (the whole gather buffer), then a second barrier: no rank may
-            # start storing the next step's slices into a buffer that its owner is still reading back
+            # buffer + flag barrier), one copy down: this rank's 1/world share of the gathered result (a
+            # contiguous range of the step's half of the gather buffer, most of it produced by peers), so that
+            # the whole gathered output of the job lands in host memory once per step.  The slots are
+            # double-buffered, so no second barrier is needed before the next step's stores.
             x_all_pin = torch.zeros(x_total, dtype=torch.float32).pin_memory()
             for name, _, K in shapes:
                 x_all_pin[x_off[name]: x_off[name] + K] = xs_pin[name].view(-1)
-            y_all_pin = torch.zeros(pg.buf.numel(), dtype=torch.float32).pin_memory()
+            share = pg.half // world
+            y_share_pin = torch.zeros(share, dtype=torch.float32).pin_memory()
+            r_share = (rank + 1) % world
+            d2h = share * 4
 
             def e2e_pass():
                 X_all.copy_(x_all_pin, non_blocking=True)
                 graph.replay()
-                y_all_pin.copy_(pg.buf, non_blocking=True)
-                pg.barrier()
+                pg.note_replays(1)
+                base = ((pg.steps - 1) % 2) * pg.half + r_share * share
+                y_share_pin.copy_(pg.buf[base: base + share], non_blocking=True)
                 torch.cuda.current_stream().synchronize()
+            e2e_note = ("per rank: one copy of all activation vectors up, the recorded step, one copy of this rank's "
+                        "1/world share of the gathered outputs down, one wait")
         else:
             yall_pin = {n: torch.zeros(world * N, dtype=torch.float32).pin_memory() for n, N, _ in shapes}
+            d2h = world * d2h
 
             def e2e_pass():
                 for name, N, K in shapes:
@@ -386,128 +467,309 @@ def run_gpu_arm(args, rank, world, local_rank):
                     lin[name].forward(X[name], Yall[name])
                     yall_pin[name].copy_(Yall[name].view(-1), non_blocking=True)
                 torch.cuda.current_stream().synchronize()
+            e2e_note = "per projection: copy up, matmul, NCCL all-gather, copy of the whole gathered output down"
 
         for _ in range(3):
             e2e_pass()
-        e2e_steps = max(1, min(args.steps, 200))
-        if dist:
-            dist.barrier()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            e2e_pass()
-        torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
-        sampler.stop()
+        e2e_steps = max(1, min(steps, 200))
+        e2e_s = float(np.median(wall_groups(torch, dist, e2e_pass, e2e_steps, groups, dev)))
+        if world == 1:
+            want = None
+            from oracle import q4k_oracle as orc
 
-    fused = None
+            want = orc.matmul(xs_h["k"], weights_h["k"], None, 1024, 4096)
+            rel = float(np.linalg.norm(ys_np["k"] - want) / np.linalg.norm(want))
+            assert rel < 1e-3, f"end-to-end output differs from the CPU checker: rel_l2={rel}"
+    sampler.stop()
+
+    extras = {}
     if world == 1:
-        # the same bytes with Q+K+V and gate+up fused by rows, as the reference's loader fuses them
-        # (fuseKQ): five launches instead of eight
-        groups = [("qkv", ["q", "k", "v"]), ("o", ["o"]), ("gate_up", ["gate", "up"]), ("down", ["down"]),
-                  ("lm_head", ["lm_head"])]
-        dims = {n: (N, K) for n, N, K in shapes}
-        FW, FX, FY = {}, {}, {}
-        for gname, members in groups:
-            packed = None
-            for mname in members:
-                pk = bp.pack_q4k(weights_h[mname], *dims[mname])
-                packed = pk if packed is None else bp.fuse_kq(packed, pk)
-            FW[gname] = ctx.upload(packed)
-            FX[gname] = X[members[0]]
-            FY[gname] = torch.zeros(1, packed.N, dtype=torch.float32, device=dev)
-
-        def fused_pass():
-            for gname, _ in groups:
-                ctx.matmul(FX[gname], FW[gname], out=FY[gname])
-
-        with torch.cuda.stream(stream):
-            fused_pass()
-            stream.synchronize()
-            fg = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(fg, stream=stream):
-                fused_pass()
-            for _ in range(3):
-                fg.replay()
-            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            f0.record(stream)
-            for _ in range(args.steps):
-                fg.replay()
-            f1.record(stream)
-            stream.synchronize()
-        fms = f0.elapsed_time(f1) / args.steps
-        fbytes = sum(synth.algorithmic_bytes(1, FW[g].N, FW[g].K) for g, _ in groups)
-        fused = {"what": "same weights, Q+K+V and gate+up fused by rows as the reference's loader does: 5 launches",
-                 "ms_per_step": fms, "value": fbytes / (fms * 1e-3) / 1e9, "unit": UNIT}
-        del FW, FY
-
-    prefill = None
-    if world == 1 and not args.no_prefill:
-        prefill = measure_prefill(ctx, torch, shapes, W, dev)
-    siblings = fusions = gguf_up = experts = None
-    if world == 1 and not args.no_siblings:
-        siblings = measure_siblings(ctx, torch, dev)
-        fusions = measure_fusions(ctx, torch, dev)
-        experts = measure_routed_experts(ctx, torch, dev)
-        gguf_up = measure_gguf_upload(ctx)
-
-    times = torch.tensor([ms, kernel_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
-    if dist:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, kernel_ms, e2e_ms = (float(v) for v in times.cpu())
+        extras["fused_projections"] = measure_fused_projections(ctx, torch, bp, shapes, weights_h, X, dev, stream, steps)
+        extras["config0"] = measure_config0(ctx, torch, bp, weights_h["q"], dev)
+        if not args.no_prefill:
+            extras["prefill"] = measure_prefill(ctx, torch, shapes, W, dev)
+        if not args.no_siblings:
+            extras["small_batch"] = measure_small_batch(ctx, torch, W["lm_head"], dev)
+            extras["kquant_siblings"] = measure_siblings(ctx, torch, dev)
+            extras["fused_prologues"] = measure_fusions(ctx, torch, dev)
+            extras["routed_experts"] = measure_routed_experts(ctx, torch, dev)
+            extras["gguf_upload"] = measure_gguf_upload(ctx)
+    # free the config-1 tensors before the 70B-shaped ones go up
+    if pg is not None:
+        pg.close()
+    del W, Y, Yall, lin
+    torch.cuda.empty_cache()
+    if not args.no_config4:
+        extras["config4"] = measure_config4(ctx, torch, dist, bp, sharded, rank, world, dev, args)
 
     if rank == 0:
         peak, peak_src = load_peaks()
         sb = step_bytes()
-        value = world * sb * args.steps / (ms * 1e-3) / 1e9
-        e2e_val = world * sb * e2e_steps / (e2e_ms * 1e-3) / 1e9
+        value = world * sb * steps / (ms * 1e-3) / 1e9
+        e2e_val = world * sb * e2e_steps / e2e_s / 1e9
         per_launch_bytes = sb / launches_per_step
-        per_launch_s = kernel_ms * 1e-3 / (args.steps * launches_per_step)
+        per_launch_s = kernel_ms * 1e-3 / (steps * launches_per_step)
         achieved = per_launch_bytes / per_launch_s / 1e9
-        cpu, _ = cpu_baseline(args.cpu_budget, shapes, weights_h, xs_h)
+        cpu = cpu_baseline(args.cpu_budget, shapes, weights_h, xs_h)
         h2d = sum(K * 4 for _, _, K in shapes)
-        d2h = world * sum(N * 4 for _, N, _ in shapes)     # every rank reads back the gathered outputs of all ranks
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak, "traffic": per_launch_bytes * TRAFFIC_RATIO,
+                    "traffic_note": "ncu dram read+write of a 151 MB launch, scaled to the average launch by bytes",
+                    "peak_source": peak_src,
+                    "kernel": "q4k matmul (M=1)", "launches_per_step": launches_per_step,
+                    "avg_launch_us": per_launch_s * 1e6, "alg_bytes_per_launch": per_launch_bytes}
+        pf = extras.get("prefill")
+        if pf:
+            roofline["prefill"] = {"bound": "tensor", "unit": "TFLOP/s", "peak": pf.get("bf16_tflops"),
+                                   "peak_sustained": pf.get("bf16_tflops_sustained"),
+                                   "modes": {k: {"achieved": v["tflops"], "frac": v["frac_of_burst_peak"],
+                                                 "meets_float_tolerance": v["meets_float_tolerance"]}
+                                             for k, v in pf["modes"].items()}}
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "gpu_launches": int(launches_per_step * steps * groups),
+            "roofline": roofline,
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "ms_per_step": e2e_s * 1e3 / e2e_steps, "what": e2e_note},
+            "cpu_baseline": cpu,
+            "clocks": sampler.summary(),
+            "parity_before_timing": parity,
             "config": {"workload": WORKLOAD, "M": 1, "projections": [list(s) for s in shapes],
                        "bytes_per_step_per_gpu": sb, "weight_bytes_per_step_per_gpu": weight_bytes_total(),
                        "l2": "inputs larger than L2 (418 MB of weights per pass vs 126 MB L2)",
+                       "timing": f"median of {groups} back-to-back groups of {steps} steps each (CUDA events, max over ranks per group)",
+                       "group_ms": group_ms,
                        "replay": "cuda graph" if graph is not None else "eager launches",
                        "sharding": ("none" if world == 1 else
-                                    "rows (N) per rank; slices stored into every rank's gather buffer by the matmul "
-                                    "epilogue (peer memory), one flag barrier per step" if pg is not None else
+                                    "rows (N) per rank, every rank a full single-GPU-sized shard (weak); slices stored into "
+                                    "every rank's double-buffered gather slots by the matmul epilogue (peer memory), one "
+                                    "flag barrier per step" if pg is not None else
                                     "rows (N) per rank; NCCL all-gather per projection")},
-            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": int(launches_per_step * args.steps),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": per_launch_bytes * TRAFFIC_RATIO,
-                         "traffic_note": "ncu dram read+write of a 151 MB launch, scaled to the average launch by bytes",
-                         "peak_source": peak_src,
-                         "kernel": "q4k matmul (M=1)", "launches_per_step": launches_per_step,
-                         "avg_launch_us": per_launch_s * 1e6, "alg_bytes_per_launch": per_launch_bytes},
-            "cpu_baseline": cpu,
-            "clocks": sampler.summary(),
         }
-        if prefill is not None:
-            line["prefill"] = prefill
-        if fused is not None:
-            line["fused_projections"] = fused
-        if siblings is not None:
-            line["kquant_siblings"] = siblings
-        if fusions is not None:
-            line["fused_prologues"] = fusions
-        if experts is not None:
-            line["routed_experts"] = experts
-        if gguf_up is not None:
-            line["gguf_upload"] = gguf_up
+        line.update(extras)
         print(json.dumps(line), flush=True)
     if dist:
         dist.barrier()
         dist.destroy_process_group()
-    _ = launches_eager
+
+
+def graph_time_us(torch, stream, fn, n_in_graph, replays=5):
+    """Capture `fn` (which launches n_in_graph calls) into a graph, replay it, return us per call."""
+    with torch.cuda.stream(stream):
+        fn()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+        g.replay()
+        ts = []
+        for _ in range(replays):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            g.replay()
+            e1.record(stream)
+            stream.synchronize()
+            ts.append(e0.elapsed_time(e1))
+    return float(np.median(ts)) * 1e3 / n_in_graph
+
+
+def measure_fused_projections(ctx, torch, bp, shapes, weights_h, X, dev, stream, steps):
+    """The same bytes with Q+K+V and gate+up fused by rows, as the reference's loader fuses them (fuseKQ):
+    five launches instead of eight."""
+    groups = [("qkv", ["q", "k", "v"]), ("o", ["o"]), ("gate_up", ["gate", "up"]), ("down", ["down"]),
+              ("lm_head", ["lm_head"])]
+    dims = {n: (N, K) for n, N, K in shapes}
+    FW, FX, FY = {}, {}, {}
+    for gname, members in groups:
+        packed = None
+        for mname in members:
+            pk = bp.pack_q4k(weights_h[mname], *dims[mname])
+            packed = pk if packed is None else bp.fuse_kq(packed, pk)
+        FW[gname] = ctx.upload(packed)
+        FX[gname] = X[members[0]]
+        FY[gname] = torch.zeros(1, packed.N, dtype=torch.float32, device=dev)
+
+    def fused_pass():
+        for gname, _ in groups:
+            ctx.matmul(FX[gname], FW[gname], out=FY[gname])
+
+    us = graph_time_us(torch, stream, fused_pass, 1, replays=max(5, min(steps, 50)))
+    fbytes = sum(synth.algorithmic_bytes(1, FW[g].N, FW[g].K) for g, _ in groups)
+    peak, _ = load_peaks()
+    return {"what": "same weights, Q+K+V and gate+up fused by rows as the reference's loader does: 5 launches",
+            "ms_per_step": us * 1e-3, "value": fbytes / us / 1e3, "unit": UNIT, "frac_of_hbm_peak": fbytes / us / 1e3 / peak}
+
+
+def measure_config0(ctx, torch, bp, raw_q, dev):
+    """Configuration 0: the single 4096 x 4096 GEMV (9.4 MB).  HBM-cold: 32 copies of the weight walked in one graph
+    (302 MB > L2); L2-warm: the same copy 32 times."""
+    N = K = 4096
+    packed = bp.pack_q4k(raw_q, N, K)
+    Ws = [ctx.upload(packed) for _ in range(32)]
+    x = torch.randn(1, K, device=dev, generator=torch.Generator(device=dev).manual_seed(3))
+    y = torch.empty(1, N, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+    cold = graph_time_us(torch, stream, lambda: [ctx.matmul(x, w, out=y) for w in Ws], 32)
+    warm = graph_time_us(torch, stream, lambda: [ctx.matmul(x, Ws[0], out=y) for _ in range(32)], 32)
+    b = synth.algorithmic_bytes(1, N, K)
+    peak, _ = load_peaks()
+    return {"workload": "single GEMV 4096 x 4096, M=1 (config 0)", "alg_bytes": b,
+            "hbm_cold": {"us_per_launch": cold, "value": b / cold / 1e3, "unit": UNIT, "frac_of_hbm_peak": b / cold / 1e3 / peak},
+            "l2_warm": {"us_per_launch": warm, "value": b / warm / 1e3, "unit": UNIT}}
+
+
+def measure_small_batch(ctx, torch, w_head, dev):
+    """Decode with several activation rows (M = 2..16) on the output head 128256 x 4096: one weight pass per call,
+    algorithmic GB/s in graph replay (296 MB per launch > L2)."""
+    peak, _ = load_peaks()
+    N, K = w_head.N, w_head.K
+    stream = torch.cuda.Stream(device=dev)
+    out = {"workload": f"{N} x {K}, Q4_K, M rows per call", "unit": UNIT, "rows": {}}
+    for M in (2, 4, 8, 12, 16):
+        x = torch.randn(M, K, device=dev, generator=torch.Generator(device=dev).manual_seed(M))
+        y = torch.empty(M, N, device=dev)
+        ctx.launch_count(reset=True)
+        ctx.matmul(x, w_head, out=y)
+        launches = ctx.launch_count()
+        us = graph_time_us(torch, stream, lambda: [ctx.matmul(x, w_head, out=y) for _ in range(4)], 4)
+        gbs = synth.algorithmic_bytes(M, N, K) / us / 1e3
+        out["rows"][str(M)] = {"us_per_call": us, "launches_per_call": launches, "value": gbs, "frac_of_hbm_peak": gbs / peak}
+    return out
+
+
+def measure_config4(ctx, torch, dist, bp, sharded, rank, world, dev, args):
+    """Configuration 4: the Llama-3-70B-shaped projections, M = 1 and M = 8, rows split N/G per rank (a STRONG
+    split of fixed matrices over G = world GPUs; every N is divisible by 8).  Per M: the kernels alone, the step
+    with the fused peer-store gather and one flag barrier, the same step with one eager NCCL all-gather per
+    projection, and end to end from pinned host memory.  Aggregate algorithmic GB/s over all ranks."""
+    shapes = synth.LLAMA3_70B
+    peak, peak_src = load_peaks()
+    steps, groups = max(min(args.steps, 50), 1), max(min(args.groups, 5), 1)
+    stream = torch.cuda.Stream(device=dev)
+    Wd, raws = {}, {}
+    for name, N, K in shapes:
+        ns = N // world
+        # this rank's rows of the global matrix: the global matrix is the concatenation of the ranks' draws
+        raws[name] = synth.make_q4k_weights(ns, K, synth.shape_seed("config4", name) + rank)
+        Wd[name] = ctx.upload(bp.pack_q4k(raws[name], ns, K))
+    out = {"workload": "llama3-70b decode projections (config 4), Q4_K, rows split N/G per rank (strong)", "G": world,
+           "unit": UNIT, "peak_gbs": peak, "peak_source": peak_src, "steps": steps, "groups": groups}
+    for M in (1, 8):
+        xs_h = {name: synth.make_activations(M, K, synth.shape_seed("config4", name + ".x") + M) for name, _, K in shapes}
+        x_off, x_total = {}, 0
+        for name, _, K in shapes:
+            x_off[name] = x_total
+            x_total += M * K
+        X_all = torch.zeros(x_total, dtype=torch.float32, device=dev)
+        X = {}
+        for name, _, K in shapes:
+            X[name] = X_all[x_off[name]: x_off[name] + M * K].view(M, K)
+            X[name].copy_(torch.from_numpy(xs_h[name]))
+        Y = {name: torch.zeros(M, N // world, dtype=torch.float32, device=dev) for name, N, _ in shapes}
+        total_bytes = sum(synth.algorithmic_bytes(M, N, K) for _, N, K in shapes)   # whole job, all ranks together
+        row = {}
+
+        def kernels_only():
+            for name, _, _ in shapes:
+                ctx.matmul(X[name], Wd[name], out=Y[name])
+
+        with torch.cuda.stream(stream):
+            kernels_only()
+            stream.synchronize()
+            kg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(kg, stream=stream):
+                kernels_only()
+            for _ in range(3):
+                kg.replay()
+            kms = float(np.median(timed_groups(torch, dist, stream, kg.replay, steps, groups, world, dev))) / steps
+        row["kernels_only"] = {"ms_per_step": kms, "value": total_bytes / kms / 1e6, "frac_of_hbm_peak": total_bytes / kms / 1e6 / (peak * world)}
+        dims = {name: (N // world, K) for name, N, K in shapes}
+        if world == 1:
+            row["parity"] = check_all_slots(torch, None, rank, 1, dev, ("k", "lm_head"), dims, xs_h, raws, lambda n: Y[n], M)
+        else:
+            pg = sharded.PeerGather(ctx, world, rank, {name: (M, N // world) for name, N, _ in shapes})
+
+            def peer_step():
+                for name, _, _ in shapes:
+                    pg.matmul(name, X[name], Wd[name])
+                pg.barrier()
+
+            peer_step()
+            torch.cuda.synchronize()
+            row["parity"] = check_all_slots(torch, dist, rank, world, dev, ("k", "lm_head"), dims, xs_h, raws,
+                                            lambda n: pg.gathered(n), M)
+            with torch.cuda.stream(stream):
+                peer_step()
+                stream.synchronize()
+                before = pg.steps
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    peer_step()
+                pg.steps = before
+                for _ in range(3):
+                    g.replay()
+                pg.note_replays(3)
+                pms = float(np.median(timed_groups(torch, dist, stream, g.replay, steps, groups, world, dev, pg.note_replays))) / steps
+            check_all_slots(torch, dist, rank, world, dev, ("k",), dims, xs_h, raws, lambda n: pg.gathered(n), M)
+            row["peer_gather"] = {"ms_per_step": pms, "value": total_bytes / pms / 1e6,
+                                  "frac_of_hbm_peak": total_bytes / pms / 1e6 / (peak * world),
+                                  "what": "matmul epilogues store the slices to every rank (double-buffered slots), one flag barrier per step, one CUDA graph"}
+            # end to end: activations up, the recorded step, this rank's share of the gathered result down
+            x_pin = torch.zeros(x_total, dtype=torch.float32).pin_memory()
+            x_pin.copy_(X_all.cpu())
+            share = pg.half // world
+            y_pin = torch.zeros(share, dtype=torch.float32).pin_memory()
+            r_share = (rank + 1) % world
+
+            def e2e_pass():
+                X_all.copy_(x_pin, non_blocking=True)
+                g.replay()
+                pg.note_replays(1)
+                base = ((pg.steps - 1) % 2) * pg.half + r_share * share
+                y_pin.copy_(pg.buf[base: base + share], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    e2e_pass()
+                es = float(np.median(wall_groups(torch, dist, e2e_pass, steps, groups, dev))) / steps
+            row["e2e"] = {"ms_per_step": es * 1e3, "value": total_bytes / es / 1e9, "h2d_bytes_per_step": x_total * 4,
+                          "d2h_bytes_per_step": share * 4}
+            pg.close()
+            # NCCL baseline: one eager all-gather per projection (never captured together with the kernels)
+            Yall = {name: torch.zeros((world, M, N // world), dtype=torch.float32, device=dev) for name, N, _ in shapes}
+            lin = {name: sharded.ShardedQ4KLinear(N, K, world, rank, Wd[name],
+                                                   lambda x, shard, out=None: ctx.matmul(x, shard, out=out))
+                   for name, N, K in shapes}
+
+            def nccl_step():
+                for name, _, _ in shapes:
+                    lin[name].forward(X[name], Yall[name])
+
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    nccl_step()
+                stream.synchronize()
+                nms = float(np.median(timed_groups(torch, dist, stream, nccl_step, steps, groups, world, dev))) / steps
+            check_all_slots(torch, dist, rank, world, dev, ("k",), dims, xs_h, raws, lambda n: Yall[n], M)
+            row["nccl_gather"] = {"ms_per_step": nms, "value": total_bytes / nms / 1e6,
+                                  "what": "one eager NCCL all-gather per projection after its matmul"}
+            del Yall, lin
+        if world == 1:
+            pins = [(torch.from_numpy(xs_h[n]).pin_memory(), torch.zeros(M, N, dtype=torch.float32).pin_memory()) for n, N, _ in shapes]
+            batch = ctx.make_host_batch([(p[0].numpy(), Wd[n], p[1].numpy(), None) for p, (n, _, _) in zip(pins, shapes)])
+            for _ in range(3):
+                ctx.matmul_host_batch(batch)
+            es = float(np.median(wall_groups(torch, None, lambda: ctx.matmul_host_batch(batch), steps, groups, dev))) / steps
+            row["e2e"] = {"ms_per_step": es * 1e3, "value": total_bytes / es / 1e9, "h2d_bytes_per_step": x_total * 4,
+                          "d2h_bytes_per_step": sum(M * N * 4 for _, N, _ in shapes)}
+        out[f"M{M}"] = row
+        del X, Y, X_all
+    del Wd
+    torch.cuda.empty_cache()
+    return out
 
 
 def measure_gguf_upload(ctx):
@@ -754,13 +1016,15 @@ def measure_prefill(ctx, torch, shapes, W, dev, M=512, reps=5):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
     ap.add_argument("--ref-budget", type=float, default=120.0, help="seconds the --impl reference run may take")
     ap.add_argument("--no-prefill", action="store_true", help="skip the M=512 (config 2) measurement")
-    ap.add_argument("--no-siblings", action="store_true", help="skip the Q5_K / Q6_K output-head measurement")
+    ap.add_argument("--no-siblings", action="store_true", help="skip the small-batch, Q5_K / Q6_K, prologue, routed-expert and loader measurements")
+    ap.add_argument("--no-config4", action="store_true", help="skip the 70B-shaped strong-split measurement (config 4)")
+    ap.add_argument("--groups", type=int, default=10, help="timed groups of --steps steps each; the median group is reported")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                     help="several ranks: fused peer-store all-gather (default) or one NCCL all-gather per projection")
     ap.add_argument("--graph-multi", action="store_true", help="with several ranks, replay the step from a CUDA graph too")

@@ -213,11 +213,23 @@ int bpq4k_matmul_allgather_f32(bpq4k_handle_t h, const float* X, const void* W, 
                                float* const* slot_ptrs, uint32_t nPeers, uint32_t M, uint32_t N, uint32_t K,
                                uint32_t rowStrideWords, void* stream);
 
+/* Double-buffered gather slots.  With one gather buffer, a rank that runs ahead could store the slices of step
+ * t+1 into a peer's buffer while that peer still reads step t; with two halves used in turn, one barrier per
+ * step is enough (a rank that has passed barrier t+1 knows every peer has queued its reads of step t's half
+ * ahead of it).  step_word is the step counter that bpq4k_peer_barrier keeps in word 63 of this rank's own
+ * flag array (epoch 0 form); the bpq4k_*_allgather_f32 calls that follow store to slot_ptrs[p] +
+ * (*step_word & 1) * stride_floats, read on the device when the kernel runs, so a CUDA graph of a step
+ * alternates by itself.  The slices of the last completed step are in half ((*step_word - 1) & 1).
+ * step_word NULL switches back to single slots.  No counterpart in the reference (single GPU). */
+int bpq4k_peer_double_buffer(bpq4k_handle_t h, const uint32_t* step_word, uint64_t stride_floats);
+
 /* Barrier between the ranks' streams over flag words in peer-mapped memory: writes `epoch` to
  * flag_ptrs[p][rank] for every p, then waits until flag_ptrs[rank][p] >= epoch for every p.
  * flag_ptrs[p] is rank p's flag array (64 words, zero-initialised); epochs must grow.  epoch 0
  * means "the next one": the count is kept in word 63 of the rank's own array, which lets a
- * barrier that is replayed from a CUDA graph advance by itself.  The
+ * barrier that is replayed from a CUDA graph advance by itself (the word is advanced when the barrier
+ * completes).  The kernel is launched with programmatic dependent launch on both sides: it is resident
+ * before the kernel ahead of it has drained, and the kernel behind it may prefetch its weights meanwhile.  The
  * wait is bounded: after timeout_ms (0: one second) the kernel gives up and sets the device
  * status word (bpq4k_device_status then reports BPQ4K_ERR_TIMEOUT); it never traps. */
 int bpq4k_peer_barrier(bpq4k_handle_t h, uint32_t* const* flag_ptrs, uint32_t nPeers, uint32_t rank,

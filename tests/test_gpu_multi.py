@@ -68,30 +68,37 @@ def _peer_worker(rank, world, port, ret):
     # name: (M, N, K, device layout, file type): Q4_K, Q5_K and the padded Q6_K single-row kernel
     cases = {"a": (1, 8192, 4096, 12, 12), "b": (8, 1024, 8192, 12, 12), "c": (3, 128, 512, 12, 12),
              "d": (1, 4096, 4096, 13, 13), "e": (5, 300, 1024, 13, 13), "f": (1, 6000, 2048, 0x10E, 14)}
-    pg = sharded.PeerGather(ctx, world, rank, {n: (c[0], sharded.shard_rows(c[1], world)) for n, c in cases.items()})
     types = {n: c[4] for n, c in cases.items()}
     cases_full, cases = cases, {n: c[:3] for n, c in cases.items()}
     ok = True
-    for rep in range(2):                       # a second step reuses buffers and flags (epoch 2)
-        xs, raws = {}, {}
-        for n, (M, N, K) in cases.items():
-            layout, ftype = cases_full[n][3], cases_full[n][4]
-            raws[n] = synth.make_kq_weights(ftype, N, K, 5 + rep)
-            xs[n] = synth.make_activations(M, K, 6 + rep)
-            ns = sharded.shard_rows(N, world)
-            w = ctx.upload(bp.pack_kq(layout, sharded.shard_raw(raws[n], N, K, world, rank, synth.KQ_BLOCK_BYTES[ftype]), ns, K))
-            pg.matmul(n, torch.from_numpy(xs[n]).cuda(), w)
-        pg.barrier()
-        torch.cuda.synchronize()
-        ok = ok and ctx.device_status() == 0
-        for n, (M, N, K) in cases.items():
-            g = pg.gathered(n)                                     # [world, M, Ns]
-            y = g.permute(1, 0, 2).reshape(M, -1)[:, :N].cpu().numpy()
-            want = orc.kq_matmul(types[n], xs[n], raws[n], None, N, K, threads=4)
-            rel = np.linalg.norm(y - want) / np.linalg.norm(want)
-            ok = ok and rel <= 1e-3 and np.abs(y - want).max() <= 2e-2 * max(1.0, float(np.abs(want).max()) / 100.0)
-        pg.barrier()                                               # nobody overwrites slots others still read
-        torch.cuda.synchronize()
+    # double-buffered slots: one barrier per step, three steps so that both halves are written and the first
+    # one is written again; single slots: a second barrier after the reads
+    for double_buffer in (True, False):
+        pg = sharded.PeerGather(ctx, world, rank, {n: (c[0], sharded.shard_rows(c[1], world)) for n, c in cases.items()},
+                                double_buffer=double_buffer)
+        for rep in range(3):
+            xs, raws = {}, {}
+            for n, (M, N, K) in cases.items():
+                layout, ftype = cases_full[n][3], cases_full[n][4]
+                raws[n] = synth.make_kq_weights(ftype, N, K, 5 + rep)
+                xs[n] = synth.make_activations(M, K, 6 + rep)
+                ns = sharded.shard_rows(N, world)
+                w = ctx.upload(bp.pack_kq(layout, sharded.shard_raw(raws[n], N, K, world, rank, synth.KQ_BLOCK_BYTES[ftype]), ns, K))
+                pg.matmul(n, torch.from_numpy(xs[n]).cuda(), w)
+            pg.barrier()
+            torch.cuda.synchronize()
+            ok = ok and ctx.device_status() == 0
+            for n, (M, N, K) in cases.items():
+                g = pg.gathered(n)                                     # [world, M, Ns]
+                y = g.permute(1, 0, 2).reshape(M, -1)[:, :N].cpu().numpy()
+                want = orc.kq_matmul(types[n], xs[n], raws[n], None, N, K, threads=4)
+                rel = np.linalg.norm(y - want) / np.linalg.norm(want)
+                ok = ok and rel <= 1e-3 and np.abs(y - want).max() <= 2e-2 * max(1.0, float(np.abs(want).max()) / 100.0)
+            if not double_buffer:
+                pg.barrier()                                           # nobody overwrites slots others still read
+                torch.cuda.synchronize()
+        pg.close()
+        dist.barrier()
     ret[rank] = bool(ok)
     dist.barrier()
     dist.destroy_process_group()
