@@ -310,6 +310,10 @@ int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
         case BPQ4K_OPT_STREAM_NO_UNIT_LIST:
             h->tune.no_unit_list = value == 2 ? 2u : value ? 1u : 0u;
             return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_PREWAIT_STAGES:
+            if (value < 0 || value > 9) return fail(h, BPQ4K_ERR_INVALID_ARG, "pre-wait stages must be 0..9");
+            h->tune.pre_wait = (uint32_t)value;
+            return BPQ4K_OK;
         default: return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown option %d", option);
     }
 }
@@ -328,6 +332,7 @@ int bpq4k_get_option(bpq4k_handle_t h, int option, int* value) {
         case BPQ4K_OPT_STREAM_FORCE_SCRATCH: *value = (int)h->tune.force_scratch; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_NO_PDL: *value = (int)h->tune.no_pdl; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_NO_UNIT_LIST: *value = (int)h->tune.no_unit_list; return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_PREWAIT_STAGES: *value = (int)h->tune.pre_wait; return BPQ4K_OK;
         case BPQ4K_OPT_BATCH_RECORDS: *value = (int)h->batch_records; return BPQ4K_OK;
         default: return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown option %d", option);
     }

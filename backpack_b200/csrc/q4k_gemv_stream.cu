@@ -45,6 +45,7 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
@@ -76,23 +77,27 @@ struct StreamArgs {
     const uint8_t* xfrag_g;
     const float* S_g;
     uint32_t nvslots;  // IND: slots times matrices (virtual slot vs: matrix vs / n_slots, slot vs % n_slots)
-    uint32_t u_base, u_extra;  // IND: CTA c takes u_base units (+1 for c < u_extra) of the unit list, in order
+    uint32_t u_base, u_extra;  // IND / contig: CTA c takes u_base units (+1 for c < u_extra) of the unit list, in order
+    uint32_t pre_wait;         // ring stages issued before the dependency wait (the rest after the activation loads)
+    uint32_t contig;           // direct form with a balanced contiguous tile range per CTA (units = tiles)
 };
 
 // Largest |xi|: its top base-128 digit still fits a signed byte.
 constexpr float kXiMax = 2080000.f;
 
-// Quantise the activations.  Work item `item` covers 8 consecutive floats of row `tok`; the four
-// items of a 32-float sub-block sit in four adjacent lanes, which agree on the sub-block's
-// max|x| with two shuffles.  Each sub-block gets its own scale kXiMax/max|x| (block floating
-// point), xi = rint(x*scale), and the three base-128 digits of xi are stored in the mma B
-// layout:
+// Quantise the activations.  Work item c8 of row `tok` belongs to 32-float sub-block c8/4 and is piece
+// t = c8%4 of it: the floats k = 4t..4t+3 and 16+4t..16+4t+3 of the sub-block (item_offset), i.e. exactly
+// the values of the two 16-byte chunks (c, t) below, so a thread writes whole chunks and nothing has to
+// move between lanes.  The four items of a sub-block sit in four adjacent lanes, which agree on the
+// sub-block's max|x| with two shuffles.  Each sub-block gets its own scale kXiMax/max|x| (block floating
+// point), xi = rint(x*scale), and the three base-128 digits of xi are stored in the mma B layout:
 //   per (token, 64-weight group G, parity): 128 B = [c: 0,1][t: 0..3][16 B]
 //   16 B of (c, t): c = 0: d0[4t..4t+3], d0[16+4t..], d2[4t..], d2[16+4t..]
 //                   c = 1: d1[4t..4t+3], d1[16+4t..], 0, 0
 // and per sub-block the two floats the kernel needs: inv = max|x|/kXiMax and sum(xi)*inv,
 //   SI[((tok*nb + blk)*2 + parity)*8 + {0: sum*inv, 4: inv} + g].
 // All 32 lanes of a warp must call this together (idle lanes pass valid = false).
+__device__ __forceinline__ uint32_t item_offset(uint32_t c8) { return (c8 >> 2) * 32u + (c8 & 3u) * 4u; }  // first float4; the second is 16 floats on
 __device__ __forceinline__ void quantize_loaded(float4 v0, float4 v1, uint32_t K, uint32_t tok, uint32_t c8, bool valid,
                                                 uint8_t* frag, float* SI) {
     float amax = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
@@ -124,20 +129,15 @@ __device__ __forceinline__ void quantize_loaded(float4 v0, float4 v1, uint32_t K
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
     if (!valid) return;
     const uint32_t nb = K / kQK, NG = K / 64u;
-    const uint32_t sbg = c8 >> 2, j8 = c8 & 3u;  // sub-block in the row, 8-float piece in the sub-block
+    const uint32_t sbg = c8 >> 2, t = c8 & 3u;  // sub-block in the row, piece of the sub-block
     const uint32_t G = sbg >> 1, par = sbg & 1u;
-    uint8_t* base = frag + ((uint64_t)(tok * NG + G) * 2u + par) * 128u;
-    const uint32_t half = j8 >> 1;  // k < 16 -> first word pair (b0), else second (b1)
-#pragma unroll
-    for (int m2 = 0; m2 < 2; m2++) {
-        const uint32_t t = 2u * (j8 & 1u) + m2;
-        uint32_t* p = reinterpret_cast<uint32_t*>(base + t * 16u + half * 4u);
-        p[0] = w0[m2];    // c = 0: d0
-        p[2] = w2[m2];    //        d2
-        p[16] = w1[m2];   // c = 1: d1
-        p[18] = 0u;       //        zeros
-    }
-    if (j8 == 0) {
+    uint8_t* base = frag + ((uint64_t)(tok * NG + G) * 2u + par) * 128u + t * 16u;
+    // Two 16-byte stores per thread.  The lanes of even sub-blocks write their c = 0 chunk first, those of odd
+    // sub-blocks their c = 1 chunk: the eight lanes that share a shared-memory wavefront then cover all 32 banks.
+    const uint4 c0 = make_uint4(w0[0], w0[1], w2[0], w2[1]), c1 = make_uint4(w1[0], w1[1], 0u, 0u);
+    *reinterpret_cast<uint4*>(base + (par ? 64u : 0u)) = par ? c1 : c0;
+    *reinterpret_cast<uint4*>(base + (par ? 0u : 64u)) = par ? c0 : c1;
+    if (t == 0) {
         float* si = SI + ((uint64_t)(tok * nb + (sbg >> 3)) * 2u + par) * 8u + ((sbg >> 1) & 3u);
         si[0] = (float)sum * inv;
         si[4] = inv;
@@ -148,9 +148,9 @@ __device__ __forceinline__ void quantize_item(const float* __restrict__ X, uint3
                                               uint32_t c8, bool valid, uint8_t* frag, float* SI) {
     float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
     if (valid && tok < M) {
-        const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok * K + (uint64_t)c8 * 8u);
+        const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok * K + item_offset(c8));
         v0 = __ldg(xp);
-        v1 = __ldg(xp + 1);
+        v1 = __ldg(xp + 4);
     }
     quantize_loaded(v0, v1, K, tok, c8, valid, frag, SI);
 }
@@ -216,6 +216,16 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
     [[maybe_unused]] const float* arow[kMaxLocalSlots] = {a.m.aux, a.m.aux, a.m.aux, a.m.aux};
     auto slot_of = [&](uint32_t vs) { return vs >= a.m.n_slots ? vs - a.m.n_slots : vs; };
     auto x_row_of = [&](uint32_t s) { return a.m.x_rows ? a.m.x_rows[s] : a.m.x_row_div ? s / a.m.x_row_div : s; };
+    if constexpr (!IND) {
+        if (a.contig) {
+            // direct form: CTA c owns the contiguous tile range [u_begin, u_end), its tile slots stride through it
+            const uint32_t u_begin = blockIdx.x * a.u_base + min(blockIdx.x, a.u_extra);
+            const uint32_t u_end = u_begin + a.u_base + (blockIdx.x < a.u_extra ? 1u : 0u);
+            tstride = a.wt;
+            tile0 = u_begin + wt;
+            my_tiles = tile0 < u_end ? (u_end - tile0 + tstride - 1u) / tstride : 0u;
+        }
+    }
     if constexpr (IND) {
         const uint32_t u_begin = blockIdx.x * a.u_base + min(blockIdx.x, a.u_extra);
         const uint32_t u_end = u_begin + a.u_base + (blockIdx.x < a.u_extra ? 1u : 0u);
@@ -292,9 +302,23 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
             }
         }
     };
-    {
-        const uint32_t pre = min(a.stages, total_units);
-        for (uint32_t i = 0; i < pre; i++) issue_next();
+    // Ring prefetch in two parts.  `pre_wait` stages go out now; the rest of the ring follows once the loads of
+    // the activations have been issued (issue_rest).  A deep ring issued in one go just before the dependency
+    // wait ends puts ~180 KB per SM in front of those loads in the memory system, and the activation staging
+    // -- the one serial step of the kernel -- then waits 1.5-2.5 us for data that is sitting in L2.
+    const uint32_t pre_total = min(a.stages, total_units);
+    const uint32_t pre_early = min(a.pre_wait, pre_total);
+    for (uint32_t i = 0; i < pre_early; i++) issue_next();
+    auto issue_rest = [&]() {
+        for (uint32_t i = pre_early; i < pre_total; i++) issue_next();
+    };
+    // Bring the activation rows into L2 (and their page into the TLBs) while waiting.  A prefetch is not a read:
+    // if the preceding kernel still writes X, its stores land in the same L2 lines.
+    if constexpr (!IND) {
+        if (!a.m.n_slots && !XG && !XC) {
+            const uint32_t lines = (M * K + 31u) / 32u;
+            for (uint32_t i = tid; i < lines; i += blockDim.x) asm volatile("prefetch.global.L2 [%0];" ::"l"(X + (uint64_t)i * 32u));
+        }
     }
     // Programmatic dependent launch: everything above touches only this CTA's shared memory
     // and READS the weights, so it may overlap the tail of the preceding kernel in the stream.
@@ -302,6 +326,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
     // have produced X, or may still read Y) before reading X or writing anything.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if constexpr (XG) issue_rest();  // nothing is staged per CTA in this mode
 
     // ---- activations: quantise to base-128 digits, once per CTA ---------------------
     const uint32_t NG = K / 64u;
@@ -324,6 +349,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                              : "memory");
             }
         }
+        issue_rest();
         uint32_t polls = 0;
         while (!mbar_try_wait(xbar, 0)) {
             if (++polls > kWaitPolls) {  // give up: flag it and carry on with whatever is there
@@ -353,12 +379,15 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
             // Fused prologue on the single activation row (the reference's q4k_matmul_norm.wgsl:47-92
             // and q4k_down_gelu.wgsl:47-62, plus the silu form of silu_mul_fused): transform while staging.
             float rstd = 1.f;
+            bool rest_issued = false;
             if (a.m.prologue == 1u) {
                 float ss = 0.f;
                 for (uint32_t i = tid; i < K / 4u; i += blockDim.x) {
                     const float4 v = __ldg(reinterpret_cast<const float4*>(X) + i);
                     ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
                 }
+                issue_rest();
+                rest_issued = true;
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
                 float* red = reinterpret_cast<float*>(smem + a.off_part);
@@ -379,14 +408,15 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                     v[j][0] = v[j][1] = w[j][0] = w[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
                     if ((uint32_t)j < nj && it < items) {
                         const uint32_t l = IND ? it / per_row : 0u, c = it - l * per_row;
-                        const float4* xp = reinterpret_cast<const float4*>(IND ? pick(xrow, l) : X) + 2u * c;
-                        const float4* ap = reinterpret_cast<const float4*>(IND ? pick(arow, l) : AUX) + 2u * c;
+                        const float4* xp = reinterpret_cast<const float4*>((IND ? pick(xrow, l) : X) + item_offset(c));
+                        const float4* ap = reinterpret_cast<const float4*>((IND ? pick(arow, l) : AUX) + item_offset(c));
                         v[j][0] = __ldg(xp);
-                        v[j][1] = __ldg(xp + 1);
+                        v[j][1] = __ldg(xp + 4);
                         w[j][0] = __ldg(ap);
-                        w[j][1] = __ldg(ap + 1);
+                        w[j][1] = __ldg(ap + 4);
                     }
                 }
+                if (!rest_issued) issue_rest(), rest_issued = true;
 #pragma unroll
                 for (int j = 0; j < UP; j++) {
                     if ((uint32_t)j >= nj) continue;
@@ -426,16 +456,18 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                 c8[j] = valid[j] ? it - tok[j] * per_row : 0u;
                 v[j][0] = v[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (valid[j]) {
-                    const float4* xp = reinterpret_cast<const float4*>((IND ? pick(xrow, tok[j]) : X + (uint64_t)tok[j] * K) + (uint64_t)c8[j] * 8u);
+                    const float4* xp = reinterpret_cast<const float4*>((IND ? pick(xrow, tok[j]) : X + (uint64_t)tok[j] * K) + item_offset(c8[j]));
                     v[j][0] = __ldg(xp);
-                    v[j][1] = __ldg(xp + 1);
+                    v[j][1] = __ldg(xp + 4);
                 }
             }
+            if (base == 0) issue_rest();
 #pragma unroll
             for (int j = 0; j < U; j++)
                 if ((uint32_t)j < nj) quantize_loaded(v[j][0], v[j][1], K, tok[j], c8[j], valid[j], frag, SI);
         }
         }
+        if (items == 0) issue_rest();  // (never with a valid launch: every CTA stages at least one row)
         __syncthreads();
     }
 
@@ -790,6 +822,16 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     }
     if (gx == 0) gx = 1;
     if (flat_grid) gx = flat_grid, slots_y = 1;  // IND: the planner fixed the grid (one CTA per SM at most)
+    StreamArgs sb = sa;
+    if (!flat_grid && slots_y == 1 && !sa.m.n_slots && !getenv("BPQ4K_OLD_SPLIT")) {
+        // Direct form: every resident CTA slot gets a contiguous, balanced share of the tiles (one CTA more or
+        // less keeps all SMs streaming; a grid that left SMs idle to equalise rounds ran at the per-SM rate).
+        gx = (uint32_t)(groups < cap ? groups : cap);
+        if (gx == 0) gx = 1;
+        sb.contig = 1;
+        sb.u_base = sa.ntiles / gx;
+        sb.u_extra = sa.ntiles % gx;
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(gx, slots_y);
     cfg.blockDim = dim3(threads);
@@ -800,7 +842,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND>, sa);
+    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND>, sb);
 }
 
 static_assert(sizeof(CUtensorMap) == 128, "TmapCache::Entry::map must hold a CUtensorMap");
@@ -969,6 +1011,15 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     if (smem > kSmemMax) return cudaErrorInvalidValue;
     sa.wk = wk; sa.wt = wt; sa.cb = cb; sa.rem = rem; sa.bpw = bpw; sa.stages = stages; sa.stage_bytes = stage_bytes;
     sa.ntiles = ntiles; sa.tokens = tokens; sa.status = status_dev;
+    {
+        // whole ring before the wait while it is small (it lands long before the activations are needed); of a deep
+        // ring only what keeps ~64 KB per SM in front of the activation loads
+        const uint32_t per_stage = warps * stage_bytes;
+        uint32_t pw = stages;
+        if ((uint64_t)per_stage * stages > 96u * 1024u) pw = per_stage >= 64u * 1024u ? 1u : (64u * 1024u) / per_stage;
+        if (tune.pre_wait) pw = tune.pre_wait >= 9 ? 0u : tune.pre_wait;
+        sa.pre_wait = pw < stages ? pw : stages;
+    }
     {
         const uint64_t rows_total = indirect ? m.w_total_rows : m.N;
         const uint32_t key_nb = q5 ? (nb | 0x50000000u) : nb;  // keeps Q5_K maps apart from Q4_K maps of the same buffer

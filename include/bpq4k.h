@@ -87,6 +87,10 @@ typedef enum bpq4k_option {
      * (slot, tile) units over a persistent 1-D grid when there are more slots than SMs or two stacks share
      * the launch, and each CTA's share spans at most four slots); 2: the unit list whenever it is possible. */
     BPQ4K_OPT_STREAM_NO_UNIT_LIST = 17,
+    /* Ring stages whose copies are issued BEFORE the dependency wait (the weight prefetch that overlaps the
+     * preceding kernel); the remaining stages are issued right after the loads of the activations.  0: automatic
+     * (the whole ring while it is small, ~64 KB per SM of a deep one), 1..8: that many, 9: none. */
+    BPQ4K_OPT_STREAM_PREWAIT_STAGES = 18,
     /* Read-only (bpq4k_get_option): how many times bpq4k_matmul_host_batch_f32 has recorded a dispatch
      * list into a replay graph on this handle.  A list is recorded again after any of the handle's
      * buffers had to grow. */
