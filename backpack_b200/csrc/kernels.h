@@ -63,6 +63,7 @@ struct StreamTuning {
     uint32_t force_scratch = 0;  // 1: always split activations into global scratch first
     uint32_t no_pdl = 0;       // 1: launch without programmatic dependent launch
     uint32_t no_unit_list = 0; // 1: indirect form always as one grid row per slot
+    uint32_t rows_per_unit = 0; // several activation rows: weight rows a warp takes at a time, 0 automatic, 16 or 32
     uint32_t pre_wait = 0;     // ring stages issued before the dependency wait: 0 automatic, 1..8, 9 = none
 };
 

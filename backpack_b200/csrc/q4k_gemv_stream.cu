@@ -98,8 +98,11 @@ constexpr float kXiMax = 2080000.f;
 //   SI[((tok*nb + blk)*2 + parity)*8 + {0: sum*inv, 4: inv} + g].
 // All 32 lanes of a warp must call this together (idle lanes pass valid = false).
 __device__ __forceinline__ uint32_t item_offset(uint32_t c8) { return (c8 >> 2) * 32u + (c8 & 3u) * 4u; }  // first float4; the second is 16 floats on
+// `rows`: the several-row kernels keep the two floats elsewhere, four activation rows side by side, so that
+// the four threads of a quad (one activation row each) read one 64-byte run without bank conflicts:
+//   SI[((((tok/4)*nb + blk)*4 + g)*4 + tok%4)*4 + parity*2 + {0: sum*inv, 1: inv}].
 __device__ __forceinline__ void quantize_loaded(float4 v0, float4 v1, uint32_t K, uint32_t tok, uint32_t c8, bool valid,
-                                                uint8_t* frag, float* SI) {
+                                                uint8_t* frag, float* SI, bool rows = false) {
     float amax = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
                        fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
@@ -138,21 +141,27 @@ __device__ __forceinline__ void quantize_loaded(float4 v0, float4 v1, uint32_t K
     *reinterpret_cast<uint4*>(base + (par ? 64u : 0u)) = par ? c1 : c0;
     *reinterpret_cast<uint4*>(base + (par ? 0u : 64u)) = par ? c0 : c1;
     if (t == 0) {
-        float* si = SI + ((uint64_t)(tok * nb + (sbg >> 3)) * 2u + par) * 8u + ((sbg >> 1) & 3u);
-        si[0] = (float)sum * inv;
-        si[4] = inv;
+        if (rows) {
+            float* si = SI + (((uint64_t)((tok >> 2) * nb + (sbg >> 3)) * 4u + ((sbg >> 1) & 3u)) * 4u + (tok & 3u)) * 4u + par * 2u;
+            si[0] = (float)sum * inv;
+            si[1] = inv;
+        } else {
+            float* si = SI + ((uint64_t)(tok * nb + (sbg >> 3)) * 2u + par) * 8u + ((sbg >> 1) & 3u);
+            si[0] = (float)sum * inv;
+            si[4] = inv;
+        }
     }
 }
 // Load the 8 floats of an item (zeros for rows past M or an idle lane), then quantise them.
 __device__ __forceinline__ void quantize_item(const float* __restrict__ X, uint32_t M, uint32_t K, uint32_t tok,
-                                              uint32_t c8, bool valid, uint8_t* frag, float* SI) {
+                                              uint32_t c8, bool valid, uint8_t* frag, float* SI, bool rows) {
     float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
     if (valid && tok < M) {
         const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)tok * K + item_offset(c8));
         v0 = __ldg(xp);
         v1 = __ldg(xp + 4);
     }
-    quantize_loaded(v0, v1, K, tok, c8, valid, frag, SI);
+    quantize_loaded(v0, v1, K, tok, c8, valid, frag, SI, rows);
 }
 
 // Q5_K: code bytes of sub-blocks 2g (low nibbles) and 2g+1 (high nibbles) of one code word, each
@@ -181,11 +190,13 @@ __device__ __forceinline__ void merge_fifth_bit(uint32_t codes, uint32_t qh, uin
 // shape, activations and offsets: the gate and up stacks of an expert layer) the list simply continues
 // over it, results to m.Y2.
 constexpr uint32_t kMaxLocalSlots = 4;
-template <int NT, bool M1, bool XG, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false>
-__global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
+template <int NT, bool M1, bool XG, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false, int RT = 1>
+__global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
     static_assert(!FP || (M1 && !XG && !XC), "the fused forms are single-row and stage the row themselves");
     static_assert(!IND || (M1 && !XG && !XC), "the unit-list form is single-row and stages its rows itself");
     static_assert(!(XG && XC), "digits are read from the scratch directly (XG) or copied into shared memory (XC)");
+    static_assert(RT == 1 || (RT == 2 && !M1), "32-row units (two mma row tiles per warp and stage) exist for several activation rows only");
+    constexpr uint32_t TR = 16u * RT;  // weight rows of one tile: what a warp takes through its ring at a time
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr uint32_t BB = Q5 ? 176u : kBlockBytes, BW = BB / 4u;  // bytes and words per super-block
     constexpr uint32_t QS = Q5 ? 48u : 16u;                          // offset of the nibble bytes
@@ -281,15 +292,15 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
         if (lane == 0) {
             const uint32_t bar = bar0 + iss_st * 8u;
             const bool full = iss_c < nfull;
-            mbar_expect_tx(bar, 16u * BB * (full ? a.cb : a.rem));
+            mbar_expect_tx(bar, TR * BB * (full ? a.cb : a.rem));
             if constexpr (IND) {
                 const uint32_t l = iss_l;
-                const uint32_t row = (l == 0 ? offs[0] : l == 1 ? offs[1] : l == 2 ? offs[2] : offs[3]) + iss_tl * 16u;
+                const uint32_t row = (l == 0 ? offs[0] : l == 1 ? offs[1] : l == 2 ? offs[2] : offs[3]) + iss_tl * TR;
                 const CUtensorMap* map = s_first + l >= a.m.n_slots ? (full ? &a.tmap_b : &a.tmap_b_rem) : (full ? &a.tmap : &a.tmap_rem);
                 tma_load_2d(ring + iss_st * a.stage_bytes, map, (b0 + iss_c * a.cb) * BW, row, bar);
             } else {
             tma_load_2d(ring + iss_st * a.stage_bytes, full ? &a.tmap : &a.tmap_rem, (b0 + iss_c * a.cb) * BW,
-                        (uint32_t)wrow0 + iss_tile * 16u, bar);
+                        (uint32_t)wrow0 + iss_tile * TR, bar);
             }
         }
         if (++iss_st == a.stages) iss_st = 0;
@@ -335,18 +346,19 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
         // warp 0 copies them in (one bulk copy per row for each), everybody waits for the bytes
         for (uint32_t i = tid; i < kZeroBytes / 4u; i += blockDim.x) reinterpret_cast<uint32_t*>(smem + a.off_zero)[i] = 0u;
         if (warp == 0) {
-            const uint32_t seg = K * 4u, sseg = nb * 64u;
-            if (lane == 0) mbar_expect_tx(xbar, (uint32_t)TOK * (seg + sseg));
+            const uint32_t seg = K * 4u, sseg = nb * 256u;  // digits of one row; scales of four interleaved rows
+            if (lane == 0) mbar_expect_tx(xbar, (uint32_t)TOK * seg + (uint32_t)(TOK / 4) * sseg);
             __syncwarp();
             for (uint32_t tok = lane; tok < (uint32_t)TOK; tok += 32u) {
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                                  smem_u32(smem + a.off_x) + tok * seg),
                              "l"(a.xfrag_g + kZeroBytes + (uint64_t)tok * seg), "r"(seg), "r"(xbar)
                              : "memory");
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                 smem_u32(smem + a.off_S) + tok * sseg),
-                             "l"(reinterpret_cast<const uint8_t*>(a.S_g) + (uint64_t)tok * sseg), "r"(sseg), "r"(xbar)
-                             : "memory");
+                if (tok < (uint32_t)(TOK / 4))
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                     smem_u32(smem + a.off_S) + tok * sseg),
+                                 "l"(reinterpret_cast<const uint8_t*>(a.S_g) + (uint64_t)tok * sseg), "r"(sseg), "r"(xbar)
+                                 : "memory");
             }
         }
         issue_rest();
@@ -368,7 +380,10 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
         const uint32_t mrows = M1 ? 1u : min(M, (uint32_t)TOK);
         if constexpr (!M1) {
             for (uint32_t i = mrows * K + tid; i < (uint32_t)TOK * K; i += blockDim.x) reinterpret_cast<uint32_t*>(frag)[i] = 0u;
-            for (uint32_t i = mrows * nb * 16u + tid; i < (uint32_t)TOK * nb * 16u; i += blockDim.x) SI[i] = 0.f;
+            // (scales of four rows are interleaved: float i belongs to row (i / (nb*64))*4 + (i % 16)/4)
+            if (mrows < (uint32_t)TOK)
+                for (uint32_t i = tid; i < (uint32_t)TOK * nb * 16u; i += blockDim.x)
+                    if ((i / (nb * 64u)) * 4u + ((i & 15u) >> 2) >= mrows) SI[i] = 0.f;
         }
         // IND: the rows of all local slots in one pass, slot l staged as "row l" of the shared-memory layout
         const uint32_t items = (IND ? nloc : mrows) * per_row;
@@ -464,7 +479,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
             if (base == 0) issue_rest();
 #pragma unroll
             for (int j = 0; j < U; j++)
-                if ((uint32_t)j < nj) quantize_loaded(v[j][0], v[j][1], K, tok[j], c8[j], valid[j], frag, SI);
+                if ((uint32_t)j < nj) quantize_loaded(v[j][0], v[j][1], K, tok[j], c8[j], valid[j], frag, SI, !M1);
         }
         }
         if (items == 0) issue_rest();  // (never with a valid launch: every CTA stages at least one row)
@@ -510,7 +525,7 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
     // several rows: column n carries activation row n/2 of the mma tile (digit column n%2); the even
     // and the odd sub-block's 128-byte blocks follow each other
     const AddrT gx_addr = xdata + (AddrT)((bn >> 1) * NG) * 256u + (bn & 1u) * 64u + bt * 16u;  // + nt*4*NG*256 + G*256 (+128)
-    const AddrT gs_addr = s_addr + (AddrT)(bt * nb) * 64u;                                         // + (nt*4*nb + blk)*64
+    const AddrT gs_addr = s_addr + (AddrT)bt * 16u;                                                // + (nt*nb + blk)*256 + g*64
     // 16-byte load at addr + OFF (OFF is folded into the instruction)
     auto load16 = [&](AddrT addr, auto off_tag) -> uint4 {
         constexpr int OFF = decltype(off_tag)::value;
@@ -546,10 +561,12 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
         }
         // single-row calls: fetch this lane's residual value now, it is added when the tile is stored
         float res_pre = 0.f;
-        if (FP && a.m.residual && wk == 0 && lane < 16u && tile * 16u + lane < N) res_pre = __ldg(a.m.residual + tile * 16u + lane);
-        float acc[NT][2];
+        if (FP && a.m.residual && wk == 0 && lane < 16u && tile * 16u + lane < N) res_pre = __ldg(a.m.residual + tile * 16u + lane);  // (FP is single-row: 16-row tiles)
+        float acc[RT][NT][2];
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = 0.f;
+        for (int t = 0; t < RT; t++)
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) acc[t][nt][0] = acc[t][nt][1] = 0.f;
 
         for (uint32_t c = 0; c < nchunks; c++) {
             const uint32_t bs = b0 + c * a.cb;
@@ -636,8 +653,8 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                         const int u_lo = c01[1] * 128 + c2[0], u_hi = c01[3] * 128 + c2[2];  // rows r, r+8
                         const bool hi = (bt & 2u) != 0;
                         const float v = fmaf((float)(hi ? c01[2] : c01[0]), 16384.f, (float)(hi ? u_hi : u_lo)) * Ig;
-                        acc[nt][0] = fmaf(dsc[0][g], v, acc[nt][0]);
-                        acc[nt][0] = fmaf(-dmn[0][g], Sg, acc[nt][0]);
+                        acc[0][nt][0] = fmaf(dsc[0][g], v, acc[0][nt][0]);
+                        acc[0][nt][0] = fmaf(-dmn[0][g], Sg, acc[0][nt][0]);
                     }
                 };
                 do_group(std::integral_constant<int, 0>{});
@@ -646,78 +663,89 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
                 do_group(std::integral_constant<int, 3>{});
                 } else {
                 // ---- several activation rows: every mma is one sub-block x four activation rows ----
-                // scales of rows r and r+8, all eight sub-blocks (odd ones carry the 1/16 of the 16q weights)
-                float dsc[2][8], dmn[2][8];
+                // headers of rows r and r+8 of each 16-row mma tile: d, dmin and the packed 6-bit scales and mins; the
+                // float scale of a sub-block is formed when its group is processed (d*(2^23+sc) - d*2^23 in one fma: exact)
+                float hd[RT][2], hm[RT][2], hnd[RT][2], hpm[RT][2];
+                uint32_t sc_lo[RT][2], sc_hi[RT][2], mn_lo[RT][2], mn_hi[RT][2];
 #pragma unroll
-                for (int r = 0; r < 2; r++) {
-                    const uint4 hv = lds128<0>(boff + hdr_off + r * 8u * pitch);
-                    const BlockHeader h{hv.x, hv.y, hv.z, hv.w};
-                    const float d = half_bits_to_float(h.w0), dmin = half_bits_to_float(h.w0 >> 16);
-                    uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
-                    unpack_scales_packed(h, sc_lo, sc_hi, mn_lo, mn_hi);
-                    const float d16 = Q5 ? d : d * 0.0625f;
-                    const float nd = -d * 8388608.f, nd16 = -d16 * 8388608.f, ndm = -dmin * 8388608.f;
+                for (int t = 0; t < RT; t++)
 #pragma unroll
-                    for (int sb = 0; sb < 8; sb++) {
-                        const uint32_t scw = __byte_perm(sb < 4 ? sc_lo : sc_hi, 0x4B000000u, 0x7440u + (sb & 3));
-                        const uint32_t mnw = __byte_perm(sb < 4 ? mn_lo : mn_hi, 0x4B000000u, 0x7440u + (sb & 3));
-                        dsc[r][sb] = (sb & 1) ? fmaf(d16, __uint_as_float(scw), nd16) : fmaf(d, __uint_as_float(scw), nd);
-                        dmn[r][sb] = fmaf(dmin, __uint_as_float(mnw), ndm);
+                    for (int r = 0; r < 2; r++) {
+                        const uint4 hv = lds128<0>(boff + hdr_off + (t * 16u + r * 8u) * pitch);
+                        const BlockHeader h{hv.x, hv.y, hv.z, hv.w};
+                        hd[t][r] = half_bits_to_float(h.w0);
+                        hm[t][r] = -half_bits_to_float(h.w0 >> 16);  // the minimum enters with a minus sign
+                        hnd[t][r] = -hd[t][r] * 8388608.f;
+                        hpm[t][r] = -hm[t][r] * 8388608.f;
+                        unpack_scales_packed(h, sc_lo[t][r], sc_hi[t][r], mn_lo[t][r], mn_hi[t][r]);
                     }
-                }
-                // per activation row of this thread (row t of each mma tile): sum(xi)*inv and inv, 8 sub-blocks
-                uint4 SIv[NT][4];  // [even: S', inv][odd: S', inv], four groups each
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    const AddrT sa = gs_addr + (AddrT)(nt * 4u * nb + blk) * 64u;
-                    SIv[nt][0] = load16(sa, std::integral_constant<int, 0>{});
-                    SIv[nt][1] = load16(sa, std::integral_constant<int, 16>{});
-                    SIv[nt][2] = load16(sa, std::integral_constant<int, 32>{});
-                    SIv[nt][3] = load16(sa, std::integral_constant<int, 48>{});
-                }
                 const uint32_t lm_addr = boff + lm_off;
-                uint32_t qh[4] = {0u, 0u, 0u, 0u};  // Q5_K: fifth bits of this thread's weights, all eight sub-blocks
-                if constexpr (Q5) ldmatrix_x4<-32>(lm_addr, qh[0], qh[1], qh[2], qh[3]);
+                uint32_t qh[RT][4];  // Q5_K: fifth bits of this thread's weights, all eight sub-blocks
+#pragma unroll
+                for (int t = 0; t < RT; t++) {
+                    qh[t][0] = qh[t][1] = qh[t][2] = qh[t][3] = 0u;
+                    if constexpr (Q5) ldmatrix_x4<-32>(lm_addr + t * 16u * pitch, qh[t][0], qh[t][1], qh[t][2], qh[t][3]);
+                }
                 const AddrT gx_blk = gx_addr + (AddrT)blk * 1024u;
+                const AddrT gs_blk = gs_addr + (AddrT)blk * 256u;
                 auto do_group = [&](auto gc) {
                     constexpr int g = decltype(gc)::value;
-                    uint32_t r0, r1, r2, r3;
-                    ldmatrix_x4<g * 32>(lm_addr, r0, r1, r2, r3);
                     [[maybe_unused]] constexpr uint32_t kLo = 0x0F0F0F0Fu, kHi = 0xF0F0F0F0u;
-                    uint32_t e[4], o[4];
-                    if constexpr (Q5) {
-                        const uint32_t rr[4] = {r0, r1, r2, r3};
+                    uint32_t e[RT][4], o[RT][4];
+                    // scales of sub-blocks 2g (even) and 2g+1 (odd) for rows r and r+8 of each mma tile
+                    float dse[RT][2], dso[RT][2], dme[RT][2], dmo[RT][2];
 #pragma unroll
-                        for (int i = 0; i < 4; i++) merge_fifth_bit<g>(rr[i], qh[i], e[i], o[i]);
-                    } else {
-                        e[0] = r0 & kLo; e[1] = r1 & kLo; e[2] = r2 & kLo; e[3] = r3 & kLo;  // q   (even sub-block)
-                        o[0] = r0 & kHi; o[1] = r1 & kHi; o[2] = r2 & kHi; o[3] = r3 & kHi;  // 16q (odd sub-block)
+                    for (int t = 0; t < RT; t++) {
+                        uint32_t r0, r1, r2, r3;
+                        ldmatrix_x4<g * 32>(lm_addr + t * 16u * pitch, r0, r1, r2, r3);
+                        if constexpr (Q5) {
+                            const uint32_t rr[4] = {r0, r1, r2, r3};
+#pragma unroll
+                            for (int i = 0; i < 4; i++) merge_fifth_bit<g>(rr[i], qh[t][i], e[t][i], o[t][i]);
+                        } else {
+                            e[t][0] = r0 & kLo; e[t][1] = r1 & kLo; e[t][2] = r2 & kLo; e[t][3] = r3 & kLo;  // q   (even sub-block)
+                            o[t][0] = r0 & kHi; o[t][1] = r1 & kHi; o[t][2] = r2 & kHi; o[t][3] = r3 & kHi;  // 16q (odd sub-block)
+                        }
+#pragma unroll
+                        for (int r = 0; r < 2; r++) {
+                            const uint32_t scw = g < 2 ? sc_lo[t][r] : sc_hi[t][r], mnw = g < 2 ? mn_lo[t][r] : mn_hi[t][r];
+                            constexpr uint32_t se = 0x7440u + ((2 * g) & 3), so = 0x7440u + ((2 * g + 1) & 3);
+                            dse[t][r] = fmaf(hd[t][r], __uint_as_float(__byte_perm(scw, 0x4B000000u, se)), hnd[t][r]);
+                            dso[t][r] = fmaf(hd[t][r], __uint_as_float(__byte_perm(scw, 0x4B000000u, so)), hnd[t][r]);
+                            dme[t][r] = fmaf(hm[t][r], __uint_as_float(__byte_perm(mnw, 0x4B000000u, se)), hpm[t][r]);
+                            dmo[t][r] = fmaf(hm[t][r], __uint_as_float(__byte_perm(mnw, 0x4B000000u, so)), hpm[t][r]);
+                        }
                     }
 #pragma unroll
                     for (int nt = 0; nt < NT; nt++) {
+                        // the digits and the two floats of this thread's activation row: loaded once, used by every mma tile
                         const AddrT xa = gx_blk + (AddrT)(nt * 4u * NG) * 256u;
                         const uint4 qa = load16(xa, std::integral_constant<int, g * 256>{});        // even sub-block digits
                         const uint4 qb = load16(xa, std::integral_constant<int, g * 256 + 128>{});  // odd sub-block digits
-                        int ce01[4], ce2[4], co01[4], co2[4];  // column pair = digits (d0, d1) resp. (d2, 0)
-                        imma16832_first(ce01, e[0], e[1], e[2], e[3], qa.x, qa.y);
-                        imma16832_first(ce2, e[0], e[1], e[2], e[3], qa.z, qa.w);
-                        imma16832_first(co01, o[0], o[1], o[2], o[3], qb.x, qb.y);
-                        imma16832_first(co2, o[0], o[1], o[2], o[3], qb.z, qb.w);
-                        auto pick = [](const uint4& v) { return g == 0 ? v.x : g == 1 ? v.y : g == 2 ? v.z : v.w; };
-                        const float Se = __uint_as_float(pick(SIv[nt][0])), Ie = __uint_as_float(pick(SIv[nt][1]));
-                        const float So = __uint_as_float(pick(SIv[nt][2])), Io = __uint_as_float(pick(SIv[nt][3]));
-                        // T = 2^14*sum(a d0) + (2^7*sum(a d1) + sum(a d2)); the bracket is exact in int32, the
-                        // top digit's sum (< 2^19) times 2^14 is exact in float
+                        const uint4 si = load16(gs_blk + (AddrT)(nt * nb) * 256u, std::integral_constant<int, g * 64>{});
+                        const float Se = __uint_as_float(si.x), Ie = __uint_as_float(si.y);
+                        const float So = __uint_as_float(si.z), Io = __uint_as_float(si.w);
 #pragma unroll
-                        for (int r = 0; r < 2; r++) {
-                            const float te = fmaf((float)ce01[2 * r], 16384.f, (float)(ce01[2 * r + 1] * 128 + ce2[2 * r])) * Ie;
-                            const float to = fmaf((float)co01[2 * r], 16384.f, (float)(co01[2 * r + 1] * 128 + co2[2 * r])) * Io;
-                            float s2 = acc[nt][r];
-                            s2 = fmaf(dsc[r][2 * g], te, s2);
-                            s2 = fmaf(-dmn[r][2 * g], Se, s2);
-                            s2 = fmaf(dsc[r][2 * g + 1], to, s2);
-                            s2 = fmaf(-dmn[r][2 * g + 1], So, s2);
-                            acc[nt][r] = s2;
+                        for (int t = 0; t < RT; t++) {
+                            int ce01[4], ce2[4], co01[4], co2[4];  // column pair = digits (d0, d1) resp. (d2, 0)
+                            imma16832_first(ce01, e[t][0], e[t][1], e[t][2], e[t][3], qa.x, qa.y);
+                            imma16832_first(ce2, e[t][0], e[t][1], e[t][2], e[t][3], qa.z, qa.w);
+                            imma16832_first(co01, o[t][0], o[t][1], o[t][2], o[t][3], qb.x, qb.y);
+                            imma16832_first(co2, o[t][0], o[t][1], o[t][2], o[t][3], qb.z, qb.w);
+                            // T = 2^14*sum(a d0) + 2^7*sum(a d1) + sum(a d2), exact in int32: |T| < 2^31 for a = q; the odd
+                            // sub-block of Q4_K arrives as a = 16q, every term is a multiple of 16 and T/16 is formed instead
+#pragma unroll
+                            for (int r = 0; r < 2; r++) {
+                                const int te = ce01[2 * r] * 16384 + ce01[2 * r + 1] * 128 + ce2[2 * r];
+                                const int to = Q5 ? co01[2 * r] * 16384 + co01[2 * r + 1] * 128 + co2[2 * r]
+                                                  : co01[2 * r] * 1024 + co01[2 * r + 1] * 8 + (co2[2 * r] >> 4);
+                                float s2 = acc[t][nt][r];
+                                s2 = fmaf(dse[t][r], (float)te * Ie, s2);
+                                s2 = fmaf(dme[t][r], Se, s2);
+                                s2 = fmaf(dso[t][r], (float)to * Io, s2);
+                                s2 = fmaf(dmo[t][r], So, s2);
+                                acc[t][nt][r] = s2;
+                            }
                         }
                     }
                 };
@@ -739,17 +767,19 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
         }
 
         // ---- tile epilogue: parities -> K slices -> bias -> Y -------------------
-        float* pbuf = part + ((uint64_t)((ti & 1u) * nwarps + warp)) * (TOK * 16u);
+        float* pbuf = part + ((uint64_t)((ti & 1u) * nwarps + warp)) * (TOK * TR);
         if constexpr (M1) {
             // the two sub-block parities of a row sit in neighbouring lanes
-            const float s = acc[0][0] + __shfl_xor_sync(0xFFFFFFFFu, acc[0][0], 1);
+            const float s = acc[0][0][0] + __shfl_xor_sync(0xFFFFFFFFu, acc[0][0][0], 1);
             if (c_par == 0) pbuf[row_a] = s;
         } else {
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-                pbuf[(nt * 4u + bt) * 16u + row_a] = acc[nt][0];
-                pbuf[(nt * 4u + bt) * 16u + row_a + 8u] = acc[nt][1];
-            }
+            for (int t = 0; t < RT; t++)
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    pbuf[(nt * 4u + bt) * TR + t * 16u + row_a] = acc[t][nt][0];
+                    pbuf[(nt * 4u + bt) * TR + t * 16u + row_a + 8u] = acc[t][nt][1];
+                }
         }
         if (a.wk > 1) {
             asm volatile("bar.sync %0, %1;" ::"r"(wt + 1u), "r"(a.wk * 32u) : "memory");
@@ -757,12 +787,12 @@ __global__ void __launch_bounds__((M1 || NT == 1) ? 512 : 384, 1) gemv_stream_ke
             __syncwarp();
         }
         if (wk == 0) {
-            const float* gbuf = part + ((uint64_t)((ti & 1u) * nwarps + warp)) * (TOK * 16u);
-            for (uint32_t idx = lane; idx < (uint32_t)TOK * 16u; idx += 32u) {
-                const uint32_t tok = idx >> 4, row = tile * 16u + (idx & 15u);
+            const float* gbuf = part + ((uint64_t)((ti & 1u) * nwarps + warp)) * (TOK * TR);
+            for (uint32_t idx = lane; idx < (uint32_t)TOK * TR; idx += 32u) {
+                const uint32_t tok = idx / TR, row = tile * TR + (idx % TR);
                 if (tok < M && row < N) {
                     float s = 0.f;
-                    for (uint32_t k2 = 0; k2 < a.wk; k2++) s += gbuf[(uint64_t)k2 * (TOK * 16u) + idx];
+                    for (uint32_t k2 = 0; k2 < a.wk; k2++) s += gbuf[(uint64_t)k2 * (TOK * TR) + idx];
                     float yv = s + (a.m.bias ? a.m.bias[row] : 0.f);
                     if (FP) yv += res_pre;
                     Y[(uint64_t)tok * N + row + par_off] = yv;
@@ -793,18 +823,18 @@ __global__ void __launch_bounds__(256) quantize_activations_kernel(const float* 
         const uint32_t it = base + threadIdx.x;
         const bool valid = it < items;
         const uint32_t tok = valid ? it / per_row : 0u;
-        quantize_item(X, M, K, tok, valid ? it - tok * per_row : 0u, valid, frag, SI);
+        quantize_item(X, M, K, tok, valid ? it - tok * per_row : 0u, valid, frag, SI, tokens > 1u);
     }
 }
 
 // Launch one instantiation.  The grid is persistent: at most as many CTAs as can be
 // resident at once (occupancy query, cached), never more than there are tile groups.
-template <int NT, bool M1, bool XG, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false>
+template <int NT, bool M1, bool XG, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false, int RT = 1>
 cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, uint32_t threads, size_t smem,
                        int sm_count, uint32_t ctas_per_sm_override, bool pdl, cudaStream_t stream, uint32_t flat_grid = 0) {
     static KernelConfig kcfg;  // per instantiation; per-device slots and a mutex inside
     int occ = 1;
-    if (cudaError_t e = kcfg.prepare(reinterpret_cast<const void*>(gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND>), threads, smem, &occ))
+    if (cudaError_t e = kcfg.prepare(reinterpret_cast<const void*>(gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND, RT>), threads, smem, &occ))
         return e;
     uint32_t per_sm = (uint32_t)occ;
     if (ctas_per_sm_override && ctas_per_sm_override < per_sm) per_sm = ctas_per_sm_override;
@@ -842,7 +872,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND>, sb);
+    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND, RT>, sb);
 }
 
 static_assert(sizeof(CUtensorMap) == 128, "TmapCache::Entry::map must hold a CUtensorMap");
@@ -864,10 +894,18 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     const bool indirect = m.n_slots != 0;
     const uint32_t M = indirect ? 1 : m.M;
     if (M == 0) return cudaSuccess;
-    if (M > 8) return cudaErrorInvalidValue;  // callers split larger M
+    if (M > 16) return cudaErrorInvalidValue;  // callers split larger M
     const uint32_t nb = m.K / kQK;
-    const uint32_t ntiles = (m.N + 15) / 16;
     const bool m1 = M == 1;
+    // Several activation rows and many weight rows: a warp takes 32 rows (two mma row tiles) through its ring at a
+    // time, so the digits and scales of the activation rows are fetched once per two tiles (they are what loads
+    // the shared-memory pipe, or L2 when they live in the global scratch).
+    // Measured (M = 8): 8192 x 28672 69.6 against 93.5 us, 4096 x 14336 20.0 against 24.4 us; no gain where the digits sit
+    // in shared memory (128256 x 4096: 98 against 100 us) and a loss at K = 8192, where twelve warps matter more.
+    const uint32_t rt = tune.rows_per_unit == 16 ? 1u : tune.rows_per_unit == 32 ? (m1 || indirect ? 1u : 2u)
+                        : (!m1 && !indirect && m.N >= 2048u && m.K >= 14336u && (uint64_t)M * m.K > 40960u) ? 2u : 1u;
+    const uint32_t tile_rows = 16u * rt;
+    const uint32_t ntiles = (m.N + tile_rows - 1) / tile_rows;
     const int NT = m1 ? 1 : (int)((M + 3) / 4);
     const uint32_t tokens = m1 ? 1 : NT * 4;
 
@@ -894,6 +932,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     }
     uint32_t warps = tune.warps ? tune.warps : m1 ? warps_m1 : NT == 1 ? (small || wide_k ? 16 : 8) : (!small && wide_k ? 12 : 8);
     if (!m1 && NT > 1 && warps > 12) warps = 12;  // the eight-row kernel is built for 384 threads (more registers each)
+    if (rt == 2 && warps > 8) warps = 8;         // 32-row units: built for 256 threads
     uint32_t wk = tune.wk;
     if (!wk) {
         if (small) {
@@ -914,7 +953,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     // Stage = dense TMA box of 16 rows x cb blocks, then one box of rem blocks for the tail of
     // the warp's K range.  An odd cb keeps the 16-byte units of the eight rows an ldmatrix
     // touches in distinct bank groups (row pitch = cb*9 units).
-    uint32_t cb = tune.cb ? tune.cb : m1 ? (small ? (bpw <= 2 ? bpw : 1) : (q5 ? 3 : 5)) : 3;  // Q5_K: 5 wide blocks leave no room for the ring
+    uint32_t cb = tune.cb ? tune.cb : m1 ? (small ? (bpw <= 2 ? bpw : 1) : (q5 ? 3 : 5)) : rt == 2 ? 2 : 3;  // Q5_K: 5 wide blocks leave no room for the ring
     if (cb > 256u / block_words) cb = 256u / block_words;  // box width <= 256 words
     if (cb > bpw) cb = bpw;
     uint32_t x_bytes = tokens * m.K * 4u, S_bytes = tokens * (m.K / 32u) * 8u;  // IND: times the local slots (set below)
@@ -924,7 +963,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         sa.off_zero = off; off += kZeroBytes;
         sa.off_S = off; off += xg ? 0 : align_up(S_bytes, 16);
         sa.off_x = align_up(off, 128); off = sa.off_x + (xg ? 0 : x_bytes);
-        sa.off_part = align_up(off, 16); off = sa.off_part + 2u * warps * tokens * 16u * 4u;
+        sa.off_part = align_up(off, 16); off = sa.off_part + 2u * warps * tokens * tile_rows * 4u;
         sa.off_ring = align_up(off, 128); off = sa.off_ring + warps * stages * stage_bytes;
         return off;
     };
@@ -969,10 +1008,10 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     if (indirect && m.residual) return cudaErrorInvalidValue;         // slots share no output row
     if (tune.force_scratch && !fused) xg = true;
     if (!xg) {
-        const uint32_t cb_min = (m1 || tune.cb || cb < 2) ? cb : 2;
+        const uint32_t cb_min = (m1 || tune.cb || cb < 2) ? cb : rt == 2 ? 1 : 2;
         auto fit = [&]() {
             for (uint32_t cb_try = cb; cb_try >= cb_min; cb_try--) {
-                stage_bytes = 16 * cb_try * block_bytes;
+                stage_bytes = tile_rows * cb_try * block_bytes;
                 uint32_t s_try = stages;
                 while (s_try >= 2 && layout(false, s_try, sa) > kSmemMax) s_try--;
                 if (s_try >= 2) {
@@ -1001,7 +1040,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     const bool xc = !xg && !m1 && !indirect && (uint64_t)tokens * m.K >= 32768u && scratch &&
                     scratch_bytes >= gemv_stream_scratch_bytes(M, m.K);
     const uint32_t rem = bpw % cb;
-    stage_bytes = 16 * cb * block_bytes;
+    stage_bytes = tile_rows * cb * block_bytes;
     if (xg) {
         while (stages > 1 && layout(true, stages, sa) > kSmemMax) stages--;
         if (indirect || fused) return cudaErrorInvalidValue;  // these stage their activations in shared memory only
@@ -1022,7 +1061,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     }
     {
         const uint64_t rows_total = indirect ? m.w_total_rows : m.N;
-        const uint32_t key_nb = q5 ? (nb | 0x50000000u) : nb;  // keeps Q5_K maps apart from Q4_K maps of the same buffer
+        const uint32_t key_nb = (q5 ? (nb | 0x50000000u) : nb) | (rt << 24);  // keeps Q5_K maps apart from Q4_K maps of the same buffer, 32-row boxes from 16-row ones
         auto get_map = [&](uint32_t width_blocks, CUtensorMap* out, const uint8_t* Wp) -> cudaError_t {
             if (tmaps) {
                 for (const auto& en : tmaps->entries)
@@ -1036,7 +1075,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
             if (!enc) return cudaErrorNotSupported;
             const cuuint64_t gdim[2] = {(cuuint64_t)nb * block_words, (cuuint64_t)rows_total};
             const cuuint64_t gstride[1] = {(cuuint64_t)m.w_row_bytes};
-            const cuuint32_t box[2] = {width_blocks * block_words, 16u};
+            const cuuint32_t box[2] = {width_blocks * block_words, tile_rows};
             const cuuint32_t estr[2] = {1u, 1u};
             const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(Wp), gdim, gstride, box, estr,
                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -1106,15 +1145,21 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
             sa.m.Y = base.Y + (uint64_t)s0 * m.N;
         }
         const uint32_t threads = warps * 32;
-#define BPQ4K_LAUNCH(NT_, M1_, XG_, XC_, FP_)                                                                          \
-    (q5 ? launch_one<NT_, M1_, XG_, true, XC_, FP_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream) \
-        : launch_one<NT_, M1_, XG_, false, XC_, FP_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream))
+#define BPQ4K_LAUNCH_RT(NT_, M1_, XG_, XC_, FP_, RT_)                                                                  \
+    (q5 ? launch_one<NT_, M1_, XG_, true, XC_, FP_, false, RT_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream) \
+        : launch_one<NT_, M1_, XG_, false, XC_, FP_, false, RT_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream))
+#define BPQ4K_LAUNCH(NT_, M1_, XG_, XC_, FP_) \
+    ((M1_) || rt == 1 ? BPQ4K_LAUNCH_RT(NT_, M1_, XG_, XC_, FP_, 1) : BPQ4K_LAUNCH_RT(NT_, false, XG_, XC_, false, 2))
         if (m1 && fused) e = BPQ4K_LAUNCH(1, true, false, false, true);
         else if (m1) e = xg ? BPQ4K_LAUNCH(1, true, true, false, false) : BPQ4K_LAUNCH(1, true, false, false, false);
-        else if (xc) e = NT == 1 ? BPQ4K_LAUNCH(1, false, false, true, false) : BPQ4K_LAUNCH(2, false, false, true, false);
-        else if (NT == 1) e = xg ? BPQ4K_LAUNCH(1, false, true, false, false) : BPQ4K_LAUNCH(1, false, false, false, false);
-        else e = xg ? BPQ4K_LAUNCH(2, false, true, false, false) : BPQ4K_LAUNCH(2, false, false, false, false);
+        else if (xc) e = NT == 1 ? BPQ4K_LAUNCH(1, false, false, true, false) : NT == 2 ? BPQ4K_LAUNCH(2, false, false, true, false)
+                       : NT == 3 ? BPQ4K_LAUNCH(3, false, false, true, false) : BPQ4K_LAUNCH(4, false, false, true, false);
+        else if (xg) e = NT == 1 ? BPQ4K_LAUNCH(1, false, true, false, false) : NT == 2 ? BPQ4K_LAUNCH(2, false, true, false, false)
+                       : NT == 3 ? BPQ4K_LAUNCH(3, false, true, false, false) : BPQ4K_LAUNCH(4, false, true, false, false);
+        else e = NT == 1 ? BPQ4K_LAUNCH(1, false, false, false, false) : NT == 2 ? BPQ4K_LAUNCH(2, false, false, false, false)
+               : NT == 3 ? BPQ4K_LAUNCH(3, false, false, false, false) : BPQ4K_LAUNCH(4, false, false, false, false);
 #undef BPQ4K_LAUNCH
+#undef BPQ4K_LAUNCH_RT
         if (launches) ++*launches;
         if (e != cudaSuccess) return e;
     }

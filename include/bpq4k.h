@@ -91,6 +91,9 @@ typedef enum bpq4k_option {
      * preceding kernel); the remaining stages are issued right after the loads of the activations.  0: automatic
      * (the whole ring while it is small, ~64 KB per SM of a deep one), 1..8: that many, 9: none. */
     BPQ4K_OPT_STREAM_PREWAIT_STAGES = 18,
+    /* Several activation rows (M = 2..16): weight rows a warp takes through its ring at a time.  32 halves the
+     * reads of the activation digits per weight byte; 0: automatic (32 from 8192 weight rows on), 16, 32. */
+    BPQ4K_OPT_STREAM_UNIT_ROWS = 19,
     /* Read-only (bpq4k_get_option): how many times bpq4k_matmul_host_batch_f32 has recorded a dispatch
      * list into a replay graph on this handle.  A list is recorded again after any of the handle's
      * buffers had to grow. */

@@ -251,9 +251,9 @@ def test_prefill_threshold_option(ctx):
     y_tc = ctx.matmul(dev(torch, x), w).cpu().numpy()
     n_tc = ctx.launch_count()
     ctx.set_option(q4k.OPT_PREFILL_MIN_M, default_min_m)
-    # eight slabs of 8 rows (one launch each; two where the activations are quantised by a kernel of their own)
+    # slabs of 8 or 16 rows (one launch each; two where the activations are quantised by a kernel of their own)
     # vs. cast + tensor-core launch (+ reduction)
-    assert n_stream in (8, 16) and n_tc in (2, 3)
+    assert n_stream in (4, 8, 16) and n_tc in (2, 3)
     check(y_stream, want)
     check(y_tc, want)
 
