@@ -158,11 +158,13 @@ __device__ __forceinline__ uint32_t pack2_lo(float a, float b, uint32_t hi_bits)
 template <bool BF16>
 __device__ __forceinline__ void dequant_word_16(uint32_t w, uint32_t dsc_e2, uint32_t ndmn_e2, uint32_t dsc_o2,
                                                 uint32_t ndmn_o2, uint32_t (&out)[4]) {
-    const uint32_t t = __byte_perm(w, 0u, 0x3120u);  // bytes (0, 2, 1, 3): neighbours land in one packed pair
+    // bytes (0, x, 1, x) and (2, x, 3, x) in the low bytes of the two halves: neighbours land in one packed pair
+    // and no further shift is needed for the low nibbles
+    const uint32_t t = __byte_perm(w, 0u, 0x3120u), t2 = __byte_perm(w, 0u, 0x1302u);
     if constexpr (BF16) {
-        const uint32_t u = t >> 4;
-        const uint32_t e0 = (t & 0x000F000Fu) | 0x43004300u, e1 = ((t >> 8) & 0x000F000Fu) | 0x43004300u;  // 128 + q
-        const uint32_t o0 = (u & 0x000F000Fu) | 0x43004300u, o1 = ((u >> 8) & 0x000F000Fu) | 0x43004300u;
+        const uint32_t u = t >> 4, u2 = t2 >> 4;
+        const uint32_t e0 = (t & 0x000F000Fu) | 0x43004300u, e1 = (t2 & 0x000F000Fu) | 0x43004300u;  // 128 + q
+        const uint32_t o0 = (u & 0x000F000Fu) | 0x43004300u, o1 = (u2 & 0x000F000Fu) | 0x43004300u;
         auto conv = [](uint32_t x, uint32_t dsc2, uint32_t ndmn2) -> uint32_t {
             const __nv_bfloat162 k128 = __float2bfloat162_rn(128.f);
             const __nv_bfloat162 q = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&x), k128);
@@ -175,8 +177,8 @@ __device__ __forceinline__ void dequant_word_16(uint32_t w, uint32_t dsc_e2, uin
         out[2] = conv(o0, dsc_o2, ndmn_o2);
         out[3] = conv(o1, dsc_o2, ndmn_o2);
     } else {
-        const uint32_t e0 = (t & 0x000F000Fu) | 0x64006400u, e1 = ((t >> 8) & 0x000F000Fu) | 0x64006400u;  // 1024 + q
-        const uint32_t o0 = (t & 0x00F000F0u) | 0x64006400u, o1 = ((t >> 8) & 0x00F000F0u) | 0x64006400u;  // 1024 + 16 q
+        const uint32_t e0 = (t & 0x000F000Fu) | 0x64006400u, e1 = (t2 & 0x000F000Fu) | 0x64006400u;  // 1024 + q
+        const uint32_t o0 = (t & 0x00F000F0u) | 0x64006400u, o1 = (t2 & 0x00F000F0u) | 0x64006400u;  // 1024 + 16 q
         const __half2 k1024 = __float2half2_rn(1024.f), k16th = __float2half2_rn(0.0625f), k64 = __float2half2_rn(64.f);
         auto fin = [](const __half2 q, uint32_t dsc2, uint32_t ndmn2) -> uint32_t {
             const __half2 r = __hfma2(q, *reinterpret_cast<const __half2*>(&dsc2), *reinterpret_cast<const __half2*>(&ndmn2));
@@ -191,13 +193,21 @@ __device__ __forceinline__ void dequant_word_16(uint32_t w, uint32_t dsc_e2, uin
 
 // Shared-memory plan (all tiles 1024-byte aligned for the 128-byte swizzle):
 //   per stage: NV versions (1, or hi+lo) of the A tile [ROWS x 128 B] and of the B tile [256 x 128 B]
-template <int ROWS, int PASSES>
+// SPLIT: dequantising threads per weight row of a stage.  Three-pass mode of Q4_K and Q5_K: two, each takes 32 of the
+// stage's 64 weights through float (128256 x 4096, M = 512: 484 against 440 TFLOP/s with one thread per row -- twice
+// the warps hide each other's latencies).  The single-pass modes keep one thread per row: two threads sharing every
+// stage measured 892 against 985 TFLOP/s over the eight projections (scale preparation and barrier traffic double
+// while the packed 16-bit dequantisation itself is short), two threads taking alternate stages 1158 against 1209
+// on the largest one.  Q6_K keeps one thread per row.
+template <int ROWS, int PASSES, int QT = 0>
 struct Plan {
+    static constexpr uint32_t SPLIT = (QT == 2 || PASSES == 1) ? 1 : 2;
     static constexpr uint32_t NV = PASSES == 3 ? 2 : 1;
     static constexpr uint32_t A_BYTES = ROWS * 128u, B_BYTES = kTokTile * 128u;
     static constexpr uint32_t STAGE_BYTES = NV * (A_BYTES + B_BYTES);
     static constexpr uint32_t STAGES = (200u * 1024u) / STAGE_BYTES;
-    static constexpr uint32_t DEQ_WARPS = ROWS / 32;
+    static constexpr uint32_t ROW_WARPS = ROWS / 32;
+    static constexpr uint32_t DEQ_WARPS = ROW_WARPS * SPLIT;
     static constexpr uint32_t THREADS = (2 + DEQ_WARPS) * 32;
     // three-pass mode: a second accumulator takes the two small cross terms (see the mma issuer)
     static constexpr uint32_t TMEM_COLS = (PASSES == 3 ? 2 : ROWS / 128) * kTokTile;
@@ -210,11 +220,11 @@ struct Plan {
 // QT = 2: Q6_K weights in the padded layout (224-byte blocks: 128 nibble bytes, 64 bit-pair bytes, 16 signed
 // scales, half d, padding); w = d*sc*(code - 32) with one scale per 16 weights.
 template <int ROWS, int PASSES, bool BF16, int QT = 0>
-__global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_kernel(const __grid_constant__ PrefillArgs a) {
+__global__ void __launch_bounds__(Plan<ROWS, PASSES, QT>::THREADS, 1) prefill_tc_kernel(const __grid_constant__ PrefillArgs a) {
     constexpr bool Q5 = QT == 1, Q6 = QT == 2;
     constexpr int BU = Q6 ? 14 : Q5 ? 11 : 9;   // 16-byte units per super-block
     constexpr int CU = Q5 ? 3 : 1;              // first unit of the nibble bytes (Q4_K, Q5_K)
-    using P = Plan<ROWS, PASSES>;
+    using P = Plan<ROWS, PASSES, QT>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -307,10 +317,12 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_ker
     } else {
         // ---------------- dequantise (thread = weight row), then drain TMEM ----------------
         const uint32_t dw = warp - 2;              // 0 .. DEQ_WARPS-1
-        const uint32_t r = dw * 32u + lane;        // row inside the tile
+        const uint32_t r = (dw % P::ROW_WARPS) * 32u + lane;  // row inside the tile
+        [[maybe_unused]] const uint32_t part = dw / P::ROW_WARPS;  // which 32 of a stage's 64 weights (SPLIT = 2)
         const uint32_t n = n0 + r;
         const bool row_ok = n < a.N;
-        const uint4* wrow = reinterpret_cast<const uint4*>(a.W + (uint64_t)(row_ok ? n : 0) * a.w_row_bytes);
+        // rows past N read the last row: their accumulator lanes are never stored
+        const uint4* wrow = reinterpret_cast<const uint4*>(a.W + (uint64_t)(row_ok ? n : (Q6 ? 0u : a.N - 1u)) * a.w_row_bytes);
         const uint32_t nblocks = blk1 - blk0;
         wrow += (uint64_t)blk0 * BU;
         bool ok = true;
@@ -426,46 +438,85 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_ker
                 }
             }
         } else {
-        uint4 raw[BU], nxt[BU];
+        // This thread's share of a super-block: the header, (Q5_K) one unit of fifth bits and, of each 64-weight
+        // group, the 16 code bytes `part` (weights 16*part .. 16*part+15 of the even and of the odd sub-block).
+        constexpr bool HALF_ROW = P::SPLIT == 2;
+        constexpr int PARTS = HALF_ROW ? 1 : 2;           // 16-byte code units per group this thread handles
+        constexpr int GH = 4;                             // 64-weight groups of a super-block
+        constexpr int RU = 1 + GH * PARTS + (Q5 ? PARTS : 0);
+        const uint32_t upart = HALF_ROW ? part : 0u;      // which half of a group's code bytes
+        uint4 raw[RU], nxt[RU];
+        auto load_block = [&](uint32_t b, uint4 (&dst)[RU]) {
+            const uint4* p = wrow + (uint64_t)b * BU;
+            dst[0] = __ldg(p);
 #pragma unroll
-        for (int i = 0; i < BU; i++) nxt[i] = (row_ok && nblocks) ? __ldg(wrow + i) : make_uint4(0, 0, 0, 0);
+            for (int gi = 0; gi < GH; gi++)
+#pragma unroll
+                for (int q = 0; q < PARTS; q++) dst[1 + gi * PARTS + q] = __ldg(p + CU + 2 * gi + upart * PARTS + q);
+            if constexpr (Q5)
+#pragma unroll
+                for (int q = 0; q < PARTS; q++) dst[1 + GH * PARTS + q] = __ldg(p + 1 + upart * PARTS + q);
+        };
+        if (nblocks) load_block(0, nxt);
+        // running pipeline position (stage, parity of the stage's previous use) instead of a division per stage
+        uint32_t st_s = 0, st_it = 0;   // stage and how often the ring has wrapped before it
+        // swizzled byte offsets of this thread's chunks inside an A tile (loop-invariant)
+        uint32_t choff[2 * PARTS][2];
+#pragma unroll
+        for (uint32_t cl = 0; cl < 2u * PARTS; cl++) {
+            const uint32_t c = 2u * PARTS * upart + cl;
+            choff[cl][0] = row_off + ((c ^ sw) << 4);
+            choff[cl][1] = row_off + (((c + 4u) ^ sw) << 4);
+        }
         for (uint32_t b = 0; b < nblocks && ok; b++) {
 #pragma unroll
-            for (int i = 0; i < BU; i++) raw[i] = nxt[i];
-            if (b + 1 < nblocks && row_ok) {
+            for (int i = 0; i < RU; i++) raw[i] = nxt[i];
+            if (b + 1 < nblocks) load_block(b + 1, nxt);
+            // Q5_K: the four words of fifth bits of this part (word w: weights 16*part + 4w..4w+3 of every sub-block)
+            [[maybe_unused]] uint32_t qhw[4 * PARTS];
+            if constexpr (Q5) {
 #pragma unroll
-                for (int i = 0; i < BU; i++) nxt[i] = __ldg(wrow + (uint64_t)(b + 1) * BU + i);
+                for (int q = 0; q < PARTS; q++) {
+                    const uint4 u = raw[1 + GH * PARTS + q];
+                    qhw[4 * q] = u.x, qhw[4 * q + 1] = u.y, qhw[4 * q + 2] = u.z, qhw[4 * q + 3] = u.w;
+                }
             }
-            // Q5_K: the eight words of fifth bits (word w: weights 4w..4w+3 of every sub-block)
-            [[maybe_unused]] const uint32_t qhw[8] = {raw[1].x, raw[1].y, raw[1].z, raw[1].w, raw[2].x, raw[2].y, raw[2].z, raw[2].w};
             const BlockHeader h{raw[0].x, raw[0].y, raw[0].z, raw[0].w};
             const float d = half_bits_to_float(h.w0), dmin = half_bits_to_float(h.w0 >> 16);
             uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
             unpack_scales_packed(h, sc_lo, sc_hi, mn_lo, mn_hi);
 #pragma unroll
-            for (uint32_t g = 0; g < 4; g++) {
-                const uint32_t kb = b * 4u + g;
-                const uint32_t s = kb % P::STAGES, it = kb / P::STAGES;
-                if (it > 0 && !wait_bar(empty_bar(s), (it - 1) & 1u, abort_flag, a.status)) {
+            for (uint32_t gi = 0; gi < (uint32_t)GH; gi++) {
+                const uint32_t g = gi;
+                const uint32_t s = st_s;
+                if (st_it > 0 && !wait_bar(empty_bar(s), (st_it - 1u) & 1u, abort_flag, a.status)) {
                     ok = false;
                     break;
                 }
+                if (++st_s == P::STAGES) st_s = 0, st_it++;
                 // w = (d*sc)*q - dmin*mn in float, rounded to 16 bits afterwards
                 const float dsc_e = d * (float)byte_of(sc_lo, sc_hi, 2 * g), dmn_e = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g);
                 const float dsc_o = d * (float)byte_of(sc_lo, sc_hi, 2 * g + 1), dmn_o = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g + 1);
-                const uint4 c0 = raw[CU + 2 * g], c1 = raw[CU + 1 + 2 * g];  // the group's 32 code bytes
-                const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-                const uint32_t ta = a_tile(s, 0) + row_off;
+                uint32_t words[4 * PARTS];  // this thread's code bytes of the group
 #pragma unroll
-                for (uint32_t c = 0; c < 4; c++) {  // chunk c: weights 8c..8c+7 of the even sub-block, chunk c+4: of the odd one
+                for (int q = 0; q < PARTS; q++) {
+                    const uint4 u = raw[1 + gi * PARTS + q];
+                    words[4 * q] = u.x, words[4 * q + 1] = u.y, words[4 * q + 2] = u.z, words[4 * q + 3] = u.w;
+                }
+                const uint32_t ta = a_tile(s, 0);
+                [[maybe_unused]] uint32_t dsc_e2 = 0, ndmn_e2 = 0, dsc_o2 = 0, ndmn_o2 = 0;
+                if constexpr (PASSES == 1 && !Q5) {
+                    dsc_e2 = pack2<BF16>(dsc_e, dsc_e), ndmn_e2 = pack2<BF16>(-dmn_e, -dmn_e);
+                    dsc_o2 = pack2<BF16>(dsc_o, dsc_o), ndmn_o2 = pack2<BF16>(-dmn_o, -dmn_o);
+                }
+#pragma unroll
+                for (uint32_t cl = 0; cl < 2u * PARTS; cl++) {  // chunk c: weights 8c..8c+7 of the even sub-block, chunk c+4: of the odd one
                     uint32_t lo_bits[4], hi_bits[4], lo_l[4], hi_l[4];
                     if constexpr (PASSES == 1 && !Q5) {
-                        const uint32_t dsc_e2 = pack2<BF16>(dsc_e, dsc_e), ndmn_e2 = pack2<BF16>(-dmn_e, -dmn_e);
-                        const uint32_t dsc_o2 = pack2<BF16>(dsc_o, dsc_o), ndmn_o2 = pack2<BF16>(-dmn_o, -dmn_o);
 #pragma unroll
                         for (uint32_t j = 0; j < 2; j++) {
                             uint32_t o4[4];
-                            dequant_word_16<BF16>(words[2 * c + j], dsc_e2, ndmn_e2, dsc_o2, ndmn_o2, o4);
+                            dequant_word_16<BF16>(words[2 * cl + j], dsc_e2, ndmn_e2, dsc_o2, ndmn_o2, o4);
                             lo_bits[2 * j] = o4[0];
                             lo_bits[2 * j + 1] = o4[1];
                             hi_bits[2 * j] = o4[2];
@@ -474,7 +525,7 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_ker
                     } else {
 #pragma unroll
                     for (uint32_t j = 0; j < 2; j++) {
-                        const uint32_t w = words[2 * c + j];
+                        const uint32_t w = words[2 * cl + j];
                         float e[4], o[4];
 #pragma unroll
                         for (uint32_t q = 0; q < 4; q++) {
@@ -483,7 +534,7 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_ker
                             // 16 bits that follows is 2^13 times coarser than the fma/mul+sub difference)
                             uint32_t ce = (w >> (8 * q)) & 15u, co = (w >> (8 * q + 4)) & 15u;
                             if constexpr (Q5) {
-                                const uint32_t hq = qhw[2 * c + j] >> (8 * q + 2 * g);  // bits 2g, 2g+1 of the weight's byte
+                                const uint32_t hq = qhw[2 * cl + j] >> (8 * q + 2 * g);  // bits 2g, 2g+1 of the weight's byte
                                 ce |= (hq & 1u) << 4;
                                 co |= (hq & 2u) << 3;
                             }
@@ -504,22 +555,18 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_ker
                         }
                     }
                     }
-                    if (!row_ok) {
-#pragma unroll
-                        for (int q = 0; q < 4; q++) lo_bits[q] = hi_bits[q] = lo_l[q] = hi_l[q] = 0u;
-                    }
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + ((c ^ sw) << 4)), "r"(lo_bits[0]),
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + choff[cl][0]), "r"(lo_bits[0]),
                                  "r"(lo_bits[1]), "r"(lo_bits[2]), "r"(lo_bits[3])
                                  : "memory");
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + (((c + 4u) ^ sw) << 4)), "r"(hi_bits[0]),
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + choff[cl][1]), "r"(hi_bits[0]),
                                  "r"(hi_bits[1]), "r"(hi_bits[2]), "r"(hi_bits[3])
                                  : "memory");
                     if constexpr (PASSES == 3) {
-                        const uint32_t tl = a_tile(s, 1) + row_off;
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tl + ((c ^ sw) << 4)), "r"(lo_l[0]),
+                        const uint32_t tl = a_tile(s, 1);
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tl + choff[cl][0]), "r"(lo_l[0]),
                                      "r"(lo_l[1]), "r"(lo_l[2]), "r"(lo_l[3])
                                      : "memory");
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tl + (((c + 4u) ^ sw) << 4)), "r"(hi_l[0]),
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tl + choff[cl][1]), "r"(hi_l[0]),
                                      "r"(hi_l[1]), "r"(hi_l[2]), "r"(hi_l[3])
                                      : "memory");
                     }
@@ -535,11 +582,14 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES>::THREADS, 1) prefill_tc_ker
         if (ok && wait_bar(acc_bar, 0, abort_flag, a.status)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t quad = warp & 3u;               // the TMEM lanes this warp may read
-            const uint32_t accum = dw / 4u;                // which 128-row accumulator
+            // the warps of one quadrant share the accumulators and, when there are more warps than accumulators, the columns
+            constexpr uint32_t NACC = (uint32_t)ROWS / 128u, NCP = P::DEQ_WARPS / 4u / NACC;
+            const uint32_t accum = (dw / 4u) % NACC;        // which 128-row accumulator
+            const uint32_t cpart = (dw / 4u) / NACC;        // which run of kTokTile / NCP columns
             const uint32_t row = n0 + accum * 128u + quad * 32u + lane;
             const float bias = (a.ksplit == 1 && a.bias && row < a.N) ? a.bias[row] : 0.f;
             float* Yout = a.ksplit == 1 ? a.Y : a.Ypart + (uint64_t)blockIdx.z * a.M * a.N;
-            for (uint32_t c0 = 0; c0 < kTokTile; c0 += 32) {
+            for (uint32_t c0 = cpart * (kTokTile / NCP); c0 < (cpart + 1u) * (kTokTile / NCP); c0 += 32) {
                 if (tok0 + c0 >= a.M) break;
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((quad * 32u) << 16) + accum * kTokTile + c0, v);
@@ -613,7 +663,7 @@ EncodeTiledFn encode_fn() {
 
 template <int ROWS, int PASSES, bool BF16, int QT = 0>
 cudaError_t launch_tc(const PrefillArgs& pa, cudaStream_t stream) {
-    using P = Plan<ROWS, PASSES>;
+    using P = Plan<ROWS, PASSES, QT>;
     static KernelConfig kcfg;  // per-device slots inside
     if (cudaError_t e = kcfg.prepare(reinterpret_cast<const void*>(prefill_tc_kernel<ROWS, PASSES, BF16, QT>), P::THREADS,
                                      P::SMEM_BYTES, nullptr))

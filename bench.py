@@ -595,7 +595,17 @@ def measure_fused_projections(ctx, torch, bp, shapes, weights_h, X, dev, stream,
         for gname, _ in groups:
             ctx.matmul(FX[gname], FW[gname], out=FY[gname])
 
-    us = graph_time_us(torch, stream, fused_pass, 1, replays=max(5, min(steps, 50)))
+    # timed like the headline: back-to-back replays between two events (a single replay between synchronisations
+    # would charge the launch of the first kernel, which the dependent launches otherwise overlap)
+    with torch.cuda.stream(stream):
+        fused_pass()
+        stream.synchronize()
+        fg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(fg, stream=stream):
+            fused_pass()
+        for _ in range(3):
+            fg.replay()
+        us = float(np.median(timed_groups(torch, None, stream, fg.replay, steps, 5, 1, dev))) * 1e3 / steps
     fbytes = sum(synth.algorithmic_bytes(1, FW[g].N, FW[g].K) for g, _ in groups)
     peak, _ = load_peaks()
     return {"what": "same weights, Q+K+V and gate+up fused by rows as the reference's loader does: 5 launches",
