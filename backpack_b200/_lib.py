@@ -121,3 +121,34 @@ def load() -> C.CDLL:
         fn.argtypes = args
     _lib = lib
     return lib
+
+
+class ModelConfig(C.Structure):
+    """bpq4k_model_config of include/bpq4k.h (the reference's ModelConfig, runtime/gguf_loader.h:164-224)."""
+    _fields_ = [("arch", C.c_char * 64)] + [(n, u32) for n in ("nLayer", "nHead", "nKvHeads", "nEmbd", "intermediateSize", "nVocab",
+                                                                 "headDim", "kvHeadDim")] + \
+               [("rmsNormEps", C.c_float), ("ropeTheta", C.c_float), ("tieWordEmbeddings", C.c_int32), ("hasQkNorm", C.c_int32),
+                ("activation", C.c_int32), ("embeddingScale", C.c_float), ("logitSoftcap", C.c_float),
+                ("slidingWindow", u32), ("nLayerAttnTypes", u32), ("hasSandwichNorm", C.c_int32), ("pleSize", u32),
+                ("sharedKvLayers", u32), ("hasMtp", C.c_int32), ("mtpNumLayers", u32)] + \
+               [(n, u32) for n in ("numExperts", "numExpertsPerTok", "moeIntermediateSize", "moeSharedIntermediateSize",
+                                   "ssmInnerSize", "ssmStateSize", "ssmConvKernel", "ssmGroupCount", "ssmTimeStepRank",
+                                   "fullAttentionInterval")] + [("ropeSections", C.c_int32 * 4)]
+
+
+class KQTensor(C.Structure):
+    """bpq4k_kq_tensor of include/bpq4k.h."""
+    _fields_ = [("w", vp), ("qtype", C.c_int32), ("N", u32), ("K", u32), ("rowStrideWords", u32), ("n_fused", u32)]
+
+
+class LayerWeights(C.Structure):
+    """bpq4k_layer_weights of include/bpq4k.h."""
+    _fields_ = [(n, KQTensor) for n in ("qkv", "q", "k", "v", "o", "gate_up", "gate", "up", "down")] + [("qkv_prefused", C.c_int32)]
+
+
+SIGNATURES["bpq4k_gguf_upload_fused"] = (C.c_int, [vp, vp, C.POINTER(u64), u32, C.c_int, C.POINTER(vp), C.POINTER(C.c_int),
+                                                   C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)])
+SIGNATURES["bpq4k_gguf_model_config"] = (C.c_int, [vp, C.POINTER(ModelConfig), vp, u32])
+SIGNATURES["bpq4k_gguf_weight_format"] = (C.c_int, [vp, C.POINTER(C.c_int), C.POINTER(C.c_int)])
+SIGNATURES["bpq4k_gguf_load_layer"] = (C.c_int, [vp, vp, u32, C.c_int, C.POINTER(LayerWeights)])
+SIGNATURES["bpq4k_free_layer"] = (C.c_int, [vp, C.POINTER(LayerWeights)])

@@ -13,8 +13,10 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <initializer_list>
 #include <new>
 #include <string>
 #include <thread>
@@ -407,34 +409,50 @@ int bpq4k_kq_respace_device(bpq4k_handle_t h, int layout_qtype, const void* raw_
     return e == cudaSuccess ? BPQ4K_OK : BPQ4K_ERR_CUDA;
 }
 
-// Load a Q4_K / Q5_K / Q6_K tensor into device memory in the layout the matmul entry points take.
-// layout_qtype: 0 = the reference's packed layout of the tensor's own type; BPQ4K_TYPE_Q6_K_PADDED for
-// a Q6_K tensor selects the padded layout.  Rows = product of all dims but the first (expert stacks
-// are row-stacked matrices).  The copy runs through four pinned 8 MB buffers, each filled by its own
-// thread and sent on its own stream, so that file reads overlap each other and the transfers; the
-// call returns when the tensor is resident.
-int bpq4k_gguf_upload_tensor(bpq4k_handle_t h, bpq4k_gguf_t g, uint64_t index, int layout_qtype, void** w_dev,
-                             int* qtype_out, uint32_t* N_out, uint32_t* K_out, uint32_t* rowStrideWords_out) {
-    if (!h || !g || !w_dev || index >= g->tensors.size()) return BPQ4K_ERR_INVALID_ARG;
+// Load Q4_K / Q5_K / Q6_K tensors into device memory in the layout the matmul entry points take.
+// layout_qtype: 0 = the reference's packed layout of the tensors' own type; BPQ4K_TYPE_Q6_K_PADDED for
+// Q6_K tensors selects the padded layout.  Rows of a tensor = product of all dims but the first (expert
+// stacks are row-stacked matrices).  Several tensors of one type and one K are concatenated by rows into
+// ONE allocation -- the reference's fuseKQ (runtime/model_runner.cpp:1002-1012) done by where the bytes
+// land instead of by a host-side copy.  The copy runs through four pinned 8 MB buffers, each filled by
+// its own thread and sent on its own stream, so that file reads overlap each other and the transfers;
+// the call returns when the tensors are resident.
+int bpq4k_gguf_upload_fused(bpq4k_handle_t h, bpq4k_gguf_t g, const uint64_t* indices, uint32_t count, int layout_qtype,
+                            void** w_dev, int* qtype_out, uint32_t* N_out, uint32_t* K_out, uint32_t* rowStrideWords_out) {
+    if (!h || !g || !w_dev || !indices || count == 0) return BPQ4K_ERR_INVALID_ARG;
     *w_dev = nullptr;
-    const TensorInfo& t = g->tensors[(size_t)index];
-    if (t.type != BPQ4K_TYPE_Q4_K && t.type != BPQ4K_TYPE_Q5_K && t.type != BPQ4K_TYPE_Q6_K)
-        return gfail(g, BPQ4K_ERR_UNSUPPORTED, t.name + ": not a Q4_K, Q5_K or Q6_K tensor");
-    int layout = layout_qtype ? layout_qtype : (int)t.type;
-    if (layout != (int)t.type && !(layout == BPQ4K_TYPE_Q6_K_PADDED && t.type == BPQ4K_TYPE_Q6_K))
-        return gfail(g, BPQ4K_ERR_INVALID_ARG, t.name + ": the requested layout does not belong to the tensor's type");
-    const uint64_t K = t.shape[0];
-    uint64_t N = 1;
-    for (uint32_t d = 1; d < t.n_dims; d++) N *= t.shape[d];
-    if (t.n_dims < 1 || K == 0 || K % 256 != 0 || N == 0 || N > 0xFFFFFFFFull || K > 0xFFFFFFFFull)
-        return gfail(g, BPQ4K_ERR_UNSUPPORTED, t.name + ": shape not supported (rows of a multiple of 256 weights)");
+    for (uint32_t i = 0; i < count; i++)
+        if (indices[i] >= g->tensors.size()) return BPQ4K_ERR_INVALID_ARG;
+    const TensorInfo& t0 = g->tensors[(size_t)indices[0]];
+    if (t0.type != BPQ4K_TYPE_Q4_K && t0.type != BPQ4K_TYPE_Q5_K && t0.type != BPQ4K_TYPE_Q6_K)
+        return gfail(g, BPQ4K_ERR_UNSUPPORTED, t0.name + ": not a Q4_K, Q5_K or Q6_K tensor");
+    int layout = layout_qtype ? layout_qtype : (int)t0.type;
+    if (layout != (int)t0.type && !(layout == BPQ4K_TYPE_Q6_K_PADDED && t0.type == BPQ4K_TYPE_Q6_K))
+        return gfail(g, BPQ4K_ERR_INVALID_ARG, t0.name + ": the requested layout does not belong to the tensor's type");
+    const uint64_t K = t0.shape[0];
+    if (t0.n_dims < 1 || K == 0 || K % 256 != 0 || K > 0xFFFFFFFFull)
+        return gfail(g, BPQ4K_ERR_UNSUPPORTED, t0.name + ": shape not supported (rows of a multiple of 256 weights)");
     const uint32_t nb = (uint32_t)(K / 256);
-    const uint64_t raw_bytes = N * nb * bpq4k_kq_block_bytes((int)t.type);
-    const uint64_t start = g->data_offset + t.offset;
-    if (start > g->file_size || raw_bytes > g->file_size - start) return gfail(g, BPQ4K_ERR_INVALID_ARG, t.name + ": data lies outside the file");
+    const uint32_t file_bb = bpq4k_kq_block_bytes((int)t0.type);
+    uint64_t N = 0;
+    std::vector<uint64_t> rows(count);
+    for (uint32_t i = 0; i < count; i++) {
+        const TensorInfo& t = g->tensors[(size_t)indices[i]];
+        if (t.type != t0.type || t.shape[0] != K)
+            return gfail(g, BPQ4K_ERR_INVALID_ARG, t.name + ": tensors fused by rows need one type and one row length");
+        uint64_t n = 1;
+        for (uint32_t d = 1; d < t.n_dims; d++) n *= t.shape[d];
+        const uint64_t bytes = n * nb * file_bb, start = g->data_offset + t.offset;
+        if (n == 0 || start > g->file_size || bytes > g->file_size - start)
+            return gfail(g, BPQ4K_ERR_INVALID_ARG, t.name + ": data lies outside the file");
+        rows[i] = n;
+        N += n;
+    }
+    if (N > 0xFFFFFFFFull) return gfail(g, BPQ4K_ERR_UNSUPPORTED, t0.name + ": more than 2^32 rows");
+    const uint64_t raw_bytes = N * nb * file_bb;
     const uint32_t rs = bpq4k_kq_row_stride_words(layout, (uint32_t)K);
     const uint64_t out_bytes = N * (uint64_t)rs * 4u;
-    const bool respace = t.type == BPQ4K_TYPE_Q6_K;  // Q4_K / Q5_K: file bytes are the device bytes
+    const bool respace = t0.type == BPQ4K_TYPE_Q6_K;  // Q4_K / Q5_K: file bytes are the device bytes
 
     int dev_prev = -1;
     cudaGetDevice(&dev_prev);
@@ -462,38 +480,48 @@ int bpq4k_gguf_upload_tensor(bpq4k_handle_t h, bpq4k_gguf_t g, uint64_t index, i
         if (!ok) {
             cudaGetLastError();
             restore();
-            return gfail(g, BPQ4K_ERR_ALLOC, t.name + ": staging allocation failed");
+            return gfail(g, BPQ4K_ERR_ALLOC, t0.name + ": staging allocation failed");
         }
     }
     if (cudaMalloc(&out, out_bytes ? out_bytes : 16) != cudaSuccess) {
         cudaGetLastError();
         restore();
-        return gfail(g, BPQ4K_ERR_ALLOC, t.name + ": device allocation failed");
+        return gfail(g, BPQ4K_ERR_ALLOC, t0.name + ": device allocation failed");
     }
     raw_dev = out;
     if (respace && cudaMalloc(&raw_dev, raw_bytes) != cudaSuccess) {
         cudaGetLastError();
         raw_dev = nullptr;
-        status = gfail(g, BPQ4K_ERR_ALLOC, t.name + ": device allocation failed");
+        status = gfail(g, BPQ4K_ERR_ALLOC, t0.name + ": device allocation failed");
     }
     auto cleanup = [&]() {
         if (raw_dev && raw_dev != out) cudaFree(raw_dev);
     };
     if (status == BPQ4K_OK) {
-        // lane i takes chunks i, i+kLanes, ...: read into its pinned buffer, copy on its stream, wait,
-        // next chunk -- file reads of one lane overlap the transfers of the others
-        const uint64_t n_chunks = (raw_bytes + kChunk - 1) / kChunk;
+        // One list of (file position, device position, bytes) chunks over all tensors; lane i takes chunks
+        // i, i+kLanes, ...: read into its pinned buffer, copy on its stream, wait, next chunk -- file reads of one
+        // lane overlap the transfers of the others
+        struct Piece { uint64_t file_pos, dev_off, n; };
+        std::vector<Piece> pieces;
+        uint64_t dev_off = 0;
+        for (uint32_t i = 0; i < count; i++) {
+            const TensorInfo& t = g->tensors[(size_t)indices[i]];
+            const uint64_t bytes = rows[i] * nb * file_bb, start = g->data_offset + t.offset;
+            for (uint64_t off = 0; off < bytes; off += kChunk)
+                pieces.push_back({start + off, dev_off + off, bytes - off < kChunk ? bytes - off : kChunk});
+            dev_off += bytes;
+        }
         int lane_status[kLanes] = {0, 0, 0, 0};
         auto work = [&](int lane) {
             cudaSetDevice(dev);
-            for (uint64_t ch = (uint64_t)lane; ch < n_chunks; ch += kLanes) {
-                const uint64_t off = ch * kChunk, n = raw_bytes - off < kChunk ? raw_bytes - off : kChunk;
-                Cursor c{g->fd, start + off, g->file_size};
-                if (!c.read(g->pinned[lane], n)) {
+            for (size_t ch = (size_t)lane; ch < pieces.size(); ch += kLanes) {
+                const Piece& pc = pieces[ch];
+                Cursor c{g->fd, pc.file_pos, g->file_size};
+                if (!c.read(g->pinned[lane], pc.n)) {
                     lane_status[lane] = 1;
                     return;
                 }
-                if (cudaMemcpyAsync(static_cast<uint8_t*>(raw_dev) + off, g->pinned[lane], n, cudaMemcpyHostToDevice,
+                if (cudaMemcpyAsync(static_cast<uint8_t*>(raw_dev) + pc.dev_off, g->pinned[lane], pc.n, cudaMemcpyHostToDevice,
                                     g->lane_stream[lane]) != cudaSuccess ||
                     cudaStreamSynchronize(g->lane_stream[lane]) != cudaSuccess) {
                     lane_status[lane] = 2;
@@ -502,15 +530,15 @@ int bpq4k_gguf_upload_tensor(bpq4k_handle_t h, bpq4k_gguf_t g, uint64_t index, i
             }
         };
         std::vector<std::thread> pool;
-        const int used = n_chunks < (uint64_t)kLanes ? (int)n_chunks : kLanes;
+        const int used = pieces.size() < (size_t)kLanes ? (int)pieces.size() : kLanes;
         for (int i = 1; i < used; i++) pool.emplace_back(work, i);
         if (used > 0) work(0);
         for (auto& th : pool) th.join();
         for (int i = 0; i < kLanes; i++) {
-            if (lane_status[i] == 1) status = gfail(g, BPQ4K_ERR_INVALID_ARG, t.name + ": short read");
+            if (lane_status[i] == 1) status = gfail(g, BPQ4K_ERR_INVALID_ARG, t0.name + ": short read");
             if (lane_status[i] == 2) {
                 cudaGetLastError();
-                status = gfail(g, BPQ4K_ERR_CUDA, t.name + ": copy to the device failed");
+                status = gfail(g, BPQ4K_ERR_CUDA, t0.name + ": copy to the device failed");
             }
         }
     }
@@ -521,11 +549,11 @@ int bpq4k_gguf_upload_tensor(bpq4k_handle_t h, bpq4k_gguf_t g, uint64_t index, i
         if (ctas > 148ull * 32) ctas = 148ull * 32;
         q6k_respace_kernel<<<(unsigned)ctas, 256, 0, st>>>(static_cast<const uint8_t*>(raw_dev), nblocks, nb, static_cast<uint8_t*>(out),
                                                          (uint64_t)rs * 4u, bpq4k_kq_block_bytes(layout));
-        if (cudaGetLastError() != cudaSuccess) status = gfail(g, BPQ4K_ERR_CUDA, t.name + ": re-spacing kernel failed to launch");
+        if (cudaGetLastError() != cudaSuccess) status = gfail(g, BPQ4K_ERR_CUDA, t0.name + ": re-spacing kernel failed to launch");
     }
     if (cudaStreamSynchronize(st) != cudaSuccess && status == BPQ4K_OK) {
         cudaGetLastError();
-        status = gfail(g, BPQ4K_ERR_CUDA, t.name + ": upload failed");
+        status = gfail(g, BPQ4K_ERR_CUDA, t0.name + ": upload failed");
     }
     cleanup();
     if (status != BPQ4K_OK) {
@@ -539,6 +567,212 @@ int bpq4k_gguf_upload_tensor(bpq4k_handle_t h, bpq4k_gguf_t g, uint64_t index, i
     if (N_out) *N_out = (uint32_t)N;
     if (K_out) *K_out = (uint32_t)K;
     if (rowStrideWords_out) *rowStrideWords_out = rs;
+    return BPQ4K_OK;
+}
+
+int bpq4k_gguf_upload_tensor(bpq4k_handle_t h, bpq4k_gguf_t g, uint64_t index, int layout_qtype, void** w_dev,
+                             int* qtype_out, uint32_t* N_out, uint32_t* K_out, uint32_t* rowStrideWords_out) {
+    return bpq4k_gguf_upload_fused(h, g, &index, 1, layout_qtype, w_dev, qtype_out, N_out, K_out, rowStrideWords_out);
+}
+
+// ---- model configuration and the per-layer K-quant tensors ---------------------------------------
+
+namespace {
+bool has_tensor(bpq4k_gguf* g, const std::string& name) { return g->index.count(name) != 0; }
+bool is_kquant(uint32_t type) { return type == BPQ4K_TYPE_Q4_K || type == BPQ4K_TYPE_Q5_K || type == BPQ4K_TYPE_Q6_K; }
+}  // namespace
+
+// extractModelConfig (runtime/gguf_loader.cpp:184-317), field for field.
+int bpq4k_gguf_model_config(bpq4k_gguf_t g, bpq4k_model_config* c, uint8_t* layer_attn_types, uint32_t cap) {
+    if (!g || !c) return BPQ4K_ERR_INVALID_ARG;
+    std::memset(c, 0, sizeof(*c));
+    auto str = [&](const std::string& key, const char* def) -> std::string {
+        auto it = g->meta.find(key);
+        return it != g->meta.end() && it->second.type == kString ? it->second.s : std::string(def);
+    };
+    auto u32 = [&](const std::string& key, uint32_t def = 0) { return bpq4k_gguf_get_u32(g, key.c_str(), def); };
+    auto f32 = [&](const std::string& key, float def) { return bpq4k_gguf_get_f32(g, key.c_str(), def); };
+    const std::string a = str("general.architecture", "llama");
+    std::snprintf(c->arch, sizeof(c->arch), "%s", a.c_str());
+    c->nLayer = u32(a + ".block_count");
+    c->nEmbd = u32(a + ".embedding_length");
+    c->intermediateSize = u32(a + ".feed_forward_length");
+    c->nHead = u32(a + ".attention.head_count");
+    c->nKvHeads = u32(a + ".attention.head_count_kv", c->nHead);
+    c->rmsNormEps = f32(a + ".attention.layer_norm_rms_epsilon", 1e-6f);
+    c->ropeTheta = f32(a + ".rope.freq_base", 1000000.0f);
+    c->tieWordEmbeddings = g->meta.count("output.weight") ? 0 : 1;  // the reference asks the metadata, not the tensor list
+    const uint32_t dense_head = c->nHead > 0 ? c->nEmbd / c->nHead : 0;
+    c->kvHeadDim = u32(a + ".attention.key_length", dense_head);
+    c->headDim = c->kvHeadDim > 0 ? c->kvHeadDim : dense_head;
+    {
+        auto it = g->index.find("token_embd.weight");
+        if (it != g->index.end()) {
+            const TensorInfo& t = g->tensors[(size_t)it->second];
+            c->nVocab = (uint32_t)(t.n_dims >= 2 ? t.shape[1] : t.shape[0]);
+        }
+    }
+    c->hasQkNorm = has_tensor(g, "blk.0.attn_q_norm.weight");
+    for (uint32_t i = 1; !c->hasQkNorm && i < c->nLayer; i++)
+        c->hasQkNorm = has_tensor(g, "blk." + std::to_string(i) + ".attn_q_norm.weight");
+    const bool gemma = a == "gemma" || a == "gemma2" || a == "gemma3" || a == "gemma4";
+    c->activation = gemma ? 1 : 0;
+    c->embeddingScale = gemma ? sqrtf((float)c->nEmbd) : 0.0f;
+    c->logitSoftcap = f32(a + ".final_logit_softcapping", 0.0f);
+    c->slidingWindow = u32(a + ".attention.sliding_window", 0);
+    c->nLayerAttnTypes = 0;
+    if (c->slidingWindow > 0 && c->nLayer > 0) {
+        c->nLayerAttnTypes = c->nLayer;
+        const MetaValue* pattern = nullptr;
+        if (a == "gemma4") {
+            auto it = g->meta.find(a + ".attention.sliding_window_pattern");
+            if (it != g->meta.end() && it->second.type == kArray && it->second.elem_type == kBool &&
+                it->second.ints.size() == c->nLayer)
+                pattern = &it->second;
+        }
+        for (uint32_t i = 0; i < c->nLayer && layer_attn_types && i < cap; i++) {
+            uint8_t sliding = 0;  // Global unless the architecture says otherwise
+            if (a == "gemma2") sliding = (i % 2 == 0);
+            if (a == "gemma3") sliding = ((i + 1) % 6 != 0);
+            if (a == "gemma4") sliding = pattern ? (pattern->ints[i] != 0) : ((i + 1) % 6 != 0);
+            layer_attn_types[i] = sliding;
+        }
+    }
+    c->sharedKvLayers = u32(a + ".attention.shared_kv_layers", 0);
+    c->pleSize = u32(a + ".embedding_length_per_layer_input", 0);
+    c->hasSandwichNorm = has_tensor(g, "blk.0.post_norm.weight") || has_tensor(g, "blk.0.attn_post_norm.weight") ||
+                         has_tensor(g, "blk.0.post_attention_norm.weight");
+    c->hasMtp = has_tensor(g, "mtp.0.blk.0.attn_q.weight") || has_tensor(g, "mtp.0.enorm.weight");
+    if (!c->hasMtp) {
+        const uint32_t nextn = u32(a + ".nextn_predict_layers", 0);
+        if (nextn > 0) {
+            c->hasMtp = 1;
+            c->mtpNumLayers = nextn;
+        }
+    }
+    c->numExperts = u32(a + ".expert_count", 0);
+    c->numExpertsPerTok = u32(a + ".expert_used_count", 0);
+    c->moeIntermediateSize = u32(a + ".expert_feed_forward_length", 0);
+    c->moeSharedIntermediateSize = u32(a + ".expert_shared_feed_forward_length", c->moeIntermediateSize);
+    c->ssmInnerSize = u32(a + ".ssm.inner_size", 0);
+    c->ssmStateSize = u32(a + ".ssm.state_size", 0);
+    c->ssmConvKernel = u32(a + ".ssm.conv_kernel", 0);
+    c->ssmGroupCount = u32(a + ".ssm.group_count", 0);
+    c->ssmTimeStepRank = u32(a + ".ssm.time_step_rank", 0);
+    c->fullAttentionInterval = u32(a + ".full_attention_interval", 0);
+    c->ropeSections[0] = 11, c->ropeSections[1] = 11, c->ropeSections[2] = 10, c->ropeSections[3] = 0;
+    {
+        auto it = g->meta.find(a + ".rope.dimension_sections");
+        if (it != g->meta.end() && it->second.type == kArray && it->second.elem_type == kI32 && it->second.ints.size() >= 4)
+            for (int i = 0; i < 4; i++) c->ropeSections[i] = (int32_t)it->second.ints[(size_t)i];
+    }
+    return BPQ4K_OK;
+}
+
+// The loader's quantisation probe (runtime/model_runner.cpp:1014-1049): the type of the first primary weight
+// tensor found, and whether attn_q, ffn_gate and ffn_down of layer 0 all carry that one K-quant type.
+int bpq4k_gguf_weight_format(bpq4k_gguf_t g, int* qtype, int* uniform_kquant) {
+    if (!g || !qtype || !uniform_kquant) return BPQ4K_ERR_INVALID_ARG;
+    *qtype = -1;
+    for (const char* name : {"blk.0.attn_q.weight", "blk.0.attn_qkv.weight", "blk.0.ffn_gate.weight", "blk.0.ffn_down.weight"}) {
+        auto it = g->index.find(name);
+        if (it != g->index.end()) {
+            *qtype = (int)g->tensors[(size_t)it->second].type;
+            break;
+        }
+    }
+    bool same = true;
+    for (const char* name : {"blk.0.attn_q.weight", "blk.0.ffn_gate.weight", "blk.0.ffn_down.weight"}) {
+        auto it = g->index.find(name);
+        if (it == g->index.end()) continue;
+        const uint32_t t = g->tensors[(size_t)it->second].type;
+        if (!is_kquant(t) || (int)t != *qtype) same = false;
+    }
+    *uniform_kquant = same && *qtype >= 0 && is_kquant((uint32_t)*qtype) ? 1 : 0;
+    return BPQ4K_OK;
+}
+
+// One transformer layer's projection weights onto the device with the loader's fusion rules
+// (runtime/model_runner.cpp:1223-1370): Q+K+V concatenated by rows into one tensor (or a file's pre-fused
+// attn_qkv taken as it is), attn_output, gate+up concatenated, ffn_down.  A group is fused when all its members
+// are K-quant tensors of ONE type and one row length; otherwise every K-quant member is uploaded on its own
+// (the reference sends such layers through its Q8 re-quantisation, which is not part of this library).
+// Members that are absent or not K-quant stay empty (w == NULL, qtype = the file's type or -1).
+int bpq4k_gguf_load_layer(bpq4k_handle_t h, bpq4k_gguf_t g, uint32_t layer, int q6_layout, bpq4k_layer_weights* out) {
+    if (!h || !g || !out) return BPQ4K_ERR_INVALID_ARG;
+    std::memset(out, 0, sizeof(*out));
+    const std::string pfx = "blk." + std::to_string(layer) + ".";
+    auto find = [&](const char* name, uint64_t* idx) {
+        auto it = g->index.find(pfx + name);
+        if (it == g->index.end()) return false;
+        *idx = it->second;
+        return true;
+    };
+    auto type_of = [&](uint64_t idx) { return g->tensors[(size_t)idx].type; };
+    auto put = [&](bpq4k_kq_tensor* dst, const uint64_t* idx, uint32_t n) -> int {
+        const int layout = (type_of(idx[0]) == BPQ4K_TYPE_Q6_K && q6_layout == BPQ4K_TYPE_Q6_K_PADDED) ? BPQ4K_TYPE_Q6_K_PADDED : 0;
+        dst->n_fused = n;
+        return bpq4k_gguf_upload_fused(h, g, idx, n, layout, &dst->w, &dst->qtype, &dst->N, &dst->K, &dst->rowStrideWords);
+    };
+    auto single = [&](const char* name, bpq4k_kq_tensor* dst) -> int {
+        uint64_t idx;
+        dst->qtype = -1;
+        if (!find(name, &idx)) return BPQ4K_OK;
+        dst->qtype = (int)type_of(idx);
+        if (!is_kquant(type_of(idx))) return BPQ4K_OK;
+        return put(dst, &idx, 1);
+    };
+    auto same_rows = [&](const uint64_t* idx, uint32_t n) {
+        for (uint32_t i = 0; i < n; i++)
+            if (!is_kquant(type_of(idx[i])) || type_of(idx[i]) != type_of(idx[0]) ||
+                g->tensors[(size_t)idx[i]].shape[0] != g->tensors[(size_t)idx[0]].shape[0])
+                return false;
+        return true;
+    };
+    int st = BPQ4K_OK;
+    uint64_t q, k, v, qkv, gi, ui;
+    out->qkv.qtype = out->q.qtype = out->k.qtype = out->v.qtype = -1;
+    out->gate_up.qtype = out->gate.qtype = out->up.qtype = -1;
+    const bool hq = find("attn_q.weight", &q), hk = find("attn_k.weight", &k), hv = find("attn_v.weight", &v);
+    if (!hq && find("attn_qkv.weight", &qkv)) {
+        out->qkv.qtype = (int)type_of(qkv);
+        if (is_kquant(type_of(qkv))) st = put(&out->qkv, &qkv, 1);
+        out->qkv_prefused = 1;
+    } else if (hq && hk && hv) {
+        const uint64_t idx[3] = {q, k, v};
+        if (same_rows(idx, 3)) {
+            st = put(&out->qkv, idx, 3);
+        } else {
+            st = single("attn_q.weight", &out->q);
+            if (st == BPQ4K_OK) st = single("attn_k.weight", &out->k);
+            if (st == BPQ4K_OK) st = single("attn_v.weight", &out->v);
+        }
+    } else if (hq) {  // layers that share K/V with an earlier layer ship attn_q only
+        st = single("attn_q.weight", &out->q);
+    }
+    if (st == BPQ4K_OK) st = single("attn_output.weight", &out->o);
+    if (st == BPQ4K_OK) {
+        if (find("ffn_gate.weight", &gi) && find("ffn_up.weight", &ui)) {
+            const uint64_t idx[2] = {gi, ui};
+            if (same_rows(idx, 2)) {
+                st = put(&out->gate_up, idx, 2);
+            } else {
+                st = single("ffn_gate.weight", &out->gate);
+                if (st == BPQ4K_OK) st = single("ffn_up.weight", &out->up);
+            }
+        }
+    }
+    if (st == BPQ4K_OK) st = single("ffn_down.weight", &out->down);
+    if (st != BPQ4K_OK) bpq4k_free_layer(h, out);
+    return st;
+}
+
+int bpq4k_free_layer(bpq4k_handle_t h, bpq4k_layer_weights* lw) {
+    if (!h || !lw) return BPQ4K_ERR_INVALID_ARG;
+    for (bpq4k_kq_tensor* t : {&lw->qkv, &lw->q, &lw->k, &lw->v, &lw->o, &lw->gate_up, &lw->gate, &lw->up, &lw->down}) {
+        if (t->w) bpq4k_free_device(h, t->w);
+        t->w = nullptr;
+    }
     return BPQ4K_OK;
 }
 

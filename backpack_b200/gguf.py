@@ -160,3 +160,56 @@ class GGUFFile:
         if st:
             raise Q4KError(st, self.lib.bpq4k_gguf_last_error(self.h).decode())
         return DeviceTensor(ctx, ptr.value, qt.value, N.value, K.value, rs.value)
+
+    def upload_fused(self, ctx: Q4KContext, names, layout: int = 0) -> DeviceTensor:
+        """Several tensors of one K-quant type and one K, concatenated by rows into one device tensor
+        (the reference's fuseKQ + uploadKQWeight, runtime/model_runner.cpp:1002-1012)."""
+        idx = (C.c_uint64 * len(names))(*[self.tensor_index[n] for n in names])
+        ptr, qt, N, K, rs = C.c_void_p(), C.c_int(), C.c_uint32(), C.c_uint32(), C.c_uint32()
+        st = self.lib.bpq4k_gguf_upload_fused(ctx.h, self.h, idx, len(names), layout, C.byref(ptr), C.byref(qt), C.byref(N),
+                                              C.byref(K), C.byref(rs))
+        if st:
+            raise Q4KError(st, self.lib.bpq4k_gguf_last_error(self.h).decode())
+        return DeviceTensor(ctx, ptr.value, qt.value, N.value, K.value, rs.value)
+
+    # -- model level (extractModelConfig and the loader's per-layer rules) -----------------
+    def model_config(self) -> dict:
+        """The reference's ModelConfig (extractModelConfig, runtime/gguf_loader.cpp:184-317) as a dict; the
+        per-layer attention types (0 global, 1 sliding window) under 'layerAttnTypes'."""
+        cfg = _lib.ModelConfig()
+        types = (C.c_uint8 * 4096)()
+        st = self.lib.bpq4k_gguf_model_config(self.h, C.byref(cfg), types, 4096)
+        if st:
+            raise Q4KError(st, "model_config")
+        out = {}
+        for name, _ in _lib.ModelConfig._fields_:
+            v = getattr(cfg, name)
+            out[name] = v.decode() if name == "arch" else list(v) if name == "ropeSections" else v
+        out["layerAttnTypes"] = [int(types[i]) for i in range(min(cfg.nLayerAttnTypes, 4096))]
+        return out
+
+    def weight_format(self):
+        """(GGML type of the first primary weight tensor, whether layer 0's attn_q / ffn_gate / ffn_down all carry
+        that one K-quant type): the loader's probe at runtime/model_runner.cpp:1014-1049."""
+        qt, uni = C.c_int(), C.c_int()
+        st = self.lib.bpq4k_gguf_weight_format(self.h, C.byref(qt), C.byref(uni))
+        if st:
+            raise Q4KError(st, "weight_format")
+        return qt.value, bool(uni.value)
+
+    def load_layer(self, ctx: Q4KContext, layer: int, q6_layout: int = 0) -> dict:
+        """One layer's projection weights on the device with the loader's fusion rules
+        (runtime/model_runner.cpp:1223-1370).  Returns {'qkv' | 'q','k','v', 'o', 'gate_up' | 'gate','up', 'down':
+        DeviceTensor} for the K-quant tensors that exist, plus 'qkv_prefused' and 'n_fused' per entry."""
+        lw = _lib.LayerWeights()
+        st = self.lib.bpq4k_gguf_load_layer(ctx.h, self.h, layer, q6_layout, C.byref(lw))
+        if st:
+            raise Q4KError(st, self.lib.bpq4k_gguf_last_error(self.h).decode())
+        out = {"qkv_prefused": bool(lw.qkv_prefused), "n_fused": {}, "file_types": {}}
+        for name, _ in _lib.LayerWeights._fields_[:-1]:
+            t = getattr(lw, name)
+            out["file_types"][name] = int(t.qtype)
+            if t.w:
+                out[name] = DeviceTensor(ctx, t.w, t.qtype, t.N, t.K, t.rowStrideWords)
+                out["n_fused"][name] = int(t.n_fused)
+        return out

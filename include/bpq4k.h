@@ -419,6 +419,59 @@ int bpq4k_gguf_read_tensor(bpq4k_gguf_t g, uint64_t index, uint64_t first, uint6
 int bpq4k_gguf_upload_tensor(bpq4k_handle_t h, bpq4k_gguf_t g, uint64_t index, int layout_qtype, void** w_dev,
                              int* qtype_out, uint32_t* N_out, uint32_t* K_out, uint32_t* rowStrideWords_out);
 
+/* Several tensors of one K-quant type and one row length, concatenated by rows into ONE device allocation:
+ * fuseKQ + uploadKQWeight (runtime/model_runner.cpp:1002-1012, 958-963) without the host-side copy.  Arguments
+ * as bpq4k_gguf_upload_tensor, with `count` tensor indices; N_out is the sum of the rows. */
+int bpq4k_gguf_upload_fused(bpq4k_handle_t h, bpq4k_gguf_t g, const uint64_t* indices, uint32_t count, int layout_qtype,
+                            void** w_dev, int* qtype_out, uint32_t* N_out, uint32_t* K_out, uint32_t* rowStrideWords_out);
+
+/* ModelConfig as extractModelConfig fills it (runtime/gguf_loader.h:164-224, runtime/gguf_loader.cpp:184-317):
+ * same fields, same keys, same defaults.  activation: 0 SiLU, 1 GELU (the Gemma family).  The per-layer
+ * attention types (0 global, 1 sliding window; present only when slidingWindow > 0) are written to
+ * layer_attn_types[0 .. min(cap, nLayerAttnTypes)) when that pointer is given. */
+typedef struct bpq4k_model_config {
+    char arch[64];
+    uint32_t nLayer, nHead, nKvHeads, nEmbd, intermediateSize, nVocab, headDim, kvHeadDim;
+    float rmsNormEps, ropeTheta;
+    int32_t tieWordEmbeddings, hasQkNorm;
+    int32_t activation;
+    float embeddingScale, logitSoftcap;
+    uint32_t slidingWindow, nLayerAttnTypes;
+    int32_t hasSandwichNorm;
+    uint32_t pleSize, sharedKvLayers;
+    int32_t hasMtp;
+    uint32_t mtpNumLayers;
+    uint32_t numExperts, numExpertsPerTok, moeIntermediateSize, moeSharedIntermediateSize;
+    uint32_t ssmInnerSize, ssmStateSize, ssmConvKernel, ssmGroupCount, ssmTimeStepRank, fullAttentionInterval;
+    int32_t ropeSections[4];
+} bpq4k_model_config;
+int bpq4k_gguf_model_config(bpq4k_gguf_t g, bpq4k_model_config* out, uint8_t* layer_attn_types, uint32_t cap);
+
+/* The loader's quantisation probe (runtime/model_runner.cpp:1014-1049): *qtype = GGML type of the first of
+ * blk.0.attn_q / attn_qkv / ffn_gate / ffn_down that exists (-1: none), *uniform_kquant = 1 when attn_q, ffn_gate
+ * and ffn_down of layer 0 all carry that one K-quant type (the reference's `isKQuant`). */
+int bpq4k_gguf_weight_format(bpq4k_gguf_t g, int* qtype, int* uniform_kquant);
+
+/* A layer's projection weights on the device, with the loader's fusion rules (runtime/model_runner.cpp:1223-1370):
+ * Q+K+V by rows into `qkv` (n_fused = 3; a file's pre-fused attn_qkv: n_fused = 1, qkv_prefused = 1), attn_output
+ * into `o`, gate+up into `gate_up` (n_fused = 2), ffn_down into `down`.  A group is fused when all members are
+ * K-quant tensors of one type and one row length; otherwise each K-quant member is uploaded on its own (q, k, v,
+ * gate, up) -- the reference sends such layers through its Q8 re-quantisation, which this library does not have,
+ * and its fuseKQ would give a mixed-type group the first member's row stride.  Absent or non-K-quant members:
+ * w = NULL, qtype = the file's GGML type or -1.  q6_layout = BPQ4K_TYPE_Q6_K_PADDED stores Q6_K tensors in the
+ * padded layout of the fast kernels.  Free with bpq4k_free_layer. */
+typedef struct bpq4k_kq_tensor {
+    void* w;
+    int32_t qtype;
+    uint32_t N, K, rowStrideWords, n_fused;
+} bpq4k_kq_tensor;
+typedef struct bpq4k_layer_weights {
+    bpq4k_kq_tensor qkv, q, k, v, o, gate_up, gate, up, down;
+    int32_t qkv_prefused;
+} bpq4k_layer_weights;
+int bpq4k_gguf_load_layer(bpq4k_handle_t h, bpq4k_gguf_t g, uint32_t layer, int q6_layout, bpq4k_layer_weights* out);
+int bpq4k_free_layer(bpq4k_handle_t h, bpq4k_layer_weights* lw);
+
 /* The small-M matmul for callers that must not allocate device memory.  It has no counterpart
  * in the reference.
  *

@@ -177,4 +177,45 @@ int64_t ref_gguf_i32_array(void* p, const char* key, int32_t* out, uint64_t cap)
     return (int64_t)a->size();
 }
 
+// extractModelConfig (runtime/gguf_loader.cpp:184-317) through a plain struct: the fields of the reference's
+// ModelConfig in the order of the library's bpq4k_model_config (tests compare the two byte for byte).
+struct ref_model_config {
+    char arch[64];
+    uint32_t nLayer, nHead, nKvHeads, nEmbd, intermediateSize, nVocab, headDim, kvHeadDim;
+    float rmsNormEps, ropeTheta;
+    int32_t tieWordEmbeddings, hasQkNorm;
+    int32_t activation;
+    float embeddingScale, logitSoftcap;
+    uint32_t slidingWindow, nLayerAttnTypes;
+    int32_t hasSandwichNorm;
+    uint32_t pleSize, sharedKvLayers;
+    int32_t hasMtp;
+    uint32_t mtpNumLayers;
+    uint32_t numExperts, numExpertsPerTok, moeIntermediateSize, moeSharedIntermediateSize;
+    uint32_t ssmInnerSize, ssmStateSize, ssmConvKernel, ssmGroupCount, ssmTimeStepRank, fullAttentionInterval;
+    int32_t ropeSections[4];
+};
+int ref_extract_model_config(void* p, ref_model_config* c, uint8_t* layer_attn_types, uint32_t cap) {
+    const ModelConfig m = extractModelConfig(*static_cast<GGUFFile*>(p));
+    std::memset(c, 0, sizeof(*c));
+    std::snprintf(c->arch, sizeof(c->arch), "%s", m.arch.c_str());
+    c->nLayer = m.nLayer; c->nHead = m.nHead; c->nKvHeads = m.nKvHeads; c->nEmbd = m.nEmbd;
+    c->intermediateSize = m.intermediateSize; c->nVocab = m.nVocab; c->headDim = m.headDim; c->kvHeadDim = m.kvHeadDim;
+    c->rmsNormEps = m.rmsNormEps; c->ropeTheta = m.ropeTheta;
+    c->tieWordEmbeddings = m.tieWordEmbeddings; c->hasQkNorm = m.hasQkNorm;
+    c->activation = m.activation == ActivationType::GELU ? 1 : 0;
+    c->embeddingScale = m.embeddingScale; c->logitSoftcap = m.logitSoftcap;
+    c->slidingWindow = m.slidingWindow; c->nLayerAttnTypes = (uint32_t)m.layerAttnTypes.size();
+    for (uint32_t i = 0; i < m.layerAttnTypes.size() && layer_attn_types && i < cap; i++)
+        layer_attn_types[i] = m.layerAttnTypes[i] == AttnLayerType::SlidingWindow ? 1 : 0;
+    c->hasSandwichNorm = m.hasSandwichNorm; c->pleSize = m.pleSize; c->sharedKvLayers = m.sharedKvLayers;
+    c->hasMtp = m.hasMtp; c->mtpNumLayers = m.mtpNumLayers;
+    c->numExperts = m.numExperts; c->numExpertsPerTok = m.numExpertsPerTok;
+    c->moeIntermediateSize = m.moeIntermediateSize; c->moeSharedIntermediateSize = m.moeSharedIntermediateSize;
+    c->ssmInnerSize = m.ssmInnerSize; c->ssmStateSize = m.ssmStateSize; c->ssmConvKernel = m.ssmConvKernel;
+    c->ssmGroupCount = m.ssmGroupCount; c->ssmTimeStepRank = m.ssmTimeStepRank; c->fullAttentionInterval = m.fullAttentionInterval;
+    for (int i = 0; i < 4; i++) c->ropeSections[i] = i < (int)m.ropeSections.size() ? m.ropeSections[i] : 0;
+    return 0;
+}
+
 }  // extern "C"
