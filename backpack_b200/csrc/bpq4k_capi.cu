@@ -623,8 +623,8 @@ int bpq4k_matmul_fused_f32(bpq4k_handle_t h, int qtype, int prologue, const floa
                            uint32_t rowStrideWords, uint32_t yOffset, void* stream) {
     if (!h) return BPQ4K_ERR_INVALID_ARG;
     if (N == 0) return BPQ4K_OK;
-    if (qtype != BPQ4K_TYPE_Q4_K && qtype != BPQ4K_TYPE_Q5_K)
-        return fail(h, BPQ4K_ERR_UNSUPPORTED, "the fused forms cover Q4_K (12) and Q5_K (13), not type %d", qtype);
+    if (qtype != BPQ4K_TYPE_Q4_K && qtype != BPQ4K_TYPE_Q5_K && qtype != BPQ4K_TYPE_Q6_K_PADDED)
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "the fused forms cover Q4_K (12), Q5_K (13) and padded Q6_K (270), not type %d", qtype);
     if (prologue < BPQ4K_PROLOGUE_NONE || prologue > BPQ4K_PROLOGUE_SILU_MUL)
         return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown prologue %d", prologue);
     if (int s = check_kq_weights(h, qtype, W, K, rowStrideWords)) return s;
@@ -647,8 +647,10 @@ int bpq4k_matmul_fused_f32(bpq4k_handle_t h, int qtype, int prologue, const floa
     a.eps = eps;
     a.residual = residual;
     int launches = 0;
-    const cudaError_t e = launch_gemv_stream(a, h->tune, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count, &h->tmaps,
-                                             static_cast<cudaStream_t>(stream), &launches, qtype);
+    const cudaError_t e = qtype == BPQ4K_TYPE_Q6_K_PADDED
+                              ? launch_q6k_stream(a, h->tune, h->dev_status, h->sm_count, &h->tmaps, static_cast<cudaStream_t>(stream), &launches)
+                              : launch_gemv_stream(a, h->tune, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count, &h->tmaps,
+                                                   static_cast<cudaStream_t>(stream), &launches, qtype);
     h->launches += (uint64_t)launches;
     if (e == cudaErrorInvalidValue) {
         cudaGetLastError();
@@ -755,8 +757,8 @@ int bpq4k_moe_ffn_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W
                       uint32_t nExperts, uint32_t H, uint32_t F, float* work, uint64_t work_floats, void* stream) {
     if (!h) return BPQ4K_ERR_INVALID_ARG;
     if (T == 0 || topk == 0) return BPQ4K_OK;
-    if (qtype != BPQ4K_TYPE_Q4_K && qtype != BPQ4K_TYPE_Q5_K)
-        return fail(h, BPQ4K_ERR_UNSUPPORTED, "the routed-expert layer covers Q4_K (12) and Q5_K (13), not type %d", qtype);
+    if (qtype != BPQ4K_TYPE_Q4_K && qtype != BPQ4K_TYPE_Q5_K && qtype != BPQ4K_TYPE_Q6_K_PADDED)
+        return fail(h, BPQ4K_ERR_UNSUPPORTED, "the routed-expert layer covers Q4_K (12), Q5_K (13) and padded Q6_K (270), not type %d", qtype);
     if (nExperts == 0 || H == 0 || F == 0) return fail(h, BPQ4K_ERR_INVALID_ARG, "nExperts, H or F is 0");
     if (H % 256u || F % 256u) return fail(h, BPQ4K_ERR_UNSUPPORTED, "H=%u and F=%u must be multiples of 256", H, F);
     const uint64_t pairs = (uint64_t)T * topk;
@@ -800,6 +802,10 @@ int bpq4k_moe_ffn_f32(bpq4k_handle_t h, int qtype, const float* X, const void* W
         if (aux) {
             a.prologue = BPQ4K_PROLOGUE_SILU_MUL;
             a.aux = aux;
+        }
+        if (qtype == BPQ4K_TYPE_Q6_K_PADDED) {
+            if (W2 || pairs > 65535u) return cudaErrorInvalidValue;  // one grid row per slot, one stack per launch
+            return launch_q6k_stream(a, h->tune, h->dev_status, h->sm_count, &h->tmaps, st, &launches);
         }
         return launch_gemv_stream(a, h->tune, nullptr, 0, h->dev_status, h->sm_count, &h->tmaps, st, &launches, qtype);
     };

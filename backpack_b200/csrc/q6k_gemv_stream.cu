@@ -116,6 +116,8 @@ __global__ void __launch_bounds__(512, 1) q6k_stream_kernel(const __grid_constan
         X += (uint64_t)(a.m.x_rows ? a.m.x_rows[s] : a.m.x_row_div ? s / a.m.x_row_div : s) * K;
         Y += (uint64_t)s * N;
     }
+    // fused prologue on the activation row (see MatmulArgs::prologue): in the indirect form slot s takes row s of aux
+    const float* AUX = a.m.aux ? a.m.aux + (a.m.n_slots ? (uint64_t)blockIdx.y * K : 0ull) : nullptr;
 
     const uint32_t tstride = gridDim.x * a.wt;
     const uint32_t tile0 = blockIdx.x * a.wt + wt;
@@ -157,6 +159,26 @@ __global__ void __launch_bounds__(512, 1) q6k_stream_kernel(const __grid_constan
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     {
+        // Fused prologue (the reference's q6k_matmul_norm.wgsl / *_down_gelu.wgsl forms and silu_mul_fused ahead of the
+        // down projection, runtime/model_runner.cpp:3755-3766): the row is transformed while it is staged.
+        const uint32_t prologue = AUX ? a.m.prologue : 0u;
+        float rstd = 1.f;
+        if (prologue == 1u) {
+            float ss = 0.f;
+            for (uint32_t i = tid; i < K / 4u; i += blockDim.x) {
+                const float4 v = __ldg(reinterpret_cast<const float4*>(X) + i);
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+            float* red = reinterpret_cast<float*>(smem + a.off_part);
+            if (lane == 0) red[warp] = ss;
+            __syncthreads();
+            float tot = 0.f;
+            for (uint32_t w2 = 0; w2 < nwarps; w2++) tot += red[w2];
+            rstd = 1.f / sqrtf(tot / (float)K + a.m.eps);
+            __syncthreads();  // red is the partial-sum buffer of the main loop
+        }
         // up to four 8-value items per thread and round, all loads issued before the first use
         constexpr int U = 4;
         const uint32_t per_row = K / 8u;
@@ -171,6 +193,24 @@ __global__ void __launch_bounds__(512, 1) q6k_stream_kernel(const __grid_constan
                     const float4* xp = reinterpret_cast<const float4*>(X + (uint64_t)it * 8u);
                     v[j][0] = __ldg(xp);
                     v[j][1] = __ldg(xp + 1);
+                    if (prologue) {
+                        const float4* ap = reinterpret_cast<const float4*>(AUX + (uint64_t)it * 8u);
+                        const float4 w0 = __ldg(ap), w1 = __ldg(ap + 1);
+                        float* vf = reinterpret_cast<float*>(v[j]);
+                        const float wf[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const float gte = vf[i];
+                            if (prologue == 1u) {
+                                vf[i] = gte * rstd * wf[i];
+                            } else if (prologue == 2u) {
+                                const float inner = 0.7978845608f * (gte + 0.044715f * gte * gte * gte);
+                                vf[i] = 0.5f * gte * (1.f + tanhf(inner)) * wf[i];
+                            } else {
+                                vf[i] = __fdividef(gte, 1.f + __expf(-gte)) * wf[i];
+                            }
+                        }
+                    }
                 }
             }
 #pragma unroll
@@ -321,7 +361,8 @@ __global__ void __launch_bounds__(512, 1) q6k_stream_kernel(const __grid_constan
             if (row < N) {
                 float s = 0.f;
                 for (uint32_t k2 = 0; k2 < a.wk; k2++) s += pbuf[k2 * 16u + lane];
-                const float yv = s + (a.m.bias ? a.m.bias[row] : 0.f);
+                float yv = s + (a.m.bias ? a.m.bias[row] : 0.f);
+                if (a.m.residual) yv += a.m.residual[row];
                 // double-buffered gather slots: the half this step writes (see MatmulArgs::slot_parity)
                 const uint64_t par_off = a.m.slot_parity ? (uint64_t)(*reinterpret_cast<const volatile uint32_t*>(a.m.slot_parity) & 1u) * a.m.slot_parity_stride : 0ull;
                 Y[row + par_off] = yv;
@@ -615,7 +656,8 @@ cudaError_t launch_q6k_stream(const MatmulArgs& m, const StreamTuning& tune, int
     if (m.N == 0) return cudaSuccess;
     if (m.M == 0 || m.M > 8) return cudaErrorInvalidValue;
     const bool indirect = m.n_slots != 0;                // slots of one row each, blockIdx.y = slot
-    if (indirect && (m.M != 1 || m.n_peers || m.W2)) return cudaErrorInvalidValue;
+    if (indirect && (m.M != 1 || m.n_peers || m.W2 || m.residual)) return cudaErrorInvalidValue;
+    if ((m.prologue || m.residual) && m.M != 1) return cudaErrorInvalidValue;  // the fused forms are single-row
     const bool rows = m.M > 1;                           // the several-row kernel
     const uint32_t tokens = rows ? (m.M + 3) / 4 * 4 : 1;
     const uint32_t nb = m.K / kQK;

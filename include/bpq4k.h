@@ -327,7 +327,7 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
  *     Y[t] = Y[t] + route_w[p] * o                          k ascending, as the reference accumulates
  * X and Y are [T][H] (Y is read and written: the caller leaves the residual stream or zeros there),
  * Wgate / Wup stack the experts' [F][H] matrices row-wise, Wdown the [H][F] matrices, all of type
- * `qtype` (Q4_K or Q5_K) with the packed row stride of their K.  expert_ids and route_w are device
+ * `qtype` (Q4_K, Q5_K or padded Q6_K; Q6_K runs gate and up as two launches) with the packed row stride of their K.  expert_ids and route_w are device
  * arrays of T*topk entries; an id >= nExperts reads zeros.  `work` is caller-owned device scratch of
  * at least bpq4k_moe_ffn_work_floats() floats (the call allocates nothing). */
 uint64_t bpq4k_moe_ffn_work_floats(uint32_t T, uint32_t topk, uint32_t H, uint32_t F);
@@ -358,7 +358,7 @@ int bpq4k_kq_matmul_allgather_f32(bpq4k_handle_t h, int qtype, const float* X, c
  *                            projection, runtime/model_runner.cpp:3755-3766)
  *   Y[yOffset + n] = sum_k x[k]*deq(W)[n][k] + bias[n] + residual[n]   (bias, residual may be NULL;
  *   the residual add is the dispatch at runtime/model_runner.cpp:3774)
- * Q4_K and Q5_K weights.  Each removes one small launch and one round trip of the activation
+ * Q4_K, Q5_K and padded Q6_K weights.  Each removes one small launch and one round trip of the activation
  * row through memory per projection.  X and aux must be 16-byte aligned. */
 enum bpq4k_prologue {
     BPQ4K_PROLOGUE_NONE = 0,

@@ -20,12 +20,13 @@ def check(y, want):
     assert float(np.abs(y - want).max()) <= 2e-2 * max(1.0, float(np.abs(want).max()) / 100.0)
 
 
-@pytest.mark.parametrize("qtype", [orc.Q4_K, orc.Q5_K])
+@pytest.mark.parametrize("qtype", [orc.Q4_K, orc.Q5_K, orc.Q6_K])
 @pytest.mark.parametrize("kind", [q4k.PROLOGUE_RMSNORM, q4k.PROLOGUE_GELU_MUL, q4k.PROLOGUE_SILU_MUL])
 @pytest.mark.parametrize("N,K", [(64, 256), (333, 1024), (4096, 4096), (1000, 14336)])
 def test_fused_prologue_matches_oracle(ctx, qtype, kind, N, K):
     import torch
 
+    layout = q4k.Q6_K_PADDED if qtype == orc.Q6_K else qtype     # Q6_K: the padded device layout of the fast kernel
     raw = synth.make_kq_weights(qtype, N, K, 300 + N)
     x = synth.make_activations(1, K, 301)[0] * (3.0 if kind == q4k.PROLOGUE_RMSNORM else 1.0)
     aux = (synth.make_activations(1, K, 302)[0] * 0.5 + 1.0).astype(np.float32)
@@ -34,7 +35,7 @@ def test_fused_prologue_matches_oracle(ctx, qtype, kind, N, K):
     eps = 1e-5
     xp = orc.prologue(kind, x, aux, eps)
     want = orc.kq_matmul(qtype, xp, raw, bias, N, K, threads=4)[0] + res
-    w = ctx.upload(pack_kq(qtype, raw, N, K))
+    w = ctx.upload(pack_kq(layout, raw, N, K))
     ctx.launch_count(reset=True)
     y = ctx.matmul_fused(dev(torch, x), w, kind, aux=dev(torch, aux), eps=eps, bias=dev(torch, bias),
                          residual=dev(torch, res)).cpu().numpy()[0]
@@ -69,7 +70,7 @@ def test_fused_errors(ctx):
     y = torch.zeros(8, device="cuda")
     s = torch.cuda.current_stream().cuda_stream
     args = (x.data_ptr(), None, 0.0, wbuf.data_ptr(), None, None, y.data_ptr(), 8, 256, 36, 0, s)
-    assert lib.bpq4k_matmul_fused_f32(ctx.h, 14, 0, *args) == 2          # Q6_K has no fused form
+    assert lib.bpq4k_matmul_fused_f32(ctx.h, 14, 0, *args) == 2          # file-format Q6_K has no fused form (the padded layout has)
     assert lib.bpq4k_matmul_fused_f32(ctx.h, 12, 7, *args) == 1          # unknown prologue
     assert lib.bpq4k_matmul_fused_f32(ctx.h, 12, 1, *args) == 1          # RMSNorm without its weight
     assert lib.bpq4k_matmul_fused_f32(ctx.h, 12, 0, *args) == 0

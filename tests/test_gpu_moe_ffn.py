@@ -15,10 +15,13 @@ def dev(torch, a):
 
 
 def make_layer(ctx, qtype, E, H, F, seed):
+    from backpack_b200 import q4k
+
+    layout = q4k.Q6_K_PADDED if qtype == orc.Q6_K else qtype     # Q6_K stacks live in the padded device layout
     raws = [synth.make_kq_weights(qtype, E * F, H, seed), synth.make_kq_weights(qtype, E * F, H, seed + 1),
             synth.make_kq_weights(qtype, E * H, F, seed + 2)]
-    ws = [ctx.upload(pack_kq(qtype, raws[0], E * F, H)), ctx.upload(pack_kq(qtype, raws[1], E * F, H)),
-          ctx.upload(pack_kq(qtype, raws[2], E * H, F))]
+    ws = [ctx.upload(pack_kq(layout, raws[0], E * F, H)), ctx.upload(pack_kq(layout, raws[1], E * F, H)),
+          ctx.upload(pack_kq(layout, raws[2], E * H, F))]
     return raws, ws
 
 
@@ -28,7 +31,7 @@ def routing_weights(T, topk, seed):
     return (w / w.sum(axis=1, keepdims=True)).astype(np.float32)
 
 
-@pytest.mark.parametrize("qtype", [orc.Q4_K, orc.Q5_K])
+@pytest.mark.parametrize("qtype", [orc.Q4_K, orc.Q5_K, orc.Q6_K])
 @pytest.mark.parametrize("E,H,F,T,topk", [(4, 256, 256, 1, 1), (8, 512, 256, 3, 2), (16, 2048, 768, 8, 8), (6, 768, 1024, 5, 3),
                                           (16, 512, 256, 32, 8)])    # 256 slots: the down matmul runs as a unit list too
 def test_moe_ffn_matches_reference_loop(ctx, qtype, E, H, F, T, topk):
@@ -109,7 +112,7 @@ def test_moe_ffn_errors(ctx):
 
     assert call() == 0
     assert call(t=0) == 0                                  # nothing to do
-    assert call(qt=orc.Q6_K) != 0                          # no expert-indexed kernel for that type
+    assert call(qt=orc.Q6_K) != 0                          # file-format Q6_K: no expert-indexed kernel (the padded layout has one)
     assert call(wn=need - 1) != 0 and "work holds" in lib.bpq4k_last_error_string(h).decode()
     assert call(xp=None) != 0
     assert call(wk=work.data_ptr() + 4) != 0               # misaligned scratch
