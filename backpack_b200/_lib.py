@@ -102,25 +102,41 @@ def build() -> None:
     subprocess.run(["make", "-s", "-C", os.path.join(PKG_DIR, "csrc")], check=True)
 
 
-def load() -> C.CDLL:
-    global _lib
-    if _lib is not None:
-        return _lib
-    if not os.path.isfile(LIB_PATH):
+def _open(path: str) -> C.CDLL:
+    if not os.path.isfile(path):
         raise LibraryMissing(
-            f"{LIB_PATH} not found. Build it with `make -C {os.path.join(PKG_DIR, 'csrc')}` "
+            f"{path} not found. Build it with `make -C {os.path.join(PKG_DIR, 'csrc')}` "
             "(needs nvcc with sm_100a support). There is no CPU or PyTorch fallback."
         )
-    lib = C.CDLL(LIB_PATH)
+    lib = C.CDLL(path)
     for name, (res, args) in SIGNATURES.items():
         try:
             fn = getattr(lib, name)
         except AttributeError as e:  # stale build
-            raise LibraryMissing(f"{LIB_PATH} does not export {name}; rebuild it") from e
+            raise LibraryMissing(f"{path} does not export {name}; rebuild it") from e
         fn.restype = res
         fn.argtypes = args
-    _lib = lib
     return lib
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = _open(LIB_PATH)
+    return _lib
+
+
+DEBUG_LIB_PATH = os.path.join(PKG_DIR, "lib", "libbpq4k_debug.so")
+_debug_lib = None
+
+
+def load_debug() -> C.CDLL:
+    """The debug build (`make -C csrc DEBUG=1`): the same library with index checks compiled into the kernels; a failed
+    check shows up as status 9 in bpq4k_device_status and the access is skipped."""
+    global _debug_lib
+    if _debug_lib is None:
+        _debug_lib = _open(DEBUG_LIB_PATH)
+    return _debug_lib
 
 
 class ModelConfig(C.Structure):

@@ -203,6 +203,7 @@ const char* bpq4k_status_string(int s) {
         case BPQ4K_ERR_TIMEOUT: return "device-side wait timed out";
         case BPQ4K_ERR_NO_DEVICE: return "no usable device";
         case BPQ4K_ERR_ALLOC: return "allocation failed";
+        case BPQ4K_ERR_DEVICE_ASSERT: return "a kernel's index check failed (debug build)";
         default: return "unknown status";
     }
 }

@@ -52,6 +52,8 @@ cudaError_t launch_dequant_f32(const uint8_t* W, uint32_t N, uint32_t K, uint64_
 
 // Value a kernel stores in the handle's device status word when a bounded wait runs out.
 constexpr int kDeviceTimeout = 6;
+// Value stored by a kernel of the debug build whose index check failed (the C ABI's BPQ4K_ERR_DEVICE_ASSERT).
+constexpr int kDeviceAssert = 9;
 
 // Tuning knobs of the streaming kernel; 0 = choose automatically.
 struct StreamTuning {

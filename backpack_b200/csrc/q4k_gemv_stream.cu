@@ -101,8 +101,13 @@ __device__ __forceinline__ uint32_t item_offset(uint32_t c8) { return (c8 >> 2) 
 // `rows`: the several-row kernels keep the two floats elsewhere, four activation rows side by side, so that
 // the four threads of a quad (one activation row each) read one 64-byte run without bank conflicts:
 //   SI[((((tok/4)*nb + blk)*4 + g)*4 + tok%4)*4 + parity*2 + {0: sum*inv, 1: inv}].
-__device__ __forceinline__ void quantize_loaded(float4 v0, float4 v1, uint32_t K, uint32_t tok, uint32_t c8, bool valid,
-                                                uint8_t* frag, float* SI, bool rows = false) {
+struct QuantItem {
+    uint4 c0, c1;    // the item's two 16-byte chunks (c = 0: top and low digits, c = 1: middle digits)
+    float sinv, inv;  // sum(xi)*inv and inv of the item's sub-block
+};
+// The arithmetic of an item, no memory access: several items of a thread are computed side by side
+// (independent dependency chains; a warp per scheduler or two has little else to hide latency with).
+__device__ __forceinline__ QuantItem quantize_compute(float4 v0, float4 v1) {
     float amax = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
                        fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
@@ -113,23 +118,32 @@ __device__ __forceinline__ void quantize_loaded(float4 v0, float4 v1, uint32_t K
         inv = amax / kXiMax;
     }
     const float xs[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-    uint32_t w0[2] = {0, 0}, w1[2] = {0, 0}, w2[2] = {0, 0};
+    int d0[8], d1[8], d2[8];
     int sum = 0;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const float vc = fminf(fmaxf(xs[i] * scale, -kXiMax), kXiMax);  // x*scale may overshoot by an ulp
         const int xi = __float2int_rn(vc);
-        const int d2 = ((xi + 64) & 127) - 64;
-        const int r1 = (xi - d2) >> 7;
-        const int d1 = ((r1 + 64) & 127) - 64;
-        const int d0 = (r1 - d1) >> 7;
+        d2[i] = (xi << 25) >> 25;  // signed low seven bits
+        const int r1 = (xi - d2[i]) >> 7;
+        d1[i] = (r1 << 25) >> 25;
+        d0[i] = (r1 - d1[i]) >> 7;
         sum += xi;
-        w0[i >> 2] |= (uint32_t)(d0 & 255) << (8 * (i & 3));
-        w1[i >> 2] |= (uint32_t)(d1 & 255) << (8 * (i & 3));
-        w2[i >> 2] |= (uint32_t)(d2 & 255) << (8 * (i & 3));
     }
+    auto pack4 = [](const int* d) {  // the low bytes of four digits
+        return __byte_perm(__byte_perm((uint32_t)d[0], (uint32_t)d[1], 0x0040), __byte_perm((uint32_t)d[2], (uint32_t)d[3], 0x0040), 0x5410);
+    };
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    QuantItem q;
+    q.c0 = make_uint4(pack4(d0), pack4(d0 + 4), pack4(d2), pack4(d2 + 4));
+    q.c1 = make_uint4(pack4(d1), pack4(d1 + 4), 0u, 0u);
+    q.sinv = (float)sum * inv;
+    q.inv = inv;
+    return q;
+}
+__device__ __forceinline__ void quantize_store(const QuantItem& q, uint32_t K, uint32_t tok, uint32_t c8, bool valid,
+                                               uint8_t* frag, float* SI, bool rows) {
     if (!valid) return;
     const uint32_t nb = K / kQK, NG = K / 64u;
     const uint32_t sbg = c8 >> 2, t = c8 & 3u;  // sub-block in the row, piece of the sub-block
@@ -137,20 +151,24 @@ __device__ __forceinline__ void quantize_loaded(float4 v0, float4 v1, uint32_t K
     uint8_t* base = frag + ((uint64_t)(tok * NG + G) * 2u + par) * 128u + t * 16u;
     // Two 16-byte stores per thread.  The lanes of even sub-blocks write their c = 0 chunk first, those of odd
     // sub-blocks their c = 1 chunk: the eight lanes that share a shared-memory wavefront then cover all 32 banks.
-    const uint4 c0 = make_uint4(w0[0], w0[1], w2[0], w2[1]), c1 = make_uint4(w1[0], w1[1], 0u, 0u);
-    *reinterpret_cast<uint4*>(base + (par ? 64u : 0u)) = par ? c1 : c0;
-    *reinterpret_cast<uint4*>(base + (par ? 0u : 64u)) = par ? c0 : c1;
+    *reinterpret_cast<uint4*>(base + (par ? 64u : 0u)) = par ? q.c1 : q.c0;
+    *reinterpret_cast<uint4*>(base + (par ? 0u : 64u)) = par ? q.c0 : q.c1;
     if (t == 0) {
         if (rows) {
             float* si = SI + (((uint64_t)((tok >> 2) * nb + (sbg >> 3)) * 4u + ((sbg >> 1) & 3u)) * 4u + (tok & 3u)) * 4u + par * 2u;
-            si[0] = (float)sum * inv;
-            si[1] = inv;
+            si[0] = q.sinv;
+            si[1] = q.inv;
         } else {
             float* si = SI + ((uint64_t)(tok * nb + (sbg >> 3)) * 2u + par) * 8u + ((sbg >> 1) & 3u);
-            si[0] = (float)sum * inv;
-            si[4] = inv;
+            si[0] = q.sinv;
+            si[4] = q.inv;
         }
     }
+}
+__device__ __forceinline__ void quantize_loaded(float4 v0, float4 v1, uint32_t K, uint32_t tok, uint32_t c8, bool valid,
+                                                uint8_t* frag, float* SI, bool rows = false) {
+    const QuantItem q = quantize_compute(v0, v1);
+    quantize_store(q, K, tok, c8, valid, frag, SI, rows);
 }
 // Load the 8 floats of an item (zeros for rows past M or an idle lane), then quantise them.
 __device__ __forceinline__ void quantize_item(const float* __restrict__ X, uint32_t M, uint32_t K, uint32_t tok,
@@ -299,6 +317,8 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
                 const CUtensorMap* map = s_first + l >= a.m.n_slots ? (full ? &a.tmap_b : &a.tmap_b_rem) : (full ? &a.tmap : &a.tmap_rem);
                 tma_load_2d(ring + iss_st * a.stage_bytes, map, (b0 + iss_c * a.cb) * BW, row, bar);
             } else {
+            if (BPQ4K_CHECK((b0 + iss_c * a.cb + (full ? a.cb : a.rem)) <= nb && iss_tile < a.ntiles && iss_st < a.stages &&
+                                (full ? a.cb : a.rem) * TR * BB <= a.stage_bytes, a.status))
             tma_load_2d(ring + iss_st * a.stage_bytes, full ? &a.tmap : &a.tmap_rem, (b0 + iss_c * a.cb) * BW,
                         (uint32_t)wrow0 + iss_tile * TR, bar);
             }
@@ -477,9 +497,21 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
                 }
             }
             if (base == 0) issue_rest();
+            // two items side by side (nj is uniform over the CTA, so every lane takes the same branch)
 #pragma unroll
-            for (int j = 0; j < U; j++)
-                if ((uint32_t)j < nj) quantize_loaded(v[j][0], v[j][1], K, tok[j], c8[j], valid[j], frag, SI, !M1);
+            for (int j = 0; j < U; j += 2) {
+                if ((uint32_t)j >= nj) break;
+                const bool two = (uint32_t)(j + 1) < nj;
+                const bool ok0 = valid[j] && BPQ4K_CHECK(tok[j] < (IND ? kMaxLocalSlots : (uint32_t)TOK) && c8[j] < per_row, a.status);
+                if (two) {
+                    const bool ok1 = valid[j + 1] && BPQ4K_CHECK(tok[j + 1] < (IND ? kMaxLocalSlots : (uint32_t)TOK) && c8[j + 1] < per_row, a.status);
+                    const QuantItem q0 = quantize_compute(v[j][0], v[j][1]), q1 = quantize_compute(v[j + 1][0], v[j + 1][1]);
+                    quantize_store(q0, K, tok[j], c8[j], ok0, frag, SI, !M1);
+                    quantize_store(q1, K, tok[j + 1], c8[j + 1], ok1, frag, SI, !M1);
+                } else {
+                    quantize_loaded(v[j][0], v[j][1], K, tok[j], c8[j], ok0, frag, SI, !M1);
+                }
+            }
         }
         }
         if (items == 0) issue_rest();  // (never with a valid launch: every CTA stages at least one row)
@@ -795,6 +827,7 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
                     for (uint32_t k2 = 0; k2 < a.wk; k2++) s += gbuf[(uint64_t)k2 * (TOK * TR) + idx];
                     float yv = s + (a.m.bias ? a.m.bias[row] : 0.f);
                     if (FP) yv += res_pre;
+                    if (BPQ4K_CHECK(tok < (IND || a.m.n_slots ? 1u : a.m.M) && row < N && idx < (uint32_t)TOK * TR, a.status))
                     Y[(uint64_t)tok * N + row + par_off] = yv;
                     // fused all-gather: the same value goes straight into every peer's gather buffer
                     for (uint32_t p = 0; p < a.m.n_peers; p++) a.m.peer_Y[p][(uint64_t)tok * N + row + par_off] = yv;
@@ -853,7 +886,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     if (gx == 0) gx = 1;
     if (flat_grid) gx = flat_grid, slots_y = 1;  // IND: the planner fixed the grid (one CTA per SM at most)
     StreamArgs sb = sa;
-    if (!flat_grid && slots_y == 1 && !sa.m.n_slots && !getenv("BPQ4K_OLD_SPLIT")) {
+    if (!flat_grid && slots_y == 1 && !sa.m.n_slots) {
         // Direct form: every resident CTA slot gets a contiguous, balanced share of the tiles (one CTA more or
         // less keeps all SMs streaming; a grid that left SMs idle to equalise rounds ran at the per-SM rate).
         gx = (uint32_t)(groups < cap ? groups : cap);

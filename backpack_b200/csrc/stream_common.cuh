@@ -11,6 +11,15 @@ namespace {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// Debug build (make DEBUG=1 -> libbpq4k_debug.so): index checks compiled into the kernels.  A failed check
+// records kDeviceAssert in the handle's status word and the guarded access is skipped -- never a trap, never a
+// fault.  In the normal build the macro disappears.
+#ifdef BPQ4K_DEBUG_CHECKS
+#define BPQ4K_CHECK(cond, status_ptr) ((cond) ? true : (((status_ptr) ? (void)atomicExch((status_ptr), kDeviceAssert) : (void)0), false))
+#else
+#define BPQ4K_CHECK(cond, status_ptr) (true)
+#endif
+
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }

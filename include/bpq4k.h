@@ -58,7 +58,8 @@ typedef enum bpq4k_status {
     BPQ4K_ERR_NCCL = 5,          /* reserved for callers that layer a collective on top */
     BPQ4K_ERR_TIMEOUT = 6,       /* a bounded device-side wait ran out */
     BPQ4K_ERR_NO_DEVICE = 7,     /* no usable sm_100 device */
-    BPQ4K_ERR_ALLOC = 8          /* device or host allocation failed */
+    BPQ4K_ERR_ALLOC = 8,         /* device or host allocation failed */
+    BPQ4K_ERR_DEVICE_ASSERT = 9  /* debug build only: a kernel's index check failed (the access was skipped) */
 } bpq4k_status;
 
 /* Options (bpq4k_set_option).  The reference selects kernels with environment
