@@ -67,6 +67,7 @@ struct StreamTuning {
     uint32_t no_unit_list = 0; // 1: indirect form always as one grid row per slot
     uint32_t rows_per_unit = 0; // several activation rows: weight rows a warp takes at a time, 0 automatic, 16 or 32
     uint32_t pre_wait = 0;     // ring stages issued before the dependency wait: 0 automatic, 1..8, 9 = none
+    uint32_t cluster = 0;      // CTAs per cluster sharing the staging of a single activation row: 0 automatic, 1, 2, 4
 };
 
 // Launch configuration of ONE kernel instantiation per device: the opt-in dynamic shared-memory size

@@ -488,12 +488,9 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES, QT>::THREADS, 1) prefill_tc
 #pragma unroll
             for (uint32_t gi = 0; gi < (uint32_t)GH; gi++) {
                 const uint32_t g = gi;
-                const uint32_t s = st_s;
-                if (st_it > 0 && !wait_bar(empty_bar(s), (st_it - 1u) & 1u, abort_flag, a.status)) {
-                    ok = false;
-                    break;
-                }
-                if (++st_s == P::STAGES) st_s = 0, st_it++;
+                // The stage's 16-bit values are computed BEFORE its buffer is waited for: in steady state the buffer
+                // is what the warp waits on, and only the stores, the fence and the arrival are left on the path
+                // between "buffer free" and "tile ready" (128256 x 4096, M = 512, bfloat16: 1157 -> see the header).
                 // w = (d*sc)*q - dmin*mn in float, rounded to 16 bits afterwards
                 const float dsc_e = d * (float)byte_of(sc_lo, sc_hi, 2 * g), dmn_e = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g);
                 const float dsc_o = d * (float)byte_of(sc_lo, sc_hi, 2 * g + 1), dmn_o = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g + 1);
@@ -503,24 +500,24 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES, QT>::THREADS, 1) prefill_tc
                     const uint4 u = raw[1 + gi * PARTS + q];
                     words[4 * q] = u.x, words[4 * q + 1] = u.y, words[4 * q + 2] = u.z, words[4 * q + 3] = u.w;
                 }
-                const uint32_t ta = a_tile(s, 0);
                 [[maybe_unused]] uint32_t dsc_e2 = 0, ndmn_e2 = 0, dsc_o2 = 0, ndmn_o2 = 0;
                 if constexpr (PASSES == 1 && !Q5) {
                     dsc_e2 = pack2<BF16>(dsc_e, dsc_e), ndmn_e2 = pack2<BF16>(-dmn_e, -dmn_e);
                     dsc_o2 = pack2<BF16>(dsc_o, dsc_o), ndmn_o2 = pack2<BF16>(-dmn_o, -dmn_o);
                 }
+                uint32_t lo_bits[2 * PARTS][4], hi_bits[2 * PARTS][4];
+                [[maybe_unused]] uint32_t lo_l[2 * PARTS][4], hi_l[2 * PARTS][4];
 #pragma unroll
                 for (uint32_t cl = 0; cl < 2u * PARTS; cl++) {  // chunk c: weights 8c..8c+7 of the even sub-block, chunk c+4: of the odd one
-                    uint32_t lo_bits[4], hi_bits[4], lo_l[4], hi_l[4];
                     if constexpr (PASSES == 1 && !Q5) {
 #pragma unroll
                         for (uint32_t j = 0; j < 2; j++) {
                             uint32_t o4[4];
                             dequant_word_16<BF16>(words[2 * cl + j], dsc_e2, ndmn_e2, dsc_o2, ndmn_o2, o4);
-                            lo_bits[2 * j] = o4[0];
-                            lo_bits[2 * j + 1] = o4[1];
-                            hi_bits[2 * j] = o4[2];
-                            hi_bits[2 * j + 1] = o4[3];
+                            lo_bits[cl][2 * j] = o4[0];
+                            lo_bits[cl][2 * j + 1] = o4[1];
+                            hi_bits[cl][2 * j] = o4[2];
+                            hi_bits[cl][2 * j + 1] = o4[3];
                         }
                     } else {
 #pragma unroll
@@ -543,31 +540,41 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES, QT>::THREADS, 1) prefill_tc
                             e[q] = fmaf(dsc_e, qe, -dmn_e);
                             o[q] = fmaf(dsc_o, qo, -dmn_o);
                         }
-                        lo_bits[2 * j] = pack2<BF16>(e[0], e[1]);
-                        lo_bits[2 * j + 1] = pack2<BF16>(e[2], e[3]);
-                        hi_bits[2 * j] = pack2<BF16>(o[0], o[1]);
-                        hi_bits[2 * j + 1] = pack2<BF16>(o[2], o[3]);
+                        lo_bits[cl][2 * j] = pack2<BF16>(e[0], e[1]);
+                        lo_bits[cl][2 * j + 1] = pack2<BF16>(e[2], e[3]);
+                        hi_bits[cl][2 * j] = pack2<BF16>(o[0], o[1]);
+                        hi_bits[cl][2 * j + 1] = pack2<BF16>(o[2], o[3]);
                         if constexpr (PASSES == 3) {
-                            lo_l[2 * j] = pack2_lo(e[0], e[1], lo_bits[2 * j]);
-                            lo_l[2 * j + 1] = pack2_lo(e[2], e[3], lo_bits[2 * j + 1]);
-                            hi_l[2 * j] = pack2_lo(o[0], o[1], hi_bits[2 * j]);
-                            hi_l[2 * j + 1] = pack2_lo(o[2], o[3], hi_bits[2 * j + 1]);
+                            lo_l[cl][2 * j] = pack2_lo(e[0], e[1], lo_bits[cl][2 * j]);
+                            lo_l[cl][2 * j + 1] = pack2_lo(e[2], e[3], lo_bits[cl][2 * j + 1]);
+                            hi_l[cl][2 * j] = pack2_lo(o[0], o[1], hi_bits[cl][2 * j]);
+                            hi_l[cl][2 * j + 1] = pack2_lo(o[2], o[3], hi_bits[cl][2 * j + 1]);
                         }
                     }
                     }
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + choff[cl][0]), "r"(lo_bits[0]),
-                                 "r"(lo_bits[1]), "r"(lo_bits[2]), "r"(lo_bits[3])
+                }
+                const uint32_t s = st_s;
+                if (st_it > 0 && !wait_bar(empty_bar(s), (st_it - 1u) & 1u, abort_flag, a.status)) {
+                    ok = false;
+                    break;
+                }
+                if (++st_s == P::STAGES) st_s = 0, st_it++;
+                const uint32_t ta = a_tile(s, 0);
+#pragma unroll
+                for (uint32_t cl = 0; cl < 2u * PARTS; cl++) {
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + choff[cl][0]), "r"(lo_bits[cl][0]),
+                                 "r"(lo_bits[cl][1]), "r"(lo_bits[cl][2]), "r"(lo_bits[cl][3])
                                  : "memory");
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + choff[cl][1]), "r"(hi_bits[0]),
-                                 "r"(hi_bits[1]), "r"(hi_bits[2]), "r"(hi_bits[3])
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + choff[cl][1]), "r"(hi_bits[cl][0]),
+                                 "r"(hi_bits[cl][1]), "r"(hi_bits[cl][2]), "r"(hi_bits[cl][3])
                                  : "memory");
                     if constexpr (PASSES == 3) {
                         const uint32_t tl = a_tile(s, 1);
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tl + choff[cl][0]), "r"(lo_l[0]),
-                                     "r"(lo_l[1]), "r"(lo_l[2]), "r"(lo_l[3])
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tl + choff[cl][0]), "r"(lo_l[cl][0]),
+                                     "r"(lo_l[cl][1]), "r"(lo_l[cl][2]), "r"(lo_l[cl][3])
                                      : "memory");
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tl + choff[cl][1]), "r"(hi_l[0]),
-                                     "r"(hi_l[1]), "r"(hi_l[2]), "r"(hi_l[3])
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tl + choff[cl][1]), "r"(hi_l[cl][0]),
+                                     "r"(hi_l[cl][1]), "r"(hi_l[cl][2]), "r"(hi_l[cl][3])
                                      : "memory");
                     }
                 }

@@ -95,6 +95,9 @@ typedef enum bpq4k_option {
     /* Several activation rows (M = 2..16): weight rows a warp takes through its ring at a time.  32 halves the
      * reads of the activation digits per weight byte; 0: automatic (32 from 8192 weight rows on), 16, 32. */
     BPQ4K_OPT_STREAM_UNIT_ROWS = 19,
+    /* One activation row: CTAs per thread-block cluster that quantise the row together (each a share, written into
+     * every member's shared memory).  0: automatic (pairs from K = 14336 on), 1: none, 2, 4. */
+    BPQ4K_OPT_STREAM_CLUSTER = 20,
     /* Read-only (bpq4k_get_option): how many times bpq4k_matmul_host_batch_f32 has recorded a dispatch
      * list into a replay graph on this handle.  A list is recorded again after any of the handle's
      * buffers had to grow. */

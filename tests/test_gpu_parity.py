@@ -258,6 +258,30 @@ def test_prefill_threshold_option(ctx):
     check(y_tc, want)
 
 
+@pytest.mark.parametrize("N,K", [(16, 256), (100, 1024), (4099, 4096), (1024, 14336), (777, 28672)])
+def test_cluster_staging_gives_identical_bits(ctx, N, K):
+    """BPQ4K_OPT_STREAM_CLUSTER: the CTAs of a cluster quantise a share of the activation row each and write it into
+    every member's shared memory.  The staged bytes are the same whoever computes them, so the outputs must be
+    bit-identical for cluster sizes 1, 2 and 4 (and within tolerance of the checker)."""
+    import torch
+
+    raw = synth.make_q4k_weights(N, K, 70)
+    x = synth.make_activations(1, K, 71)
+    w = ctx.upload(pack_q4k(raw, N, K))
+    want = orc.matmul(x, raw, None, N, K)
+    default = ctx.get_option(q4k.OPT_STREAM_CLUSTER)
+    ys = []
+    try:
+        for cs in (1, 2, 4):
+            ctx.set_option(q4k.OPT_STREAM_CLUSTER, cs)
+            ys.append(ctx.matmul(dev(torch, x), w).cpu().numpy())
+            assert ctx.device_status() == 0
+    finally:
+        ctx.set_option(q4k.OPT_STREAM_CLUSTER, default)
+    check(ys[0], want)
+    assert np.array_equal(ys[0], ys[1]) and np.array_equal(ys[0], ys[2])
+
+
 # ---------------------------------------------------------------- MoE indirect form
 
 @pytest.mark.parametrize("variant", VARIANTS, ids=VARIANT_IDS)
