@@ -324,6 +324,13 @@ int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
             if (value != 0 && value != 1 && value != 2 && value != 4) return fail(h, BPQ4K_ERR_INVALID_ARG, "cluster size must be 0, 1, 2 or 4");
             h->tune.cluster = (uint32_t)value;
             return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_STAGING_WARPS:
+            if (value < 0 || value > 16) return fail(h, BPQ4K_ERR_INVALID_ARG, "staging warps must be 0..16");
+            h->tune.staging_warps = (uint32_t)value;
+            return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_NO_TAIL_SPLIT:
+            h->tune.no_tail_split = value ? 1u : 0u;
+            return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_PREWAIT_STAGES:
             if (value < 0 || value > 9) return fail(h, BPQ4K_ERR_INVALID_ARG, "pre-wait stages must be 0..9");
             h->tune.pre_wait = (uint32_t)value;
@@ -348,6 +355,8 @@ int bpq4k_get_option(bpq4k_handle_t h, int option, int* value) {
         case BPQ4K_OPT_STREAM_NO_UNIT_LIST: *value = (int)h->tune.no_unit_list; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_UNIT_ROWS: *value = (int)h->tune.rows_per_unit; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_CLUSTER: *value = (int)h->tune.cluster; return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_NO_TAIL_SPLIT: *value = (int)h->tune.no_tail_split; return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_STAGING_WARPS: *value = (int)h->tune.staging_warps; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_PREWAIT_STAGES: *value = (int)h->tune.pre_wait; return BPQ4K_OK;
         case BPQ4K_OPT_BATCH_RECORDS: *value = (int)h->batch_records; return BPQ4K_OK;
         default: return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown option %d", option);

@@ -68,6 +68,8 @@ struct StreamTuning {
     uint32_t rows_per_unit = 0; // several activation rows: weight rows a warp takes at a time, 0 automatic, 16 or 32
     uint32_t pre_wait = 0;     // ring stages issued before the dependency wait: 0 automatic, 1..8, 9 = none
     uint32_t cluster = 0;      // CTAs per cluster sharing the staging of a single activation row: 0 automatic, 1, 2, 4
+    uint32_t staging_warps = 0;  // single row: warps that stage the activation row (helpers leave before the main loop): 0 automatic (16), 1..16
+    uint32_t no_tail_split = 0;  // 1: the tiles that do not fill a round of a CTA's tile slots keep their slot instead of being split over K
 };
 
 // Launch configuration of ONE kernel instantiation per device: the opt-in dynamic shared-memory size

@@ -82,6 +82,10 @@ struct StreamArgs {
     uint32_t pre_wait;         // ring stages issued before the dependency wait (the rest after the activation loads)
     uint32_t contig;           // direct form with a balanced contiguous tile range per CTA (units = tiles)
     uint32_t csize;            // CTAs per cluster that share the staging of the activation row (1: none)
+    // Tail split (single row, direct form): the tiles of a CTA's share that do not fill a round of its wt tile
+    // slots are split over K between ALL its warps, tail_tb blocks each (0: off), through this map's boxes.
+    CUtensorMap tmap_tail;
+    uint32_t tail_tb;
 };
 
 // Largest |xi|: its top base-128 digit still fits a signed byte.
@@ -249,7 +253,11 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
     constexpr int TOK = M1 ? 1 : NT * 4;  // activation-row slots (four per 8-column mma tile)
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t nwarps = blockDim.x >> 5;
+    // Warps beyond the plan's wk x wt are helpers: they take part in the staging of the activations (the one serial
+    // step of the kernel, faster with one item per thread) and leave before the main loop.
+    const uint32_t swarps = blockDim.x >> 5;
+    const uint32_t nwarps = a.wk * a.wt;
+    const bool helper = warp >= nwarps;
     const uint32_t wk = warp % a.wk, wt = warp / a.wk;
     const uint32_t K = a.m.K, N = a.m.N, nb = K / kQK;
     // every warp of a tile takes the same number of blocks: full stages of cb, then one of rem
@@ -265,6 +273,7 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
     const float* AUX = FP ? a.m.aux : nullptr;
     uint32_t tstride = gridDim.x * a.wt;
     uint32_t tile0 = blockIdx.x * a.wt + wt;   // IND: a unit index, not a tile
+    [[maybe_unused]] uint32_t tail_n = 0, tail_tile0 = 0;  // tail split: how many tiles, the first of them
     uint32_t my_tiles = tile0 < a.ntiles ? (a.ntiles - tile0 + tstride - 1) / tstride : 0;
     // IND: this CTA's first virtual slot, how many it touches, and their first weight rows
     [[maybe_unused]] uint32_t s_first = 0, nloc = 1;
@@ -280,7 +289,17 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
             const uint32_t u_end = u_begin + a.u_base + (blockIdx.x < a.u_extra ? 1u : 0u);
             tstride = a.wt;
             tile0 = u_begin + wt;
-            my_tiles = tile0 < u_end ? (u_end - tile0 + tstride - 1u) / tstride : 0u;
+            // A single tile left over after whole rounds of the wt tile slots would keep one slot busy and the others
+            // idle for a whole tile: it is split over K between all warps instead (28672 x 4096, 12 or 13 tiles per
+            // CTA: 15.1 -> 14.3 us).  Two or three left-over tiles keep their slots: taking them one after the other
+            // through all warps measured slower (128256 x 4096: 48.2 -> 48.7 us).
+            if (a.tail_tb && (u_end - u_begin) % a.wt == 1u) {
+                tail_n = 1;
+                tail_tile0 = u_end - 1u;
+                my_tiles = (u_end - u_begin) / a.wt;
+            } else {
+                my_tiles = tile0 < u_end ? (u_end - tile0 + tstride - 1u) / tstride : 0u;
+            }
         }
     }
     if constexpr (IND) {
@@ -312,7 +331,9 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
         if (FP && AUX) AUX += (uint64_t)s * K;
         M = 1;
     }
+    if (helper) my_tiles = 0, tail_n = 0;
     const uint32_t total_units = my_tiles * nchunks;
+    const uint32_t all_units = total_units + tail_n;  // every warp takes one chunk of each tail tile
 
     const uint32_t bar0 = smem_u32(smem) + warp * kMaxStages * 8u;
     const uint32_t ring = smem_u32(smem + a.off_ring) + warp * a.stages * a.stage_bytes;
@@ -376,11 +397,27 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
     // the activations have been issued (issue_rest).  A deep ring issued in one go just before the dependency
     // wait ends puts ~180 KB per SM in front of those loads in the memory system, and the activation staging
     // -- the one serial step of the kernel -- then waits 1.5-2.5 us for data that is sitting in L2.
-    const uint32_t pre_total = min(a.stages, total_units);
+    // the units of the tail split follow the warp's own: tile tail_tile0 + t, blocks [warp*tail_tb, +tail_tb)
+    uint32_t iss_n = 0;
+    auto issue_unit = [&]() {
+        if (iss_n < total_units) {
+            issue_next();
+        } else {
+            if (lane == 0) {
+                const uint32_t bar = bar0 + iss_st * 8u;
+                mbar_expect_tx(bar, 16u * BB * a.tail_tb);
+                if (BPQ4K_CHECK((warp + 1u) * a.tail_tb <= nb && tail_tile0 + (iss_n - total_units) < a.ntiles && 16u * BB * a.tail_tb <= a.stage_bytes, a.status))
+                tma_load_2d(ring + iss_st * a.stage_bytes, &a.tmap_tail, warp * a.tail_tb * BW, (uint32_t)wrow0 + (tail_tile0 + (iss_n - total_units)) * 16u, bar);
+            }
+            if (++iss_st == a.stages) iss_st = 0;
+        }
+        iss_n++;
+    };
+    const uint32_t pre_total = min(a.stages, all_units);
     const uint32_t pre_early = min(a.pre_wait, pre_total);
-    for (uint32_t i = 0; i < pre_early; i++) issue_next();
+    for (uint32_t i = 0; i < pre_early; i++) issue_unit();
     auto issue_rest = [&]() {
-        for (uint32_t i = pre_early; i < pre_total; i++) issue_next();
+        for (uint32_t i = pre_early; i < pre_total; i++) issue_unit();
     };
     // Bring the activation rows into L2 (and their page into the TLBs) while waiting.  A prefetch is not a read:
     // if the preceding kernel still writes X, its stores land in the same L2 lines.
@@ -468,7 +505,7 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
                 if (lane == 0) red[warp] = ss;
                 __syncthreads();
                 float tot = 0.f;
-                for (uint32_t w2 = 0; w2 < nwarps; w2++) tot += red[w2];
+                for (uint32_t w2 = 0; w2 < swarps; w2++) tot += red[w2];
                 rstd = 1.f / sqrtf(tot / (float)K + a.m.eps);
                 __syncthreads();  // red is the partial-sum buffer of the main loop
             }
@@ -604,6 +641,8 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
         }
     }
 
+    if (helper) return;  // (no CTA-wide barrier follows: the tile epilogues use named barriers over the plan's warps)
+
     // ---- per-lane constants ----------------------------------------------------
     // ldmatrix row addresses: lanes 0-7 rows 0-7 bytes [0,16), 8-15 rows 8-15 bytes [0,16),
     // 16-23 rows 0-7 bytes [16,32), 24-31 rows 8-15 bytes [16,32)
@@ -662,55 +701,17 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
         while (cur_tl >= a.ntiles) cur_tl -= a.ntiles, cur_l++;
     }
 
-    for (uint32_t ti = 0; ti < my_tiles; ti++) {
-        uint32_t tile = tile0 + ti * tstride;
-        // IND: the unit's slot selects the staged row (data lanes only; zero lanes stay in the zero region),
-        // its scales and the output row
-        [[maybe_unused]] AddrT pa_t = pa0, pb_t = pb0, s_t = s0_addr;
-        if constexpr (IND) {
-            const uint32_t l = cur_l, vs = s_first + l;
-            tile = cur_tl;
-            cur_tl += tstride;
-            while (cur_tl >= a.ntiles) cur_tl -= a.ntiles, cur_l++;
-            pa_t += b_par == 0 ? l * K * 4u : 0u;
-            pb_t += b_par == 1 ? l * K * 4u : 0u;
-            s_t += l * nb * 64u;
-            Y = vs >= a.m.n_slots ? a.m.Y2 + (uint64_t)(vs - a.m.n_slots) * N : a.m.Y + (uint64_t)vs * N;
-        }
-        // single-row calls: fetch this lane's residual value now, it is added when the tile is stored
-        float res_pre = 0.f;
-        if (FP && a.m.residual && wk == 0 && lane < 16u && tile * 16u + lane < N) res_pre = __ldg(a.m.residual + tile * 16u + lane);  // (FP is single-row: 16-row tiles)
-        float acc[RT][NT][2];
-#pragma unroll
-        for (int t = 0; t < RT; t++)
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++) acc[t][nt][0] = acc[t][nt][1] = 0.f;
-
-        for (uint32_t c = 0; c < nchunks; c++) {
-            const uint32_t bs = b0 + c * a.cb;
-            const uint32_t nblk = c < nfull ? a.cb : a.rem;
-            const uint32_t pitch = nblk * BB;
-            const uint32_t lm_off = lm_row * pitch + lm_col, hdr_off = row_a * pitch;
-            const uint32_t bar = bar0 + st * 8u;
-            if (!failed) {
-                uint32_t polls = 0;
-                while (!mbar_try_wait(bar, ph)) {
-                    if (++polls > kWaitPolls) {  // give up: flag it, keep the barriers matched
-                        failed = 1;
-                        if (lane == 0 && a.status) atomicExch(a.status, kDeviceTimeout);
-                        break;
-                    }
-                }
-            }
-            uint32_t boff = ring + st * a.stage_bytes;
-            for (uint32_t blk = bs; blk < bs + nblk; blk++, boff += BB) {
-                if constexpr (M1) {
+    // One super-block of a 16-row tile against the single activation row (M1): boff = the block in the ring, hdr_off /
+    // lm_off = this lane's header and ldmatrix offsets for the stage's row pitch, blk = the block's index in the row.
+    [[maybe_unused]] auto m1_block = [&](uint32_t boff, uint32_t hdr_off, uint32_t lm_off, uint32_t blk, [[maybe_unused]] AddrT pa_t,
+                                         [[maybe_unused]] AddrT pb_t, [[maybe_unused]] AddrT s_t, float (&acc)[RT][NT][2]) {
+        if constexpr (M1) {
                 // scales of this thread's rows, its parity's four sub-blocks; the odd sub-block's
                 // weights reach the mma as 16*q, so its scale carries the 1/16
                 float dsc[1][4], dmn[1][4];
 #pragma unroll
                 for (int r = 0; r < 1; r++) {
-                    const uint4 hv = lds128<0>(boff + hdr_off + r * 8u * pitch);
+                    const uint4 hv = lds128<0>(boff + hdr_off);
                     const BlockHeader h{hv.x, hv.y, hv.z, hv.w};
                     const float d = half_bits_to_float(h.w0) * par_scale, dmin = half_bits_to_float(h.w0 >> 16);
                     uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
@@ -779,6 +780,53 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
                 do_group(std::integral_constant<int, 1>{});
                 do_group(std::integral_constant<int, 2>{});
                 do_group(std::integral_constant<int, 3>{});
+        }
+    };
+
+    for (uint32_t ti = 0; ti < my_tiles; ti++) {
+        uint32_t tile = tile0 + ti * tstride;
+        // IND: the unit's slot selects the staged row (data lanes only; zero lanes stay in the zero region),
+        // its scales and the output row
+        [[maybe_unused]] AddrT pa_t = pa0, pb_t = pb0, s_t = s0_addr;
+        if constexpr (IND) {
+            const uint32_t l = cur_l, vs = s_first + l;
+            tile = cur_tl;
+            cur_tl += tstride;
+            while (cur_tl >= a.ntiles) cur_tl -= a.ntiles, cur_l++;
+            pa_t += b_par == 0 ? l * K * 4u : 0u;
+            pb_t += b_par == 1 ? l * K * 4u : 0u;
+            s_t += l * nb * 64u;
+            Y = vs >= a.m.n_slots ? a.m.Y2 + (uint64_t)(vs - a.m.n_slots) * N : a.m.Y + (uint64_t)vs * N;
+        }
+        // single-row calls: fetch this lane's residual value now, it is added when the tile is stored
+        float res_pre = 0.f;
+        if (FP && a.m.residual && wk == 0 && lane < 16u && tile * 16u + lane < N) res_pre = __ldg(a.m.residual + tile * 16u + lane);  // (FP is single-row: 16-row tiles)
+        float acc[RT][NT][2];
+#pragma unroll
+        for (int t = 0; t < RT; t++)
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) acc[t][nt][0] = acc[t][nt][1] = 0.f;
+
+        for (uint32_t c = 0; c < nchunks; c++) {
+            const uint32_t bs = b0 + c * a.cb;
+            const uint32_t nblk = c < nfull ? a.cb : a.rem;
+            const uint32_t pitch = nblk * BB;
+            const uint32_t lm_off = lm_row * pitch + lm_col, hdr_off = row_a * pitch;
+            const uint32_t bar = bar0 + st * 8u;
+            if (!failed) {
+                uint32_t polls = 0;
+                while (!mbar_try_wait(bar, ph)) {
+                    if (++polls > kWaitPolls) {  // give up: flag it, keep the barriers matched
+                        failed = 1;
+                        if (lane == 0 && a.status) atomicExch(a.status, kDeviceTimeout);
+                        break;
+                    }
+                }
+            }
+            uint32_t boff = ring + st * a.stage_bytes;
+            for (uint32_t blk = bs; blk < bs + nblk; blk++, boff += BB) {
+                if constexpr (M1) {
+                m1_block(boff, hdr_off, lm_off, blk, pa_t, pb_t, s_t, acc);
                 } else {
                 // ---- several activation rows: every mma is one sub-block x four activation rows ----
                 // headers of rows r and r+8 of each 16-row mma tile: d, dmin and the packed 6-bit scales and mins; the
@@ -876,7 +924,7 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
             // the stage is free: refill it with the unit `stages` ahead
             __syncwarp();
             fence_proxy_async();
-            if (u + a.stages < total_units) issue_next();
+            if (u + a.stages < all_units) issue_unit();
             u++;
             if (++st == a.stages) {
                 st = 0;
@@ -917,6 +965,55 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
                     Y[(uint64_t)tok * N + row + par_off] = yv;
                     // fused all-gather: the same value goes straight into every peer's gather buffer
                     for (uint32_t p = 0; p < a.m.n_peers; p++) a.m.peer_Y[p][(uint64_t)tok * N + row + par_off] = yv;
+                }
+            }
+        }
+    }
+
+    // ---- tail split: the tiles that did not fill a round, every warp a K slice of each ----------------------
+    if constexpr (M1 && !IND) {
+        if (tail_n) {
+            float* tpart = part + 2u * nwarps * 16u;  // its own partial sums: a slower tile slot may still be reading the others
+            const uint32_t pitch = a.tail_tb * BB;
+            const uint32_t lm_off = lm_row * pitch + lm_col, hdr_off = row_a * pitch;
+            for (uint32_t t = 0; t < tail_n; t++) {
+                float acc[RT][NT][2];
+                acc[0][0][0] = acc[0][0][1] = 0.f;
+                const uint32_t bar = bar0 + st * 8u;
+                if (!failed) {
+                    uint32_t polls = 0;
+                    while (!mbar_try_wait(bar, ph)) {
+                        if (++polls > kWaitPolls) {
+                            failed = 1;
+                            if (lane == 0 && a.status) atomicExch(a.status, kDeviceTimeout);
+                            break;
+                        }
+                    }
+                }
+                uint32_t boff = ring + st * a.stage_bytes;
+                for (uint32_t blk = warp * a.tail_tb; blk < (warp + 1u) * a.tail_tb; blk++, boff += BB)
+                    m1_block(boff, hdr_off, lm_off, blk, pa0, pb0, s0_addr, acc);
+                __syncwarp();
+                fence_proxy_async();
+                if (u + a.stages < all_units) issue_unit();
+                u++;
+                if (++st == a.stages) {
+                    st = 0;
+                    ph ^= 1u;
+                }
+                const float sv = acc[0][0][0] + __shfl_xor_sync(0xFFFFFFFFu, acc[0][0][0], 1);
+                if (c_par == 0) tpart[((t & 1u) * nwarps + warp) * 16u + row_a] = sv;
+                asm volatile("bar.sync 0, %0;" ::"r"(nwarps * 32u) : "memory");  // (the helper warps have left)
+                if (warp == 0 && lane < 16u) {
+                    const uint32_t row = (tail_tile0 + t) * 16u + lane;
+                    if (row < N) {
+                        float sum = 0.f;
+                        for (uint32_t w2 = 0; w2 < nwarps; w2++) sum += tpart[((t & 1u) * nwarps + w2) * 16u + lane];
+                        float yv = sum + (a.m.bias ? a.m.bias[row] : 0.f);
+                        if (FP && a.m.residual) yv += __ldg(a.m.residual + row);
+                        Y[(uint64_t)row + par_off] = yv;
+                        for (uint32_t p = 0; p < a.m.n_peers; p++) a.m.peer_Y[p][(uint64_t)row + par_off] = yv;
+                    }
                 }
             }
         }
@@ -1103,7 +1200,9 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     if (!wk) {
         if (small) {
             wk = 1;
-            while (wk * 2 <= warps && nb % (wk * 2) == 0 && tiles_total * (wk * 2) <= (uint64_t)sm_count * warps) wk *= 2;
+            // (up to 1.3 warps' worth of K slices per resident warp: 6144 x 4096 -- 384 tiles, 3072 slices on 2368 warps --
+            //  runs 5.98 us split eight ways over 148 CTAs against 6.32 us split four ways over 96)
+            while (wk * 2 <= warps && nb % (wk * 2) == 0 && tiles_total * (wk * 2) * 10u <= (uint64_t)sm_count * warps * 13u) wk *= 2;
         } else if (m1) {
             wk = nb >= 64 ? 8 : nb >= 32 ? 4 : nb >= 16 ? 2 : 1;
         } else {
@@ -1129,7 +1228,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         sa.off_zero = off; off += kZeroBytes;
         sa.off_S = off; off += xg ? 0 : align_up(S_bytes, 16);
         sa.off_x = align_up(off, 128); off = sa.off_x + (xg ? 0 : x_bytes);
-        sa.off_part = align_up(off, 16); off = sa.off_part + 2u * warps * tokens * tile_rows * 4u;
+        sa.off_part = align_up(off, 16); off = sa.off_part + (m1 ? 4u : 2u) * warps * tokens * tile_rows * 4u;  // single row: + the tail split's partial sums
         sa.off_ring = align_up(off, 128); off = sa.off_ring + warps * stages * stage_bytes;
         return off;
     };
@@ -1263,6 +1362,17 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         } else {
             sa.tmap_rem = sa.tmap;
         }
+        // Tail split: direct single-row form with several tile slots per CTA, K divisible into one box per warp
+        // that fits a ring stage (128256 x 4096 on 148 SMs: 54 or 55 tiles per CTA = 13 rounds of 4 + 2 or 3 tiles).
+        sa.tail_tb = 0;
+        sa.tmap_tail = sa.tmap;
+        if (m1 && !indirect && !xg && !tune.no_tail_split && wt > 1 && nb % warps == 0) {
+            const uint32_t tb = nb / warps;
+            if (tb * block_words <= 256u && tile_rows * tb * block_bytes <= stage_bytes) {
+                if (cudaError_t e = get_map(tb, &sa.tmap_tail, m.W)) return e;
+                sa.tail_tb = tb;
+            }
+        }
         if (m.W2) {
             if (cudaError_t e = get_map(cb, &sa.tmap_b, m.W2)) return e;
             if (rem) {
@@ -1293,7 +1403,9 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     cudaError_t e = cudaSuccess;
     if (flat_grid) {
         if (xg || !m1) return cudaErrorInvalidValue;
-        const uint32_t threads = warps * 32;
+        // single row staged per CTA: up to 16 warps stage it (helpers beyond the plan's warps leave afterwards)
+        const uint32_t swarps_h = (m1 && !xg) ? (tune.staging_warps ? tune.staging_warps : 16u) : 0u;
+        const uint32_t threads = (swarps_h > warps ? swarps_h : warps) * 32;
         const bool pdl = !tune.no_pdl;
         if (fused)
             e = q5 ? launch_one<1, true, false, true, false, true, true>(sa, groups, 1, threads, smem, sm_count, 1, pdl, stream, flat_grid)
@@ -1313,7 +1425,9 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
             sa.m.X = base.x_rows ? base.X : base.X + (uint64_t)s0 * m.K;
             sa.m.Y = base.Y + (uint64_t)s0 * m.N;
         }
-        const uint32_t threads = warps * 32;
+        // single row staged per CTA: up to 16 warps stage it (helpers beyond the plan's warps leave afterwards)
+        const uint32_t swarps_h = (m1 && !xg) ? (tune.staging_warps ? tune.staging_warps : 16u) : 0u;
+        const uint32_t threads = (swarps_h > warps ? swarps_h : warps) * 32;
 #define BPQ4K_LAUNCH_RT(NT_, M1_, XG_, XC_, FP_, RT_)                                                                  \
     (q5 ? launch_one<NT_, M1_, XG_, true, XC_, FP_, false, RT_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream) \
         : launch_one<NT_, M1_, XG_, false, XC_, FP_, false, RT_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream))

@@ -37,6 +37,8 @@ OPT_STREAM_NO_PDL = 16
 OPT_STREAM_NO_UNIT_LIST = 17
 OPT_STREAM_PREWAIT_STAGES = 18
 OPT_STREAM_CLUSTER = 20
+OPT_STREAM_STAGING_WARPS = 21
+OPT_STREAM_NO_TAIL_SPLIT = 22
 OPT_STREAM_UNIT_ROWS = 19
 OPT_BATCH_RECORDS = 30   # read-only: replay graphs recorded by matmul_host_batch
 GEMV_AUTO, GEMV_FP32, GEMV_STREAM = 0, 1, 2

@@ -98,6 +98,12 @@ typedef enum bpq4k_option {
     /* One activation row: CTAs per thread-block cluster that quantise the row together (each a share, written into
      * every member's shared memory).  0: automatic (pairs from K = 14336 on), 1: none, 2, 4. */
     BPQ4K_OPT_STREAM_CLUSTER = 20,
+    /* One activation row: warps per CTA that quantise the row; those beyond the plan's warps (BPQ4K_OPT_STREAM_WARPS)
+     * leave before the main loop.  0: automatic (16), 1..16 (values below the plan's warp count change nothing). */
+    BPQ4K_OPT_STREAM_STAGING_WARPS = 21,
+    /* One activation row: the tiles of a CTA's share that do not fill a round of its tile slots are normally split
+     * over K between all its warps (results of those rows then sum their K slices in a different grouping).  1: off. */
+    BPQ4K_OPT_STREAM_NO_TAIL_SPLIT = 22,
     /* Read-only (bpq4k_get_option): how many times bpq4k_matmul_host_batch_f32 has recorded a dispatch
      * list into a replay graph on this handle.  A list is recorded again after any of the handle's
      * buffers had to grow. */
