@@ -19,6 +19,8 @@ struct bpq4k_context {
     char err[512] = "no error";
     int gemv_variant = BPQ4K_GEMV_AUTO;
     int prefill_mode = BPQ4K_PREFILL_F16X3;
+    int prefill_variant = 0;  // BPQ4K_OPT_PREFILL_VARIANT
+    int prefill_arg() const { return prefill_mode | (prefill_variant << 4); }  // what the launcher takes
     int prefill_min_m = 25;  // four 8-row slabs of the streaming kernel cost as much as one tensor-core pass
     uint64_t launches = 0;
     // staging for the *_host entry point
@@ -155,11 +157,11 @@ int run_matmul(bpq4k_context* h, const MatmulArgs& a, cudaStream_t st) {
         e = launch_gemv_fp32(a, st, &launches);
     } else if (!a.n_slots && a.M >= (uint32_t)h->prefill_min_m && h->gemv_variant == BPQ4K_GEMV_AUTO) {
         // prefill: tensor-core kernel; its 16-bit copy of the activations lives in the handle's scratch
-        const size_t need = prefill_scratch_bytes(a.M, a.N, a.K, h->prefill_mode, h->sm_count);
+        const size_t need = prefill_scratch_bytes(a.M, a.N, a.K, h->prefill_arg(), h->sm_count);
         if (need > h->scratch_bytes) {
             if (int s = ensure_bytes(h, &h->scratch, &h->scratch_bytes, need)) return s;
         }
-        e = launch_prefill_tc(a, h->prefill_mode, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count, st, &launches);
+        e = launch_prefill_tc(a, h->prefill_arg(), h->scratch, h->scratch_bytes, h->dev_status, h->sm_count, st, &launches);
     } else {
         const uint32_t Mtot = a.n_slots ? 1 : a.M;
         const size_t need = a.n_slots ? 0 : gemv_stream_scratch_bytes(Mtot < kStreamMaxM ? Mtot : kStreamMaxM, a.K);
@@ -331,6 +333,10 @@ int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
         case BPQ4K_OPT_STREAM_NO_TAIL_SPLIT:
             h->tune.no_tail_split = value ? 1u : 0u;
             return BPQ4K_OK;
+        case BPQ4K_OPT_PREFILL_VARIANT:
+            if (value < 0 || value > 2) return fail(h, BPQ4K_ERR_INVALID_ARG, "prefill variant must be 0, 1 or 2");
+            h->prefill_variant = value;
+            return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_PREWAIT_STAGES:
             if (value < 0 || value > 9) return fail(h, BPQ4K_ERR_INVALID_ARG, "pre-wait stages must be 0..9");
             h->tune.pre_wait = (uint32_t)value;
@@ -344,6 +350,7 @@ int bpq4k_get_option(bpq4k_handle_t h, int option, int* value) {
     switch (option) {
         case BPQ4K_OPT_GEMV_VARIANT: *value = h->gemv_variant; return BPQ4K_OK;
         case BPQ4K_OPT_PREFILL_MODE: *value = h->prefill_mode; return BPQ4K_OK;
+        case BPQ4K_OPT_PREFILL_VARIANT: *value = h->prefill_variant; return BPQ4K_OK;
         case BPQ4K_OPT_PREFILL_MIN_M: *value = h->prefill_min_m; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_WARPS: *value = (int)h->tune.warps; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_KSPLIT: *value = (int)h->tune.wk; return BPQ4K_OK;
@@ -600,11 +607,11 @@ int bpq4k_kq_matmul_f32(bpq4k_handle_t h, int qtype, const float* X, const void*
         if (e == cudaErrorInvalidValue) launches = 0;  // not even one row fits: the plain kernel below
     }
     if (tensor_cores) {
-        const size_t need = prefill_scratch_bytes(M, N, K, h->prefill_mode, h->sm_count);
+        const size_t need = prefill_scratch_bytes(M, N, K, h->prefill_arg(), h->sm_count);
         if (need > h->scratch_bytes) {
             if (int s = ensure_bytes(h, &h->scratch, &h->scratch_bytes, need)) return s;
         }
-        e = launch_prefill_tc(a, h->prefill_mode, h->scratch, h->scratch_bytes, h->dev_status, h->sm_count,
+        e = launch_prefill_tc(a, h->prefill_arg(), h->scratch, h->scratch_bytes, h->dev_status, h->sm_count,
                               static_cast<cudaStream_t>(stream), &launches, qtype);
     } else
     // Q5_K: the streaming kernel in slabs of 8 rows (each slab re-reads the weights)
@@ -1142,7 +1149,7 @@ int bpq4k_matmul_host_batch_f32(bpq4k_handle_t h, const bpq4k_host_matmul* items
     uint64_t key = 1469598103934665603ull;
     key = fnv1a(key, items, sizeof(bpq4k_host_matmul) * count);
     key = fnv1a(key, &h->tune, sizeof(h->tune));
-    const int opts[3] = {h->gemv_variant, h->prefill_mode, h->prefill_min_m};
+    const int opts[3] = {h->gemv_variant, h->prefill_arg(), h->prefill_min_m};
     key = fnv1a(key, opts, sizeof(opts));
     const void* bufs[3] = {h->stage_x, h->stage_y, h->scratch};  // the graph holds these addresses
     key = fnv1a(key, bufs, sizeof(bufs));

@@ -624,6 +624,485 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES, QT>::THREADS, 1) prefill_tc
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// Single-pass modes, Q4_K, with the dequantised weights in TENSOR MEMORY instead of shared memory
+// (BPQ4K_OPT_PREFILL_VARIANT = 2).  tcgen05.mma can take its A operand from TMEM (lane = row, a 32-bit column = two
+// consecutive k).  The dequantising thread of a weight row writes its 64 values of a k-step straight into its TMEM
+// lane (tcgen05.st, 32 columns), so the weights never pass through shared memory and the activation tiles get a ring
+// of their own, eight deep.
+//   TMEM (512 columns): accumulators of the two 128-row halves at columns 0 and 128 (128 activation rows each),
+//   four A stages at 256 + 64*s (32 columns per half).  Shared memory: a ring of eight 16 KB activation tiles.
+// A CTA owns 256 weight rows x 128 activation rows; the CTAs that share a weight tile are neighbours in the grid.
+// The accumulators and the A stages share the 512 columns, which caps the activation tile at 128 rows: every
+// dequantised weight then serves half as many rows as in the kernel above, and the dequantisation becomes the bound
+// (128256 x 4096, M = 512, bfloat16: 825 against 1207 TFLOP/s; same bits).  Not the default.
+struct PlanTS {
+    static constexpr uint32_t TOK = 128, SA = 4, SB = 8;
+    static constexpr uint32_t B_BYTES = TOK * 128u;
+    static constexpr uint32_t THREADS = 10 * 32;
+    static constexpr uint32_t TMEM_COLS = 512, A_COL0 = 256;
+    static constexpr uint32_t SMEM_BYTES = 1024 + SB * B_BYTES + 512;
+};
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+        "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
+        "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]),
+        "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(PlanTS::THREADS, 1) prefill_tc_ts_kernel(const __grid_constant__ PrefillArgs a) {
+    using P = PlanTS;
+    constexpr int BU = 9;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bar_base = base + P::SB * P::B_BYTES;
+    auto a_full = [&](uint32_t s) { return bar_base + s * 8u; };
+    auto a_empty = [&](uint32_t s) { return bar_base + (P::SA + s) * 8u; };
+    auto b_full = [&](uint32_t s) { return bar_base + (2u * P::SA + s) * 8u; };
+    auto b_empty = [&](uint32_t s) { return bar_base + (2u * P::SA + P::SB + s) * 8u; };
+    const uint32_t acc_bar = bar_base + (2u * P::SA + 2u * P::SB) * 8u;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + P::SB * P::B_BYTES + (2u * P::SA + 2u * P::SB) * 8u + 16u);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + P::SB * P::B_BYTES + (2u * P::SA + 2u * P::SB) * 8u + 32u);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t tok0 = blockIdx.x * P::TOK, n0 = blockIdx.y * 256u;
+    const uint32_t blk0 = blockIdx.z * a.bps;
+    const uint32_t blk1 = min(a.K / kQK, blk0 + a.bps);
+    const uint32_t nkb = (blk1 - blk0) * 4u;
+    const uint32_t kbase = blk0 * kQK;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < P::SA; s++) {
+            mbar_init(a_full(s), 8);
+            mbar_init(a_empty(s), 1);
+        }
+        for (uint32_t s = 0; s < P::SB; s++) {
+            mbar_init(b_full(s), 1);
+            mbar_init(b_empty(s), 1);
+        }
+        mbar_init(acc_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(P::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    auto b_tile = [&](uint32_t s) { return base + s * P::B_BYTES; };
+
+    if (warp == 0) {
+        // ---------------- TMA producer: activation tiles, eight deep ----------------
+        if (lane == 0) {
+            for (uint32_t kb = 0; kb < nkb; kb++) {
+                const uint32_t s = kb % P::SB, it = kb / P::SB;
+                if (it > 0 && !wait_bar(b_empty(s), (it - 1) & 1u, abort_flag, a.status)) break;
+                mbar_expect_tx(b_full(s), P::B_BYTES);
+                tma_load_2d(b_tile(s), &a.tmap_x[0], kbase + kb * kKStep, tok0, b_full(s));
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: A from tensor memory, B from shared memory ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | ((BF16 ? 1u : 0u) << 7) | ((BF16 ? 1u : 0u) << 10) | ((P::TOK >> 3) << 17) | ((128u >> 4) << 24);
+            bool ok = true;
+            for (uint32_t kb = 0; kb < nkb && ok; kb++) {
+                const uint32_t sa = kb % P::SA, sb = kb % P::SB;
+                ok = wait_bar(a_full(sa), (kb / P::SA) & 1u, abort_flag, a.status) && wait_bar(b_full(sb), (kb / P::SB) & 1u, abort_flag, a.status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (uint32_t ks = 0; ks < kKStep / 16; ks++) {
+                    const uint32_t acc = (kb | ks) ? 1u : 0u;
+                    const uint64_t db = umma_desc(b_tile(sb) + ks * 32u);
+#pragma unroll
+                    for (uint32_t h = 0; h < 2; h++)
+                        umma_f16_ts(tmem_base + h * P::TOK, tmem_base + P::A_COL0 + sa * 64u + h * 32u + ks * 8u, db, idesc, acc);
+                }
+                umma_commit(a_empty(sa));
+                umma_commit(b_empty(sb));
+            }
+            if (ok) umma_commit(acc_bar);
+        }
+    } else {
+        // ---------------- dequantise into this thread's TMEM lane, then drain the accumulators ----------------
+        const uint32_t dw = warp - 2;
+        const uint32_t h = dw >> 2, quad = warp & 3u;  // row half; the TMEM lane quarter this warp may access
+        const uint32_t r = h * 128u + quad * 32u + lane;
+        const uint32_t n = n0 + r;
+        const uint4* wrow = reinterpret_cast<const uint4*>(a.W + (uint64_t)(n < a.N ? n : a.N - 1u) * a.w_row_bytes);
+        const uint32_t nblocks = blk1 - blk0;
+        wrow += (uint64_t)blk0 * BU;
+        const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16);
+        bool ok = true;
+        uint4 raw[BU], nxt[BU];
+        auto load_block = [&](uint32_t b, uint4 (&dst)[BU]) {
+            const uint4* p = wrow + (uint64_t)b * BU;
+#pragma unroll
+            for (int i = 0; i < BU; i++) dst[i] = __ldg(p + i);
+        };
+        if (nblocks) load_block(0, nxt);
+        uint32_t st_s = 0, st_it = 0;
+        for (uint32_t b = 0; b < nblocks && ok; b++) {
+#pragma unroll
+            for (int i = 0; i < BU; i++) raw[i] = nxt[i];
+            if (b + 1 < nblocks) load_block(b + 1, nxt);
+            const BlockHeader hd{raw[0].x, raw[0].y, raw[0].z, raw[0].w};
+            const float d = half_bits_to_float(hd.w0), dmin = half_bits_to_float(hd.w0 >> 16);
+            uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
+            unpack_scales_packed(hd, sc_lo, sc_hi, mn_lo, mn_hi);
+#pragma unroll
+            for (uint32_t g = 0; g < 4; g++) {
+                const float dsc_e = d * (float)byte_of(sc_lo, sc_hi, 2 * g), dmn_e = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g);
+                const float dsc_o = d * (float)byte_of(sc_lo, sc_hi, 2 * g + 1), dmn_o = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g + 1);
+                const uint32_t dsc_e2 = pack2<BF16>(dsc_e, dsc_e), ndmn_e2 = pack2<BF16>(-dmn_e, -dmn_e);
+                const uint32_t dsc_o2 = pack2<BF16>(dsc_o, dsc_o), ndmn_o2 = pack2<BF16>(-dmn_o, -dmn_o);
+                const uint4 u0 = raw[1 + 2 * g], u1 = raw[2 + 2 * g];
+                const uint32_t words[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+                // column j of the stage holds k = 2j, 2j+1: the even sub-block's 32 weights, then the odd one's
+                uint32_t v[32];
+#pragma unroll
+                for (uint32_t wv = 0; wv < 8; wv++) {
+                    uint32_t o4[4];
+                    dequant_word_16<BF16>(words[wv], dsc_e2, ndmn_e2, dsc_o2, ndmn_o2, o4);
+                    v[2 * wv] = o4[0];
+                    v[2 * wv + 1] = o4[1];
+                    v[16 + 2 * wv] = o4[2];
+                    v[16 + 2 * wv + 1] = o4[3];
+                }
+                const uint32_t s = st_s;
+                if (st_it > 0 && !wait_bar(a_empty(s), (st_it - 1u) & 1u, abort_flag, a.status)) ok = false;
+                ok = __all_sync(0xFFFFFFFFu, ok);  // the tensor-memory store below is a whole-warp instruction
+                if (!ok) break;
+                if (++st_s == P::SA) st_s = 0, st_it++;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                tmem_st32(lane_addr + P::A_COL0 + s * 64u + h * 32u, v);
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(a_full(s));
+            }
+        }
+        if (ok) ok = wait_bar(acc_bar, 0, abort_flag, a.status);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float bias = (a.ksplit == 1 && a.bias && n < a.N) ? a.bias[n] : 0.f;
+            float* Yout = a.ksplit == 1 ? a.Y : a.Ypart + (uint64_t)blockIdx.z * a.M * a.N;
+            for (uint32_t c0 = 0; c0 < P::TOK; c0 += 32) {
+                if (tok0 + c0 >= a.M) break;
+                uint32_t v[32];
+                tmem_ld32(lane_addr + h * P::TOK + c0, v);
+                if (n < a.N) {
+#pragma unroll
+                    for (uint32_t t = 0; t < 32; t++)
+                        if (tok0 + c0 + t < a.M) Yout[(uint64_t)(tok0 + c0 + t) * a.N + n] = __uint_as_float(v[t]) + bias;
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P::TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Pair kernel (single-pass modes, Q4_K, M > 256; BPQ4K_OPT_PREFILL_VARIANT = 1): two CTAs of a cluster share one
+// tcgen05.mma.cta_group::2.  The pair owns 256 weight rows x 512 activation rows.  Each CTA dequantises ITS 128 weight
+// rows (the A operand of its half of M = 256) and loads HALF of each 256-row activation tile (the B operand is read
+// from both CTAs' shared memory); its TMEM holds the 128 x 512 accumulators of its weight rows.  Against two
+// independent CTAs of 256 x 256 this halves the dequantisation per flop and reads every weight byte once per 512
+// activation rows.  Same bits as the one-CTA kernel; measured slower on B200 (128256 x 4096, M = 512, bfloat16:
+// 990 against 1207 TFLOP/s, whether the second CTA's activation loads complete on the leader's barrier directly or
+// are forwarded by a thread, with one or two dequantising threads per row), so it is not the default.
+//
+// Roles.  warp 0: TMA loads of this CTA's activation halves (cp.async.bulk.tensor with .cta_group::2 and NO multicast:
+// the bytes land in the issuing CTA, the completion is counted on the LEADER's full barrier).  warp 1 of the leader
+// (cluster rank 0): issues the mmas of the pair and the commits (to the barriers of both CTAs).  warps 2-9: two threads
+// per weight row dequantise and arrive on the leader's full barrier (a remote arrive from the second CTA), then all
+// eight drain the accumulators.  Every wait is bounded; the two cluster barriers are reached by every thread on every path.
+struct PlanPair {
+    static constexpr uint32_t A_BYTES = 128u * 128u, B_BYTES = 128u * 128u;  // 128 rows x 64 k x 2 B
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + 2u * B_BYTES;          // two activation tiles of 256 rows, half each
+    static constexpr uint32_t STAGES = 4;
+    static constexpr uint32_t DEQ_WARPS = 8, EPI_WARPS = 8;
+    static constexpr uint32_t THREADS = (2 + EPI_WARPS) * 32;
+    static constexpr uint32_t TMEM_COLS = 512;
+    static constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+};
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+__device__ __forceinline__ bool wait_bar_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    for (uint32_t i = 0; i < kWaitLimit; i++) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    if (status) atomicExch(status, kDeviceTimeout);
+    return false;
+}
+// arrive on a barrier of another CTA of the cluster (address from mapa)
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 2-D tile load whose completion is counted on a barrier of the pair's leader CTA (cluster address); no multicast:
+// the bytes land in the issuing CTA's shared memory only
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* tmap, uint32_t x, uint32_t y, uint32_t leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(tmap), "r"(x), "r"(y), "r"(leader_bar)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// commit of the pair's mmas: arrives on the barrier at this offset in BOTH CTAs
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"(mask)
+                 : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(PlanPair::THREADS, 1) prefill_tc_pair_kernel(const __grid_constant__ PrefillArgs a) {
+    using P = PlanPair;
+    constexpr int BU = 9;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bar_base = base + P::STAGES * P::STAGE_BYTES;
+    auto full_bar = [&](uint32_t s) { return bar_base + s * 8u; };                       // leader's: 4 + 4 dequant warps, 2 tile arrivals
+    auto empty_bar = [&](uint32_t s) { return bar_base + (P::STAGES + s) * 8u; };        // both CTAs: the pair's commit
+    const uint32_t acc_bar = bar_base + 3u * P::STAGES * 8u;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + P::STAGES * P::STAGE_BYTES + 3u * P::STAGES * 8u + 16u);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + P::STAGES * P::STAGE_BYTES + 3u * P::STAGES * 8u + 32u);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    uint32_t crank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+    const bool leader = crank == 0;
+    const uint32_t n0 = (blockIdx.x >> 1) * 256u + crank * 128u, tok0 = blockIdx.y * 512u;
+    const uint32_t blk0 = blockIdx.z * a.bps;
+    const uint32_t blk1 = min(a.K / kQK, blk0 + a.bps);
+    const uint32_t nkb = (blk1 - blk0) * 4u;
+    const uint32_t kbase = blk0 * kQK;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < P::STAGES; s++) {
+            mbar_init(full_bar(s), 2u * P::DEQ_WARPS + 1u);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(acc_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {  // the same warp of both CTAs allocates the pair's TMEM
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(P::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    cluster_sync_all();  // both CTAs' barriers initialised and TMEM allocated before anything crosses over
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    auto a_tile = [&](uint32_t s) { return base + s * P::STAGE_BYTES; };
+    auto b_tile = [&](uint32_t s, uint32_t j) { return base + s * P::STAGE_BYTES + P::A_BYTES + j * P::B_BYTES; };
+    auto leader_full = [&](uint32_t s) {
+        uint32_t r;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(full_bar(s)), "r"(0u));
+        return r;
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer: this CTA's 128 rows of each of the two activation tiles ----------------
+        if (lane == 0) {
+            const uint32_t lfull_tma = leader_full(0);
+            for (uint32_t kb = 0; kb < nkb; kb++) {
+                const uint32_t s = kb % P::STAGES, it = kb / P::STAGES;
+                if (it > 0 && !wait_bar(empty_bar(s), (it - 1) & 1u, abort_flag, a.status)) break;
+                if (leader) mbar_expect_tx(full_bar(s), 4u * P::B_BYTES);  // both CTAs' halves of both tiles
+                const uint32_t lbar = lfull_tma + s * 8u;
+                for (uint32_t j = 0; j < 2; j++)
+                    tma_load_2d_pair(b_tile(s, j), &a.tmap_x[0], kbase + kb * kKStep, tok0 + j * 256u + crank * 128u, lbar);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            // ---------------- MMA issuer of the pair ----------------
+            constexpr uint32_t idesc = (1u << 4) | ((BF16 ? 1u : 0u) << 7) | ((BF16 ? 1u : 0u) << 10) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
+            bool ok = true;
+            for (uint32_t kb = 0; kb < nkb && ok; kb++) {
+                const uint32_t s = kb % P::STAGES, it = kb / P::STAGES;
+                ok = wait_bar_cluster(full_bar(s), it & 1u, abort_flag, a.status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (uint32_t ks = 0; ks < kKStep / 16; ks++) {
+                    const uint32_t acc = (kb | ks) ? 1u : 0u;
+                    const uint64_t da = umma_desc(a_tile(s) + ks * 32u);
+#pragma unroll
+                    for (uint32_t j = 0; j < 2; j++) umma_f16_pair(tmem_base + j * 256u, da, umma_desc(b_tile(s, j) + ks * 32u), idesc, acc);
+                }
+                umma_commit_pair(empty_bar(s));
+            }
+            if (ok) umma_commit_pair(acc_bar);
+        }
+    } else {
+        const uint32_t dw = warp - 2;  // 0..7
+        bool ok = true;
+        {
+            // ---------------- dequantise (two threads per weight row of this CTA's 128) ----------------
+            const uint32_t r = (dw & 3u) * 32u + lane;
+            const uint32_t part = dw >> 2;  // which 16 of a sub-block's 32 weights (two threads per row)
+            const uint32_t n = n0 + r;
+            const uint4* wrow = reinterpret_cast<const uint4*>(a.W + (uint64_t)(n < a.N ? n : a.N - 1u) * a.w_row_bytes);
+            const uint32_t nblocks = blk1 - blk0;
+            wrow += (uint64_t)blk0 * BU;
+            const uint32_t row_off = (r >> 3) * 1024u + (r & 7u) * 128u;
+            const uint32_t sw = r & 7u;
+            const uint32_t lfull0 = leader_full(0);  // the leader's full barriers follow each other, 8 bytes apart
+            constexpr int RU2 = 5;  // header + one code unit per 64-weight group
+            uint4 raw[RU2], nxt[RU2];
+            auto load_block = [&](uint32_t b, uint4 (&dst)[RU2]) {
+                const uint4* p = wrow + (uint64_t)b * BU;
+                dst[0] = __ldg(p);
+#pragma unroll
+                for (int g = 0; g < 4; g++) dst[1 + g] = __ldg(p + 1 + 2 * g + part);
+            };
+            if (nblocks) load_block(0, nxt);
+            uint32_t st_s = 0, st_it = 0;
+            uint32_t choff[2][2];
+#pragma unroll
+            for (uint32_t cl = 0; cl < 2; cl++) {
+                const uint32_t c = 2u * part + cl;
+                choff[cl][0] = row_off + ((c ^ sw) << 4);
+                choff[cl][1] = row_off + (((c + 4u) ^ sw) << 4);
+            }
+            for (uint32_t b = 0; b < nblocks && ok; b++) {
+#pragma unroll
+                for (int i = 0; i < RU2; i++) raw[i] = nxt[i];
+                if (b + 1 < nblocks) load_block(b + 1, nxt);
+                const BlockHeader h{raw[0].x, raw[0].y, raw[0].z, raw[0].w};
+                const float d = half_bits_to_float(h.w0), dmin = half_bits_to_float(h.w0 >> 16);
+                uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
+                unpack_scales_packed(h, sc_lo, sc_hi, mn_lo, mn_hi);
+#pragma unroll
+                for (uint32_t g = 0; g < 4; g++) {
+                    const uint32_t s = st_s;
+                    if (st_it > 0 && !wait_bar(empty_bar(s), (st_it - 1u) & 1u, abort_flag, a.status)) {
+                        ok = false;
+                        break;
+                    }
+                    if (++st_s == P::STAGES) st_s = 0, st_it++;
+                    const float dsc_e = d * (float)byte_of(sc_lo, sc_hi, 2 * g), dmn_e = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g);
+                    const float dsc_o = d * (float)byte_of(sc_lo, sc_hi, 2 * g + 1), dmn_o = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g + 1);
+                    const uint32_t dsc_e2 = pack2<BF16>(dsc_e, dsc_e), ndmn_e2 = pack2<BF16>(-dmn_e, -dmn_e);
+                    const uint32_t dsc_o2 = pack2<BF16>(dsc_o, dsc_o), ndmn_o2 = pack2<BF16>(-dmn_o, -dmn_o);
+                    const uint4 u0 = raw[1 + g];
+                    const uint32_t words[4] = {u0.x, u0.y, u0.z, u0.w};
+                    const uint32_t ta = a_tile(s);
+#pragma unroll
+                    for (uint32_t c = 0; c < 2; c++) {
+                        uint32_t lo_bits[4], hi_bits[4];
+#pragma unroll
+                        for (uint32_t j = 0; j < 2; j++) {
+                            uint32_t o4[4];
+                            dequant_word_16<BF16>(words[2 * c + j], dsc_e2, ndmn_e2, dsc_o2, ndmn_o2, o4);
+                            lo_bits[2 * j] = o4[0];
+                            lo_bits[2 * j + 1] = o4[1];
+                            hi_bits[2 * j] = o4[2];
+                            hi_bits[2 * j + 1] = o4[3];
+                        }
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + choff[c][0]), "r"(lo_bits[0]),
+                                     "r"(lo_bits[1]), "r"(lo_bits[2]), "r"(lo_bits[3])
+                                     : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ta + choff[c][1]), "r"(hi_bits[0]),
+                                     "r"(hi_bits[1]), "r"(hi_bits[2]), "r"(hi_bits[3])
+                                     : "memory");
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (leader) mbar_arrive(full_bar(s));
+                        else mbar_arrive_remote(lfull0 + s * 8u);
+                    }
+                }
+            }
+        }
+        // ---------------- epilogue: this CTA's 128 x 512 accumulators -> Y ----------------
+        if (ok && wait_bar(acc_bar, 0, abort_flag, a.status)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t quad = warp & 3u;   // the TMEM lanes this warp may read
+            const uint32_t jt = dw >> 2;       // which 256-row activation tile
+            const uint32_t row = n0 + quad * 32u + lane;
+            const float bias = (a.ksplit == 1 && a.bias && row < a.N) ? a.bias[row] : 0.f;
+            float* Yout = a.ksplit == 1 ? a.Y : a.Ypart + (uint64_t)blockIdx.z * a.M * a.N;
+            for (uint32_t c0 = 0; c0 < 256u; c0 += 32) {
+                const uint32_t t0 = tok0 + jt * 256u + c0;
+                if (t0 >= a.M) break;
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((quad * 32u) << 16) + jt * 256u + c0, v);
+                if (row < a.N) {
+#pragma unroll
+                    for (uint32_t t = 0; t < 32; t++)
+                        if (t0 + t < a.M) Yout[(uint64_t)(t0 + t) * a.N + row] = __uint_as_float(v[t]) + bias;
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    cluster_sync_all();  // both CTAs have drained their accumulators; nothing crosses over any more
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P::TMEM_COLS) : "memory");
+    }
+}
+
 // X float32 [M][K] -> 16-bit [M][K] (and, for the three-pass mode, the low part of the half split)
 template <bool BF16, bool SPLIT>
 __global__ void __launch_bounds__(256) cast_activations_kernel(const float* __restrict__ X, uint64_t count4,
@@ -680,14 +1159,54 @@ cudaError_t launch_tc(const PrefillArgs& pa, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
+
+template <bool BF16>
+cudaError_t launch_tc_ts(const PrefillArgs& pa, cudaStream_t stream) {
+    using P = PlanTS;
+    static KernelConfig kcfg;
+    if (cudaError_t e = kcfg.prepare(reinterpret_cast<const void*>(prefill_tc_ts_kernel<BF16>), P::THREADS, P::SMEM_BYTES, nullptr))
+        return e;
+    const dim3 grid((pa.M + P::TOK - 1) / P::TOK, (pa.N + 255u) / 256u, pa.ksplit);
+    prefill_tc_ts_kernel<BF16><<<grid, P::THREADS, P::SMEM_BYTES, stream>>>(pa);
+    return cudaGetLastError();
+}
+
+template <bool BF16>
+cudaError_t launch_tc_pair(const PrefillArgs& pa, cudaStream_t stream) {
+    using P = PlanPair;
+    static KernelConfig kcfg;
+    if (cudaError_t e = kcfg.prepare(reinterpret_cast<const void*>(prefill_tc_pair_kernel<BF16>), P::THREADS, P::SMEM_BYTES, nullptr))
+        return e;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2u * ((pa.N + 255u) / 256u), (pa.M + 511u) / 512u, pa.ksplit);
+    cfg.blockDim = dim3(P::THREADS);
+    cfg.dynamicSmemBytes = P::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, prefill_tc_pair_kernel<BF16>, pa);
+}
+
 }  // namespace
 
 // K slices per problem: enough CTAs to occupy the machine when there are few output tiles, slices
 // of at least 1024 k, and (three-pass mode) at most 4096 k per slice so that the accumulation
 // error of the tensor core stays inside the tolerance of the path.
-static uint32_t choose_ksplit(uint32_t M, uint32_t N, uint32_t K, int mode, int sm_count) {
+// `mode` carries the precision mode in its low four bits and the single-pass variant above them (0: one CTA per tile,
+// weights through shared memory; 1: CTA pairs; 2: weights through tensor memory).
+static int variant_of(int mode, uint32_t M) {
+    const int v = (mode & 15) == 0 ? 0 : mode >> 4;
+    return (v == 1 && M <= kTokTile) ? 0 : v;  // a pair's tile is 512 activation rows: nothing to share below 257
+}
+static uint32_t choose_ksplit(uint32_t M, uint32_t N, uint32_t K, int mode_v, int sm_count) {
+    const int mode = mode_v & 15, variant = variant_of(mode_v, M);
     const uint32_t rows = mode == 0 ? 128u : 256u;
-    const uint32_t tiles = ((N + rows - 1) / rows) * ((M + kTokTile - 1) / kTokTile);
+    const uint32_t tiles = variant == 1   ? 2u * ((N + 255u) / 256u) * ((M + 511u) / 512u)
+                           : variant == 2 ? ((N + 255u) / 256u) * ((M + 127u) / 128u)
+                                          : ((N + rows - 1) / rows) * ((M + kTokTile - 1) / kTokTile);
     const uint32_t nblk = K / kQK;
     uint32_t z = tiles >= (uint32_t)sm_count ? 1u : (uint32_t)sm_count / tiles;  // stay within one wave of CTAs
     const uint32_t zmax = nblk / 4u ? nblk / 4u : 1u;  // >= 1024 k per slice
@@ -699,20 +1218,23 @@ static uint32_t choose_ksplit(uint32_t M, uint32_t N, uint32_t K, int mode, int 
     return (nblk + bps - 1) / bps;            // no empty slice
 }
 
-size_t prefill_scratch_bytes(uint32_t M, uint32_t N, uint32_t K, int mode, int sm_count) {
+size_t prefill_scratch_bytes(uint32_t M, uint32_t N, uint32_t K, int mode_v, int sm_count) {
+    const int mode = mode_v & 15;
     const size_t one = ((size_t)M * K * 2u + 255u) & ~(size_t)255u;
-    const uint32_t z = choose_ksplit(M, N, K, mode, sm_count);
+    const uint32_t z = choose_ksplit(M, N, K, mode_v, sm_count);
     return (mode == 0 ? 2 * one : one) + (z > 1 ? (size_t)z * M * N * 4u : 0);
 }
 
 // mode: 0 = three-pass half split, 1 = one pass half, 2 = one pass bfloat16 (the values of bpq4k_prefill_mode)
-cudaError_t launch_prefill_tc(const MatmulArgs& m, int mode, void* scratch, size_t scratch_bytes, int* status_dev,
+cudaError_t launch_prefill_tc(const MatmulArgs& m, int mode_v, void* scratch, size_t scratch_bytes, int* status_dev,
                               int sm_count, cudaStream_t stream, int* launches, int qtype) {
     if (m.M == 0 || m.N == 0) return cudaSuccess;
     if (qtype != 12 && qtype != 13 && qtype != kQ6PaddedType) return cudaErrorInvalidValue;
     const bool q5 = qtype == 13, q6 = qtype == kQ6PaddedType;
     if (m.n_slots) return cudaErrorInvalidValue;
-    if (!scratch || scratch_bytes < prefill_scratch_bytes(m.M, m.N, m.K, mode, sm_count)) return cudaErrorInvalidValue;
+    if (q5 || q6) mode_v &= 15;  // the variants exist for Q4_K
+    const int mode = mode_v & 15, variant = variant_of(mode_v, m.M);
+    if (!scratch || scratch_bytes < prefill_scratch_bytes(m.M, m.N, m.K, mode_v, sm_count)) return cudaErrorInvalidValue;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return cudaErrorNotSupported;
     uint8_t* hi = static_cast<uint8_t*>(scratch);
@@ -738,13 +1260,13 @@ cudaError_t launch_prefill_tc(const MatmulArgs& m, int mode, void* scratch, size
     pa.K = m.K;
     pa.w_row_bytes = m.w_row_bytes;
     pa.status = status_dev;
-    pa.ksplit = choose_ksplit(m.M, m.N, m.K, mode, sm_count);
+    pa.ksplit = choose_ksplit(m.M, m.N, m.K, mode_v, sm_count);
     pa.bps = (m.K / kQK + pa.ksplit - 1) / pa.ksplit;
     pa.Ypart = reinterpret_cast<float*>(lo + (mode == 0 ? (((size_t)m.M * m.K * 2u + 255u) & ~(size_t)255u) : 0));
     for (int v = 0; v < (mode == 0 ? 2 : 1); v++) {
         const cuuint64_t gdim[2] = {(cuuint64_t)m.K, (cuuint64_t)m.M};
         const cuuint64_t gstride[1] = {(cuuint64_t)m.K * 2u};
-        const cuuint32_t box[2] = {kKStep, kTokTile};
+        const cuuint32_t box[2] = {kKStep, variant ? 128u : kTokTile};  // pairs and the tensor-memory form load 128 activation rows per copy
         const cuuint32_t estr[2] = {1u, 1u};
         const CUresult r = enc(&pa.tmap_x[v], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, v == 0 ? hi : lo, gdim, gstride, box, estr,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -752,7 +1274,9 @@ cudaError_t launch_prefill_tc(const MatmulArgs& m, int mode, void* scratch, size
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
     if (mode != 0) pa.tmap_x[1] = pa.tmap_x[0];
-    if (mode == 0) e = q6 ? launch_tc<128, 3, false, 2>(pa, stream) : q5 ? launch_tc<128, 3, false, 1>(pa, stream) : launch_tc<128, 3, false>(pa, stream);
+    if (variant == 2) e = mode == 1 ? launch_tc_ts<false>(pa, stream) : launch_tc_ts<true>(pa, stream);
+    else if (variant == 1) e = mode == 1 ? launch_tc_pair<false>(pa, stream) : launch_tc_pair<true>(pa, stream);
+    else if (mode == 0) e = q6 ? launch_tc<128, 3, false, 2>(pa, stream) : q5 ? launch_tc<128, 3, false, 1>(pa, stream) : launch_tc<128, 3, false>(pa, stream);
     else if (mode == 1) e = q6 ? launch_tc<256, 1, false, 2>(pa, stream) : q5 ? launch_tc<256, 1, false, 1>(pa, stream) : launch_tc<256, 1, false>(pa, stream);
     else e = q6 ? launch_tc<256, 1, true, 2>(pa, stream) : q5 ? launch_tc<256, 1, true, 1>(pa, stream) : launch_tc<256, 1, true>(pa, stream);
     if (launches) ++*launches;

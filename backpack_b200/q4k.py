@@ -39,6 +39,8 @@ OPT_STREAM_PREWAIT_STAGES = 18
 OPT_STREAM_CLUSTER = 20
 OPT_STREAM_STAGING_WARPS = 21
 OPT_STREAM_NO_TAIL_SPLIT = 22
+OPT_PREFILL_VARIANT = 23
+PREFILL_ONE_CTA, PREFILL_CTA_PAIR, PREFILL_TMEM_WEIGHTS = 0, 1, 2
 OPT_STREAM_UNIT_ROWS = 19
 OPT_BATCH_RECORDS = 30   # read-only: replay graphs recorded by matmul_host_batch
 GEMV_AUTO, GEMV_FP32, GEMV_STREAM = 0, 1, 2

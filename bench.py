@@ -1019,6 +1019,24 @@ def measure_prefill(ctx, torch, shapes, W, dev, M=512, reps=5):
         out["modes"][name] = {"ms_per_pass": ms, "tflops": tf,
                               "frac_of_burst_peak": tf / peaks["bf16_tflops"] if peaks.get("bf16_tflops") else None,
                               "meets_float_tolerance": name == "f16x3"}
+    # the two other forms of the single-pass kernel (same bits, kept for comparison): bfloat16, the whole pass
+    out["variants_bf16"] = {}
+    ctx.set_option(q4k.OPT_PREFILL_MODE, q4k.PREFILL_BF16)
+    for variant, name in ((q4k.PREFILL_CTA_PAIR, "cta_pair_cta_group2"), (q4k.PREFILL_TMEM_WEIGHTS, "weights_in_tmem")):
+        ctx.set_option(q4k.OPT_PREFILL_VARIANT, variant)
+        for n, N, K in shapes:
+            ctx.matmul(xs[K], W[n], out=ys[n])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            for n, N, K in shapes:
+                ctx.matmul(xs[K], W[n], out=ys[n])
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        out["variants_bf16"][name] = {"ms_per_pass": ms, "tflops": flops / (ms * 1e-3) / 1e12}
+    ctx.set_option(q4k.OPT_PREFILL_VARIANT, q4k.PREFILL_ONE_CTA)
     ctx.set_option(q4k.OPT_PREFILL_MODE, q4k.PREFILL_F16X3)
     return out
 

@@ -104,6 +104,13 @@ typedef enum bpq4k_option {
     /* One activation row: the tiles of a CTA's share that do not fill a round of its tile slots are normally split
      * over K between all its warps (results of those rows then sum their K slices in a different grouping).  1: off. */
     BPQ4K_OPT_STREAM_NO_TAIL_SPLIT = 22,
+    /* Single-pass precision modes of the tensor-core kernel, Q4_K: how a weight tile meets the activations.
+     * 0 (default): one CTA per 256 weight rows x 256 activation rows, dequantised weights through shared memory.
+     * 1: two CTAs of a cluster share tcgen05.mma.cta_group::2 (2 x 128 weight rows x 512 activation rows; M > 256).
+     * 2: dequantised weights go to tensor memory (tcgen05.st) and the mma takes its A operand from there
+     *    (256 weight rows x 128 activation rows per CTA).
+     * All three give identical bits; 1 and 2 measured slower on B200 and exist for comparison. */
+    BPQ4K_OPT_PREFILL_VARIANT = 23,
     /* Read-only (bpq4k_get_option): how many times bpq4k_matmul_host_batch_f32 has recorded a dispatch
      * list into a replay graph on this handle.  A list is recorded again after any of the handle's
      * buffers had to grow. */

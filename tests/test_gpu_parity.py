@@ -233,6 +233,39 @@ def test_prefill_tensor_core(ctx, M, N, K, mode, name):
         assert rel_l2(y, want) <= tol
 
 
+@pytest.mark.parametrize("variant", [q4k.PREFILL_CTA_PAIR, q4k.PREFILL_TMEM_WEIGHTS], ids=["cta_pair", "weights_in_tmem"])
+@pytest.mark.parametrize("M,N,K", [(257, 256, 256), (512, 1000, 1024), (300, 2100, 2048), (700, 777, 4096), (64, 300, 512)])
+def test_prefill_variants_give_the_bits_of_the_default_kernel(ctx, variant, M, N, K):
+    """BPQ4K_OPT_PREFILL_VARIANT: CTA pairs sharing tcgen05.mma.cta_group::2, and dequantised weights as a tensor-memory
+    operand.  Each output element is the same sum of the same 16-bit products in the same k order, so with one K slice
+    (K <= 1024 here) the outputs must equal the default kernel's bit for bit; always within the mode's tolerance of the
+    checker."""
+    import torch
+
+    raw = synth.make_q4k_weights(N, K, 80)
+    x = synth.make_activations(M, K, 81)
+    bias = np.linspace(-2, 2, N).astype(np.float32)
+    w = ctx.upload(pack_q4k(raw, N, K))
+    want = orc.matmul(x, raw, bias, N, K)
+    for mode, tol in ((q4k.PREFILL_F16, 1e-3), (q4k.PREFILL_BF16, 8e-3)):
+        ctx.set_option(q4k.OPT_PREFILL_MODE, mode)
+        try:
+            ctx.set_option(q4k.OPT_PREFILL_VARIANT, q4k.PREFILL_ONE_CTA)
+            y0 = ctx.matmul(dev(torch, x), w, bias=dev(torch, bias)).cpu().numpy()
+            ctx.set_option(q4k.OPT_PREFILL_VARIANT, variant)
+            y1 = ctx.matmul(dev(torch, x), w, bias=dev(torch, bias)).cpu().numpy()
+            assert ctx.device_status() == 0
+        finally:
+            ctx.set_option(q4k.OPT_PREFILL_VARIANT, q4k.PREFILL_ONE_CTA)
+            ctx.set_option(q4k.OPT_PREFILL_MODE, q4k.PREFILL_F16X3)
+        assert rel_l2(y1, want) <= tol
+        # the K slices per problem follow the tile count, which differs between the forms: compare bits where both use one slice
+        if K <= 1024:
+            assert np.array_equal(y0, y1)
+        else:
+            assert rel_l2(y1, y0) <= 1e-5
+
+
 def test_prefill_threshold_option(ctx):
     """BPQ4K_OPT_PREFILL_MIN_M moves the hand-over point between the streaming and the tensor-core kernel."""
     import torch
