@@ -229,22 +229,35 @@ def run_reference_arm(args, rank):
 # --------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------
-def timed_groups(torch, dist, stream, run_step, steps, groups, world, dev, after_step=None):
-    """`groups` back-to-back groups of exactly `steps` steps, each group between two CUDA events on `stream`.
-    Several ranks: a host barrier, then one untimed step (its flag barrier, or its collectives, line the
+def capture_steps(torch, stream, one_step, n):
+    """One CUDA graph of `n` consecutive steps.  A decode loop replays a graph of hundreds of launches per token; a
+    graph of a single 8-launch step would pay the replay boundary (no dependent-launch overlap across it) every
+    eight launches, which no caller of the path does."""
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        for _ in range(n):
+            one_step()
+    return g
+
+
+def timed_groups(torch, dist, stream, run_step, steps, groups, world, dev, after_step=None, steps_per_call=1):
+    """`groups` back-to-back groups of exactly `steps` steps, each group between two CUDA events on `stream`
+    (`run_step` performs `steps_per_call` steps: a replay of a graph of that many).
+    Several ranks: a host barrier, then one untimed call (its flag barriers, or its collectives, line the
     devices up), then the groups; every group's time is the maximum over ranks.  Returns the per-group
     milliseconds (max over ranks)."""
+    assert steps % steps_per_call == 0
     if dist:
         dist.barrier()
     torch.cuda.synchronize()
     run_step()
     if after_step:
-        after_step(1)
+        after_step(steps_per_call)
     evs = []
     for _ in range(groups):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        for _ in range(steps):
+        for _ in range(steps // steps_per_call):
             run_step()
         e1.record(stream)
         evs.append((e0, e1))
@@ -398,7 +411,15 @@ def run_gpu_arm(args, rank, world, local_rank):
             note(max(args.warmup, 3))
         stream.synchronize()
         ctx.launch_count(reset=True)
-        group_ms = timed_groups(torch, dist, stream, run_step, steps, groups, world, dev, note)
+        if graph is not None:
+            # the timed groups replay ONE graph of `steps` steps each
+            steps_before = pg.steps if pg is not None else 0
+            graph_k = capture_steps(torch, stream, one_pass, steps)
+            if pg is not None:
+                pg.steps = steps_before
+            group_ms = timed_groups(torch, dist, stream, graph_k.replay, steps, groups, world, dev, note, steps_per_call=steps)
+        else:
+            group_ms = timed_groups(torch, dist, stream, run_step, steps, groups, world, dev, note)
         ms = float(np.median(group_ms))
 
         # the gathered outputs after the timed replays are still right (slot check on the last step)
@@ -410,15 +431,12 @@ def run_gpu_arm(args, rank, world, local_rank):
             for name, N, K in shapes:
                 ctx.matmul(X[name], W[name], out=Y[name])
 
-        kgraph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(kgraph, stream=stream):
-            kernels_only()
+        kgraph = capture_steps(torch, stream, kernels_only, steps)
         ctx.launch_count(reset=True)
         kernels_only()
         launches_per_step = ctx.launch_count()
-        for _ in range(3):
-            kgraph.replay()
-        kernel_ms = float(np.median(timed_groups(torch, dist, stream, kgraph.replay, steps, groups, world, dev)))
+        kgraph.replay()
+        kernel_ms = float(np.median(timed_groups(torch, dist, stream, kgraph.replay, steps, groups, world, dev, steps_per_call=steps)))
 
         # ---- end to end through the host-buffer entry point ---------------
         xs_pin = {n: torch.from_numpy(xs_h[n]).pin_memory() for n, _, _ in shapes}
@@ -539,7 +557,8 @@ def run_gpu_arm(args, rank, world, local_rank):
             "config": {"workload": WORKLOAD, "M": 1, "projections": [list(s) for s in shapes],
                        "bytes_per_step_per_gpu": sb, "weight_bytes_per_step_per_gpu": weight_bytes_total(),
                        "l2": "inputs larger than L2 (418 MB of weights per pass vs 126 MB L2)",
-                       "timing": f"median of {groups} back-to-back groups of {steps} steps each (CUDA events, max over ranks per group)",
+                       "timing": f"median of {groups} back-to-back groups of {steps} steps each (CUDA events, max over ranks per group); "
+                                 f"a group is one replay of a CUDA graph of {steps} steps",
                        "group_ms": group_ms,
                        "replay": "cuda graph" if graph is not None else "eager launches",
                        "sharding": ("none" if world == 1 else
@@ -600,12 +619,9 @@ def measure_fused_projections(ctx, torch, bp, shapes, weights_h, X, dev, stream,
     with torch.cuda.stream(stream):
         fused_pass()
         stream.synchronize()
-        fg = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(fg, stream=stream):
-            fused_pass()
-        for _ in range(3):
-            fg.replay()
-        us = float(np.median(timed_groups(torch, None, stream, fg.replay, steps, 5, 1, dev))) * 1e3 / steps
+        fg = capture_steps(torch, stream, fused_pass, steps)
+        fg.replay()
+        us = float(np.median(timed_groups(torch, None, stream, fg.replay, steps, 5, 1, dev, steps_per_call=steps))) * 1e3 / steps
     fbytes = sum(synth.algorithmic_bytes(1, FW[g].N, FW[g].K) for g, _ in groups)
     peak, _ = load_peaks()
     return {"what": "same weights, Q+K+V and gate+up fused by rows as the reference's loader does: 5 launches",
@@ -688,12 +704,9 @@ def measure_config4(ctx, torch, dist, bp, sharded, rank, world, dev, args):
         with torch.cuda.stream(stream):
             kernels_only()
             stream.synchronize()
-            kg = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(kg, stream=stream):
-                kernels_only()
-            for _ in range(3):
-                kg.replay()
-            kms = float(np.median(timed_groups(torch, dist, stream, kg.replay, steps, groups, world, dev))) / steps
+            kg = capture_steps(torch, stream, kernels_only, steps)
+            kg.replay()
+            kms = float(np.median(timed_groups(torch, dist, stream, kg.replay, steps, groups, world, dev, steps_per_call=steps))) / steps
         row["kernels_only"] = {"ms_per_step": kms, "value": total_bytes / kms / 1e6, "frac_of_hbm_peak": total_bytes / kms / 1e6 / (peak * world)}
         dims = {name: (N // world, K) for name, N, K in shapes}
         if world == 1:
@@ -721,7 +734,10 @@ def measure_config4(ctx, torch, dist, bp, sharded, rank, world, dev, args):
                 for _ in range(3):
                     g.replay()
                 pg.note_replays(3)
-                pms = float(np.median(timed_groups(torch, dist, stream, g.replay, steps, groups, world, dev, pg.note_replays))) / steps
+                before = pg.steps
+                gk = capture_steps(torch, stream, peer_step, steps)
+                pg.steps = before
+                pms = float(np.median(timed_groups(torch, dist, stream, gk.replay, steps, groups, world, dev, pg.note_replays, steps_per_call=steps))) / steps
             check_all_slots(torch, dist, rank, world, dev, ("k",), dims, xs_h, raws, lambda n: pg.gathered(n), M)
             row["peer_gather"] = {"ms_per_step": pms, "value": total_bytes / pms / 1e6,
                                   "frac_of_hbm_peak": total_bytes / pms / 1e6 / (peak * world),
