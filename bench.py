@@ -536,6 +536,11 @@ def run_gpu_arm(args, rank, world, local_rank):
                     "peak_source": peak_src,
                     "kernel": "q4k matmul (M=1)", "launches_per_step": launches_per_step,
                     "avg_launch_us": per_launch_s * 1e6, "alg_bytes_per_launch": per_launch_bytes}
+        fp = extras.get("fused_projections")
+        if fp:
+            # the same step as the reference's loader lays the weights out (Q+K+V and gate+up fused by rows): 5 launches
+            roofline["fused_step"] = {"launches_per_step": 5, "achieved": fp["value"], "frac": fp["frac_of_hbm_peak"],
+                                      "avg_launch_us": fp["ms_per_step"] * 1e3 / 5}
         pf = extras.get("prefill")
         if pf:
             roofline["prefill"] = {"bound": "tensor", "unit": "TFLOP/s", "peak": pf.get("bf16_tflops"),
