@@ -490,7 +490,8 @@ __global__ void __launch_bounds__(Plan<ROWS, PASSES, QT>::THREADS, 1) prefill_tc
                 const uint32_t g = gi;
                 // The stage's 16-bit values are computed BEFORE its buffer is waited for: in steady state the buffer
                 // is what the warp waits on, and only the stores, the fence and the arrival are left on the path
-                // between "buffer free" and "tile ready" (128256 x 4096, M = 512, bfloat16: 1157 -> see the header).
+                // between "buffer free" and "tile ready" (no measurable change by itself: the stores and the fence
+                // are the long part of that path).
                 // w = (d*sc)*q - dmin*mn in float, rounded to 16 bits afterwards
                 const float dsc_e = d * (float)byte_of(sc_lo, sc_hi, 2 * g), dmn_e = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g);
                 const float dsc_o = d * (float)byte_of(sc_lo, sc_hi, 2 * g + 1), dmn_o = dmin * (float)byte_of(mn_lo, mn_hi, 2 * g + 1);
