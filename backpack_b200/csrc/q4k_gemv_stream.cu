@@ -350,7 +350,7 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
     __syncwarp();
     // Cluster staging (single row, plain form): the CTAs of a cluster quantise a share of the row each and write it
     // into every member's shared memory.  First cluster phase: every member is running (its shared memory exists).
-    constexpr bool CL = M1 && !XG && !XC && !FP && !IND;
+    constexpr bool CL = M1 && !XG && !XC && !IND;
     [[maybe_unused]] uint32_t crank = 0;
     const uint32_t cs = CL ? a.csize : 1u;
     if constexpr (CL) {
@@ -488,12 +488,32 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
         [[maybe_unused]] auto pick = [&](const float* const* rows, uint32_t l) {
             return l == 0 ? rows[0] : l == 1 ? rows[1] : l == 2 ? rows[2] : rows[3];
         };
-        if (FP && a.m.prologue) {
-            // Fused prologue on the single activation row (the reference's q4k_matmul_norm.wgsl:47-92
-            // and q4k_down_gelu.wgsl:47-62, plus the silu form of silu_mul_fused): transform while staging.
+        // Fused prologue on the single activation row (the reference's q4k_matmul_norm.wgsl:47-92
+        // and q4k_down_gelu.wgsl:47-62, plus the silu form of silu_mul_fused): transform while staging.
+        [[maybe_unused]] auto prologue_item = [&](float4 (&v)[2], const float4 (&w)[2], float rstd) {
+            float* vf = reinterpret_cast<float*>(v);
+            const float* wf = reinterpret_cast<const float*>(w);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float g = vf[i];
+                if (a.m.prologue == 1u) {
+                    vf[i] = g * rstd * wf[i];
+                } else if (a.m.prologue == 2u) {
+                    const float inner = 0.7978845608f * (g + 0.044715f * g * g * g);
+                    vf[i] = 0.5f * g * (1.f + tanhf(inner)) * wf[i];
+                } else {
+                    vf[i] = __fdividef(g, 1.f + __expf(-g)) * wf[i];  // relative error ~1e-6: far inside the digits' 2^-22
+                }
+            }
+        };
+        if (FP && a.m.prologue && !(CL && cs > 1u)) {
             float rstd = 1.f;
             bool rest_issued = false;
-            if (a.m.prologue == 1u) {
+            constexpr int UP = 4;  // items per thread and round, loads of x and aux issued together
+            // RMSNorm of a row that fits one round: the values stay in registers between the sum of squares and the
+            // transform (one pass over X instead of two)
+            const bool one_round = !IND && items <= blockDim.x * UP;
+            if (a.m.prologue == 1u && !one_round) {
                 float ss = 0.f;
                 for (uint32_t i = tid; i < K / 4u; i += blockDim.x) {
                     const float4 v = __ldg(reinterpret_cast<const float4*>(X) + i);
@@ -511,7 +531,6 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
                 rstd = 1.f / sqrtf(tot / (float)K + a.m.eps);
                 __syncthreads();  // red is the partial-sum buffer of the main loop
             }
-            constexpr int UP = 4;  // items per thread and round, loads of x and aux issued together
             for (uint32_t base = 0; base < items; base += blockDim.x * UP) {
                 const uint32_t nj = min((uint32_t)UP, (items - base + blockDim.x - 1) / blockDim.x);  // uniform over the CTA
                 float4 v[UP][2], w[UP][2];
@@ -530,26 +549,41 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
                     }
                 }
                 if (!rest_issued) issue_rest(), rest_issued = true;
+                if (a.m.prologue == 1u && one_round) {  // (one_round: this is the loop's only iteration, for every thread)
+                    float ss = 0.f;
 #pragma unroll
-                for (int j = 0; j < UP; j++) {
-                    if ((uint32_t)j >= nj) continue;
-                    const uint32_t it = base + j * blockDim.x + tid;
-                    float* vf = reinterpret_cast<float*>(v[j]);
-                    const float* wf = reinterpret_cast<const float*>(w[j]);
+                    for (int j = 0; j < UP; j++) {  // items that were not loaded are zeros
+                        const float* vf = reinterpret_cast<const float*>(v[j]);
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const float g = vf[i];
-                        if (a.m.prologue == 1u) {
-                            vf[i] = g * rstd * wf[i];
-                        } else if (a.m.prologue == 2u) {
-                            const float inner = 0.7978845608f * (g + 0.044715f * g * g * g);
-                            vf[i] = 0.5f * g * (1.f + tanhf(inner)) * wf[i];
-                        } else {
-                            vf[i] = __fdividef(g, 1.f + __expf(-g)) * wf[i];  // relative error ~1e-6: far inside the digits' 2^-22
-                        }
+                        for (int i = 0; i < 8; i++) ss = fmaf(vf[i], vf[i], ss);
                     }
-                    const uint32_t l = (IND && it < items) ? it / per_row : 0u;
-                    quantize_loaded(v[j][0], v[j][1], K, l, it < items ? it - l * per_row : 0u, it < items, frag, SI);
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+                    float* red = reinterpret_cast<float*>(smem + a.off_part);
+                    if (lane == 0) red[warp] = ss;
+                    __syncthreads();
+                    float tot = 0.f;
+                    for (uint32_t w2 = 0; w2 < swarps; w2++) tot += red[w2];
+                    rstd = 1.f / sqrtf(tot / (float)K + a.m.eps);
+                    __syncthreads();  // red is the partial-sum buffer of the main loop
+                }
+                // two items side by side
+#pragma unroll
+                for (int j = 0; j < UP; j += 2) {
+                    if ((uint32_t)j >= nj) break;
+                    const uint32_t it0 = base + j * blockDim.x + tid, it1 = it0 + blockDim.x;
+                    const bool two = (uint32_t)(j + 1) < nj;
+                    const uint32_t l0 = (IND && it0 < items) ? it0 / per_row : 0u;
+                    prologue_item(v[j], w[j], rstd);
+                    if (two) {
+                        const uint32_t l1 = (IND && it1 < items) ? it1 / per_row : 0u;
+                        prologue_item(v[j + 1], w[j + 1], rstd);
+                        const QuantItem q0 = quantize_compute(v[j][0], v[j][1]), q1 = quantize_compute(v[j + 1][0], v[j + 1][1]);
+                        quantize_store(q0, K, l0, it0 < items ? it0 - l0 * per_row : 0u, it0 < items, frag, SI, false);
+                        quantize_store(q1, K, l1, it1 < items ? it1 - l1 * per_row : 0u, it1 < items, frag, SI, false);
+                    } else {
+                        quantize_loaded(v[j][0], v[j][1], K, l0, it0 < items ? it0 - l0 * per_row : 0u, it0 < items, frag, SI);
+                    }
                 }
             }
         } else if (CL && cs > 1u) {
@@ -569,6 +603,7 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
             bool started = false;
             for (uint32_t base = 0; base < mine || !started; base += blockDim.x * U) {
                 float4 v[U][2];
+                [[maybe_unused]] float4 w[U][2];
                 uint32_t c8[U];
                 bool valid[U];
 #pragma unroll
@@ -577,13 +612,25 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
                     valid[j] = li < mine;
                     c8[j] = valid[j] ? it0 + li : 0u;
                     v[j][0] = v[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if constexpr (FP) w[j][0] = w[j][1] = v[j][0];
                     if (valid[j]) {
                         const float4* xp = reinterpret_cast<const float4*>(X + item_offset(c8[j]));
                         v[j][0] = __ldg(xp);
                         v[j][1] = __ldg(xp + 4);
+                        if (FP && a.m.prologue) {  // (element-wise prologues only: the host keeps RMSNorm rows unclustered)
+                            const float4* ap = reinterpret_cast<const float4*>(AUX + item_offset(c8[j]));
+                            w[j][0] = __ldg(ap);
+                            w[j][1] = __ldg(ap + 4);
+                        }
                     }
                 }
                 if (!started) issue_rest();
+                if constexpr (FP) {
+                    if (a.m.prologue) {
+                        prologue_item(v[0], w[0], 1.f);
+                        prologue_item(v[1], w[1], 1.f);
+                    }
+                }
                 const QuantItem q0 = quantize_compute(v[0][0], v[0][1]), q1 = quantize_compute(v[1][0], v[1][1]);
                 if (!started) {  // every member runs: its shared memory may be written
                     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -1093,7 +1140,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     }
     // Cluster staging: only the plain single-row form, only with a contiguous split, and only as many CTAs as the
     // device can keep resident as whole clusters (queried once per device, kernel and cluster size)
-    uint32_t cs = (M1 && !XG && !XC && !FP && !IND && sb.contig) ? sa.csize : 1u;
+    uint32_t cs = (M1 && !XG && !XC && !IND && sb.contig && !(FP && sa.m.prologue == 1u)) ? sa.csize : 1u;  // (RMSNorm needs the whole row in every CTA)
     if (cs > 1u) {
         static std::mutex mu;
         static int max_clusters[16][5];  // [device][cluster size], 0 = not asked yet
