@@ -28,6 +28,7 @@ launch streams its weights from HBM.
 
 ``prefill``   (1 GPU) the same projections at M = 512 through the tensor-core
               kernel, useful TFLOP/s per precision mode.
+``per_shape``  (1 GPU) every distinct projection shape of the step alone, HBM-cold.
 ``fused_projections`` (1 GPU) the step with Q+K+V and gate+up fused by rows.
 ``kquant_siblings``   (1 GPU) the output head in Q5_K and Q6_K, M = 1.
 ``fused_prologues``   (1 GPU) launch time with and without a fused RMSNorm /
@@ -502,6 +503,7 @@ def run_gpu_arm(args, rank, world, local_rank):
 
     extras = {}
     if world == 1:
+        extras["per_shape"] = measure_per_shape(ctx, torch, bp, shapes, weights_h, dev)
         extras["fused_projections"] = measure_fused_projections(ctx, torch, bp, shapes, weights_h, X, dev, stream, steps)
         extras["config0"] = measure_config0(ctx, torch, bp, weights_h["q"], dev)
         if not args.no_prefill:
@@ -649,6 +651,34 @@ def measure_config0(ctx, torch, bp, raw_q, dev):
     return {"workload": "single GEMV 4096 x 4096, M=1 (config 0)", "alg_bytes": b,
             "hbm_cold": {"us_per_launch": cold, "value": b / cold / 1e3, "unit": UNIT, "frac_of_hbm_peak": b / cold / 1e3 / peak},
             "l2_warm": {"us_per_launch": warm, "value": b / warm / 1e3, "unit": UNIT}}
+
+
+def measure_per_shape(ctx, torch, bp, shapes, weights_h, dev):
+    """Configuration 1 shape by shape: each distinct projection shape alone, M = 1, launched back to back over enough
+    copies of the weight that every launch streams from HBM (>= 400 MB walked per graph replay)."""
+    peak, _ = load_peaks()
+    out = {"unit": UNIT, "what": "one launch per copy of the weight, >= 400 MB of copies walked per replay (HBM-cold)", "shapes": {}}
+    stream = torch.cuda.Stream(device=dev)
+    seen = {}
+    for name, N, K in shapes:
+        if (N, K) in seen:
+            seen[(N, K)].append(name)
+            continue
+        seen[(N, K)] = [name]
+        wb = synth.weight_bytes(N, K)
+        nc = max(2, min(160, int(400e6 // wb) + 1))
+        packed = bp.pack_q4k(weights_h[name], N, K)
+        Ws = [ctx.upload(packed) for _ in range(nc)]
+        x = torch.randn(1, K, device=dev, generator=torch.Generator(device=dev).manual_seed(11))
+        y = torch.empty(1, N, device=dev)
+        reps = max(1, 64 // nc)
+        us = graph_time_us(torch, stream, lambda: [ctx.matmul(x, w, out=y) for _ in range(reps) for w in Ws], nc * reps)
+        b = synth.algorithmic_bytes(1, N, K)
+        out["shapes"][f"{N}x{K}"] = {"projections": seen[(N, K)], "alg_bytes": b, "us_per_launch": us, "value": b / us / 1e3,
+                                    "frac_of_hbm_peak": b / us / 1e3 / peak}
+        del Ws
+        torch.cuda.empty_cache()
+    return out
 
 
 def measure_small_batch(ctx, torch, w_head, dev):
