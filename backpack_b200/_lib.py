@@ -24,6 +24,7 @@ SIGNATURES = {
     "bpq4k_last_error_string": (C.c_char_p, [vp]),
     "bpq4k_set_option": (C.c_int, [vp, C.c_int, C.c_int]),
     "bpq4k_get_option": (C.c_int, [vp, C.c_int, C.POINTER(C.c_int)]),
+    "bpq4k_read_stream_stamps": (C.c_int, [vp, vp, C.c_size_t, C.POINTER(C.c_uint32)]),
     "bpq4k_launch_count": (u64, [vp, C.c_int]),
     "bpq4k_device_status": (C.c_int, [vp, vp, C.POINTER(C.c_int)]),
     "bpq4k_n_blocks": (u32, [u32]),

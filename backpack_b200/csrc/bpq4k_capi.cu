@@ -46,6 +46,7 @@ struct bpq4k_context {
     // double-buffered gather slots of the fused all-gather (bpq4k_peer_double_buffer)
     const uint32_t* peer_parity = nullptr;
     uint64_t peer_parity_stride = 0;
+    uint32_t stamp_next = 0;     // launches stamped so far (BPQ4K_OPT_STREAM_STAMPS); tune.stamp_next points here
     uint32_t batch_records = 0;  // how many times a list was captured into a graph (BPQ4K_OPT_BATCH_RECORDS)
     // device blocks that were outgrown; freed at destroy (see ensure_bytes)
     static constexpr uint32_t kMaxRetired = 48;
@@ -259,6 +260,7 @@ int bpq4k_destroy(bpq4k_handle_t h) {
         if (h->stage_y) cudaFree(h->stage_y);
         if (h->scratch) cudaFree(h->scratch);
         if (h->dev_status) cudaFree(h->dev_status);
+        if (h->tune.stamps) cudaFree(h->tune.stamps);
         for (uint32_t i = 0; i < h->n_retired; i++) cudaFree(h->retired[i]);
         if (h->batch_exec) cudaGraphExecDestroy(h->batch_exec);
         if (h->batch_stream) cudaStreamDestroy(h->batch_stream);
@@ -333,6 +335,29 @@ int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
         case BPQ4K_OPT_STREAM_NO_TAIL_SPLIT:
             h->tune.no_tail_split = value ? 1u : 0u;
             return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_STAMPS: {
+            if (value < 0 || value > 4096) return fail(h, BPQ4K_ERR_INVALID_ARG, "stamp slots must be 0..4096");
+            DeviceGuard g(h->device);
+            drop_batch_graph(h);  // (a recorded list carries the old buffer and slots)
+            if (h->tune.stamps) {
+                cudaDeviceSynchronize();
+                cudaFree(h->tune.stamps);
+            }
+            h->tune.stamps = nullptr;
+            h->tune.stamp_next = nullptr;
+            h->tune.stamp_launches = 0;
+            h->stamp_next = 0;
+            if (value > 0) {
+                const size_t bytes = (size_t)value * kStreamStampCtas * 8u * sizeof(unsigned long long);
+                if (cudaMalloc(reinterpret_cast<void**>(&h->tune.stamps), bytes) != cudaSuccess || cudaMemset(h->tune.stamps, 0, bytes) != cudaSuccess) {
+                    h->tune.stamps = nullptr;
+                    return fail(h, BPQ4K_ERR_CUDA, "stamp buffer: %s", cudaGetErrorString(cudaGetLastError()));
+                }
+                h->tune.stamp_next = &h->stamp_next;
+                h->tune.stamp_launches = (uint32_t)value;
+            }
+            return BPQ4K_OK;
+        }
         case BPQ4K_OPT_PREFILL_VARIANT:
             if (value < 0 || value > 2) return fail(h, BPQ4K_ERR_INVALID_ARG, "prefill variant must be 0, 1 or 2");
             h->prefill_variant = value;
@@ -351,6 +376,7 @@ int bpq4k_get_option(bpq4k_handle_t h, int option, int* value) {
         case BPQ4K_OPT_GEMV_VARIANT: *value = h->gemv_variant; return BPQ4K_OK;
         case BPQ4K_OPT_PREFILL_MODE: *value = h->prefill_mode; return BPQ4K_OK;
         case BPQ4K_OPT_PREFILL_VARIANT: *value = h->prefill_variant; return BPQ4K_OK;
+        case BPQ4K_OPT_STREAM_STAMPS: *value = (int)h->tune.stamp_launches; return BPQ4K_OK;
         case BPQ4K_OPT_PREFILL_MIN_M: *value = h->prefill_min_m; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_WARPS: *value = (int)h->tune.warps; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_KSPLIT: *value = (int)h->tune.wk; return BPQ4K_OK;
@@ -368,6 +394,18 @@ int bpq4k_get_option(bpq4k_handle_t h, int option, int* value) {
         case BPQ4K_OPT_BATCH_RECORDS: *value = (int)h->batch_records; return BPQ4K_OK;
         default: return fail(h, BPQ4K_ERR_INVALID_ARG, "unknown option %d", option);
     }
+}
+
+int bpq4k_read_stream_stamps(bpq4k_handle_t h, unsigned long long* dst, size_t words, uint32_t* launches_stamped) {
+    if (!h || !dst) return BPQ4K_ERR_INVALID_ARG;
+    if (!h->tune.stamps) return fail(h, BPQ4K_ERR_INVALID_ARG, "time stamps are off (BPQ4K_OPT_STREAM_STAMPS)");
+    const size_t have = (size_t)h->tune.stamp_launches * kStreamStampCtas * 8u;
+    if (words > have) words = have;
+    DeviceGuard g(h->device);
+    if (cudaDeviceSynchronize() != cudaSuccess || cudaMemcpy(dst, h->tune.stamps, words * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess)
+        return fail(h, BPQ4K_ERR_CUDA, "stamp read: %s", cudaGetErrorString(cudaGetLastError()));
+    if (launches_stamped) *launches_stamped = h->stamp_next;
+    return BPQ4K_OK;
 }
 
 uint64_t bpq4k_launch_count(bpq4k_handle_t h, int reset) {

@@ -56,6 +56,7 @@ constexpr int kDeviceTimeout = 6;
 constexpr int kDeviceAssert = 9;
 
 // Tuning knobs of the streaming kernel; 0 = choose automatically.
+constexpr uint32_t kStreamStampCtas = 160;
 struct StreamTuning {
     uint32_t warps = 0;        // warps per CTA (<= 16)
     uint32_t wk = 0;           // warps that split K of one 16-row tile
@@ -70,6 +71,11 @@ struct StreamTuning {
     uint32_t cluster = 0;      // CTAs per cluster sharing the staging of a single activation row: 0 automatic, 1, 2, 4
     uint32_t staging_warps = 0;  // single row: warps that stage the activation row (helpers leave before the main loop): 0 automatic (16), 1..16
     uint32_t no_tail_split = 0;  // 1: the tiles that do not fill a round of a CTA's tile slots keep their slot instead of being split over K
+    // time stamps of the single-row streaming kernel (BPQ4K_OPT_STREAM_STAMPS): device buffer of stamp_launches slots of
+    // kStreamStampCtas CTAs x 8 words, the handle's running launch counter
+    unsigned long long* stamps = nullptr;
+    uint32_t* stamp_next = nullptr;
+    uint32_t stamp_launches = 0;
 };
 
 // Launch configuration of ONE kernel instantiation per device: the opt-in dynamic shared-memory size

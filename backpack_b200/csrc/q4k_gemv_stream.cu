@@ -86,6 +86,9 @@ struct StreamArgs {
     // slots are split over K between ALL its warps, tail_tb blocks each (0: off), through this map's boxes.
     CUtensorMap tmap_tail;
     uint32_t tail_tb;
+    // optional time stamps (BPQ4K_OPT_STREAM_STAMPS): eight words per CTA of this launch's slot, written by thread 0
+    unsigned long long* stamps;
+    uint32_t stamp_slot;
 };
 
 // Largest |xi|: its top base-128 digit still fits a signed byte.
@@ -242,6 +245,7 @@ __device__ __forceinline__ void merge_fifth_bit(uint32_t codes, uint32_t qh, uin
 // shape, activations and offsets: the gate and up stacks of an expert layer) the list simply continues
 // over it, results to m.Y2.
 constexpr uint32_t kMaxLocalSlots = 4;
+constexpr uint32_t kStampCtas = kStreamStampCtas;  // CTAs per launch that leave time stamps
 template <int NT, bool M1, bool XG, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false, int RT = 1>
 __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
     static_assert(!FP || (M1 && !XG && !XC), "the fused forms are single-row and stage the row themselves");
@@ -255,6 +259,17 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
     constexpr int TOK = M1 ? 1 : NT * 4;  // activation-row slots (four per 8-column mma tile)
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    // Time stamps for the attribution of a launch's microseconds (off unless the caller asked for them): 0 start,
+    // 1 before the dependency wait, 2 released, 3 activations staged, 4 last tile slot of thread 0 done, 5 end;
+    // word 7 = SM id and grid size.
+    auto stamp = [&](uint32_t i) {
+        if (a.stamps && tid == 0 && blockIdx.y == 0 && blockIdx.x < kStampCtas) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            a.stamps[((uint64_t)a.stamp_slot * kStampCtas + blockIdx.x) * 8u + i] = t;
+        }
+    };
+    stamp(0);
     // Warps beyond the plan's wk x wt are helpers: they take part in the staging of the activations (the one serial
     // step of the kernel, faster with one item per thread) and leave before the main loop.
     const uint32_t swarps = blockDim.x >> 5;
@@ -433,8 +448,10 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
     // and READS the weights, so it may overlap the tail of the preceding kernel in the stream.
     // Let the next kernel start its own prologue, then wait for the preceding kernel (which may
     // have produced X, or may still read Y) before reading X or writing anything.
+    stamp(1);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    stamp(2);
     if constexpr (XG) issue_rest();  // nothing is staged per CTA in this mode
 
     // ---- activations: quantise to base-128 digits, once per CTA ---------------------
@@ -690,6 +707,7 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
         }
     }
 
+    stamp(3);
     if (helper) return;  // (no CTA-wide barrier follows: the tile epilogues use named barriers over the plan's warps)
 
     // ---- per-lane constants ----------------------------------------------------
@@ -1019,6 +1037,7 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
         }
     }
 
+    stamp(4);
     // ---- tail split: the tiles that did not fill a round, every warp a K slice of each ----------------------
     if constexpr (M1 && !IND) {
         if (tail_n) {
@@ -1066,6 +1085,12 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
                 }
             }
         }
+    }
+    stamp(5);
+    if (a.stamps && tid == 0 && blockIdx.y == 0 && blockIdx.x < kStampCtas) {
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        a.stamps[((uint64_t)a.stamp_slot * kStampCtas + blockIdx.x) * 8u + 7u] = smid | ((unsigned long long)gridDim.x << 32);
     }
 }
 
@@ -1366,6 +1391,10 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     sa.ntiles = ntiles; sa.tokens = tokens; sa.status = status_dev;
     // Long rows: the CTAs of a cluster share the staging of the activation row (4096 x 14336: 11.07 -> 10.33 us,
     // 8192 x 28672: 29.4 -> 27.9 us with pairs).  At K = 4096 a clustered launch starts ~0.5 us later than it stages faster.
+    if (tune.stamps && tune.stamp_next && tune.stamp_launches) {
+        sa.stamps = tune.stamps;
+        sa.stamp_slot = (*tune.stamp_next)++ % tune.stamp_launches;
+    }
     sa.csize = tune.cluster ? tune.cluster : (m1 && !indirect && m.K >= 14336u) ? 2u : 1u;
     {
         // whole ring before the wait while it is small (it lands long before the activations are needed); of a deep

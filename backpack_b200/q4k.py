@@ -40,6 +40,7 @@ OPT_STREAM_CLUSTER = 20
 OPT_STREAM_STAGING_WARPS = 21
 OPT_STREAM_NO_TAIL_SPLIT = 22
 OPT_PREFILL_VARIANT = 23
+OPT_STREAM_STAMPS = 24
 PREFILL_ONE_CTA, PREFILL_CTA_PAIR, PREFILL_TMEM_WEIGHTS = 0, 1, 2
 OPT_STREAM_UNIT_ROWS = 19
 OPT_BATCH_RECORDS = 30   # read-only: replay graphs recorded by matmul_host_batch
@@ -179,6 +180,16 @@ class Q4KContext:
         v = C.c_int()
         self._check(self.lib.bpq4k_get_option(self.h, option, C.byref(v)))
         return v.value
+
+    def stream_stamps(self, slots: int):
+        """Time stamps of the single-row streaming kernel (BPQ4K_OPT_STREAM_STAMPS must be on): a uint64 array
+        [slots, 160, 8] of GPU-timer nanoseconds and the number of launches stamped so far."""
+        import numpy as np
+
+        buf = np.zeros((slots, 160, 8), np.uint64)
+        n = C.c_uint32()
+        self._check(self.lib.bpq4k_read_stream_stamps(self.h, buf.ctypes.data, buf.size, C.byref(n)))
+        return buf, n.value
 
     def device_status(self) -> int:
         """Status word set by kernels whose bounded waits ran out (0 = none); synchronises."""

@@ -111,6 +111,11 @@ typedef enum bpq4k_option {
      *    (256 weight rows x 128 activation rows per CTA).
      * All three give identical bits; 1 and 2 measured slower on B200 and exist for comparison. */
     BPQ4K_OPT_PREFILL_VARIANT = 23,
+    /* Time stamps of the single-row streaming kernel, for attributing a launch's microseconds.  n > 0: keep the
+     * stamps of the last n launches (a device buffer of n x 160 CTAs x 8 words; launch i writes slot i mod n;
+     * launches captured into a graph keep the slot they were given at capture); 0: off (default, no cost).
+     * Read with bpq4k_read_stream_stamps.  No counterpart in the reference. */
+    BPQ4K_OPT_STREAM_STAMPS = 24,
     /* Read-only (bpq4k_get_option): how many times bpq4k_matmul_host_batch_f32 has recorded a dispatch
      * list into a replay graph on this handle.  A list is recorded again after any of the handle's
      * buffers had to grow. */
@@ -149,6 +154,13 @@ int bpq4k_device_index(bpq4k_handle_t h);
 
 int bpq4k_set_option(bpq4k_handle_t h, int option, int value);
 int bpq4k_get_option(bpq4k_handle_t h, int option, int* value);
+
+/* Copies the time-stamp buffer to the host (after a device synchronisation): per stamped launch slot 160 CTAs x 8 words
+ * of the GPU's nanosecond timer: [0] kernel start, [1] before the dependency wait, [2] released by the preceding
+ * kernel, [3] activation row staged, [4] thread 0's last tile done, [5] kernel end, [7] SM id | grid size << 32
+ * (zero for CTAs the launch did not have).  `words` is clipped to the buffer; *launches_stamped (may be NULL)
+ * receives how many launches have been stamped since the option was set.  No counterpart in the reference. */
+int bpq4k_read_stream_stamps(bpq4k_handle_t h, unsigned long long* dst, size_t words, uint32_t* launches_stamped);
 
 /* Number of kernels this handle has launched since creation (or since the
  * counter was last reset with reset != 0).  The reference counts dispatches in
