@@ -345,6 +345,33 @@ def test_tail_split_matches_checker(ctx, N, K):
     assert len(np.unique(differ)) <= 148   # at most one tile per CTA
 
 
+def test_stream_time_stamps(ctx):
+    """BPQ4K_OPT_STREAM_STAMPS: thread 0 of every CTA of a single-row launch leaves six ordered time stamps and its SM
+    id; the result of the call is unchanged; reading with the option off is an argument error."""
+    import torch
+
+    N, K = 4096, 4096
+    raw = synth.make_q4k_weights(N, K, 90)
+    x = synth.make_activations(1, K, 91)
+    w = ctx.upload(pack_q4k(raw, N, K))
+    y0 = ctx.matmul(dev(torch, x), w).cpu().numpy()
+    with pytest.raises(q4k.Q4KError):
+        ctx.stream_stamps(4)
+    ctx.set_option(q4k.OPT_STREAM_STAMPS, 4)
+    try:
+        y1 = ctx.matmul(dev(torch, x), w).cpu().numpy()
+        ts, n = ctx.stream_stamps(4)
+    finally:
+        ctx.set_option(q4k.OPT_STREAM_STAMPS, 0)
+    assert n == 1 and np.array_equal(y0, y1)
+    grid = int(ts[0, 0, 7] >> np.uint64(32))
+    assert 1 <= grid <= 160
+    t = ts[0, :grid, :6].astype(np.int64)
+    assert (t > 0).all() and (np.diff(t, axis=1) >= 0).all()
+    assert (t[:, 5] - t[:, 0]).max() < 1_000_000       # a launch of 9 MB ends within a millisecond
+    assert not ts[1:].any()
+
+
 # ---------------------------------------------------------------- MoE indirect form
 
 @pytest.mark.parametrize("variant", VARIANTS, ids=VARIANT_IDS)
