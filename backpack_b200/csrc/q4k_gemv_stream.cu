@@ -1209,7 +1209,15 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     cfg.gridDim = dim3(gx, slots_y);
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND, RT>, sb);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND, RT>, sb);
+    if (e != cudaSuccess && cs > 1u) {
+        // a context that cannot place clusters (restricted SM sets): the same launch without them
+        cudaGetLastError();
+        sb.csize = 1;
+        cfg.numAttrs = na - 1;  // the cluster attribute is the last one
+        e = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND, RT>, sb);
+    }
+    return e;
 }
 
 static_assert(sizeof(CUtensorMap) == 128, "TmapCache::Entry::map must hold a CUtensorMap");
