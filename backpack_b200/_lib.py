@@ -140,6 +140,19 @@ def load_debug() -> C.CDLL:
     return _debug_lib
 
 
+STAMPS_LIB_PATH = os.path.join(PKG_DIR, "lib", "libbpq4k_stamps.so")
+_stamps_lib = None
+
+
+def load_stamps() -> C.CDLL:
+    """The build with in-kernel time stamps (`make -C csrc stamps`): the product library with the streaming kernel
+    compiled again with BPQ4K_OPT_STREAM_STAMPS support."""
+    global _stamps_lib
+    if _stamps_lib is None:
+        _stamps_lib = _open(STAMPS_LIB_PATH)
+    return _stamps_lib
+
+
 class ModelConfig(C.Structure):
     """bpq4k_model_config of include/bpq4k.h (the reference's ModelConfig, runtime/gguf_loader.h:164-224)."""
     _fields_ = [("arch", C.c_char * 64)] + [(n, u32) for n in ("nLayer", "nHead", "nKvHeads", "nEmbd", "intermediateSize", "nVocab",

@@ -337,6 +337,8 @@ int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
             return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_STAMPS: {
             if (value < 0 || value > 4096) return fail(h, BPQ4K_ERR_INVALID_ARG, "stamp slots must be 0..4096");
+            if (value > 0 && !gemv_stream_stamps_built())
+                return fail(h, BPQ4K_ERR_INVALID_ARG, "this build has no time stamps: load libbpq4k_stamps.so (make -C csrc stamps)");
             DeviceGuard g(h->device);
             drop_batch_graph(h);  // (a recorded list carries the old buffer and slots)
             if (h->tune.stamps) {

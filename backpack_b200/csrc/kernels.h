@@ -145,6 +145,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& a, const StreamTuning& tune, vo
 
 // Tensor-core prefill matmul (tcgen05 + TMEM).  mode follows bpq4k_prefill_mode: 0 three-pass half
 // split, 1 one pass half, 2 one pass bfloat16.  `scratch` holds the 16-bit activations.
+bool gemv_stream_stamps_built();  // true in libbpq4k_stamps.so
 size_t prefill_scratch_bytes(uint32_t M, uint32_t N, uint32_t K, int mode, int sm_count);
 cudaError_t launch_prefill_tc(const MatmulArgs& a, int mode, void* scratch, size_t scratch_bytes, int* status_dev,
                               int sm_count, cudaStream_t stream, int* launches, int qtype = 12);  // 12 Q4_K, 13 Q5_K, 0x10E padded Q6_K

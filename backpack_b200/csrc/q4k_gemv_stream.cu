@@ -259,9 +259,11 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
     constexpr int TOK = M1 ? 1 : NT * 4;  // activation-row slots (four per 8-column mma tile)
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    // Time stamps for the attribution of a launch's microseconds (off unless the caller asked for them): 0 start,
-    // 1 before the dependency wait, 2 released, 3 activations staged, 4 last tile slot of thread 0 done, 5 end;
-    // word 7 = SM id and grid size.
+    // Time stamps for the attribution of a launch's microseconds: 0 start, 1 before the dependency wait, 2 released,
+    // 3 activations staged, 4 last tile slot of thread 0 done, 5 end; word 7 = SM id and grid size.  Compiled into
+    // libbpq4k_stamps.so only (make stamps): in the product library even the six untaken branches cost the
+    // eight-launch decode step 1.9 us.
+#ifdef BPQ4K_STAMPS
     auto stamp = [&](uint32_t i) {
         if (a.stamps && tid == 0 && blockIdx.y == 0 && blockIdx.x < kStampCtas) {
             unsigned long long t;
@@ -269,6 +271,9 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
             a.stamps[((uint64_t)a.stamp_slot * kStampCtas + blockIdx.x) * 8u + i] = t;
         }
     };
+#else
+    auto stamp = [](uint32_t) {};
+#endif
     stamp(0);
     // Warps beyond the plan's wk x wt are helpers: they take part in the staging of the activations (the one serial
     // step of the kernel, faster with one item per thread) and leave before the main loop.
@@ -1087,11 +1092,13 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
         }
     }
     stamp(5);
+#ifdef BPQ4K_STAMPS
     if (a.stamps && tid == 0 && blockIdx.y == 0 && blockIdx.x < kStampCtas) {
         uint32_t smid;
         asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
         a.stamps[((uint64_t)a.stamp_slot * kStampCtas + blockIdx.x) * 8u + 7u] = smid | ((unsigned long long)gridDim.x << 32);
     }
+#endif
 }
 
 // ---------------------------------------------------------------------------
@@ -1223,6 +1230,14 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
 static_assert(sizeof(CUtensorMap) == 128, "TmapCache::Entry::map must hold a CUtensorMap");
 
 }  // namespace
+
+bool gemv_stream_stamps_built() {
+#ifdef BPQ4K_STAMPS
+    return true;
+#else
+    return false;
+#endif
+}
 
 size_t gemv_stream_scratch_bytes(uint32_t M, uint32_t K) {
     const uint32_t tokens = M <= 1 ? 1 : (M + 3) / 4 * 4;

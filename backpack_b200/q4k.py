@@ -140,11 +140,11 @@ class Q4KWeight:
 class Q4KContext:
     """One handle on one device; not thread-safe (like the reference's GPUContext)."""
 
-    def __init__(self, device: int = 0, debug: bool = False):
+    def __init__(self, device: int = 0, debug: bool = False, stamps: bool = False):
         import torch
 
         self._torch = torch
-        self.lib = _lib.load_debug() if debug else _lib.load()
+        self.lib = _lib.load_debug() if debug else _lib.load_stamps() if stamps else _lib.load()
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: this library has no CPU path")
         self.device = int(device)

@@ -27,7 +27,7 @@ def main() -> None:
     shapes = {"8b": synth.LLAMA3_8B, "70b": synth.LLAMA3_70B,
               "fused": [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336),
                         ("lm_head", 128256, 4096)]}[which]
-    ctx = bp.Q4KContext(0)
+    ctx = bp.Q4KContext(0, stamps=True)      # libbpq4k_stamps.so: the product library with the stamps compiled in
     dev = "cuda:0"
     for kv in sys.argv[1:]:
         if "=" in kv:

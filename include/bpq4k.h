@@ -114,7 +114,9 @@ typedef enum bpq4k_option {
     /* Time stamps of the single-row streaming kernel, for attributing a launch's microseconds.  n > 0: keep the
      * stamps of the last n launches (a device buffer of n x 160 CTAs x 8 words; launch i writes slot i mod n;
      * launches captured into a graph keep the slot they were given at capture); 0: off (default, no cost).
-     * Read with bpq4k_read_stream_stamps.  No counterpart in the reference. */
+     * Read with bpq4k_read_stream_stamps.  Only libbpq4k_stamps.so (make -C backpack_b200/csrc stamps: the product
+     * library with the streaming kernel compiled again) has the stamps; the product library answers n > 0 with
+     * BPQ4K_ERR_INVALID_ARG (even untaken, the six branches cost its decode step 2 %).  No counterpart in the reference. */
     BPQ4K_OPT_STREAM_STAMPS = 24,
     /* Read-only (bpq4k_get_option): how many times bpq4k_matmul_host_batch_f32 has recorded a dispatch
      * list into a replay graph on this handle.  A list is recorded again after any of the handle's

@@ -346,23 +346,30 @@ def test_tail_split_matches_checker(ctx, N, K):
 
 
 def test_stream_time_stamps(ctx):
-    """BPQ4K_OPT_STREAM_STAMPS: thread 0 of every CTA of a single-row launch leaves six ordered time stamps and its SM
-    id; the result of the call is unchanged; reading with the option off is an argument error."""
+    """BPQ4K_OPT_STREAM_STAMPS (libbpq4k_stamps.so: the product library with the streaming kernel compiled again with
+    the stamps): thread 0 of every CTA of a single-row launch leaves six ordered time stamps and its SM id; the result
+    equals the product library's bit for bit; the product library refuses the option."""
     import torch
+
+    import backpack_b200 as bp
 
     N, K = 4096, 4096
     raw = synth.make_q4k_weights(N, K, 90)
     x = synth.make_activations(1, K, 91)
-    w = ctx.upload(pack_q4k(raw, N, K))
-    y0 = ctx.matmul(dev(torch, x), w).cpu().numpy()
+    y0 = ctx.matmul(dev(torch, x), ctx.upload(pack_q4k(raw, N, K))).cpu().numpy()
     with pytest.raises(q4k.Q4KError):
-        ctx.stream_stamps(4)
-    ctx.set_option(q4k.OPT_STREAM_STAMPS, 4)
+        ctx.set_option(q4k.OPT_STREAM_STAMPS, 4)
+    sctx = bp.Q4KContext(0, stamps=True)
     try:
-        y1 = ctx.matmul(dev(torch, x), w).cpu().numpy()
-        ts, n = ctx.stream_stamps(4)
+        w = sctx.upload(pack_q4k(raw, N, K))
+        with pytest.raises(q4k.Q4KError):
+            sctx.stream_stamps(4)                       # not switched on yet
+        sctx.set_option(q4k.OPT_STREAM_STAMPS, 4)
+        y1 = sctx.matmul(dev(torch, x), w).cpu().numpy()
+        ts, n = sctx.stream_stamps(4)
+        sctx.set_option(q4k.OPT_STREAM_STAMPS, 0)
     finally:
-        ctx.set_option(q4k.OPT_STREAM_STAMPS, 0)
+        sctx.close()
     assert n == 1 and np.array_equal(y0, y1)
     grid = int(ts[0, 0, 7] >> np.uint64(32))
     assert 1 <= grid <= 160
