@@ -332,9 +332,6 @@ int bpq4k_set_option(bpq4k_handle_t h, int option, int value) {
             if (value < 0 || value > 16) return fail(h, BPQ4K_ERR_INVALID_ARG, "staging warps must be 0..16");
             h->tune.staging_warps = (uint32_t)value;
             return BPQ4K_OK;
-        case BPQ4K_OPT_STREAM_NO_TAIL_SPLIT:
-            h->tune.no_tail_split = value ? 1u : 0u;
-            return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_STAMPS: {
             if (value < 0 || value > 4096) return fail(h, BPQ4K_ERR_INVALID_ARG, "stamp slots must be 0..4096");
             if (value > 0 && !gemv_stream_stamps_built())
@@ -390,7 +387,6 @@ int bpq4k_get_option(bpq4k_handle_t h, int option, int* value) {
         case BPQ4K_OPT_STREAM_NO_UNIT_LIST: *value = (int)h->tune.no_unit_list; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_UNIT_ROWS: *value = (int)h->tune.rows_per_unit; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_CLUSTER: *value = (int)h->tune.cluster; return BPQ4K_OK;
-        case BPQ4K_OPT_STREAM_NO_TAIL_SPLIT: *value = (int)h->tune.no_tail_split; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_STAGING_WARPS: *value = (int)h->tune.staging_warps; return BPQ4K_OK;
         case BPQ4K_OPT_STREAM_PREWAIT_STAGES: *value = (int)h->tune.pre_wait; return BPQ4K_OK;
         case BPQ4K_OPT_BATCH_RECORDS: *value = (int)h->batch_records; return BPQ4K_OK;

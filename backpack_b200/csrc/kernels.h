@@ -70,7 +70,6 @@ struct StreamTuning {
     uint32_t pre_wait = 0;     // ring stages issued before the dependency wait: 0 automatic, 1..8, 9 = none
     uint32_t cluster = 0;      // CTAs per cluster sharing the staging of a single activation row: 0 automatic, 1, 2, 4
     uint32_t staging_warps = 0;  // single row: warps that stage the activation row (helpers leave before the main loop): 0 automatic (16), 1..16
-    uint32_t no_tail_split = 0;  // 1: the tiles that do not fill a round of a CTA's tile slots keep their slot instead of being split over K
     // time stamps of the single-row streaming kernel (BPQ4K_OPT_STREAM_STAMPS): device buffer of stamp_launches slots of
     // kStreamStampCtas CTAs x 8 words, the handle's running launch counter
     unsigned long long* stamps = nullptr;

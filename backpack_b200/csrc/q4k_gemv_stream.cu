@@ -82,10 +82,6 @@ struct StreamArgs {
     uint32_t pre_wait;         // ring stages issued before the dependency wait (the rest after the activation loads)
     uint32_t contig;           // direct form with a balanced contiguous tile range per CTA (units = tiles)
     uint32_t csize;            // CTAs per cluster that share the staging of the activation row (1: none)
-    // Tail split (single row, direct form): the tiles of a CTA's share that do not fill a round of its wt tile
-    // slots are split over K between ALL its warps, tail_tb blocks each (0: off), through this map's boxes.
-    CUtensorMap tmap_tail;
-    uint32_t tail_tb;
     // optional time stamps (BPQ4K_OPT_STREAM_STAMPS): eight words per CTA of this launch's slot, written by thread 0
     unsigned long long* stamps;
     uint32_t stamp_slot;
@@ -245,7 +241,7 @@ __device__ __forceinline__ void merge_fifth_bit(uint32_t codes, uint32_t qh, uin
 // shape, activations and offsets: the gate and up stacks of an expert layer) the list simply continues
 // over it, results to m.Y2.
 constexpr uint32_t kMaxLocalSlots = 4;
-constexpr uint32_t kStampCtas = kStreamStampCtas;  // CTAs per launch that leave time stamps
+[[maybe_unused]] constexpr uint32_t kStampCtas = kStreamStampCtas;  // CTAs per launch that leave time stamps
 template <int NT, bool M1, bool XG, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false, int RT = 1>
 __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
     static_assert(!FP || (M1 && !XG && !XC), "the fused forms are single-row and stage the row themselves");
@@ -295,7 +291,6 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
     const float* AUX = FP ? a.m.aux : nullptr;
     uint32_t tstride = gridDim.x * a.wt;
     uint32_t tile0 = blockIdx.x * a.wt + wt;   // IND: a unit index, not a tile
-    [[maybe_unused]] uint32_t tail_n = 0, tail_tile0 = 0;  // tail split: how many tiles, the first of them
     uint32_t my_tiles = tile0 < a.ntiles ? (a.ntiles - tile0 + tstride - 1) / tstride : 0;
     // IND: this CTA's first virtual slot, how many it touches, and their first weight rows
     [[maybe_unused]] uint32_t s_first = 0, nloc = 1;
@@ -311,17 +306,7 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
             const uint32_t u_end = u_begin + a.u_base + (blockIdx.x < a.u_extra ? 1u : 0u);
             tstride = a.wt;
             tile0 = u_begin + wt;
-            // A single tile left over after whole rounds of the wt tile slots would keep one slot busy and the others
-            // idle for a whole tile: it is split over K between all warps instead (28672 x 4096, 12 or 13 tiles per
-            // CTA: 15.1 -> 14.3 us).  Two or three left-over tiles keep their slots: taking them one after the other
-            // through all warps measured slower (128256 x 4096: 48.2 -> 48.7 us).
-            if (a.tail_tb && (u_end - u_begin) % a.wt == 1u) {
-                tail_n = 1;
-                tail_tile0 = u_end - 1u;
-                my_tiles = (u_end - u_begin) / a.wt;
-            } else {
-                my_tiles = tile0 < u_end ? (u_end - tile0 + tstride - 1u) / tstride : 0u;
-            }
+            my_tiles = tile0 < u_end ? (u_end - tile0 + tstride - 1u) / tstride : 0u;
         }
     }
     if constexpr (IND) {
@@ -353,9 +338,8 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
         if (FP && AUX) AUX += (uint64_t)s * K;
         M = 1;
     }
-    if (helper) my_tiles = 0, tail_n = 0;
+    if (helper) my_tiles = 0;
     const uint32_t total_units = my_tiles * nchunks;
-    const uint32_t all_units = total_units + tail_n;  // every warp takes one chunk of each tail tile
 
     const uint32_t bar0 = smem_u32(smem) + warp * kMaxStages * 8u;
     const uint32_t ring = smem_u32(smem + a.off_ring) + warp * a.stages * a.stage_bytes;
@@ -419,27 +403,11 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
     // the activations have been issued (issue_rest).  A deep ring issued in one go just before the dependency
     // wait ends puts ~180 KB per SM in front of those loads in the memory system, and the activation staging
     // -- the one serial step of the kernel -- then waits 1.5-2.5 us for data that is sitting in L2.
-    // the units of the tail split follow the warp's own: tile tail_tile0 + t, blocks [warp*tail_tb, +tail_tb)
-    uint32_t iss_n = 0;
-    auto issue_unit = [&]() {
-        if (iss_n < total_units) {
-            issue_next();
-        } else {
-            if (lane == 0) {
-                const uint32_t bar = bar0 + iss_st * 8u;
-                mbar_expect_tx(bar, 16u * BB * a.tail_tb);
-                if (BPQ4K_CHECK((warp + 1u) * a.tail_tb <= nb && tail_tile0 + (iss_n - total_units) < a.ntiles && 16u * BB * a.tail_tb <= a.stage_bytes, a.status))
-                tma_load_2d(ring + iss_st * a.stage_bytes, &a.tmap_tail, warp * a.tail_tb * BW, (uint32_t)wrow0 + (tail_tile0 + (iss_n - total_units)) * 16u, bar);
-            }
-            if (++iss_st == a.stages) iss_st = 0;
-        }
-        iss_n++;
-    };
-    const uint32_t pre_total = min(a.stages, all_units);
+    const uint32_t pre_total = min(a.stages, total_units);
     const uint32_t pre_early = min(a.pre_wait, pre_total);
-    for (uint32_t i = 0; i < pre_early; i++) issue_unit();
+    for (uint32_t i = 0; i < pre_early; i++) issue_next();
     auto issue_rest = [&]() {
-        for (uint32_t i = pre_early; i < pre_total; i++) issue_unit();
+        for (uint32_t i = pre_early; i < pre_total; i++) issue_next();
     };
     // Bring the activation rows into L2 (and their page into the TLBs) while waiting.  A prefetch is not a read:
     // if the preceding kernel still writes X, its stores land in the same L2 lines.
@@ -996,7 +964,7 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
             // the stage is free: refill it with the unit `stages` ahead
             __syncwarp();
             fence_proxy_async();
-            if (u + a.stages < all_units) issue_unit();
+            if (u + a.stages < total_units) issue_next();
             u++;
             if (++st == a.stages) {
                 st = 0;
@@ -1043,54 +1011,6 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
     }
 
     stamp(4);
-    // ---- tail split: the tiles that did not fill a round, every warp a K slice of each ----------------------
-    if constexpr (M1 && !IND) {
-        if (tail_n) {
-            float* tpart = part + 2u * nwarps * 16u;  // its own partial sums: a slower tile slot may still be reading the others
-            const uint32_t pitch = a.tail_tb * BB;
-            const uint32_t lm_off = lm_row * pitch + lm_col, hdr_off = row_a * pitch;
-            for (uint32_t t = 0; t < tail_n; t++) {
-                float acc[RT][NT][2];
-                acc[0][0][0] = acc[0][0][1] = 0.f;
-                const uint32_t bar = bar0 + st * 8u;
-                if (!failed) {
-                    uint32_t polls = 0;
-                    while (!mbar_try_wait(bar, ph)) {
-                        if (++polls > kWaitPolls) {
-                            failed = 1;
-                            if (lane == 0 && a.status) atomicExch(a.status, kDeviceTimeout);
-                            break;
-                        }
-                    }
-                }
-                uint32_t boff = ring + st * a.stage_bytes;
-                for (uint32_t blk = warp * a.tail_tb; blk < (warp + 1u) * a.tail_tb; blk++, boff += BB)
-                    m1_block(boff, hdr_off, lm_off, blk, pa0, pb0, s0_addr, acc);
-                __syncwarp();
-                fence_proxy_async();
-                if (u + a.stages < all_units) issue_unit();
-                u++;
-                if (++st == a.stages) {
-                    st = 0;
-                    ph ^= 1u;
-                }
-                const float sv = acc[0][0][0] + __shfl_xor_sync(0xFFFFFFFFu, acc[0][0][0], 1);
-                if (c_par == 0) tpart[((t & 1u) * nwarps + warp) * 16u + row_a] = sv;
-                asm volatile("bar.sync 0, %0;" ::"r"(nwarps * 32u) : "memory");  // (the helper warps have left)
-                if (warp == 0 && lane < 16u) {
-                    const uint32_t row = (tail_tile0 + t) * 16u + lane;
-                    if (row < N) {
-                        float sum = 0.f;
-                        for (uint32_t w2 = 0; w2 < nwarps; w2++) sum += tpart[((t & 1u) * nwarps + w2) * 16u + lane];
-                        float yv = sum + (a.m.bias ? a.m.bias[row] : 0.f);
-                        if (FP && a.m.residual) yv += __ldg(a.m.residual + row);
-                        Y[(uint64_t)row + par_off] = yv;
-                        for (uint32_t p = 0; p < a.m.n_peers; p++) a.m.peer_Y[p][(uint64_t)row + par_off] = yv;
-                    }
-                }
-            }
-        }
-    }
     stamp(5);
 #ifdef BPQ4K_STAMPS
     if (a.stamps && tid == 0 && blockIdx.y == 0 && blockIdx.x < kStampCtas) {
@@ -1325,7 +1245,7 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         sa.off_zero = off; off += kZeroBytes;
         sa.off_S = off; off += xg ? 0 : align_up(S_bytes, 16);
         sa.off_x = align_up(off, 128); off = sa.off_x + (xg ? 0 : x_bytes);
-        sa.off_part = align_up(off, 16); off = sa.off_part + (m1 ? 4u : 2u) * warps * tokens * tile_rows * 4u;  // single row: + the tail split's partial sums
+        sa.off_part = align_up(off, 16); off = sa.off_part + 2u * warps * tokens * tile_rows * 4u;
         sa.off_ring = align_up(off, 128); off = sa.off_ring + warps * stages * stage_bytes;
         return off;
     };
@@ -1462,17 +1382,6 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
             if (cudaError_t e = get_map(rem, &sa.tmap_rem, m.W)) return e;
         } else {
             sa.tmap_rem = sa.tmap;
-        }
-        // Tail split: direct single-row form with several tile slots per CTA, K divisible into one box per warp
-        // that fits a ring stage (128256 x 4096 on 148 SMs: 54 or 55 tiles per CTA = 13 rounds of 4 + 2 or 3 tiles).
-        sa.tail_tb = 0;
-        sa.tmap_tail = sa.tmap;
-        if (m1 && !indirect && !xg && !tune.no_tail_split && wt > 1 && nb % warps == 0) {
-            const uint32_t tb = nb / warps;
-            if (tb * block_words <= 256u && tile_rows * tb * block_bytes <= stage_bytes) {
-                if (cudaError_t e = get_map(tb, &sa.tmap_tail, m.W)) return e;
-                sa.tail_tb = tb;
-            }
         }
         if (m.W2) {
             if (cudaError_t e = get_map(cb, &sa.tmap_b, m.W2)) return e;

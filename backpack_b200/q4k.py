@@ -38,7 +38,6 @@ OPT_STREAM_NO_UNIT_LIST = 17
 OPT_STREAM_PREWAIT_STAGES = 18
 OPT_STREAM_CLUSTER = 20
 OPT_STREAM_STAGING_WARPS = 21
-OPT_STREAM_NO_TAIL_SPLIT = 22
 OPT_PREFILL_VARIANT = 23
 OPT_STREAM_STAMPS = 24
 PREFILL_ONE_CTA, PREFILL_CTA_PAIR, PREFILL_TMEM_WEIGHTS = 0, 1, 2

@@ -101,9 +101,6 @@ typedef enum bpq4k_option {
     /* One activation row: warps per CTA that quantise the row; those beyond the plan's warps (BPQ4K_OPT_STREAM_WARPS)
      * leave before the main loop.  0: automatic (16), 1..16 (values below the plan's warp count change nothing). */
     BPQ4K_OPT_STREAM_STAGING_WARPS = 21,
-    /* One activation row: the tiles of a CTA's share that do not fill a round of its tile slots are normally split
-     * over K between all its warps (results of those rows then sum their K slices in a different grouping).  1: off. */
-    BPQ4K_OPT_STREAM_NO_TAIL_SPLIT = 22,
     /* Single-pass precision modes of the tensor-core kernel, Q4_K: how a weight tile meets the activations.
      * 0 (default): one CTA per 256 weight rows x 256 activation rows, dequantised weights through shared memory.
      * 1: two CTAs of a cluster share tcgen05.mma.cta_group::2 (2 x 128 weight rows x 512 activation rows; M > 256).

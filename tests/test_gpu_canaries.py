@@ -56,8 +56,7 @@ def run_guarded_matmul(ctx, qtype, layout, M, N, K, seed, with_bias=True):
 
 
 SMALL = [(M, N, nb * 256) for M in (1, 5, 9) for N in (1, 7, 8, 9) for nb in (1, 2, 3)]
-# (the last three: cluster-shared staging of a long row; a tile count that leaves single tiles over for the K split of a
-#  CTA's last tile on a 148-SM device, ragged; the same with whole tiles)
+# (the last three: cluster-shared staging of a long row; uneven tile counts per CTA on a 148-SM device, ragged and whole)
 LARGE = [(1, 4096, 4096), (8, 1000, 8192), (3, 130, 14336), (16, 257, 2048), (40, 300, 1024),
          (1, 1030, 14336), (1, 16 * 148 * 4 + 9, 4096), (1, 28672, 4096)]
 

@@ -304,9 +304,6 @@ def test_cluster_staging_gives_identical_bits(ctx, N, K):
     want = orc.matmul(x, raw, None, N, K)
     default = ctx.get_option(q4k.OPT_STREAM_CLUSTER)
     ys = []
-    # (the tail split regroups the K slices of a CTA's last tile, and which tile that is depends on the grid, which a
-    #  cluster size may round down: off for this comparison)
-    ctx.set_option(q4k.OPT_STREAM_NO_TAIL_SPLIT, 1)
     try:
         for cs in (1, 2, 4):
             ctx.set_option(q4k.OPT_STREAM_CLUSTER, cs)
@@ -314,35 +311,8 @@ def test_cluster_staging_gives_identical_bits(ctx, N, K):
             assert ctx.device_status() == 0
     finally:
         ctx.set_option(q4k.OPT_STREAM_CLUSTER, default)
-        ctx.set_option(q4k.OPT_STREAM_NO_TAIL_SPLIT, 0)
     check(ys[0], want)
     assert np.array_equal(ys[0], ys[1]) and np.array_equal(ys[0], ys[2])
-
-
-@pytest.mark.parametrize("N,K", [(16 * 149, 4096), (16 * 148 * 4 + 16, 4096), (28672, 4096), (16 * 148 * 2 + 32, 8192), (2375, 1024)])
-def test_tail_split_matches_checker(ctx, N, K):
-    """A CTA whose share of the tiles leaves ONE tile over after whole rounds of its tile slots splits that tile over K
-    between all its warps (BPQ4K_OPT_STREAM_NO_TAIL_SPLIT turns that off).  Both forms against the checker, with a
-    bias; rows outside the split tiles must be bit-identical between the two."""
-    import torch
-
-    raw = synth.make_q4k_weights(N, K, 72)
-    x = synth.make_activations(1, K, 73)
-    bias = np.linspace(-1, 1, N).astype(np.float32)
-    w = ctx.upload(pack_q4k(raw, N, K))
-    want = orc.matmul(x, raw, bias, N, K)
-    ys = []
-    try:
-        for off in (0, 1):
-            ctx.set_option(q4k.OPT_STREAM_NO_TAIL_SPLIT, off)
-            ys.append(ctx.matmul(dev(torch, x), w, bias=dev(torch, bias)).cpu().numpy())
-            assert ctx.device_status() == 0
-    finally:
-        ctx.set_option(q4k.OPT_STREAM_NO_TAIL_SPLIT, 0)
-    check(ys[0], want)
-    check(ys[1], want)
-    differ = np.flatnonzero(ys[0][0] != ys[1][0]) // 16
-    assert len(np.unique(differ)) <= 148   # at most one tile per CTA
 
 
 def test_stream_time_stamps(ctx):
