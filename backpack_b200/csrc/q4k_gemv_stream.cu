@@ -242,7 +242,7 @@ __device__ __forceinline__ void merge_fifth_bit(uint32_t codes, uint32_t qh, uin
 // over it, results to m.Y2.
 constexpr uint32_t kMaxLocalSlots = 4;
 [[maybe_unused]] constexpr uint32_t kStampCtas = kStreamStampCtas;  // CTAs per launch that leave time stamps
-template <int NT, bool M1, bool XG, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false, int RT = 1>
+template <int NT, bool M1, bool XG, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false, int RT = 1, bool PEER = false>
 __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
     static_assert(!FP || (M1 && !XG && !XC), "the fused forms are single-row and stage the row themselves");
     static_assert(!IND || (M1 && !XG && !XC), "the unit-list form is single-row and stages its rows itself");
@@ -733,7 +733,9 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
     float* part = reinterpret_cast<float*>(smem + a.off_part);
     // double-buffered gather slots: which half this step writes (the word was last written by the barrier
     // kernel that closed the previous step, which precedes this kernel in the stream)
-    const uint64_t par_off = a.m.slot_parity ? (uint64_t)(*reinterpret_cast<const volatile uint32_t*>(a.m.slot_parity) & 1u) * a.m.slot_parity_stride : 0ull;
+    // (PEER: the fused all-gather's instantiations.  Left in the plain ones, the peer stores and this word cost the
+    //  single-GPU decode step 1.4 us although they never ran.)
+    const uint64_t par_off = (PEER && a.m.slot_parity) ? (uint64_t)(*reinterpret_cast<const volatile uint32_t*>(a.m.slot_parity) & 1u) * a.m.slot_parity_stride : 0ull;
     uint32_t st = 0, ph = 0, u = 0, failed = 0;
     [[maybe_unused]] uint32_t cur_l = 0, cur_tl = 0;
     if constexpr (IND) {
@@ -1004,7 +1006,8 @@ __global__ void __launch_bounds__(RT == 2 ? 256 : (M1 || NT == 1) ? 512 : 384, 1
                     if (BPQ4K_CHECK(tok < (IND || a.m.n_slots ? 1u : a.m.M) && row < N && idx < (uint32_t)TOK * TR, a.status))
                     Y[(uint64_t)tok * N + row + par_off] = yv;
                     // fused all-gather: the same value goes straight into every peer's gather buffer
-                    for (uint32_t p = 0; p < a.m.n_peers; p++) a.m.peer_Y[p][(uint64_t)tok * N + row + par_off] = yv;
+                    if constexpr (PEER)
+                        for (uint32_t p = 0; p < a.m.n_peers; p++) a.m.peer_Y[p][(uint64_t)tok * N + row + par_off] = yv;
                 }
             }
         }
@@ -1046,12 +1049,12 @@ __global__ void __launch_bounds__(256) quantize_activations_kernel(const float* 
 
 // Launch one instantiation.  The grid is persistent: at most as many CTAs as can be
 // resident at once (occupancy query, cached), never more than there are tile groups.
-template <int NT, bool M1, bool XG, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false, int RT = 1>
+template <int NT, bool M1, bool XG, bool Q5 = false, bool XC = false, bool FP = false, bool IND = false, int RT = 1, bool PEER = false>
 cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, uint32_t threads, size_t smem,
                        int sm_count, uint32_t ctas_per_sm_override, bool pdl, cudaStream_t stream, uint32_t flat_grid = 0) {
     static KernelConfig kcfg;  // per instantiation; per-device slots and a mutex inside
     int occ = 1;
-    if (cudaError_t e = kcfg.prepare(reinterpret_cast<const void*>(gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND, RT>), threads, smem, &occ))
+    if (cudaError_t e = kcfg.prepare(reinterpret_cast<const void*>(gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND, RT, PEER>), threads, smem, &occ))
         return e;
     uint32_t per_sm = (uint32_t)occ;
     if (ctas_per_sm_override && ctas_per_sm_override < per_sm) per_sm = ctas_per_sm_override;
@@ -1112,7 +1115,7 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
                 qa[0].val.clusterDim.x = cs, qa[0].val.clusterDim.y = 1, qa[0].val.clusterDim.z = 1;
                 q.attrs = qa;
                 q.numAttrs = 1;
-                if (cudaOccupancyMaxActiveClusters(&mc, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND, RT>, &q) != cudaSuccess || mc <= 0) {
+                if (cudaOccupancyMaxActiveClusters(&mc, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND, RT, PEER>, &q) != cudaSuccess || mc <= 0) {
                     cudaGetLastError();
                     mc = -1;
                 }
@@ -1136,13 +1139,13 @@ cudaError_t launch_one(const StreamArgs& sa, uint32_t groups, uint32_t slots_y, 
     cfg.gridDim = dim3(gx, slots_y);
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND, RT>, sb);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND, RT, PEER>, sb);
     if (e != cudaSuccess && cs > 1u) {
         // a context that cannot place clusters (restricted SM sets): the same launch without them
         cudaGetLastError();
         sb.csize = 1;
         cfg.numAttrs = na - 1;  // the cluster attribute is the last one
-        e = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND, RT>, sb);
+        e = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT, M1, XG, Q5, XC, FP, IND, RT, PEER>, sb);
     }
     return e;
 }
@@ -1182,7 +1185,8 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
     // the shared-memory pipe, or L2 when they live in the global scratch).
     // Measured (M = 8): 8192 x 28672 69.6 against 93.5 us, 4096 x 14336 20.0 against 24.4 us; no gain where the digits sit
     // in shared memory (128256 x 4096: 98 against 100 us) and a loss at K = 8192, where twelve warps matter more.
-    const uint32_t rt = tune.rows_per_unit == 16 ? 1u : tune.rows_per_unit == 32 ? (m1 || indirect ? 1u : 2u)
+    const bool peer = m.n_peers != 0 || m.slot_parity != nullptr;  // the fused all-gather's instantiations (16-row units only)
+    const uint32_t rt = peer || tune.rows_per_unit == 16 ? 1u : tune.rows_per_unit == 32 ? (m1 || indirect ? 1u : 2u)
                         : (!m1 && !indirect && m.N >= 2048u && m.K >= 14336u && (uint64_t)M * m.K > 40960u) ? 2u : 1u;
     const uint32_t tile_rows = 16u * rt;
     const uint32_t ntiles = (m.N + tile_rows - 1) / tile_rows;
@@ -1438,20 +1442,23 @@ cudaError_t launch_gemv_stream(const MatmulArgs& m, const StreamTuning& tune, vo
         // single row staged per CTA: up to 16 warps stage it (helpers beyond the plan's warps leave afterwards)
         const uint32_t swarps_h = (m1 && !xg) ? (tune.staging_warps ? tune.staging_warps : 16u) : 0u;
         const uint32_t threads = (swarps_h > warps ? swarps_h : warps) * 32;
-#define BPQ4K_LAUNCH_RT(NT_, M1_, XG_, XC_, FP_, RT_)                                                                  \
-    (q5 ? launch_one<NT_, M1_, XG_, true, XC_, FP_, false, RT_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream) \
-        : launch_one<NT_, M1_, XG_, false, XC_, FP_, false, RT_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream))
-#define BPQ4K_LAUNCH(NT_, M1_, XG_, XC_, FP_) \
-    ((M1_) || rt == 1 ? BPQ4K_LAUNCH_RT(NT_, M1_, XG_, XC_, FP_, 1) : BPQ4K_LAUNCH_RT(NT_, false, XG_, XC_, false, 2))
-        if (m1 && fused) e = BPQ4K_LAUNCH(1, true, false, false, true);
+#define BPQ4K_LAUNCH_RT(NT_, M1_, XG_, XC_, FP_, RT_, PEER_)                                                           \
+    (q5 ? launch_one<NT_, M1_, XG_, true, XC_, FP_, false, RT_, PEER_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream) \
+        : launch_one<NT_, M1_, XG_, false, XC_, FP_, false, RT_, PEER_>(sa, groups, cnt, threads, smem, sm_count, tune.ctas_per_sm, !tune.no_pdl, stream))
+#define BPQ4K_LAUNCH_NP(NT_, M1_, XG_, XC_, FP_) \
+    ((M1_) || rt == 1 ? BPQ4K_LAUNCH_RT(NT_, M1_, XG_, XC_, FP_, 1, false) : BPQ4K_LAUNCH_RT(NT_, false, XG_, XC_, false, 2, false))
+#define BPQ4K_LAUNCH(NT_, M1_, XG_, XC_, FP_) (peer ? BPQ4K_LAUNCH_RT(NT_, M1_, XG_, XC_, FP_, 1, true) : BPQ4K_LAUNCH_NP(NT_, M1_, XG_, XC_, FP_))
+        if (peer && (indirect || fused || NT > 2)) return cudaErrorInvalidValue;  // the gather covers plain calls of up to eight rows
+        if (m1 && fused) e = BPQ4K_LAUNCH_NP(1, true, false, false, true);
         else if (m1) e = xg ? BPQ4K_LAUNCH(1, true, true, false, false) : BPQ4K_LAUNCH(1, true, false, false, false);
         else if (xc) e = NT == 1 ? BPQ4K_LAUNCH(1, false, false, true, false) : NT == 2 ? BPQ4K_LAUNCH(2, false, false, true, false)
-                       : NT == 3 ? BPQ4K_LAUNCH(3, false, false, true, false) : BPQ4K_LAUNCH(4, false, false, true, false);
+                       : NT == 3 ? BPQ4K_LAUNCH_NP(3, false, false, true, false) : BPQ4K_LAUNCH_NP(4, false, false, true, false);
         else if (xg) e = NT == 1 ? BPQ4K_LAUNCH(1, false, true, false, false) : NT == 2 ? BPQ4K_LAUNCH(2, false, true, false, false)
-                       : NT == 3 ? BPQ4K_LAUNCH(3, false, true, false, false) : BPQ4K_LAUNCH(4, false, true, false, false);
+                       : NT == 3 ? BPQ4K_LAUNCH_NP(3, false, true, false, false) : BPQ4K_LAUNCH_NP(4, false, true, false, false);
         else e = NT == 1 ? BPQ4K_LAUNCH(1, false, false, false, false) : NT == 2 ? BPQ4K_LAUNCH(2, false, false, false, false)
-               : NT == 3 ? BPQ4K_LAUNCH(3, false, false, false, false) : BPQ4K_LAUNCH(4, false, false, false, false);
+               : NT == 3 ? BPQ4K_LAUNCH_NP(3, false, false, false, false) : BPQ4K_LAUNCH_NP(4, false, false, false, false);
 #undef BPQ4K_LAUNCH
+#undef BPQ4K_LAUNCH_NP
 #undef BPQ4K_LAUNCH_RT
         if (launches) ++*launches;
         if (e != cudaSuccess) return e;
