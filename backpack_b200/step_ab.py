@@ -80,7 +80,11 @@ def main() -> None:
             for o, v in opts:
                 ctx.set_option(o, v)
             for fname, fn in forms:
-                fn()
+                try:
+                    fn()                     # eager first: an option set a shape cannot take fails here, outside any capture
+                except Exception as e:       # noqa: BLE001
+                    print(f"{name}: {fname}: not applicable ({e})", flush=True)
+                    continue
                 torch.cuda.synchronize()
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, stream=main_s):
@@ -101,7 +105,8 @@ def main() -> None:
                 if it >= 2:
                     res[k].append(e0.elapsed_time(e1) * 1e3 / reps)
     for name, _ in cfgs:
-        print(f"{name:16s} " + "   ".join(f"{fname}: {np.median(res[(name, fname)]):7.2f} us (min {min(res[(name, fname)]):7.2f})" for fname, _ in forms), flush=True)
+        print(f"{name:16s} " + "   ".join(f"{fname}: {np.median(res[(name, fname)]):7.2f} us (min {min(res[(name, fname)]):7.2f})"
+                                          for fname, _ in forms if (name, fname) in res), flush=True)
     assert ctx.device_status() == 0
 
 
