@@ -70,7 +70,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # DRAM read+write bytes of the streaming kernel divided by its algorithmic bytes, from one ncu capture
 # on a 151 MB case (65536 x 4096, M = 1); traffic grows with the rows, so a launch's traffic is this
 # ratio times its algorithmic bytes.
-TRAFFIC_RATIO = 1.026
+TRAFFIC_RATIO = 1.022
 
 
 def load_peaks():
