@@ -507,7 +507,7 @@ def run_gpu_arm(args, rank, world, local_rank):
         extras["fused_projections"] = measure_fused_projections(ctx, torch, bp, shapes, weights_h, X, dev, stream, steps)
         extras["config0"] = measure_config0(ctx, torch, bp, weights_h["q"], dev)
         if not args.no_prefill:
-            extras["prefill"] = measure_prefill(ctx, torch, shapes, W, dev)
+            extras["prefill"] = measure_prefill(ctx, torch, shapes, W, dev, weights_h=weights_h)
         if not args.no_siblings:
             extras["small_batch"] = measure_small_batch(ctx, torch, W["lm_head"], dev)
             extras["kquant_siblings"] = measure_siblings(ctx, torch, dev)
@@ -1031,7 +1031,7 @@ def measure_siblings(ctx, torch, dev, reps=8):
     return out
 
 
-def measure_prefill(ctx, torch, shapes, W, dev, M=512, reps=5):
+def measure_prefill(ctx, torch, shapes, W, dev, M=512, reps=5, weights_h=None):
     """Config 2: the same projections at M = 512 through the tensor-core kernel; useful TFLOP/s
     (2*M*N*K, extra passes not counted) per precision mode, summed over the eight projections."""
     from backpack_b200 import q4k
@@ -1070,6 +1070,19 @@ def measure_prefill(ctx, torch, shapes, W, dev, M=512, reps=5):
         out["modes"][name] = {"ms_per_pass": ms, "tflops": tf,
                               "frac_of_burst_peak": tf / peaks["bf16_tflops"] if peaks.get("bf16_tflops") else None,
                               "meets_float_tolerance": name == "f16x3"}
+        if weights_h is not None:
+            # error of this mode against the CPU checker (the reference's float dot) on the first 64 weight rows of a
+            # K = 4096 and of the K = 14336 projection, all 512 activation rows
+            from oracle import q4k_oracle as orc
+            errs = {}
+            for pname in ("gate", "down"):
+                N, K = W[pname].N, W[pname].K
+                rows = 64
+                want = orc.matmul(xs[K].cpu().numpy(), np.ascontiguousarray(weights_h[pname][:rows]), None, rows, K, threads=4)
+                got = ys[pname][:, :rows].cpu().numpy()
+                errs[f"K={K}"] = {"rel_l2": float(np.linalg.norm(got - want) / np.linalg.norm(want)),
+                                  "max_abs": float(np.abs(got - want).max()), "out_rms": float(np.sqrt(np.mean(want * want)))}
+            out["modes"][name]["error_vs_checker"] = errs
     # the two other forms of the single-pass kernel (same bits, kept for comparison): bfloat16, the whole pass
     out["variants_bf16"] = {}
     ctx.set_option(q4k.OPT_PREFILL_MODE, q4k.PREFILL_BF16)
